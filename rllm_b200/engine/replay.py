@@ -1,0 +1,106 @@
+"""Trace replay: feed given token ids through a model step by step and write
+the logits.  Nothing is sampled.
+
+    bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+
+It drives the framework's own model, step function, cache manager and kernels
+- the ones generation uses - and has no forward pass, cache or loader of its
+own.  Steps come from standard input, one JSON object a line:
+
+    {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
+
+``entries``: for each request its next tokens and the places among them whose
+logits are asked for; all entries of a step are one batch.  ``end``: requests
+that are finished after this step; their pages and slot are given back.  For a
+step that asks for logits, ``<out>/<step>.f32`` holds them as little-endian
+float32 [wanted, vocab] in the order of the entries and of ``want``.  After
+every step a line ``done <step>`` is printed and flushed.  ``--max-tokens`` is
+the most tokens live requests hold at any time (each request rounded up to a
+multiple of 64); the page pool is made for exactly that many, so pages of
+finished requests are used again.
+
+The reference has nothing comparable; the nearest is its hand-stepped sampler
+check (crates/rllm-bench/tests/correctness.rs:120-188).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+from typing import Dict, List
+
+PAGE_SIZE = 16
+MAX_LIVE = 8
+
+
+def build_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
+    p.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    p.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    p.add_argument("--out", required=True, help="folder for <step>.f32 files")
+    p.add_argument("--max-tokens", type=int, required=True,
+                   help="most tokens live requests hold at any time")
+    p.add_argument("--block-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
+    p.add_argument("--device", default="cuda:0")
+    return p
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    print("[trace_run] loading", args.model, file=sys.stderr, flush=True)
+    import numpy as np
+    import torch
+
+    from ..cache import CacheManager, CacheStorage
+    from .loading import load_model
+    from .runner import ModelRunner, StepEntry
+
+    os.makedirs(args.out, exist_ok=True)
+    _, model = load_model(args.model, dtype=args.dtype, device=args.device)
+    page = args.block_size
+    num_pages = max(1, -(-args.max_tokens // page))
+    paged = [n for n in model.layout.groups if hasattr(n, "num_kv_heads")]
+    cache = CacheManager(model.layout.groups, page, [num_pages] * len(paged), MAX_LIVE)
+    storage = CacheStorage(model.layout, page, [num_pages] * len(paged), MAX_LIVE, model.dtype, model.device)
+    runner = ModelRunner(model, cache, storage)
+    fed: Dict[str, int] = {}
+
+    for line in sys.stdin:
+        line = line.strip()
+        if not line:
+            continue
+        rec = json.loads(line)
+        step = rec["step"]
+        entries: List[StepEntry] = []
+        for e in rec.get("entries", []):
+            rid, tokens = str(e["id"]), list(e["tokens"])
+            if not tokens:
+                continue
+            if rid not in fed:
+                cache.admit(rid)
+                fed[rid] = 0
+            start = fed[rid]
+            if not cache.ensure(rid, start, start + len(tokens)):
+                print(f"trace_run: step {step}: request {rid!r} needs more pages than --max-tokens "
+                      f"{args.max_tokens} leaves free", file=sys.stderr)
+                return 3
+            entries.append(StepEntry(rid, tokens, start, list(e.get("want", []))))
+            fed[rid] = start + len(tokens)
+        logits = runner.step(entries)
+        runner.check_errors()
+        if logits.shape[0]:
+            logits.cpu().numpy().astype("<f4").tofile(os.path.join(args.out, f"{step}.f32"))
+        else:
+            torch.cuda.synchronize()
+        for rid in rec.get("end", []):
+            rid = str(rid)
+            if rid in fed:
+                cache.free(rid)
+                del fed[rid]
+        print(f"done {step}", flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

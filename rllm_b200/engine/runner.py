@@ -1,0 +1,169 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``ModelRunner.step(entries)`` takes any mix of prompt portions and single
+decoded tokens, cut anywhere.  It runs exactly the tokens it is given, as one
+flat batch, against the cache that earlier steps left, writes their keys and
+values (and states) into the cache, and returns float32 logits at the places
+that were asked for, in the order of the entries and of each entry's ``want``.
+It does no request bookkeeping: the caller (scheduler or replay) owns
+positions and pages.
+
+The reference's counterpart builds its flat batch in
+crates/rllm-worker/src/model_runner.rs:136-256 (prefills first, then decodes,
+positions from ``num_computed``; slot rule :806-826) and its attention metadata
+at :262-344; its executor computes logits for every row and keeps one per
+sequence (crates/rllm-executor/src/uniproc.rs:167-175).  Here a decode is just
+a portion of length 1, sequences with one token are placed first so that the
+decode attention kernel sees a contiguous range, and the head runs on the
+wanted rows only.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from ..models.decoder import DecoderModel
+from ..parts.base import StepContext
+
+
+class StepError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    req: Hashable
+    tokens: Sequence[int]
+    start: int                       # position of tokens[0] in its sequence
+    want: Sequence[int] = ()         # indices into ``tokens`` whose logits are asked for
+
+
+_ERR_BITS = {1: "a token id outside the vocabulary", 2: "a cache write to a page the request does not hold",
+             4: "an attention read from a page the request does not hold"}
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, storage: CacheStorage):
+        if model.device is None:
+            raise StepError("the model has no weights yet")
+        if model.device.type != "cuda":
+            raise StepError("the engine runs on a CUDA device only; there is no CPU path")
+        self.model, self.cache, self.storage = model, cache, storage
+        self.device = model.device
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # ring of pinned staging buffers; a buffer is reused only after its copy has run
+        self._ring: List[list] = [[None, None] for _ in range(4)]
+        self._ring_next = 0
+
+    # ------------------------------------------------------------------
+    def _stage(self, n: int):
+        slot = self._ring[self._ring_next]
+        self._ring_next = (self._ring_next + 1) % len(self._ring)
+        if slot[1] is not None:
+            slot[1].synchronize()
+        if slot[0] is None or slot[0].numel() < n:
+            slot[0] = torch.empty(max(n, 1 << 16), dtype=torch.int32, pin_memory=True)
+        if slot[1] is None:
+            slot[1] = torch.cuda.Event()
+        return slot[0][:n], slot[1]
+
+    def build_context(self, entries: Sequence[StepEntry]):
+        """Flatten the entries: (StepContext, token ids, logit rows)."""
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise StepError(f"request {e.req!r}: an entry needs at least one token")
+            if e.start < 0:
+                raise StepError(f"request {e.req!r}: negative position")
+            for w in e.want:
+                if not 0 <= w < len(e.tokens):
+                    raise StepError(f"request {e.req!r}: wanted place {w} outside its {len(e.tokens)} tokens")
+        if len({e.req for e in entries}) != len(entries):
+            raise StepError("a request appears twice in one step")
+        order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
+        num_decode = sum(1 for e in entries if len(e.tokens) == 1)
+        S = len(entries)
+        q_lens = [len(entries[i].tokens) for i in order]
+        T = sum(q_lens)
+        q_start = np.zeros(S + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=q_start[1:])
+        first_of = {order[s]: int(q_start[s]) for s in range(S)}     # entry index -> first flat token
+        token_ids = np.empty(T, dtype=np.int32)
+        positions = np.empty(T, dtype=np.int32)
+        token_seq = np.empty(T, dtype=np.int32)
+        seq_lens = np.empty(S, dtype=np.int32)
+        slots = np.empty(S, dtype=np.int32)
+        paged = self.cache.paged
+        tables = []
+        for s, i in enumerate(order):
+            e = entries[i]
+            a, b = q_start[s], q_start[s + 1]
+            token_ids[a:b] = np.asarray(e.tokens, dtype=np.int64)
+            positions[a:b] = np.arange(e.start, e.start + (b - a), dtype=np.int32)
+            token_seq[a:b] = s
+            seq_lens[s] = e.start + (b - a)
+            slots[s] = self.cache.slot(e.req)
+        rows = np.asarray([first_of[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int32)
+        for g in paged:
+            per_seq = [self.cache.table(entries[i].req, g) for i in order]
+            need = [-(-int(seq_lens[s]) // self.cache.page_size) for s in range(S)]
+            for s, (tb, n) in enumerate(zip(per_seq, need)):
+                if len(tb) < n:
+                    raise StepError(f"request {entries[order[s]].req!r} holds {len(tb)} pages of group {g}, "
+                                    f"its {int(seq_lens[s])} tokens need {n}")
+            width = max(1, max(need))
+            tab = np.full((S, width), -1, dtype=np.int32)
+            for s, (tb, n) in enumerate(zip(per_seq, need)):
+                tab[s, :n] = tb[:n]
+            tables.append(tab)
+        # one pinned staging buffer, one copy to the device
+        parts = [token_ids, positions, token_seq, q_start, seq_lens, slots, rows] + [t.ravel() for t in tables]
+        sizes = [p.size for p in parts]
+        total = sum(sizes)
+        stage, copied = self._stage(total)
+        host = stage.numpy()
+        off = 0
+        for p, n in zip(parts, sizes):
+            host[off:off + n] = p
+            off += n
+        dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        dev.copy_(stage, non_blocking=True)
+        copied.record()
+        views, off = [], 0
+        for n in sizes:
+            views.append(dev[off:off + n])
+            off += n
+        d_tokens, d_pos, d_tseq, d_qstart, d_seqlens, d_slots, d_rows = views[:7]
+        block_tables: List[Optional[torch.Tensor]] = [None] * len(self.cache.needs)
+        for g, tab, v in zip(paged, tables, views[7:]):
+            block_tables[g] = v.view(tab.shape)
+        ctx = StepContext(
+            num_tokens=T, num_seqs=S, num_decode=num_decode, positions=d_pos, token_seq=d_tseq,
+            q_start=d_qstart, seq_lens=d_seqlens, q_lens_host=q_lens,
+            seq_lens_host=[int(x) for x in seq_lens], block_tables=block_tables, state_slots=d_slots,
+            state_slots_host=[int(x) for x in slots], err=self.err, act_dtype=self.model.dtype)
+        ctx.extras["starts_host"] = [entries[i].start for i in order]
+        return ctx, d_tokens, d_rows
+
+    # ------------------------------------------------------------------
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Logits float32 [sum of len(want), vocab] on the device."""
+        if not entries:
+            return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            self.storage.zero_slots(self.cache.take_fresh_slots())
+            ctx, token_ids, rows = self.build_context(entries)
+            return self.model.forward(token_ids, ctx, rows, self.storage)
+
+    def check_errors(self) -> None:
+        """Raise if a kernel of an earlier step flagged a bad index (synchronises)."""
+        code = int(self.err.item())
+        if code:
+            self.err.zero_()
+            what = "; ".join(msg for bit, msg in _ERR_BITS.items() if code & bit)
+            raise StepError(f"a kernel refused an index: {what}")

@@ -1,0 +1,65 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, warp and
+// block reductions, and the argument checks that every entry point runs before
+// it launches.  All entry points are extern "C", take raw device pointers and
+// a stream, allocate nothing and return 0, a CUDA error code (> 0), or a
+// negative RLLM_E* code when they refuse the sizes they were given.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define RLLM_DT_F32 0
+#define RLLM_DT_BF16 1
+
+#define RLLM_E_BADARG (-1)     // a size or pointer the kernel cannot take
+#define RLLM_E_UNSUPPORTED (-2) // a legal size this build has no kernel for
+
+#define RLLM_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define RLLM_LAUNCH_CHECK()                          \
+  do {                                               \
+    cudaError_t e__ = cudaGetLastError();            \
+    if (e__ != cudaSuccess) return (int)e__;         \
+  } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The
+// order of the additions depends only on blockDim, never on the data.
+__device__ __forceinline__ float block_sum(float v, float* smem32) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) smem32[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? smem32[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// Dispatch helpers ---------------------------------------------------------
+#define RLLM_DISPATCH_DTYPE(code, T, ...)                    \
+  do {                                                       \
+    if ((code) == RLLM_DT_F32) { typedef float T; __VA_ARGS__; } \
+    else if ((code) == RLLM_DT_BF16) { typedef bf16 T; __VA_ARGS__; } \
+    else return RLLM_E_BADARG;                               \
+  } while (0)

@@ -1,0 +1,237 @@
+// Memory-bound kernels of the step: embedding gather, RMSNorm fused with the
+// residual add, rotary position encoding fused with the write of keys and
+// values into cache pages, SiLU-gate multiply.  One source for float32 and
+// bfloat16 activations; all arithmetic is float32 (rotation angles float64).
+//
+// The residual stream is float32 in both modes: the embedding writes it, the
+// fused norm adds a block's output to it (float32 add) and hands the normed
+// row on in the activation dtype.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// embedding: out[t, :] = table[ids[t], :]   (no scaling;
+// crates/rllm-model/src/llama.rs:329-337)
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                                 float* __restrict__ out, int H, int V, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* o = out + (size_t)t * H;
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0) atomicOr(err, 1);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.f;
+    return;
+  }
+  const TW* row = table + (size_t)id * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+RLLM_EXPORT int rllm_embedding(const int* ids, const void* table, int table_dtype, float* out,
+                               int T, int H, int V, int* err, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || V <= 0) return RLLM_E_BADARG;
+  int threads = H >= 1024 ? 256 : 128;
+  RLLM_DISPATCH_DTYPE(table_dtype, TW,
+    (embedding_kernel<TW><<<T, threads, 0, stream>>>(ids, (const TW*)table, out, H, V, err)));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm: y = x / sqrt(mean(x^2) + eps) * w   (eps inside the root, w as it
+// is; crates/rllm-model/src/layers.rs:133-140).
+//   x      float32 rows (the residual stream)
+//   delta  optional rows in the activation dtype, added to x first (float32);
+//          with writeback the sum is stored back into x
+//   rows   optional row indices: output row r reads input row rows[r]
+// One block per output row.  The order of the additions of a row depends on
+// H and the block size only.
+// ---------------------------------------------------------------------------
+template <typename TD, typename TW, typename TO>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                               const int* __restrict__ rows, const TW* __restrict__ w,
+                               TO* __restrict__ out, int H, float eps, int writeback) {
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* xr = x + (size_t)src * H;
+  const TD* dr = delta ? delta + (size_t)src * H : nullptr;
+  TO* o = out + (size_t)r * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = xr[i];
+    if (dr) {
+      v += to_f32(dr[i]);
+      if (writeback) xr[i] = v;
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = xr[i];
+    if (dr && !writeback) v += to_f32(dr[i]);
+    o[i] = from_f32<TO>(v * inv * to_f32(w[i]));
+  }
+}
+
+template <typename TD, typename TO>
+static int rmsnorm_launch_w(float* x, const void* delta, const int* rows, const void* w, int w_dtype,
+                            void* out, int R, int H, float eps, int writeback, cudaStream_t stream) {
+  int threads = H >= 4096 ? 1024 : (H >= 1024 ? 512 : (H >= 256 ? 128 : 64));
+  if (w_dtype == RLLM_DT_F32)
+    rmsnorm_kernel<TD, float, TO><<<R, threads, 0, stream>>>(x, (const TD*)delta, rows, (const float*)w,
+                                                            (TO*)out, H, eps, writeback);
+  else if (w_dtype == RLLM_DT_BF16)
+    rmsnorm_kernel<TD, bf16, TO><<<R, threads, 0, stream>>>(x, (const TD*)delta, rows, (const bf16*)w,
+                                                           (TO*)out, H, eps, writeback);
+  else
+    return RLLM_E_BADARG;
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// act_dtype is the dtype of delta and of out.
+RLLM_EXPORT int rllm_rmsnorm(float* x, const void* delta, const int* rows, const void* w, int w_dtype,
+                             void* out, int act_dtype, int R, int H, float eps, int writeback,
+                             cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (H <= 0 || !(eps > 0.f)) return RLLM_E_BADARG;
+  if (rows && writeback) return RLLM_E_BADARG;
+  if (act_dtype == RLLM_DT_F32)
+    return rmsnorm_launch_w<float, float>(x, delta, rows, w, w_dtype, out, R, H, eps, writeback, stream);
+  if (act_dtype == RLLM_DT_BF16)
+    return rmsnorm_launch_w<bf16, bf16>(x, delta, rows, w, w_dtype, out, R, H, eps, writeback, stream);
+  return RLLM_E_BADARG;
+}
+
+// x[t, :] += delta[t, :]  (float32 add), for a block's output that no norm follows.
+template <typename TD>
+__global__ void residual_add_kernel(float* __restrict__ x, const TD* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] += to_f32(delta[i]);
+}
+
+RLLM_EXPORT int rllm_residual_add(float* x, const void* delta, int act_dtype, long long n,
+                                  cudaStream_t stream) {
+  if (n <= 0) return 0;
+  unsigned blocks = (unsigned)((n + 255) / 256);
+  RLLM_DISPATCH_DTYPE(act_dtype, TD,
+    (residual_add_kernel<TD><<<blocks, 256, 0, stream>>>(x, (const TD*)delta, (size_t)n)));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Rotary position encoding + write of K and V into cache pages.
+//   qkv [T, (nq + 2*nkv) * d]: q heads, then k heads, then v heads of a token.
+//   q is rotated in place; k is rotated and stored into its page; v is stored.
+// Rotate-half convention over the first rotary_dim dims of a head
+// (crates/rllm-model/src/rope.rs:57-82): for i < rd/2
+//   out[i]        = x[i] * cos(p f_i) - x[i + rd/2] * sin(p f_i)
+//   out[i + rd/2] = x[i + rd/2] * cos(p f_i) + x[i] * sin(p f_i)
+// The angle p * f_i and its cosine and sine are computed in float64 and then
+// rounded to float32, like the reference's table (rope.rs:13-31); the
+// rotation is float32.  rotary_dim 0 rotates nothing.
+// Cache layout per layer: K and V each [num_pages, nkv, page_size, d]; token
+// at position p of sequence s lies in page block_table[s][p / page_size] at
+// row p % page_size (slot rule of crates/rllm-worker/src/model_runner.rs:806-826).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ token_seq,
+                                     const double* __restrict__ inv_freq, int rotary_dim,
+                                     const int* __restrict__ block_table, int max_blocks,
+                                     T* __restrict__ kcache, T* __restrict__ vcache, int nq, int nkv,
+                                     int d, int page_size, int num_pages, int write_kv,
+                                     int* __restrict__ err) {
+  extern __shared__ float cs[];  // cos[rd/2], sin[rd/2]
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rotary_dim >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double a = (double)pos * inv_freq[i];
+    double s, c;
+    sincos(a, &s, &c);
+    cs[i] = (float)c;
+    cs[half + i] = (float)s;
+  }
+  __syncthreads();
+  T* row = qkv + (size_t)t * (nq + 2 * nkv) * d;
+  // q: rotate in place
+  for (int idx = threadIdx.x; idx < nq * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    T* x = row + h * d;
+    const float a = to_f32(x[i]), b = to_f32(x[i + half]);
+    const float c = cs[i], s = cs[half + i];
+    x[i] = from_f32<T>(a * c - b * s);
+    x[i + half] = from_f32<T>(b * c + a * s);
+  }
+  if (!write_kv) return;
+  const int seq = token_seq[t];
+  const int page = block_table[(size_t)seq * max_blocks + pos / page_size];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(err, 2);
+    return;
+  }
+  const int slot = pos % page_size;
+  const T* ksrc = row + nq * d;
+  const T* vsrc = row + (nq + nkv) * d;
+  for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
+    const int h = idx / d, i = idx - h * d;
+    const size_t dst = (((size_t)page * nkv + h) * page_size + slot) * d + i;
+    float kv = to_f32(ksrc[idx]);
+    if (i < rotary_dim) {
+      if (i < half) kv = kv * cs[i] - to_f32(ksrc[idx + half]) * cs[half + i];
+      else          kv = kv * cs[i - half] + to_f32(ksrc[idx - half]) * cs[i];
+    }
+    kcache[dst] = from_f32<T>(kv);
+    vcache[dst] = vsrc[idx];
+  }
+}
+
+RLLM_EXPORT int rllm_rope_kv_write(void* qkv, int dtype, const int* positions, const int* token_seq,
+                                   const double* inv_freq, int rotary_dim, const int* block_table,
+                                   int max_blocks, void* kcache, void* vcache, int T, int nq, int nkv,
+                                   int d, int page_size, int num_pages, int write_kv, int* err,
+                                   cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (nq <= 0 || nkv < 0 || d <= 0 || rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1))
+    return RLLM_E_BADARG;
+  if (write_kv && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0)) return RLLM_E_BADARG;
+  size_t smem = (size_t)rotary_dim * sizeof(float);
+  if (smem > 48 * 1024) return RLLM_E_UNSUPPORTED;
+  RLLM_DISPATCH_DTYPE(dtype, T_,
+    (rope_kv_write_kernel<T_><<<T, 128, smem, stream>>>((T_*)qkv, positions, token_seq, inv_freq,
+        rotary_dim, block_table, max_blocks, (T_*)kcache, (T_*)vcache, nq, nkv, d, page_size,
+        num_pages, write_kv, err)));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i],  silu(z) = z / (1 + exp(-z))
+// (crates/rllm-model/src/layers.rs:214-220), float32 arithmetic.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const size_t t = idx / I;
+  const int i = (int)(idx - t * I);
+  const float g = to_f32(gu[t * 2 * I + i]);
+  const float u = to_f32(gu[t * 2 * I + I + i]);
+  out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+
+RLLM_EXPORT int rllm_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (I <= 0) return RLLM_E_BADARG;
+  size_t n = (size_t)T * I;
+  unsigned blocks = (unsigned)((n + 255) / 256);
+  RLLM_DISPATCH_DTYPE(dtype, T_,
+    (silu_mul_kernel<T_><<<blocks, 256, 0, stream>>>((const T_*)gu, (T_*)out, I, n)));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,342 @@
+// Sampling over float32 logits [R, V], one block per row, with the reference's
+// pipeline (crates/rllm-sampling/src/sampler.rs:62-169): penalties and biases
+// (rllm_logit_edits), masks (rllm_logit_mask), then per row: greedy when
+// temperature <= 0 or top_k == 1 (:117), else temperature, top-k, top-p, min-p
+// (crates/rllm-sampling/src/logits.rs:5-93) and a draw from the softmax of
+// what is left (sampler.rs:194-214).
+//
+// Differences from the reference, on purpose:
+//  * the random number of a draw comes from Philox4x32-10 keyed by the
+//    request's seed with the index of the generated token as counter, so a
+//    request's samples do not depend on the batch it is in (the reference
+//    shares one generator between all requests and ignores the request's
+//    seed, sampler.rs:37-51, 200-203);
+//  * probability mass is summed in 64-bit fixed point (exp(y - max) * 2^40),
+//    which is exact and independent of the order of the additions, so neither
+//    the top-p cut nor the draw depends on how threads split a row;
+//  * greedy ties go to the lowest index (the reference's max_by gives the
+//    last, sampler.rs:184-191); top_k keeps the k largest values and their
+//    ties (the reference's threshold, logits.rs:26-31, is the (k+1)-th largest,
+//    which keeps k+1); top-p keeps all ties of its last value; the draw takes
+//    the first index whose running sum exceeds u, so a masked token is never
+//    drawn (the reference's `>=` draws index 0 when u is 0, sampler.rs:208).
+#include "common.cuh"
+#include <math.h>
+
+#define SAMPLE_THREADS 1024
+#define FX_ONE 1099511627776.0f  // 2^40
+
+__device__ __forceinline__ unsigned f2key(float f) {
+  unsigned b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key2f(unsigned k) {
+  unsigned b = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(b);
+}
+__device__ __forceinline__ unsigned long long fx_mass(float y, float mx) {
+  return (unsigned long long)(expf(y - mx) * FX_ONE);
+}
+
+__device__ void philox4x32_10(unsigned c0, unsigned c1, unsigned c2, unsigned c3, unsigned k0,
+                              unsigned k1, unsigned* out) {
+  const unsigned M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const unsigned hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
+    const unsigned hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
+    const unsigned n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += W0; k1 += W1;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+struct ArgMax { float v; int i; };
+__device__ __forceinline__ ArgMax argmax_better(ArgMax a, ArgMax b) {
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+__device__ ArgMax block_argmax(ArgMax a, ArgMax* sm) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax b; b.v = __shfl_xor_sync(0xffffffffu, a.v, o); b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    a = argmax_better(a, b);
+  }
+  __syncthreads();
+  if (lane == 0) sm[warp] = a;
+  __syncthreads();
+  ArgMax r = sm[0];
+  for (int w = 1; w < (int)(blockDim.x >> 5); ++w) r = argmax_better(r, sm[w]);
+  return r;
+}
+
+// Radix descent over the 32-bit order keys of a row, 8 bits a pass, from the
+// largest value down.  With by_mass false it finds the key of the k-th largest
+// element (target = k, every element weighs 1); with by_mass true the key at
+// which the mass of the elements >= it first reaches `target`.  Only elements
+// with key >= floor_key take part.
+__device__ unsigned radix_select(const float* __restrict__ x, int V, float inv_t, float mx,
+                                 unsigned floor_key, unsigned long long target, bool by_mass,
+                                 unsigned long long* hist, unsigned* sh_prefix,
+                                 unsigned long long* sh_cum) {
+  unsigned prefix = 0;
+  unsigned long long cum = 0;  // weight of elements above the current prefix range
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+    for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0ull;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float y = x[i] * inv_t;
+      const unsigned key = f2key(y);
+      if (key < floor_key || (key & himask) != prefix) continue;
+      const unsigned long long w = by_mass ? fx_mass(y, mx) : 1ull;
+      if (w) atomicAdd(&hist[(key >> shift) & 0xffu], w);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned long long c = cum;
+      int b = 255;
+      for (; b > 0; --b) {
+        if (c + hist[b] >= target) break;
+        c += hist[b];
+      }
+      *sh_prefix = prefix | ((unsigned)b << shift);
+      *sh_cum = c;
+    }
+    __syncthreads();
+    prefix = *sh_prefix;
+    cum = *sh_cum;
+    __syncthreads();
+  }
+  return prefix;
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const float* __restrict__ min_p, const unsigned long long* __restrict__ seeds,
+              const long long* __restrict__ gen_index, int* __restrict__ out_tokens) {
+  __shared__ ArgMax sm_arg[32];
+  __shared__ unsigned long long hist[256];
+  __shared__ unsigned long long seg_sum[SAMPLE_THREADS];
+  __shared__ unsigned sh_prefix;
+  __shared__ unsigned long long sh_cum;
+  __shared__ int sh_pick;
+  const int r = blockIdx.x;
+  const float* x = logits + (size_t)r * ld;
+  const float temp = temperature[r];
+  const int k = top_k[r];
+  const bool greedy = !(temp > 0.f) || k == 1;
+  const float inv_t = greedy ? 1.0f : 1.0f / temp;
+
+  ArgMax best; best.v = -INFINITY; best.i = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    ArgMax c; c.v = x[i] * inv_t; c.i = i;
+    best = argmax_better(best, c);
+  }
+  best = block_argmax(best, sm_arg);
+  if (greedy || best.v == -INFINITY) {
+    if (threadIdx.x == 0) out_tokens[r] = best.i == 0x7fffffff ? 0 : best.i;
+    return;
+  }
+  const float mx = best.v;
+  unsigned thr_key = 0u;  // keep keys >= thr_key
+  if (k > 0 && k < V) {
+    const unsigned kk = radix_select(x, V, inv_t, mx, 0u, (unsigned long long)k, false, hist,
+                                     &sh_prefix, &sh_cum);
+    thr_key = max(thr_key, kk);
+  }
+  const float p = top_p[r];
+  if (p > 0.f && p < 1.f) {
+    // mass of what top-k left
+    unsigned long long z = 0;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float y = x[i] * inv_t;
+      if (f2key(y) >= thr_key) z += fx_mass(y, mx);
+    }
+    seg_sum[threadIdx.x] = z;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned long long t = 0;
+      for (int i = 0; i < (int)blockDim.x; ++i) t += seg_sum[i];
+      sh_cum = t;
+    }
+    __syncthreads();
+    const unsigned long long total = sh_cum;
+    __syncthreads();
+    unsigned long long target = (unsigned long long)((double)total * (double)p);
+    if (target < 1ull) target = 1ull;
+    const unsigned pk = radix_select(x, V, inv_t, mx, thr_key, target, true, hist, &sh_prefix, &sh_cum);
+    thr_key = max(thr_key, pk);
+  }
+  const float mp = min_p[r];
+  if (mp > 0.f) {
+    const unsigned mk = f2key(logf(mp) + mx);
+    thr_key = max(thr_key, mk);
+  }
+  // the draw: contiguous segment per thread, exact integer prefix sums
+  const int seg = (V + blockDim.x - 1) / blockDim.x;
+  const int lo = threadIdx.x * seg, hi = min(V, lo + seg);
+  unsigned long long mine = 0;
+  for (int i = lo; i < hi; ++i) {
+    const float y = x[i] * inv_t;
+    if (f2key(y) >= thr_key) mine += fx_mass(y, mx);
+  }
+  seg_sum[threadIdx.x] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long total = 0;
+    for (int i = 0; i < (int)blockDim.x; ++i) total += seg_sum[i];
+    unsigned w[4];
+    const unsigned long long seed = seeds[r];
+    const unsigned long long ctr = (unsigned long long)gen_index[r];
+    philox4x32_10((unsigned)ctr, (unsigned)(ctr >> 32), 0u, 0u, (unsigned)seed, (unsigned)(seed >> 32), w);
+    const unsigned long long u24 = w[0] >> 8;  // u = u24 / 2^24 in [0, 1)
+    const unsigned long long thi = __umul64hi(total, u24), tlo = total * u24;
+    const unsigned long long target = (thi << 40) | (tlo >> 24);  // floor(total * u)
+    unsigned long long c = 0;
+    int pick = blockDim.x - 1;
+    for (int i = 0; i < (int)blockDim.x; ++i) {
+      if (c + seg_sum[i] > target) { pick = i; break; }
+      c += seg_sum[i];
+    }
+    sh_pick = pick;
+    sh_cum = target - c;  // what is left to pass inside the picked segment
+  }
+  __syncthreads();
+  if ((int)threadIdx.x == sh_pick) {
+    const unsigned long long rest = sh_cum;
+    unsigned long long c = 0;
+    int tok = -1, last_kept = -1;
+    for (int i = lo; i < hi; ++i) {
+      const float y = x[i] * inv_t;
+      if (f2key(y) < thr_key) continue;
+      const unsigned long long w = fx_mass(y, mx);
+      if (w) last_kept = i;
+      c += w;
+      if (c > rest) { tok = i; break; }
+    }
+    if (tok < 0) tok = last_kept >= 0 ? last_kept : best.i;
+    out_tokens[r] = tok;
+  }
+}
+
+RLLM_EXPORT int rllm_sample(const float* logits, int R, int V, int ld, const float* temperature,
+                            const int* top_k, const float* top_p, const float* min_p,
+                            const unsigned long long* seeds, const long long* gen_index,
+                            int* out_tokens, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0 || ld < V) return RLLM_E_BADARG;
+  sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, ld, temperature, top_k, top_p, min_p,
+                                                  seeds, gen_index, out_tokens);
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// Greedy only: out[r] = lowest index of the largest logit of row r.
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out_tokens) {
+  __shared__ ArgMax sm_arg[32];
+  const float* x = logits + (size_t)blockIdx.x * ld;
+  ArgMax best; best.v = -INFINITY; best.i = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    ArgMax c; c.v = x[i]; c.i = i;
+    best = argmax_better(best, c);
+  }
+  best = block_argmax(best, sm_arg);
+  if (threadIdx.x == 0) out_tokens[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
+RLLM_EXPORT int rllm_argmax(const float* logits, int R, int V, int ld, int* out_tokens,
+                            cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0 || ld < V) return RLLM_E_BADARG;
+  argmax_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, ld, out_tokens);
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Penalties and biases on single logits.  One entry per (row, distinct token):
+// bias is added first (logits.rs:147-154); then the repetition penalty is
+// applied `count` times, dividing a positive logit and multiplying any other
+// (:95-110, once per occurrence in the context like the reference's loop);
+// then frequency * count and, if count > 0, presence are subtracted (:113-144).
+// ---------------------------------------------------------------------------
+__global__ void logit_edits_kernel(float* __restrict__ logits, int V, int ld, int n,
+                                   const int* __restrict__ rows, const int* __restrict__ tokens,
+                                   const int* __restrict__ counts, const float* __restrict__ bias,
+                                   const float* __restrict__ rep, const float* __restrict__ freq,
+                                   const float* __restrict__ pres) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n) return;
+  const int r = rows[e], t = tokens[e], c = counts[e];
+  if (t < 0 || t >= V) return;
+  float* p = logits + (size_t)r * ld + t;
+  float v = *p + bias[e];
+  const float rp = rep[r];
+  if (rp != 1.0f)
+    for (int i = 0; i < c; ++i) v = v > 0.f ? v / rp : v * rp;
+  if (c > 0) {
+    if (freq[r] != 0.f) v -= freq[r] * (float)c;
+    if (pres[r] != 0.f) v -= pres[r];
+  }
+  *p = v;
+}
+
+RLLM_EXPORT int rllm_logit_edits(float* logits, int V, int ld, int n, const int* rows,
+                                 const int* tokens, const int* counts, const float* bias,
+                                 const float* rep, const float* freq, const float* pres,
+                                 cudaStream_t stream) {
+  if (n <= 0) return 0;
+  logit_edits_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, V, ld, n, rows, tokens, counts, bias,
+                                                          rep, freq, pres);
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// Masks.  Row r keeps only the tokens of its sorted list allowed[allowed_start[r]
+// .. allowed_start[r+1]) if that list is not empty (logits.rs:157-166); then the
+// n_suppress pairs (row, token) are set to -inf (:169-181, :184-191).
+__global__ void allowed_mask_kernel(float* __restrict__ logits, int V, int ld,
+                                    const int* __restrict__ allowed_start,
+                                    const int* __restrict__ allowed) {
+  const int r = blockIdx.y;
+  const int b = allowed_start[r], e = allowed_start[r + 1];
+  if (e <= b) return;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= V) return;
+  int lo = b, hi = e;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (allowed[mid] < i) lo = mid + 1; else hi = mid;
+  }
+  if (!(lo < e && allowed[lo] == i)) logits[(size_t)r * ld + i] = -INFINITY;
+}
+__global__ void suppress_kernel(float* __restrict__ logits, int V, int ld, int n,
+                                const int* __restrict__ rows, const int* __restrict__ tokens) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n) return;
+  const int t = tokens[e];
+  if (t >= 0 && t < V) logits[(size_t)rows[e] * ld + t] = -INFINITY;
+}
+
+RLLM_EXPORT int rllm_logit_mask(float* logits, int R, int V, int ld, const int* allowed_start,
+                                const int* allowed, int n_suppress, const int* sup_rows,
+                                const int* sup_tokens, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (allowed_start) {
+    dim3 grid((V + 255) / 256, R);
+    allowed_mask_kernel<<<grid, 256, 0, stream>>>(logits, V, ld, allowed_start, allowed);
+    RLLM_LAUNCH_CHECK();
+  }
+  if (n_suppress > 0) {
+    suppress_kernel<<<(n_suppress + 255) / 256, 256, 0, stream>>>(logits, V, ld, n_suppress, sup_rows,
+                                                                  sup_tokens);
+    RLLM_LAUNCH_CHECK();
+  }
+  return 0;
+}

@@ -1,0 +1,218 @@
+"""Python faces of the CUDA kernels: torch tensors in, kernel launched on the
+current stream.  There is no fallback: a tensor that is not on a CUDA device,
+a missing compiler or a size that a kernel refuses raises an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+DT_F32, DT_BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt is torch.float32:
+        return DT_F32
+    if dt is torch.bfloat16:
+        return DT_BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dt}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    if t is None:
+        return c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError("the engine's kernels run on CUDA tensors only; there is no CPU path")
+    return c_void_p(t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise KernelError(f"{what}: refused its arguments (bad size or pointer)")
+    if code == -2:
+        raise KernelError(f"{what}: this size is legal but no kernel of this build takes it")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _contig(t: torch.Tensor, name: str) -> None:
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+# ---------------------------------------------------------------------------
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] as float32; ids int32 [T], out float32 [T, H]."""
+    lib = build.load_library("elementwise")
+    T, (V, H) = ids.numel(), table.shape
+    assert ids.dtype is torch.int32 and out.dtype is torch.float32 and out.shape == (T, H)
+    _contig(table, "table"); _contig(out, "out")
+    _check(lib.rllm_embedding(_ptr(ids), _ptr(table), c_int(dtype_code(table.dtype)), _ptr(out),
+                              c_int(T), c_int(H), c_int(V), _ptr(err), _stream()), "embedding")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+            writeback: bool = False) -> None:
+    """out = rmsnorm(x [+ delta]) * weight; x float32 [., H]; out [R, H] in the
+    activation dtype.  ``writeback`` stores x + delta into x.  ``rows`` (int32
+    [R]) picks the input row of each output row."""
+    lib = build.load_library("elementwise")
+    H = x.shape[-1]
+    R = out.shape[0]
+    assert x.dtype is torch.float32 and out.shape[-1] == H and weight.numel() == H
+    _contig(x, "x"); _contig(out, "out"); _contig(weight, "weight")
+    if delta is not None:
+        assert delta.dtype is out.dtype and delta.shape == x.shape
+        _contig(delta, "delta")
+    if rows is not None:
+        assert rows.dtype is torch.int32 and rows.numel() == R
+    else:
+        assert x.shape[0] == R
+    _check(lib.rllm_rmsnorm(_ptr(x), _ptr(delta), _ptr(rows), _ptr(weight),
+                            c_int(dtype_code(weight.dtype)), _ptr(out), c_int(dtype_code(out.dtype)),
+                            c_int(R), c_int(H), c_float(eps), c_int(1 if writeback else 0), _stream()),
+           "rmsnorm")
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+    lib = build.load_library("elementwise")
+    assert x.dtype is torch.float32 and x.shape == delta.shape
+    _contig(x, "x"); _contig(delta, "delta")
+    _check(lib.rllm_residual_add(_ptr(x), _ptr(delta), c_int(dtype_code(delta.dtype)),
+                                 c_longlong(x.numel()), _stream()), "residual_add")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor,
+                  inv_freq: Optional[torch.Tensor], rotary_dim: int, block_table: Optional[torch.Tensor],
+                  kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor], nq: int, nkv: int,
+                  d: int, err: torch.Tensor, write_kv: bool = True) -> None:
+    """Rotates q (in place) and k, stores k and v of every token into its page.
+
+    qkv [T, (nq + 2 nkv) d]; caches [pages, nkv, page_size, d]; inv_freq float64
+    [rotary_dim / 2]; block_table int32 [S, max_blocks]."""
+    lib = build.load_library("elementwise")
+    T = qkv.shape[0]
+    assert qkv.shape[1] == (nq + 2 * nkv) * d
+    _contig(qkv, "qkv")
+    if rotary_dim:
+        assert inv_freq is not None and inv_freq.dtype is torch.float64 and inv_freq.numel() == rotary_dim // 2
+    if write_kv:
+        assert kcache.dtype is qkv.dtype and vcache.dtype is qkv.dtype
+        assert kcache.shape == vcache.shape and kcache.shape[1] == nkv and kcache.shape[3] == d
+        _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
+        pages, page_size, max_blocks = kcache.shape[0], kcache.shape[2], block_table.shape[1]
+    else:
+        pages = page_size = max_blocks = 0
+    _check(lib.rllm_rope_kv_write(_ptr(qkv), c_int(dtype_code(qkv.dtype)), _ptr(positions),
+                                  _ptr(token_seq), _ptr(inv_freq), c_int(rotary_dim),
+                                  _ptr(block_table), c_int(max_blocks), _ptr(kcache), _ptr(vcache),
+                                  c_int(T), c_int(nq), c_int(nkv), c_int(d), c_int(page_size),
+                                  c_int(pages), c_int(1 if write_kv else 0), _ptr(err), _stream()),
+           "rope_kv_write")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    lib = build.load_library("elementwise")
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.dtype is out.dtype
+    _contig(gate_up, "gate_up"); _contig(out, "out")
+    _check(lib.rllm_silu_mul(_ptr(gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(I),
+                             _stream()), "silu_mul")
+
+
+def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
+                   vcache: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
+                   token_seq: torch.Tensor, nq: int, nkv: int, d: int, window: int, scale: float,
+                   err: torch.Tensor) -> None:
+    """Paged causal attention of T query tokens, one warp per (token, head).
+
+    q: T rows of nq*d values with row stride q_stride (elements); out [T, nq*d]."""
+    lib = build.load_library("attention_simt")
+    T = out.shape[0]
+    _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
+    assert kcache.dtype is q.dtype and out.dtype is q.dtype
+    _check(lib.rllm_attention_simt(_ptr(q), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
+                                   c_int(dtype_code(q.dtype)), _ptr(block_table),
+                                   c_int(block_table.shape[1]), _ptr(positions), _ptr(token_seq),
+                                   c_int(T), c_int(nq), c_int(nkv), c_int(d), c_int(kcache.shape[2]),
+                                   c_int(kcache.shape[0]), c_int(window), c_float(scale), _ptr(err),
+                                   _stream()), "attention_simt")
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] . w[N, K]^T, float32 FFMA."""
+    lib = build.load_library("gemm_f32")
+    M, K = a.shape
+    N = w.shape[0]
+    assert a.dtype is torch.float32 and w.dtype is torch.float32 and out.dtype is torch.float32
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(lib.rllm_gemm_f32(_ptr(a), c_int(a.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out),
+                             c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), _stream()), "gemm_f32")
+
+
+# ---------------------------------------------------------------------------
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    lib = build.load_library("sampling")
+    R, V = logits.shape
+    assert logits.dtype is torch.float32 and out.dtype is torch.int32 and logits.stride(1) == 1
+    _check(lib.rllm_argmax(_ptr(logits), c_int(R), c_int(V), c_int(logits.stride(0)), _ptr(out),
+                           _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, seeds: torch.Tensor, gen_index: torch.Tensor, out: torch.Tensor) -> None:
+    lib = build.load_library("sampling")
+    R, V = logits.shape
+    assert logits.dtype is torch.float32 and logits.stride(1) == 1
+    assert temperature.dtype is torch.float32 and top_k.dtype is torch.int32
+    assert top_p.dtype is torch.float32 and min_p.dtype is torch.float32
+    assert seeds.dtype is torch.int64 and gen_index.dtype is torch.int64 and out.dtype is torch.int32
+    _check(lib.rllm_sample(_ptr(logits), c_int(R), c_int(V), c_int(logits.stride(0)), _ptr(temperature),
+                           _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(seeds), _ptr(gen_index),
+                           _ptr(out), _stream()), "sample")
+
+
+def logit_edits(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor, counts: torch.Tensor,
+                bias: torch.Tensor, rep: torch.Tensor, freq: torch.Tensor, pres: torch.Tensor) -> None:
+    lib = build.load_library("sampling")
+    R, V = logits.shape
+    _check(lib.rllm_logit_edits(_ptr(logits), c_int(V), c_int(logits.stride(0)), c_int(rows.numel()),
+                                _ptr(rows), _ptr(tokens), _ptr(counts), _ptr(bias), _ptr(rep),
+                                _ptr(freq), _ptr(pres), _stream()), "logit_edits")
+
+
+def logit_mask(logits: torch.Tensor, allowed_start: Optional[torch.Tensor],
+               allowed: Optional[torch.Tensor], sup_rows: Optional[torch.Tensor],
+               sup_tokens: Optional[torch.Tensor]) -> None:
+    lib = build.load_library("sampling")
+    R, V = logits.shape
+    n = 0 if sup_rows is None else sup_rows.numel()
+    _check(lib.rllm_logit_mask(_ptr(logits), c_int(R), c_int(V), c_int(logits.stride(0)),
+                               _ptr(allowed_start), _ptr(allowed), c_int(n), _ptr(sup_rows),
+                               _ptr(sup_tokens), _stream()), "logit_mask")
+
+
+def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
+                    vcache: torch.Tensor, block_table: torch.Tensor, ctx, nq: int, nkv: int, d: int,
+                    window: int, scale: float) -> None:
+    """Attention of all query tokens of a step over the paged cache; picks the
+    kernel for the dtype and the shape of the batch (``ctx`` is a StepContext)."""
+    attention_simt(q, q_stride, out, kcache, vcache, block_table, ctx.positions, ctx.token_seq,
+                   nq, nkv, d, window, scale, ctx.err)

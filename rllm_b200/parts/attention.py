@@ -1,0 +1,101 @@
+"""Grouped-query causal attention over a paged cache: the Llama mixer.
+
+q, k, v projections without bias (one fused matrix product over the stacked
+weights), head split, position encoding on q and k, write of k and v into the
+run's cache pages, attention of every query token over its sequence's cache
+through the block table, output projection
+(crates/rllm-model/src/layers.rs:280-347 for the math, :363-571 for the paged
+intent).  kv head of query head h is h // (nq // nkv)
+(crates/rllm-kernels/src/cuda/paged_attention.cu:113); scores are scaled by
+1/sqrt(head_dim) (layers.rs:326-329) unless ``scale`` is given.
+
+Portions of prompts and single decoded tokens are one code path: the tokens
+of this step are written to the cache first and every query then reads keys
+0 .. its own position (or its window) from the cache.
+
+params: hidden_size, num_heads, num_kv_heads, head_dim, window (None: all
+keys), scale (None: 1/sqrt(head_dim)), position (PartSpec), shares_kv (True:
+the run reads another run's cache, has no k/v projections and writes nothing).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import ops
+from .base import KVCacheView, Mixer, StepContext
+from .linear import linear
+from .registry import build_part, register_part
+from .spec import KVPagesNeed, PartSpec, TensorSpec
+
+
+@register_part("mixer", "attention")
+class PagedAttention(Mixer):
+    def __init__(self, spec: PartSpec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        p = spec.get()
+        self.hidden = int(p["hidden_size"])
+        self.nq = int(p["num_heads"])
+        self.nkv = int(p["num_kv_heads"])
+        self.d = int(p["head_dim"])
+        self.window = p.get("window")
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.d)
+        self.shares_kv = bool(p.get("shares_kv", False))
+        if self.nq % self.nkv:
+            raise ValueError(f"num_heads {self.nq} must be a multiple of num_kv_heads {self.nkv}")
+        if self.d % 16 or self.d > 256:
+            raise ValueError(f"head_dim {self.d}: the attention kernels take multiples of 16 up to 256")
+        pos = p.get("position")
+        self.position = build_part("position_encoding", pos if pos is not None else PartSpec.of("none"))
+        self.w_qkv: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+
+    # -- weights ----------------------------------------------------------
+    def _names(self):
+        p = self.prefix
+        return (p + "q_proj.weight", p + "k_proj.weight", p + "v_proj.weight", p + "o_proj.weight")
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        q, k, v, o = self._names()
+        specs = [TensorSpec(q, (self.nq * self.d, self.hidden))]
+        if not self.shares_kv:
+            specs += [TensorSpec(k, (self.nkv * self.d, self.hidden)),
+                      TensorSpec(v, (self.nkv * self.d, self.hidden))]
+        specs.append(TensorSpec(o, (self.hidden, self.nq * self.d)))
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        q, k, v, o = self._names()
+        if self.shares_kv:
+            self.w_qkv = tensors[q]
+        else:
+            # stacked [Wq; Wk; Wv]: one matrix product gives a token's q, k and v side by side
+            self.w_qkv = torch.cat([tensors[q], tensors[k], tensors[v]], dim=0).contiguous()
+        self.w_o = tensors[o]
+
+    def cache_need(self):
+        return KVPagesNeed(self.nkv, self.d, self.window)
+
+    # -- compute ----------------------------------------------------------
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: KVCacheView) -> torch.Tensor:
+        T = x.shape[0]
+        nkv_here = 0 if self.shares_kv else self.nkv
+        qkv = linear(x, self.w_qkv)                                   # [T, (nq + 2 nkv) d]
+        table = ctx.block_tables[cache.group]
+        fused = self.position.fused_rotary(x.device)
+        writes = cache.writes and not self.shares_kv
+        if fused is None:
+            q = qkv[:, : self.nq * self.d].view(T, self.nq, self.d)
+            k = qkv[:, self.nq * self.d: (self.nq + nkv_here) * self.d].view(T, nkv_here, self.d) \
+                if nkv_here else None
+            self.position.apply(q, k, ctx.positions)
+            fused = (None, 0)
+        inv_freq, rd = fused
+        ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, inv_freq, rd, table, cache.k, cache.v,
+                          self.nq, nkv_here, self.d, ctx.err, write_kv=writes)
+        out = torch.empty((T, self.nq * self.d), dtype=x.dtype, device=x.device)
+        ops.paged_attention(qkv, qkv.shape[1], out, cache.k, cache.v, table, ctx, self.nq, self.nkv,
+                            self.d, int(self.window or 0), self.scale)
+        return linear(out, self.w_o)

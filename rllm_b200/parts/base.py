@@ -1,0 +1,135 @@
+"""Interfaces of the parts a layer is put together from, and the per-step
+context they are handed.
+
+Every part is built from a ``PartSpec`` (its sizes and constants) and a tensor
+name prefix, declares its tensors (``tensor_specs``), receives them
+(``load``) and computes (``forward``).  A part never sees a model
+configuration.
+
+Interfaces
+----------
+Norm            forward(x_f32[T,H]) -> act[T,H]
+                add_forward(x_f32[T,H] (updated in place: x += delta), delta act[T,H]) -> act[T,H]
+                gather_forward(x_f32, delta|None, rows int32[R]) -> act[R,H]
+PositionEncoding  apply(q[T,nq,d], k[T,nkv,d], positions) in place; optionally
+                fused_rotary(device) -> (inv_freq float64[rd/2], rd) so that a mixer can
+                fuse the rotation into its cache write
+Mixer           cache_need() -> KVPagesNeed | StateNeed | None
+                forward(x act[T,H], ctx StepContext, cache view) -> act[T,H]
+FeedForward     forward(x act[T,H]) -> act[T,H]
+Block           forward(h_f32[T,H], pending act[T,H]|None, ctx, cache) -> (h_f32, pending)
+                where the true hidden state is h + pending (the last add is
+                left to the next norm, which fuses it)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .spec import PartSpec, TensorSpec
+
+
+@dataclass
+class StepContext:
+    """One batch of (request, its next tokens), flattened.
+
+    Sequences with a single token this step come first (``num_decode`` of
+    them).  Token i belongs to sequence ``token_seq[i]`` and has absolute
+    position ``positions[i]``; sequence s owns tokens
+    ``q_start[s] .. q_start[s+1]`` and holds ``seq_lens[s]`` tokens in the cache
+    after this step.  ``block_tables[g]`` is the page table of cache group g,
+    int32 [S, max_blocks], -1 where a page was given back.
+    """
+
+    num_tokens: int
+    num_seqs: int
+    num_decode: int
+    positions: torch.Tensor
+    token_seq: torch.Tensor
+    q_start: torch.Tensor
+    seq_lens: torch.Tensor
+    q_lens_host: List[int]
+    seq_lens_host: List[int]
+    block_tables: List[torch.Tensor]
+    state_slots: torch.Tensor
+    state_slots_host: List[int]
+    err: torch.Tensor
+    act_dtype: torch.dtype = torch.bfloat16
+    extras: Dict[str, object] = field(default_factory=dict)
+
+    @property
+    def max_q_len(self) -> int:
+        return max(self.q_lens_host) if self.q_lens_host else 0
+
+    @property
+    def max_seq_len(self) -> int:
+        return max(self.seq_lens_host) if self.seq_lens_host else 0
+
+
+@dataclass
+class KVCacheView:
+    """The pages of one run's attention: K and V [pages, nkv, page_size, d]."""
+
+    k: torch.Tensor
+    v: torch.Tensor
+    group: int
+    writes: bool
+
+
+@dataclass
+class StateCacheView:
+    """Fixed-size per-request state of one run: float32 [slots, *shape]."""
+
+    state: torch.Tensor
+    group: int
+    writes: bool
+
+
+class Part:
+    def __init__(self, spec: PartSpec, prefix: str = ""):
+        self.spec = spec
+        self.prefix = prefix
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return []
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Take this part's tensors (by full name) from ``tensors``."""
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_forward(self, x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def gather_forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor,
+                       act_dtype: torch.dtype) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def fused_rotary(self, device=None) -> Optional[Tuple[Optional[torch.Tensor], int]]:
+        """(float64 frequency table [rd/2] on ``device``, rd) if the encoding is a
+        rotate-half rotation that a mixer may fuse into its cache write (rd 0:
+        nothing to rotate); None if the mixer has to call ``apply``."""
+        return None
+
+    def apply(self, q: torch.Tensor, k: Optional[torch.Tensor], positions: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self):
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError

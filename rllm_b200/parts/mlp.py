@@ -1,0 +1,48 @@
+"""SiLU-gated feed-forward: down(silu(gate(x)) * up(x)), no bias
+(crates/rllm-model/src/layers.rs:214-220).  gate and up are one matrix product
+over the stacked weights [Wgate; Wup]; silu(z) = z / (1 + exp(-z)) and the
+product with up are computed in float32.
+
+params: hidden_size, intermediate_size.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import ops
+from .base import FeedForward
+from .linear import linear
+from .registry import register_part
+from .spec import PartSpec, TensorSpec
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMLP(FeedForward):
+    def __init__(self, spec: PartSpec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def _names(self):
+        p = self.prefix
+        return p + "gate_proj.weight", p + "up_proj.weight", p + "down_proj.weight"
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        g, u, d = self._names()
+        return [TensorSpec(g, (self.inter, self.hidden)), TensorSpec(u, (self.inter, self.hidden)),
+                TensorSpec(d, (self.hidden, self.inter))]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        g, u, d = self._names()
+        self.w_gate_up = torch.cat([tensors[g], tensors[u]], dim=0).contiguous()
+        self.w_down = tensors[d]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gate_up = linear(x, self.w_gate_up)                       # [T, 2I]
+        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+        ops.silu_mul(gate_up, act)
+        return linear(act, self.w_down)

@@ -1,0 +1,108 @@
+"""Trace replay against the plain implementation: the same requests whole, with
+the last 32 tokens decoded one by one, in portions of changing size, and mixed
+with other requests so that pages are used again; in float32 and in bfloat16;
+for both tiny configurations.  Every logits row of every mode is compared with
+the plain implementation's row for the same (request, position)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+import replay_util as ru
+from conftest import TINY
+
+pytestmark = pytest.mark.gpu
+
+# max |engine - plain| over a request's logits, relative to max |plain|
+TOL = {"float32": 1e-4, "bfloat16": 2e-2}
+
+LENGTHS = {"A": [5, 12, 17, 70, 100, 33, 64, 49], "B": [1, 31, 70, 150, 300, 97, 2, 210]}
+
+
+def make_requests(name: str):
+    cfg, _, _ = TINY[name]
+    rng = np.random.default_rng(1 if name == "A" else 3)
+    return {f"r{i}": [int(t) for t in rng.integers(0, cfg["vocab_size"], size=n)]
+            for i, n in enumerate(LENGTHS[name])}
+
+
+_plain_cache = {}
+
+
+def plain_logits(model_dirs, name: str, dtype: str):
+    key = (name, dtype)
+    if key not in _plain_cache:
+        model = plain_llama.read_model_dir(model_dirs[name],
+                                           round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+        _plain_cache[key] = {rid: model.logits(toks).numpy() for rid, toks in make_requests(name).items()}
+    return _plain_cache[key]
+
+
+def compare(got, want_by_req, reqs, dtype, what):
+    worst = 0.0
+    for rid, toks in reqs.items():
+        want = want_by_req[rid]
+        have = np.stack([got[(rid, p)] for p in range(len(toks))])
+        assert np.isfinite(have).all(), f"{what}: request {rid} has non-finite logits"
+        err = np.abs(have - want).max(axis=1) / np.abs(want).max()
+        bad = np.nonzero(err > TOL[dtype])[0]
+        assert bad.size == 0, (f"{what}: request {rid} (length {len(toks)}): first wrong position "
+                               f"{int(bad[0])}, error {err[bad[0]]:.3e} > {TOL[dtype]:.0e}; "
+                               f"wrong positions {bad[:20].tolist()}")
+        worst = max(worst, float(err.max()))
+    return worst
+
+
+MODES = {
+    "whole": lambda reqs: ru.trace_whole(reqs),
+    "tail_decode": lambda reqs: ru.trace_tail_decode(reqs, 32),
+    "portions": lambda reqs: ru.trace_portions(reqs, seed=5),
+    "mixed": lambda reqs: ru.trace_mixed(reqs, seed=11, live=4, tail=32),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("mode", list(MODES))
+def test_replay_matches_plain(model_dirs, name, dtype, mode):
+    cfg, _, page = TINY[name]
+    reqs = make_requests(name)
+    tb = MODES[mode](reqs)
+    if mode == "mixed":
+        # so few pages that later requests get pages that earlier ones gave back
+        total = sum(ru.round64(len(t)) for t in reqs.values())
+        assert tb.peak < total
+    got = ru.run_trace(model_dirs[name], dtype, tb, cfg["vocab_size"], page_size=page)
+    worst = compare(got, plain_logits(model_dirs, name, dtype), reqs, dtype, f"{name}/{dtype}/{mode}")
+    print(f"{name} {dtype} {mode}: worst relative error {worst:.3e}")
+
+
+def test_modes_agree_in_float32(model_dirs):
+    """The cuts agree with each other far more closely than with the oracle's
+    float64: a row's arithmetic does not depend on the cut."""
+    cfg, _, page = TINY["B"]
+    reqs = make_requests("B")
+    a = ru.run_trace(model_dirs["B"], "float32", ru.trace_whole(reqs), cfg["vocab_size"], page_size=page)
+    b = ru.run_trace(model_dirs["B"], "float32", ru.trace_mixed(reqs, seed=2), cfg["vocab_size"], page_size=page)
+    for key in a:
+        scale = np.abs(a[key]).max()
+        assert np.abs(a[key] - b[key]).max() <= 2e-6 * scale, key
+
+
+def test_trace_run_program(model_dirs):
+    """The program itself, as a child process: bin/trace_run."""
+    cfg, _, page = TINY["A"]
+    reqs = {k: v for k, v in list(make_requests("A").items())[:3]}
+    tb = ru.trace_mixed(reqs, seed=4, live=2, tail=4)
+    got = ru.run_trace(model_dirs["A"], "float32", tb, cfg["vocab_size"], page_size=page, subprocess_mode=True)
+    compare(got, plain_logits(model_dirs, "A", "float32"), reqs, "float32", "program")
+
+
+def test_too_few_pages_is_an_error(model_dirs):
+    cfg, _, page = TINY["A"]
+    reqs = {"r0": list(range(100))}
+    tb = ru.trace_whole(reqs)
+    with pytest.raises(AssertionError):
+        ru.run_trace(model_dirs["A"], "float32", tb, cfg["vocab_size"], page_size=page, max_tokens=64)
