@@ -116,6 +116,8 @@ class CacheManager:
                 if page >= 0:
                     self.pools[g].free(page)
         self._free_slots.append(r.slot)
+        if r.slot in self.fresh_slots:
+            self.fresh_slots.remove(r.slot)
 
     def slot(self, req: Hashable) -> int:
         return self.requests[req].slot

@@ -1,0 +1,179 @@
+"""The engine: requests in, tokens out, one step at a time.
+
+``step`` = schedule -> run the batch through the step function -> sample at
+the rows whose portion ended at the last known token -> append the tokens ->
+stop checks -> give finished requests' pages back
+(crates/rllm-engine/src/engine_core.rs:91-226).  Stop checks, in the
+reference's order (:153-163): an EOS token unless ``ignore_eos``, a token of
+``stop_token_ids`` -> ``stop``; ``max_tokens`` generated -> ``length``; the
+scheduler's limit ``max_model_len`` -> ``length``
+(crates/rllm-scheduler/src/scheduler.rs:349-353).
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass, field
+from typing import Any, Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache import CacheManager, CacheStorage, page_bytes
+from ..config.engine_args import EngineArgs
+from ..models.decoder import DecoderModel
+from ..parts.spec import KVPagesNeed
+from ..sampling import Sampler, SamplingParams, SamplingRow
+from .runner import ModelRunner, StepEntry
+from .scheduler import Request, RequestStatus, Scheduler, SchedulerConfig, SchedulerOutput
+
+
+@dataclass
+class Usage:
+    """crates/rllm-core/src/output.rs:29-34."""
+
+    prompt_tokens: int
+    completion_tokens: int
+    total_tokens: int
+
+
+@dataclass
+class CompletionOutput:
+    """crates/rllm-core/src/output.rs:13-20 (no text: the engine works on ids)."""
+
+    index: int
+    token_ids: List[int]
+    finish_reason: Optional[str] = None      # "stop" | "length" | "aborted"
+
+
+@dataclass
+class RequestOutput:
+    """crates/rllm-core/src/output.rs:6-11, plus the prompt for convenience."""
+
+    request_id: Hashable
+    prompt_token_ids: List[int]
+    outputs: List[CompletionOutput]
+    finished: bool
+    usage: Usage
+
+
+def plan_cache_pages(model: DecoderModel, args: EngineArgs, max_model_len: int, device: torch.device) -> int:
+    """Pages per paged group.  ``num_gpu_blocks`` if given; else what fits into
+    ``gpu_memory_utilization`` of the device's memory beside the weights and a
+    reserve for activations, capped at the reference's sizing rule
+    max_num_seqs * ceil(max_model_len / block_size)
+    (crates/rllm-server/src/server.rs:367-370)."""
+    if args.num_gpu_blocks is not None:
+        return args.num_gpu_blocks
+    elem = 2 if model.dtype is torch.bfloat16 else 4
+    per_page = 0
+    for g, need in enumerate(model.layout.groups):
+        if isinstance(need, KVPagesNeed):
+            per_page += page_bytes(need, args.block_size, elem) * len(model.layout.owners[g])
+    cap = args.max_num_seqs * -(-max_model_len // args.block_size)
+    if per_page == 0:
+        return 1
+    free, total = torch.cuda.mem_get_info(device)
+    spec = model.spec
+    act = args.max_num_batched_tokens * (spec.hidden_size * 16 + 64 * 1024) + \
+        min(args.max_num_seqs, args.max_num_batched_tokens) * spec.vocab_size * 8 + (1 << 30)
+    budget = int(total * args.gpu_memory_utilization) - (total - free) - act
+    if budget < per_page * 4:
+        raise RuntimeError(f"no room for a KV cache: {free >> 20} MiB free of {total >> 20} MiB with "
+                           f"gpu_memory_utilization {args.gpu_memory_utilization}")
+    return max(4, min(cap, budget // per_page))
+
+
+class EngineCore:
+    def __init__(self, model: DecoderModel, args: Optional[EngineArgs] = None):
+        self.args = args or EngineArgs()
+        self.args.validate()
+        self.model = model
+        self.device = model.device
+        spec = model.spec
+        self.max_model_len = min(self.args.max_model_len or spec.max_positions, spec.max_positions)
+        n_paged = sum(1 for n in model.layout.groups if isinstance(n, KVPagesNeed))
+        pages = plan_cache_pages(model, self.args, self.max_model_len, self.device)
+        self.cache = CacheManager(model.layout.groups, self.args.block_size, [pages] * n_paged,
+                                  self.args.max_num_seqs, self.args.enable_prefix_caching)
+        self.storage = CacheStorage(model.layout, self.args.block_size, [pages] * n_paged,
+                                    self.args.max_num_seqs, model.dtype, self.device)
+        self.runner = ModelRunner(model, self.cache, self.storage)
+        self.sampler = Sampler(self.device)
+        self.scheduler = Scheduler(SchedulerConfig(
+            max_num_seqs=self.args.max_num_seqs, max_num_batched_tokens=self.args.max_num_batched_tokens,
+            long_prefill_token_threshold=self.args.long_prefill_token_threshold,
+            enable_chunked_prefill=self.args.enable_chunked_prefill, max_model_len=self.max_model_len),
+            self.cache)
+        self.eos_token_ids = tuple(spec.eos_token_ids)
+        self._arrivals = itertools.count()
+        self.num_steps = 0
+        self.last_schedule: Optional[SchedulerOutput] = None
+
+    # ------------------------------------------------------------------
+    def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
+                    request_id: Optional[Hashable] = None) -> Hashable:
+        """crates/rllm-engine/src/engine_core.rs:55-80."""
+        params = params or SamplingParams()
+        params.validate()
+        arrival = next(self._arrivals)
+        rid = request_id if request_id is not None else arrival
+        vocab = self.model.spec.vocab_size
+        prompt = [int(t) for t in prompt_token_ids]
+        if any(t < 0 or t >= vocab for t in prompt):
+            raise ValueError(f"request {rid!r}: a prompt token lies outside the vocabulary of {vocab}")
+        max_tokens = params.max_tokens if params.max_tokens is not None else self.max_model_len - len(prompt)
+        seed = params.seed if params.seed is not None else (self.args.seed * 1000003 + arrival)
+        self.scheduler.add_request(Request(rid, prompt, params, arrival, seed, max_tokens))
+        return rid
+
+    def abort_request(self, request_id: Hashable) -> bool:
+        return self.scheduler.abort_request(request_id)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------
+    def step(self) -> List[RequestOutput]:
+        sched = self.scheduler.schedule()
+        self.last_schedule = sched
+        self.num_steps += 1
+        if not sched.scheduled:
+            return []
+        entries, rows, sampled_reqs = [], [], []
+        for s in sched.scheduled:
+            req = s.request
+            toks = req.all_token_ids[s.start:s.start + s.num_tokens]
+            entries.append(StepEntry(req.request_id, toks, s.start, [s.num_tokens - 1] if s.want_logits else []))
+            if s.want_logits:
+                ctx_needed = req.params.edits_logits
+                rows.append(SamplingRow(req.params, req.seed, len(req.output_token_ids),
+                                        req.all_token_ids if ctx_needed else (), self.eos_token_ids))
+                sampled_reqs.append(req)
+        logits = self.runner.step(entries)
+        tokens = self.sampler.sample(logits, rows).tolist() if rows else []
+        self.runner.check_errors()
+        self.scheduler.after_step(sched)
+        outputs = []
+        for req, tok in zip(sampled_reqs, tokens):
+            req.output_token_ids.append(int(tok))
+            reason = self._finish_reason(req, int(tok))
+            if reason is not None:
+                self.scheduler.finish(req, RequestStatus.FINISHED_STOPPED if reason == "stop"
+                                      else RequestStatus.FINISHED_LENGTH)
+            n_prompt, n_out = len(req.prompt_token_ids), len(req.output_token_ids)
+            outputs.append(RequestOutput(req.request_id, req.prompt_token_ids,
+                                         [CompletionOutput(0, [int(tok)], reason)], reason is not None,
+                                         Usage(n_prompt, n_out, n_prompt + n_out)))
+        return outputs
+
+    def _finish_reason(self, req: Request, token: int) -> Optional[str]:
+        p = req.params
+        if (token in self.eos_token_ids and not p.ignore_eos) or token in p.stop_token_ids:
+            return "stop"
+        if len(req.output_token_ids) >= req.max_tokens:
+            return "length"
+        if req.num_tokens >= self.max_model_len:
+            return "length"
+        return None
+
+    def stats(self) -> dict:
+        return dict(self.scheduler.stats(), num_steps=self.num_steps)

@@ -1,0 +1,252 @@
+"""Continuous batching: which requests run which tokens in the next step.
+
+Each call of ``schedule`` (1) lets every running request go on, in order of
+arrival: one token if it is decoding, the next portion of its prompt
+otherwise; (2) admits waiting requests, first come first served, while the
+token budget lasts, fewer than ``max_num_seqs`` run and a state slot is free.
+A prompt is cut into portions under the step's token budget
+(``max_num_batched_tokens``) and the portion cap
+(``long_prefill_token_threshold``), anywhere, and continues over as many steps
+as it needs.  This is the reference's order
+(crates/rllm-scheduler/src/scheduler.rs:175-233; running :328-397, waiting
+:402-532, budgets :480-495), except that there a prompt's later portions are
+never scheduled as portions (:355-382) and a token is sampled after every
+portion; here logits are asked for only when a portion ends at the last known
+token.
+
+When pages run out: a waiting request is simply not admitted yet (:497-505).
+A running request that needs a page and cannot get one makes room by
+preemption (:357-375, :606-625): the newest running request (latest arrival)
+loses all its pages and its slot and goes back to the front of the waiting
+queue by arrival order; that is repeated until the page is there or the
+request that asked is itself the newest, in which case it is the one
+preempted.  A preempted request keeps its prompt and what it generated and
+computes them again when readmitted; its samples are unchanged because its
+random stream is indexed by the generated token.  A request that could never
+fit (prompt plus ``max_tokens`` beyond ``max_model_len`` or beyond all pages)
+is refused when it is added, so the loop cannot wait for ever.
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+from ..cache.manager import CacheManager
+from ..sampling.params import SamplingParams
+
+
+class RequestStatus(enum.Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED_STOPPED = "stop"
+    FINISHED_LENGTH = "length"
+    FINISHED_ABORTED = "aborted"
+
+    @property
+    def finished(self) -> bool:
+        return self.name.startswith("FINISHED")
+
+
+class RequestRefused(ValueError):
+    """A request that can never be served with this engine's limits."""
+
+
+@dataclass
+class Request:
+    request_id: Hashable
+    prompt_token_ids: List[int]
+    params: SamplingParams
+    arrival: int
+    seed: int
+    max_tokens: int
+    output_token_ids: List[int] = field(default_factory=list)
+    num_computed: int = 0            # tokens whose keys and values are in the cache
+    num_cached_prefix: int = 0       # tokens taken over from shared pages at admission
+    num_preemptions: int = 0
+    status: RequestStatus = RequestStatus.WAITING
+
+    @property
+    def all_token_ids(self) -> List[int]:
+        return self.prompt_token_ids + self.output_token_ids
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt_token_ids) + len(self.output_token_ids)
+
+
+@dataclass
+class Scheduled:
+    request: Request
+    start: int
+    num_tokens: int
+    want_logits: bool
+
+
+@dataclass
+class SchedulerOutput:
+    scheduled: List[Scheduled]
+    preempted: List[Hashable]
+    num_prefill_tokens: int = 0
+    num_decode_tokens: int = 0
+
+    @property
+    def total_tokens(self) -> int:
+        return sum(s.num_tokens for s in self.scheduled)
+
+
+@dataclass
+class SchedulerConfig:
+    """Names of crates/rllm-core/src/config.rs:92-101."""
+
+    max_num_seqs: int = 256
+    max_num_batched_tokens: int = 4096
+    long_prefill_token_threshold: int = 2048
+    enable_chunked_prefill: bool = True
+    max_model_len: int = 4096
+
+
+class Scheduler:
+    def __init__(self, config: SchedulerConfig, cache: CacheManager):
+        self.config = config
+        self.cache = cache
+        self.waiting: List[Request] = []
+        self.running: List[Request] = []
+        self.requests: Dict[Hashable, Request] = {}
+        self.num_preemptions = 0
+        self.prefix_hit_tokens = 0
+
+    # ------------------------------------------------------------------
+    def add_request(self, req: Request) -> None:
+        if req.request_id in self.requests:
+            raise RequestRefused(f"request id {req.request_id!r} is in use")
+        if not req.prompt_token_ids:
+            raise RequestRefused("a request needs at least one prompt token")
+        most = len(req.prompt_token_ids) + req.max_tokens
+        if most > self.config.max_model_len:
+            raise RequestRefused(f"prompt ({len(req.prompt_token_ids)}) plus max_tokens ({req.max_tokens}) "
+                                 f"exceeds max_model_len ({self.config.max_model_len})")
+        if not self.cache.fits_at_all(most):
+            raise RequestRefused(f"prompt plus max_tokens ({most} tokens) needs more cache pages than exist")
+        if not self.config.enable_chunked_prefill and len(req.prompt_token_ids) > self.config.max_num_batched_tokens:
+            raise RequestRefused("the prompt exceeds max_num_batched_tokens and chunked prefill is off")
+        self.requests[req.request_id] = req
+        self._enqueue(req)
+
+    def _enqueue(self, req: Request) -> None:
+        req.status = RequestStatus.WAITING
+        i = 0
+        while i < len(self.waiting) and self.waiting[i].arrival < req.arrival:
+            i += 1
+        self.waiting.insert(i, req)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------
+    def _portion(self, req: Request, budget: int) -> int:
+        left = req.num_tokens - req.num_computed
+        n = min(left, budget)
+        if left > 1 and self.config.long_prefill_token_threshold > 0:
+            n = min(n, self.config.long_prefill_token_threshold)
+        return n
+
+    def _preempt(self, req: Request, out: SchedulerOutput) -> None:
+        self.cache.free(req.request_id)
+        req.num_computed = 0
+        req.num_cached_prefix = 0
+        req.num_preemptions += 1
+        self.num_preemptions += 1
+        self.running.remove(req)
+        self._enqueue(req)
+        out.preempted.append(req.request_id)
+        out.scheduled[:] = [s for s in out.scheduled if s.request is not req]
+
+    def schedule(self) -> SchedulerOutput:
+        out = SchedulerOutput([], [])
+        budget = self.config.max_num_batched_tokens
+        # (1) running requests go on
+        for req in list(self.running):
+            if req.status is not RequestStatus.RUNNING:
+                continue                      # preempted while an older request was scheduled
+            if budget <= 0:
+                break
+            n = self._portion(req, budget)
+            if n <= 0:
+                continue
+            if n < req.num_tokens - req.num_computed and not self.config.enable_chunked_prefill:
+                continue
+            while not self.cache.ensure(req.request_id, req.num_computed, req.num_computed + n):
+                victim = max(self.running, key=lambda r: r.arrival)
+                self._preempt(victim, out)
+                if victim is req:
+                    break
+            if req.status is not RequestStatus.RUNNING:
+                continue
+            out.scheduled.append(Scheduled(req, req.num_computed, n, req.num_computed + n == req.num_tokens))
+            budget -= n
+        # the budget of requests preempted after they were scheduled comes back
+        budget = self.config.max_num_batched_tokens - out.total_tokens
+        # (2) admit waiting requests, first come first served
+        while self.waiting and budget > 0 and len(self.running) < self.config.max_num_seqs \
+                and self.cache.has_free_slot():
+            req = self.waiting[0]
+            if req.request_id in out.preempted:
+                break                         # just preempted: not in the same step
+            tokens = req.all_token_ids
+            self.cache.admit(req.request_id)
+            cached = self.cache.adopt_prefix(req.request_id, tokens)
+            req.num_computed = cached
+            n = self._portion(req, budget)
+            whole = n == req.num_tokens - req.num_computed
+            if (not whole and not self.config.enable_chunked_prefill) or \
+                    not self.cache.ensure(req.request_id, req.num_computed, req.num_computed + n):
+                self.cache.free(req.request_id)
+                req.num_computed = 0
+                break
+            req.num_cached_prefix = cached
+            self.prefix_hit_tokens += cached
+            self.waiting.pop(0)
+            req.status = RequestStatus.RUNNING
+            self.running.append(req)
+            self.running.sort(key=lambda r: r.arrival)
+            out.scheduled.append(Scheduled(req, req.num_computed, n, whole))
+            budget -= n
+        for s in out.scheduled:
+            if s.num_tokens == 1 and s.start >= len(s.request.prompt_token_ids):
+                out.num_decode_tokens += 1
+            else:
+                out.num_prefill_tokens += s.num_tokens
+        return out
+
+    # ------------------------------------------------------------------
+    def after_step(self, out: SchedulerOutput) -> None:
+        """The step ran: its tokens' keys and values are in the cache."""
+        for s in out.scheduled:
+            req = s.request
+            req.num_computed = s.start + s.num_tokens
+            self.cache.register_computed(req.request_id, req.all_token_ids, req.num_computed)
+
+    def finish(self, req: Request, status: RequestStatus) -> None:
+        """Take a request out and give back what it holds."""
+        if req.status is RequestStatus.RUNNING:
+            self.running.remove(req)
+            self.cache.free(req.request_id)
+        elif req.status is RequestStatus.WAITING:
+            self.waiting.remove(req)
+        req.status = status
+        self.requests.pop(req.request_id, None)
+
+    def abort_request(self, request_id: Hashable) -> bool:
+        """crates/rllm-scheduler/src/scheduler.rs:165-171."""
+        req = self.requests.get(request_id)
+        if req is None:
+            return False
+        self.finish(req, RequestStatus.FINISHED_ABORTED)
+        return True
+
+    def stats(self) -> dict:
+        """Fields of crates/rllm-scheduler/src/output.rs:51-64, plus prefix hits."""
+        return {"num_running": len(self.running), "num_waiting": len(self.waiting),
+                "num_preemptions": self.num_preemptions, "prefix_hit_tokens": self.prefix_hit_tokens,
+                "cache": self.cache.usage()}

@@ -275,7 +275,11 @@ def process_logits(logits: np.ndarray, *, context: Sequence[int] = (), logit_bia
                    top_p: float = 1.0, min_p: float = 0.0) -> np.ndarray:
     """The reference's order of logits processors
     (crates/rllm-sampling/src/sampler.rs:62-133 with the functions of
-    crates/rllm-sampling/src/logits.rs:5-185), in float32 like the reference."""
+    crates/rllm-sampling/src/logits.rs:5-185), in float32 like the reference.
+    Two deliberate differences, shared with the engine: top_k keeps the k
+    largest values and their ties (the reference's threshold at logits.rs:26-31
+    is the (k+1)-th largest, which keeps k+1), and top_p keeps every tie of the
+    last value it takes (the reference cuts among equal values in sort order)."""
     x = np.array(logits, dtype=np.float32).copy()
     n = x.shape[0]
     if logit_bias:
@@ -310,22 +314,19 @@ def process_logits(logits: np.ndarray, *, context: Sequence[int] = (), logit_bia
     if abs(temperature - 1.0) >= np.finfo(np.float32).eps:
         x = x * np.float32(1.0 / np.float32(temperature))
     if 0 < top_k < n:
-        kth = np.sort(x)[::-1][top_k]            # logits.rs:31: threshold is the (k+1)-th largest
+        kth = np.sort(x)[::-1][top_k - 1]        # keep the k largest (and their ties)
         x[x < kth] = -np.inf
     if 0.0 < top_p < 1.0:
         order = np.argsort(-x, kind="stable")
-        order = order[np.isfinite(x[order]) | (x[order] > -np.inf)]
-        vals = x[order]
-        e = np.exp(vals - vals[0]).astype(np.float32)
-        probs = e / e.sum(dtype=np.float32)
-        cum = np.float32(0.0)
-        cutoff = len(order)
-        for i, p in enumerate(probs):
-            cum = np.float32(cum + p)
-            if cum >= np.float32(top_p):
-                cutoff = i + 1
-                break
-        x[order[cutoff:]] = -np.inf
+        order = order[x[order] > -np.inf]
+        vals = x[order].astype(np.float64)
+        probs = np.exp(vals - vals[0])
+        probs /= probs.sum()
+        cum = np.cumsum(probs)
+        cutoff = int(np.searchsorted(cum, top_p, side="left")) + 1     # first prefix with cum >= p
+        cutoff = min(cutoff, len(order))
+        last = vals[cutoff - 1]
+        x[x < np.float32(last)] = -np.inf                               # ties of the last value stay
     if min_p > 0.0:
         m = x.max()
         if m > -np.inf:
@@ -335,13 +336,14 @@ def process_logits(logits: np.ndarray, *, context: Sequence[int] = (), logit_bia
 
 def sample_row(processed: np.ndarray, temperature: float, top_k: int, u: float) -> int:
     """Greedy when temperature <= 0 or top_k == 1 (sampler.rs:117), else
-    softmax and the first index whose running sum reaches u (sampler.rs:194-214).
-    Greedy ties go to the lowest index."""
+    softmax and the first index whose running sum exceeds u (sampler.rs:194-214
+    has ``>=``, which would draw a masked token 0 when u is 0).  Greedy ties go
+    to the lowest index."""
     if temperature <= 0.0 or top_k == 1:
         return int(np.argmax(processed))
     x = processed.astype(np.float64)
     e = np.exp(x - x.max())
     p = e / e.sum()
     cum = np.cumsum(p)
-    idx = int(np.searchsorted(cum, u, side="left"))
+    idx = int(np.searchsorted(cum, u, side="right"))
     return min(idx, len(p) - 1)

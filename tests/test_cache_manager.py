@@ -1,0 +1,174 @@
+"""The cache manager on the host: no page lost, held twice or freed twice,
+under random orders of requests; windows give pages back; prefix sharing
+(mirrors crates/rllm-cache/src/block_pool.rs:421-635, manager.rs:271-516)."""
+import random
+
+import pytest
+
+from rllm_b200.cache import BlockPool, CacheManager, NoCapacity, PagePoolError, page_hashes
+from rllm_b200.parts.spec import KVPagesNeed, StateNeed
+
+FULL = KVPagesNeed(2, 16, None)
+
+
+def test_pool_counts_and_double_free():
+    pool = BlockPool(4)
+    pages = [pool.allocate() for _ in range(4)]
+    assert sorted(pages) == [0, 1, 2, 3] and pool.allocate() is None and pool.num_free == 0
+    pool.free(pages[0])
+    with pytest.raises(PagePoolError):
+        pool.free(pages[0])
+    assert pool.num_free == 1 and pool.allocate() == pages[0]
+    pool.check()
+
+
+def test_pool_prefers_pages_without_content_and_evicts_oldest():
+    pool = BlockPool(3)
+    a, b, c = (pool.allocate() for _ in range(3))
+    pool.register(a, b"A"); pool.register(b, b"B")
+    pool.free(a); pool.free(b); pool.free(c)
+    assert pool.allocate() == c                       # no content: first choice
+    assert pool.peek(b"A") == a and pool.peek(b"B") == b
+    assert pool.allocate() == a and pool.peek(b"A") is None   # least recently freed content goes first
+    assert pool.acquire_cached(b"B") == b and pool.refcount[b] == 1
+    pool.check()
+
+
+def test_shared_page_needs_both_frees():
+    pool = BlockPool(2)
+    a = pool.allocate()
+    pool.register(a, b"A")
+    assert pool.acquire_cached(b"A") == a and pool.is_shared(a)
+    pool.free(a)
+    assert pool.num_free == 1
+    pool.free(a)
+    assert pool.num_free == 2
+    with pytest.raises(PagePoolError):
+        pool.free(99)
+    assert pool.acquire_cached(b"A") == a
+    with pytest.raises(PagePoolError):
+        pool.reset_prefix_cache()                     # refused while a hashed page is held
+    pool.free(a)
+    pool.reset_prefix_cache()
+    assert pool.peek(b"A") is None
+    pool.check()
+
+
+def test_all_or_nothing():
+    m = CacheManager([FULL], 16, 4, 8)
+    m.admit("a"); m.admit("b")
+    assert m.ensure("a", 0, 40)                       # 3 pages
+    assert not m.ensure("b", 0, 40)                   # needs 3, 1 free: nothing taken
+    assert m.num_free_pages() == 1 and m.table("b", 0) == []
+    assert m.ensure("b", 0, 16)
+    m.free("a")
+    assert m.ensure("b", 16, 60)
+    m.check()
+
+
+def test_slots():
+    m = CacheManager([FULL], 16, 4, 2)
+    s0, s1 = m.admit("a"), m.admit("b")
+    assert {s0, s1} == {0, 1} and sorted(m.take_fresh_slots()) == [0, 1]
+    with pytest.raises(NoCapacity):
+        m.admit("c")
+    m.free("a")
+    assert m.admit("c") == s0 and m.take_fresh_slots() == [s0]
+    m.check()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_lose_nothing(seed):
+    rng = random.Random(seed)
+    needs = [FULL, KVPagesNeed(1, 32, 24), StateNeed((4,))]
+    m = CacheManager(needs, 8, [40, 12], 5)
+    live = {}
+    for step in range(600):
+        op = rng.random()
+        if op < 0.25 and len(live) < 5:
+            rid = f"r{step}"
+            m.admit(rid)
+            live[rid] = 0
+        elif op < 0.8 and live:
+            rid = rng.choice(list(live))
+            n = live[rid] + rng.choice([1, 1, 1, 2, 7, 23])
+            if m.ensure(rid, live[rid], n):
+                live[rid] = n
+                tb = m.table(rid, 1)          # the windowed group holds only what queries can still see
+                held = [k for k, p in enumerate(tb) if p >= 0]
+                assert all(k * 8 + 7 >= max(0, live[rid] - 1 - 24 + 1) - 23 for k in held)
+        elif live:
+            rid = rng.choice(list(live))
+            m.free(rid)
+            del live[rid]
+        m.check()
+    for rid in list(live):
+        m.free(rid)
+    m.check()
+    assert m.num_free_pages(0) == 40 and m.num_free_pages(1) == 12 and m.usage()["free_slots"] == 5
+
+
+def test_window_gives_pages_back_and_reuses_them():
+    m = CacheManager([KVPagesNeed(1, 16, 10)], 4, 5, 2)
+    m.admit("a")
+    pos, seen = 0, set()
+    while pos < 200:
+        assert m.ensure("a", pos, pos + 3), pos         # 5 pages are enough for ever
+        pos += 3
+        tb = m.table("a", 0)
+        seen.update(p for p in tb if p >= 0)
+        first_needed = max(0, pos - 3 - 10 + 1) // 4
+        assert all(p == -1 for p in tb[:first_needed]) and all(p >= 0 for p in tb[first_needed:])
+    assert seen <= {0, 1, 2, 3, 4} and len(m.table("a", 0)) == 51      # 51 pages went through 5
+    m.check()
+
+
+def test_a_prompt_that_starts_behind_its_window_holds_no_early_pages():
+    m = CacheManager([KVPagesNeed(1, 16, 8)], 4, 4, 1)
+    m.admit("a")
+    assert m.ensure("a", 0, 6)
+    assert m.ensure("a", 6, 40) is False               # one portion of 34 tokens sees 8 + 34 keys: 11 pages
+    assert m.ensure("a", 6, 14)
+    m.check()
+
+
+def test_page_hashes_chain():
+    toks = list(range(40))
+    h = page_hashes(toks, 16)
+    assert len(h) == 2 and h[0] != h[1]
+    assert page_hashes(toks[:16] + [99] + toks[17:], 16)[0] == h[0]
+    assert page_hashes([1] + toks[1:], 16)[1] != h[1]        # a page's hash covers all pages before it
+    assert page_hashes(toks, 16, salt=b"x")[0] != h[0]
+    assert page_hashes(toks, 16, start=1, parent=h[0]) == h[1:]
+
+
+def test_prefix_sharing():
+    m = CacheManager([FULL], 4, 16, 4, enable_prefix_caching=True)
+    toks = list(range(100, 118))                       # 4 full pages + 2 tokens
+    m.admit("a")
+    assert m.match_prefix(toks) == 0 and m.adopt_prefix("a", toks) == 0
+    assert m.ensure("a", 0, 18)
+    m.register_computed("a", toks, 10)                 # only 2 pages have all their keys
+    assert m.match_prefix(toks) == 8                   # a lookup takes no reference
+    m.check()
+    m.register_computed("a", toks, 18)
+    m.admit("b")
+    assert m.adopt_prefix("b", toks + [7, 8, 9]) == 16
+    assert m.table("b", 0) == m.table("a", 0)[:4]
+    m.check()
+    m.free("a")
+    m.check()
+    m.admit("c")
+    assert m.match_prefix(toks[:16]) == 12             # wholly cached: the last page is computed again
+    assert m.adopt_prefix("c", toks[:16]) == 12
+    m.free("b"); m.free("c")
+    m.check()
+    assert m.num_free_pages() == 16
+    m.admit("d")
+    assert m.adopt_prefix("d", toks) == 16             # freed pages stay findable until they are reused
+    m.check()
+
+
+def test_prefix_sharing_is_off_with_windows_or_state():
+    assert not CacheManager([KVPagesNeed(1, 16, 8)], 4, 4, 1, enable_prefix_caching=True).prefix_caching
+    assert not CacheManager([FULL, StateNeed((2,))], 4, 4, 1, enable_prefix_caching=True).prefix_caching

@@ -1,0 +1,187 @@
+"""The scheduler's decisions, on the host, with a scripted step function in
+place of the model (the reference's engine tests use a fake executor the same
+way: crates/rllm-engine/tests/engine_tests.rs:16-122; scheduler tests:
+crates/rllm-scheduler/src/scheduler.rs:650-882)."""
+import random
+
+import pytest
+
+from rllm_b200.cache import CacheManager
+from rllm_b200.engine.scheduler import (Request, RequestRefused, RequestStatus, Scheduler,
+                                        SchedulerConfig)
+from rllm_b200.parts.spec import KVPagesNeed
+from rllm_b200.sampling import SamplingParams
+
+NEED = KVPagesNeed(2, 16, None)
+
+
+def make(pages=64, page=16, seqs=8, prefix=False, **cfg):
+    cache = CacheManager([NEED], page, pages, seqs, enable_prefix_caching=prefix)
+    conf = SchedulerConfig(**{**dict(max_num_seqs=seqs, max_num_batched_tokens=64,
+                                     long_prefill_token_threshold=0, max_model_len=4096), **cfg})
+    return Scheduler(conf, cache), cache
+
+
+def req(i, n_prompt, max_tokens=8, first=1000):
+    return Request(f"r{i}", list(range(first, first + n_prompt)), SamplingParams(max_tokens=max_tokens),
+                   arrival=i, seed=i, max_tokens=max_tokens)
+
+
+def run_step(s, token=lambda r: 7):
+    """What the engine does around schedule(): run, append a token where the
+    portion ended at the last known token, finish by length."""
+    out = s.schedule()
+    s.after_step(out)
+    for sc in out.scheduled:
+        assert sc.num_tokens >= 1 and sc.start == sc.request.num_computed - sc.num_tokens
+        if sc.want_logits:
+            sc.request.output_token_ids.append(token(sc.request))
+            if len(sc.request.output_token_ids) >= sc.request.max_tokens:
+                s.finish(sc.request, RequestStatus.FINISHED_LENGTH)
+    s.cache.check()
+    return out
+
+
+def test_fcfs_and_budget():
+    s, _ = make(max_num_batched_tokens=50)
+    for i, n in enumerate([30, 30, 30]):
+        s.add_request(req(i, n))
+    out = run_step(s)
+    assert [(x.request.request_id, x.start, x.num_tokens, x.want_logits) for x in out.scheduled] == \
+        [("r0", 0, 30, True), ("r1", 0, 20, False)]
+    out = run_step(s)
+    # running first: r0 decodes, r1 finishes its prompt, then r2 gets what is left of the budget
+    assert [(x.request.request_id, x.start, x.num_tokens, x.want_logits) for x in out.scheduled] == \
+        [("r0", 30, 1, True), ("r1", 20, 10, True), ("r2", 0, 30, True)]
+    assert out.num_decode_tokens == 1 and out.num_prefill_tokens == 40
+
+
+def test_portion_cap_and_logits_only_at_the_end():
+    s, _ = make(max_num_batched_tokens=64, long_prefill_token_threshold=16)
+    s.add_request(req(0, 40))
+    seen = []
+    while s.has_work() and len(seen) < 3:
+        out = run_step(s)
+        seen.append([(x.start, x.num_tokens, x.want_logits) for x in out.scheduled])
+    assert seen == [[(0, 16, False)], [(16, 16, False)], [(32, 8, True)]]
+
+
+def test_max_num_seqs():
+    s, _ = make(seqs=2)
+    for i in range(4):
+        s.add_request(req(i, 5, max_tokens=2))
+    out = run_step(s)
+    assert [x.request.request_id for x in out.scheduled] == ["r0", "r1"]
+    out = run_step(s)                     # both finish here (2 tokens each)
+    out = run_step(s)
+    assert [x.request.request_id for x in out.scheduled] == ["r2", "r3"]
+
+
+def test_no_chunking_admits_whole_prompts_only():
+    s, _ = make(max_num_batched_tokens=50, enable_chunked_prefill=False)
+    s.add_request(req(0, 30)); s.add_request(req(1, 30))
+    out = run_step(s)
+    assert [(x.request.request_id, x.num_tokens) for x in out.scheduled] == [("r0", 30)]
+    with pytest.raises(RequestRefused, match="chunked prefill"):
+        s.add_request(req(2, 60))
+
+
+def test_requests_that_can_never_fit_are_refused():
+    s, _ = make(pages=4, max_model_len=100)
+    with pytest.raises(RequestRefused, match="max_model_len"):
+        s.add_request(req(0, 95, max_tokens=10))
+    with pytest.raises(RequestRefused, match="more cache pages"):
+        s.add_request(req(1, 60, max_tokens=10))
+    with pytest.raises(RequestRefused, match="at least one"):
+        s.add_request(req(2, 0))
+    s.add_request(req(3, 50, max_tokens=14))
+    with pytest.raises(RequestRefused, match="in use"):
+        s.add_request(req(3, 5))
+
+
+def test_waiting_request_is_not_admitted_without_pages():
+    s, cache = make(pages=4)
+    s.add_request(req(0, 40, max_tokens=20)); s.add_request(req(1, 40, max_tokens=20))
+    out = run_step(s)
+    assert [x.request.request_id for x in out.scheduled] == ["r0"] and not out.preempted
+    assert cache.usage()["num_requests"] == 1          # the failed admission left nothing behind
+    assert s.waiting[0].request_id == "r1"
+
+
+def test_out_of_pages_preempts_the_newest_and_it_recomputes():
+    s, cache = make(pages=4, page=16)
+    s.add_request(req(0, 30, max_tokens=34)); s.add_request(req(1, 30, max_tokens=34))
+    run_step(s)                                        # both prompts: 2 pages each, pool is full
+    assert cache.num_free_pages() == 0
+    out = run_step(s)                                  # token 31, 32: still inside page 2
+    out = run_step(s)
+    assert not out.preempted
+    out = run_step(s)                                  # r0 needs a third page: r1, the newest, gives way
+    assert out.preempted == ["r1"] and [x.request.request_id for x in out.scheduled] == ["r0"]
+    r1 = s.requests["r1"]
+    assert r1.status is RequestStatus.WAITING and r1.num_computed == 0 and len(r1.output_token_ids) == 3
+    assert s.waiting[0] is r1 and s.num_preemptions == 1
+    # r0 runs to its end; r1 comes back and computes prompt + generated again in one portion
+    while "r0" in s.requests:
+        out = run_step(s)
+    out = run_step(s)
+    back = [x for x in out.scheduled if x.request is r1]
+    assert back and back[0].start == 0 and back[0].num_tokens == 33 and back[0].want_logits
+    while s.has_work():
+        run_step(s)
+    assert len(r1.output_token_ids) == 34 and cache.num_free_pages() == 4
+
+
+def test_a_lone_request_that_runs_out_preempts_itself_and_finishes_later():
+    s, cache = make(pages=4, page=16)
+    s.add_request(req(0, 20, max_tokens=30)); s.add_request(req(1, 20, max_tokens=30))
+    steps = 0
+    while s.has_work():
+        run_step(s)
+        steps += 1
+        assert steps < 500
+    assert s.num_preemptions >= 1 and cache.num_free_pages() == 4
+
+
+def test_abort():
+    s, cache = make()
+    s.add_request(req(0, 20)); s.add_request(req(1, 20))
+    run_step(s)
+    assert s.abort_request("r0") and not s.abort_request("nobody")
+    assert [r.request_id for r in s.running] == ["r1"] and cache.usage()["num_requests"] == 1
+    s.add_request(req(2, 5))
+    assert s.abort_request("r2") and not s.waiting
+
+
+def test_prefix_hits_skip_computed_pages():
+    s, cache = make(prefix=True, page=4, max_num_batched_tokens=100)
+    s.add_request(Request("a", list(range(50, 68)), SamplingParams(max_tokens=2), 0, 0, 2))
+    run_step(s); run_step(s)
+    s.add_request(Request("b", list(range(50, 66)) + [1, 2, 3], SamplingParams(max_tokens=2), 1, 1, 2))
+    out = run_step(s)
+    assert [(x.start, x.num_tokens) for x in out.scheduled] == [(16, 3)] and s.prefix_hit_tokens == 16
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_random_workloads_finish_within_limits(seed):
+    """Never more than max_num_seqs running or max_num_batched_tokens in a step;
+    every request finishes; nothing is held at the end
+    (crates/rllm-bench/tests/correctness.rs:247-326)."""
+    rng = random.Random(seed)
+    s, cache = make(pages=24, page=8, seqs=4, max_num_batched_tokens=48,
+                    long_prefill_token_threshold=rng.choice([0, 16]))
+    todo = [req(i, rng.randint(1, 90), max_tokens=rng.randint(1, 40)) for i in range(14)]
+    done, steps = {}, 0
+    while todo or s.has_work():
+        for _ in range(rng.randint(0, 2)):
+            if todo:
+                r = todo.pop(0)
+                s.add_request(r)
+                done[r.request_id] = r
+        out = run_step(s)
+        assert out.total_tokens <= 48 and len(s.running) <= 4
+        assert len({x.request.request_id for x in out.scheduled}) == len(out.scheduled)
+        steps += 1
+        assert steps < 5000
+    assert all(len(r.output_token_ids) == r.max_tokens for r in done.values())
+    assert cache.num_free_pages() == 24 and cache.usage()["free_slots"] == 4

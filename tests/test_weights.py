@@ -1,0 +1,139 @@
+"""Weights by name: the writer, the reader and the one error that lists what
+does not fit (the reference's loader tests: crates/rllm-model/src/loader.rs:381-444)."""
+import json
+import os
+
+import pytest
+import torch
+
+from conftest import TINY_A, TINY_B
+from rllm_b200.config import load_model_description
+from rllm_b200.engine.loading import write_random_model
+from rllm_b200.models import DecoderModel
+from rllm_b200.weights import (FolderSource, RandomSource, SafetensorsFile, WeightsError, WeightsMismatch,
+                               check_tensors, draw_tensor, find_weight_files, load_tensors,
+                               write_safetensors)
+
+
+def specs_of(model_dir):
+    _, spec = load_model_description(model_dir)
+    return DecoderModel(spec).tensor_specs()
+
+
+def test_written_folder_is_read_by_the_safetensors_library(model_dirs):
+    from safetensors import safe_open
+    src = FolderSource(model_dirs["B"])
+    with safe_open(os.path.join(model_dirs["B"], "model.safetensors"), framework="pt") as f:
+        assert sorted(f.keys()) == sorted(src.names())
+        for name in f.keys():
+            assert torch.equal(f.get_tensor(name), src.read(name))
+    assert "lm_head.weight" in src.names()
+
+
+def test_tied_model_has_no_head_tensor(model_dirs):
+    assert "lm_head.weight" not in FolderSource(model_dirs["A"]).names()
+    check_tensors(specs_of(model_dirs["A"]), FolderSource(model_dirs["A"]))
+
+
+def test_same_seed_same_weights_and_names_are_independent(tmp_path):
+    write_random_model(str(tmp_path / "a"), TINY_A, 5, "float32")
+    write_random_model(str(tmp_path / "b"), TINY_A, 5, "float32")
+    write_random_model(str(tmp_path / "c"), TINY_A, 6, "float32")
+    a, b, c = (FolderSource(str(tmp_path / x)) for x in "abc")
+    name = "model.layers.1.mlp.down_proj.weight"
+    assert torch.equal(a.read(name), b.read(name)) and not torch.equal(a.read(name), c.read(name))
+    assert abs(float(a.read(name).std()) - 0.02) < 2e-3
+    norm = a.read("model.layers.0.input_layernorm.weight")
+    assert abs(float(norm.mean()) - 1.0) < 0.1 and 0.03 < float(norm.std()) < 0.2
+    # a tensor's values depend on seed and name only, not on the rest of the model
+    cfg = dict(TINY_A, num_hidden_layers=1)
+    write_random_model(str(tmp_path / "d"), cfg, 5, "float32")
+    assert torch.equal(FolderSource(str(tmp_path / "d")).read("model.layers.0.mlp.up_proj.weight"),
+                       a.read("model.layers.0.mlp.up_proj.weight"))
+
+
+def test_bfloat16_storage_round_trip(tmp_path):
+    write_random_model(str(tmp_path / "m"), dict(TINY_B, torch_dtype="bfloat16"), 1)
+    src = FolderSource(str(tmp_path / "m"))
+    dt, shape = src.info("model.embed_tokens.weight")
+    assert dt is torch.bfloat16 and shape == (389, 96)
+    t = src.read("model.embed_tokens.weight")
+    spec = [s for s in specs_of(str(tmp_path / "m")) if s.name == "model.embed_tokens.weight"][0]
+    assert torch.equal(t, draw_tensor(spec, 1).to(torch.bfloat16))
+
+
+def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path, model_dirs):
+    src = FolderSource(model_dirs["B"])
+    tensors = {n: src.read(n) for n in src.names()}
+    del tensors["model.layers.1.self_attn.k_proj.weight"]
+    del tensors["model.norm.weight"]
+    tensors["model.layers.9.extra.weight"] = torch.zeros(3)
+    tensors["model.layers.0.mlp.gate_proj.weight"] = torch.zeros(264, 95)
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)   # ignored, as in checkpoints
+    d = tmp_path / "broken"
+    d.mkdir()
+    write_safetensors(str(d / "model.safetensors"), tensors)
+    (d / "config.json").write_text(json.dumps(TINY_B))
+    with pytest.raises(WeightsMismatch) as e:
+        check_tensors(specs_of(str(d)), FolderSource(str(d)))
+    err = e.value
+    assert err.missing == ["model.layers.1.self_attn.k_proj.weight", "model.norm.weight"]
+    assert err.unexpected == ["model.layers.9.extra.weight"]
+    assert err.wrong_shape == [("model.layers.0.mlp.gate_proj.weight", (264, 95), (264, 96))]
+    text = str(err)
+    for word in ("missing (2)", "unexpected (1)", "wrong shape (1)", "k_proj", "extra", "[264, 95]"):
+        assert word in text
+
+
+def test_untied_model_needs_its_head(tmp_path, model_dirs):
+    src = FolderSource(model_dirs["B"])
+    tensors = {n: src.read(n) for n in src.names() if n != "lm_head.weight"}
+    d = tmp_path / "nohead"
+    d.mkdir()
+    write_safetensors(str(d / "model.safetensors"), tensors)
+    (d / "config.json").write_text(json.dumps(TINY_B))
+    with pytest.raises(WeightsMismatch, match="lm_head.weight"):
+        check_tensors(specs_of(str(d)), FolderSource(str(d)))
+
+
+def test_held_dtypes(model_dirs):
+    specs = specs_of(model_dirs["A"])
+    got = load_tensors(specs, FolderSource(model_dirs["A"]), torch.bfloat16, torch.device("cpu"))
+    assert got["model.embed_tokens.weight"].dtype is torch.bfloat16
+    assert got["model.norm.weight"].dtype is torch.float32       # stored in 32-bit: stays so
+    got = load_tensors(specs, FolderSource(model_dirs["A"]), torch.float32, torch.device("cpu"))
+    assert all(t.dtype is torch.float32 for t in got.values())
+
+
+def test_integer_tables_become_int32():
+    from rllm_b200.parts.spec import TensorSpec
+    specs = [TensorSpec("table", (7, 3), role="int", init=("randint", 100))]
+    got = load_tensors(specs, RandomSource(specs, 0), torch.bfloat16, torch.device("cpu"))
+    assert got["table"].dtype is torch.int32 and int(got["table"].max()) < 100
+
+
+def test_shard_discovery(tmp_path):
+    with pytest.raises(WeightsError, match="does not exist"):
+        find_weight_files(str(tmp_path / "nope"))
+    with pytest.raises(WeightsError, match="no safetensors"):
+        find_weight_files(str(tmp_path))
+    for n in ("model-00001-of-00002.safetensors", "model-00002-of-00002.safetensors"):
+        write_safetensors(str(tmp_path / n), {n[:11]: torch.zeros(2)})
+    assert [os.path.basename(p) for p in find_weight_files(str(tmp_path))] == [
+        "model-00001-of-00002.safetensors", "model-00002-of-00002.safetensors"]
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(
+        {"weight_map": {"a": "model-00002-of-00002.safetensors", "b": "model-00002-of-00002.safetensors"}}))
+    assert [os.path.basename(p) for p in find_weight_files(str(tmp_path))] == ["model-00002-of-00002.safetensors"]
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"a": "../evil.safetensors"}}))
+    with pytest.raises(WeightsError, match="leaves the model folder"):
+        find_weight_files(str(tmp_path))
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"a": "gone.safetensors"}}))
+    with pytest.raises(WeightsError, match="does not exist"):
+        find_weight_files(str(tmp_path))
+
+
+def test_corrupt_file(tmp_path):
+    p = tmp_path / "model.safetensors"
+    p.write_bytes(b"\xff" * 20)
+    with pytest.raises(WeightsError, match="header"):
+        SafetensorsFile(str(p))
