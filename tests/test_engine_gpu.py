@@ -1,0 +1,160 @@
+"""Generation through the Python entry point against the plain implementation:
+greedy tokens, seeded temperature sampling, and that a request's output does
+not depend on batching, portion sizes, preemption or prefix sharing."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+from conftest import TINY
+
+pytestmark = pytest.mark.gpu
+
+
+def prompts_for(name, lengths, seed):
+    cfg, _, _ = TINY[name]
+    rng = np.random.default_rng(seed)
+    return [[int(t) for t in rng.integers(8, cfg["vocab_size"], size=n)] for n in lengths]
+
+
+def make_llm(model_dirs, name, dtype="fp32", **kw):
+    from rllm_b200 import LLM
+    _, _, page = TINY[name]
+    kw.setdefault("num_gpu_blocks", 256)
+    kw.setdefault("max_num_seqs", 8)
+    return LLM(model_dirs[name], dtype=dtype, block_size=page, **kw)
+
+
+@pytest.mark.parametrize("name,lengths,seed,steps", [("A", [5, 12, 17], 1, 8), ("B", [1, 31, 70, 150], 3, 10)])
+def test_greedy_generation_equals_plain_greedy(model_dirs, name, lengths, seed, steps):
+    from rllm_b200 import SamplingParams
+    prompts = prompts_for(name, lengths, seed)
+    llm = make_llm(model_dirs, name, max_num_batched_tokens=64, long_prefill_token_threshold=16)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=steps, ignore_eos=True))
+    plain = pl.read_model_dir(model_dirs[name])
+    for p, o in zip(prompts, outs):
+        assert o.outputs[0].token_ids == plain.greedy(p, steps)
+        assert o.outputs[0].finish_reason == "length" and o.finished
+        assert (o.usage.prompt_tokens, o.usage.completion_tokens, o.usage.total_tokens) == \
+            (len(p), steps, len(p) + steps)
+    assert llm.engine.cache.usage()["num_requests"] == 0
+
+
+def test_greedy_generation_in_bfloat16(model_dirs):
+    """bfloat16 follows the oracle (run on bfloat16-rounded weights) wherever
+    the oracle's own choice is clear: top-two margin above the bf16 tolerance."""
+    from rllm_b200 import SamplingParams
+    prompts = prompts_for("B", [31, 70], 3)
+    llm = make_llm(model_dirs, "B", dtype="bf16")
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    plain = pl.read_model_dir(model_dirs["B"], round_to=torch.bfloat16)
+    for p, o in zip(prompts, outs):
+        toks = list(p)
+        for t in o.outputs[0].token_ids:
+            row = plain.logits(toks)[-1]
+            top = torch.topk(row, 2).values
+            if float(top[0] - top[1]) > 4e-2 * float(row.abs().max()):
+                assert t == int(torch.argmax(row))
+            toks.append(t)
+
+
+def test_temperature_sampling_matches_plain_and_ignores_batching(model_dirs):
+    from rllm_b200 import SamplingParams
+    name = "B"
+    prompts = prompts_for(name, [1, 31, 70, 150], 3)
+    params = [SamplingParams(temperature=0.7, max_tokens=10, seed=100 + i, ignore_eos=True) for i in range(4)]
+    together = make_llm(model_dirs, name, max_num_batched_tokens=40, long_prefill_token_threshold=16)
+    outs = together.generate(prompts, params)
+    # the plain model, given the engine's own tokens so far, draws the same next token
+    plain = pl.read_model_dir(model_dirs[name])
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        toks = list(p)
+        for j, t in enumerate(o.outputs[0].token_ids):
+            x = pl.process_logits(plain.logits(toks)[-1].numpy(), temperature=0.7)
+            assert t == pl.sample_row(x, 0.7, -1, pl.uniform_for(100 + i, j)), (i, j)
+            toks.append(t)
+    # one by one gives the same tokens (crates/rllm-bench/tests/correctness.rs:73-117)
+    alone = make_llm(model_dirs, name)
+    for p, sp, o in zip(prompts, params, outs):
+        assert alone.generate([p], sp)[0].outputs[0].token_ids == o.outputs[0].token_ids
+
+
+def test_stop_conditions(model_dirs):
+    from rllm_b200 import SamplingParams
+    llm = make_llm(model_dirs, "A")
+    p = prompts_for("A", [9], 5)[0]
+    free_run = llm.generate([p], SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))[0].outputs[0].token_ids
+    stop_at = free_run[4]
+    first = free_run.index(stop_at)
+    out = llm.generate([p], SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=[stop_at], ignore_eos=True))[0]
+    assert out.outputs[0].token_ids == free_run[:first + 1] and out.outputs[0].finish_reason == "stop"
+    # an EOS of config.json stops unless ignore_eos; min_tokens keeps it away
+    eos_cfg = dict(TINY["A"][0], eos_token_id=stop_at)
+    import json, os, shutil, tempfile
+    d = tempfile.mkdtemp()
+    shutil.copy(os.path.join(model_dirs["A"], "model.safetensors"), d)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(eos_cfg, f)
+    from rllm_b200 import LLM
+    llm2 = LLM(d, dtype="fp32", num_gpu_blocks=64, max_num_seqs=4)
+    out = llm2.generate([p], SamplingParams(temperature=0.0, max_tokens=12))[0]
+    assert out.outputs[0].token_ids == free_run[:first + 1] and out.outputs[0].finish_reason == "stop"
+    out = llm2.generate([p], SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))[0]
+    assert out.outputs[0].token_ids == free_run
+    out = llm2.generate([p], SamplingParams(temperature=0.0, max_tokens=first + 3, min_tokens=first + 2))[0]
+    assert stop_at not in out.outputs[0].token_ids[:first + 2]
+    shutil.rmtree(d)
+
+
+def test_preemption_does_not_change_outputs(model_dirs):
+    from rllm_b200 import SamplingParams
+    name = "B"
+    prompts = prompts_for(name, [40, 33, 25, 47], 8)
+    params = [SamplingParams(temperature=0.9, top_p=0.95, max_tokens=40, seed=7 + i, ignore_eos=True) for i in range(4)]
+    roomy = make_llm(model_dirs, name)
+    want = [o.outputs[0].token_ids for o in roomy.generate(prompts, params)]
+    tight = make_llm(model_dirs, name, num_gpu_blocks=24, enable_prefix_caching=False)   # 192 tokens of cache
+    got = [o.outputs[0].token_ids for o in tight.generate(prompts, params)]
+    assert tight.engine.scheduler.num_preemptions > 0
+    assert got == want
+    assert tight.engine.cache.num_free_pages() == 24
+
+
+def test_prefix_sharing_does_not_change_outputs(model_dirs):
+    from rllm_b200 import SamplingParams
+    name = "A"
+    common = prompts_for(name, [50], 2)[0]
+    prompts = [common + tail for tail in prompts_for(name, [3, 9, 1], 4)] + [list(common[:48])]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    off = make_llm(model_dirs, name, enable_prefix_caching=False)
+    want = [o.outputs[0].token_ids for o in off.generate(prompts, sp)]
+    on = make_llm(model_dirs, name, enable_prefix_caching=True, max_num_seqs=1)     # one after the other
+    got = [o.outputs[0].token_ids for o in on.generate(prompts, sp)]
+    assert on.engine.scheduler.prefix_hit_tokens == 48 + 48 + 32    # the last prompt is cached whole: one page is redone
+    assert got == want
+    on.engine.cache.check()
+
+
+def test_requests_beyond_the_limits_are_refused(model_dirs):
+    from rllm_b200 import SamplingParams
+    from rllm_b200.engine.scheduler import RequestRefused
+    llm = make_llm(model_dirs, "A", num_gpu_blocks=4)
+    with pytest.raises(RequestRefused):
+        llm.add_request(list(range(100)), SamplingParams(max_tokens=40))     # beyond max_position_embeddings 128
+    with pytest.raises(RequestRefused):
+        llm.add_request(list(range(60)), SamplingParams(max_tokens=16))      # beyond 4 pages of 16
+    with pytest.raises(ValueError, match="vocabulary"):
+        llm.add_request([1, 2, 256])
+
+
+def test_command_line(model_dirs, capsys):
+    from rllm_b200.cli import main
+    import json
+    code = main(["generate", model_dirs["A"], "--prompt-ids", "5,6,7", "-p", "9,10", "--max-tokens", "4",
+                 "--temperature", "0", "--dtype", "fp32", "--num-gpu-blocks", "32", "--max-num-seqs", "4",
+                 "--ignore-eos", "--json"])
+    assert code == 0
+    lines = [json.loads(l) for l in capsys.readouterr().out.strip().split("\n")]
+    plain = pl.read_model_dir(model_dirs["A"])
+    assert [l["token_ids"] for l in lines] == [plain.greedy([5, 6, 7], 4), plain.greedy([9, 10], 4)]
+    assert lines[0]["finish_reason"] == "length" and lines[0]["usage"]["total_tokens"] == 7

@@ -1,0 +1,219 @@
+"""Each CUDA kernel alone against a plain float64 formulation of the same
+operation, at sizes other than the tiny models' (odd widths, head sizes in
+steps of 16, group sizes 1..8, vocabularies that are no power of two)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dt):
+    return 2e-6 if dt is torch.float32 else 1.6e-2
+
+
+def rel_err(got, want):
+    want = want.double().cpu()
+    return float((got.double().cpu() - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from rllm_b200.kernels import ops
+    return ops
+
+
+@pytest.fixture()
+def err():
+    return torch.zeros(1, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("V,H", [(1000, 72), (37, 2048 + 8)])
+def test_embedding(ops, err, dt, V, H):
+    torch.manual_seed(0)
+    table = torch.randn(V, H, device=DEV).to(dt)
+    ids = torch.randint(0, V, (19,), device=DEV, dtype=torch.int32)
+    out = torch.empty(19, H, device=DEV)
+    ops.embedding(ids, table, out, err)
+    assert torch.equal(out, table.float()[ids.long()]) and int(err.item()) == 0
+    ids[3] = V
+    ops.embedding(ids, table, out, err)
+    assert int(err.item()) == 1 and float(out[3].abs().max()) == 0.0      # refused, not read out of bounds
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("wdt", DTYPES)
+@pytest.mark.parametrize("H,eps", [(72, 1e-5), (1000, 1e-6), (5120 + 24, 1e-3)])
+def test_rmsnorm(ops, dt, wdt, H, eps):
+    torch.manual_seed(1)
+    x = torch.randn(7, H, device=DEV) * 3
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(wdt)
+    delta = torch.randn(7, H, device=DEV).to(dt)
+    want = pl.rms_norm(x.double().cpu(), w.double().cpu(), eps)
+    out = torch.empty(7, H, device=DEV, dtype=dt)
+    ops.rmsnorm(x, w, eps, out)
+    assert rel_err(out, want) <= tol(dt)
+    # fused residual add: x += delta (float32), then the norm of the sum
+    x2 = x.clone()
+    ops.rmsnorm(x2, w, eps, out, delta=delta, writeback=True)
+    assert torch.equal(x2, x + delta.float())
+    assert rel_err(out, pl.rms_norm((x + delta.float()).double().cpu(), w.double().cpu(), eps)) <= tol(dt)
+    # gathered rows, no write-back
+    rows = torch.tensor([5, 0, 5], device=DEV, dtype=torch.int32)
+    x3 = x.clone()
+    out3 = torch.empty(3, H, device=DEV, dtype=dt)
+    ops.rmsnorm(x3, w, eps, out3, delta=delta, rows=rows)
+    assert torch.equal(x3, x) and torch.equal(out3, out[rows.long()])
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_residual_add_and_silu_mul(ops, dt):
+    torch.manual_seed(2)
+    x = torch.randn(5, 136, device=DEV)
+    d = torch.randn(5, 136, device=DEV).to(dt)
+    want = x + d.float()
+    ops.residual_add(x, d)
+    assert torch.equal(x, want)
+    gu = (torch.randn(9, 2 * 200, device=DEV) * 4).to(dt)
+    out = torch.empty(9, 200, device=DEV, dtype=dt)
+    ops.silu_mul(gu, out)
+    g, u = gu.double().cpu()[:, :200], gu.double().cpu()[:, 200:]
+    assert rel_err(out, pl.silu(g) * u) <= tol(dt)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rd,page", [(6, 2, 48, 48, 4), (5, 5, 16, 8, 16), (8, 1, 128, 128, 32), (2, 1, 256, 64, 8)])
+def test_rope_and_cache_write(ops, err, dt, nq, nkv, d, rd, page):
+    torch.manual_seed(3)
+    T, S, pages = 11, 2, 40
+    theta = 123456.0
+    inv = torch.tensor([theta ** (-(2 * i) / rd) for i in range(rd // 2)], dtype=torch.float64)
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV).to(dt)
+    src = qkv.clone()
+    positions = torch.tensor([70000, 70001, 70002, 70003, 70004, 3, 4, 5, 6, 7, 8], dtype=torch.int32, device=DEV)
+    token_seq = torch.tensor([0] * 5 + [1] * 6, dtype=torch.int32, device=DEV)
+    maxb = 70005 // page + 1
+    table = torch.full((S, maxb), -1, dtype=torch.int32, device=DEV)
+    perm = torch.randperm(pages)
+    table[0, 70000 // page: 70004 // page + 1] = perm[:70004 // page - 70000 // page + 1].int().to(DEV)
+    table[1, : 8 // page + 1] = perm[20:20 + 8 // page + 1].int().to(DEV)
+    kc = torch.zeros(pages, nkv, page, d, device=DEV, dtype=dt)
+    vc = torch.zeros_like(kc)
+    ops.rope_kv_write(qkv, positions, token_seq, inv.to(DEV), rd, table, kc, vc, nq, nkv, d, err)
+    assert int(err.item()) == 0
+    x = src.double().cpu().view(T, nq + 2 * nkv, d)
+    def rot(h):
+        out = h.clone()
+        out[..., :rd] = pl.apply_rope(h[..., :rd], positions.cpu(), inv)
+        return out
+    assert rel_err(qkv.view(T, nq + 2 * nkv, d)[:, :nq], rot(x[:, :nq])) <= tol(dt)
+    k_want, v_want = rot(x[:, nq:nq + nkv]), x[:, nq + nkv:]
+    for t in range(T):
+        p, s = int(positions[t]), int(token_seq[t])
+        pg = int(table[s, p // page])
+        assert rel_err(kc[pg, :, p % page], k_want[t]) <= tol(dt)
+        assert torch.equal(vc[pg, :, p % page].double().cpu(), v_want[t])
+    assert int((kc.abs().sum(dim=(1, 3)) > 0).sum()) == T           # nothing else was written
+    # v untouched in the buffer; a token whose page is missing is refused
+    assert torch.equal(qkv.view(T, nq + 2 * nkv, d)[:, nq + nkv:], src.view(T, nq + 2 * nkv, d)[:, nq + nkv:])
+    table[1, 0] = -1
+    ops.rope_kv_write(src.clone(), positions, token_seq, inv.to(DEV), rd, table, kc, vc, nq, nkv, d, err)
+    assert int(err.item()) == 2
+
+
+def paged_case(dt, nq, nkv, d, page, lens, q_lens, pages=64, seed=4):
+    """Sequences with contexts ``lens`` whose last ``q_lens`` tokens are queries."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(lens)
+    ks = [torch.randn(n, nkv, d, generator=g).to(dt) for n in lens]
+    vs = [torch.randn(n, nkv, d, generator=g).to(dt) for n in lens]
+    qs = [torch.randn(m, nq, d, generator=g).to(dt) for m in q_lens]
+    maxb = max(-(-n // page) for n in lens)
+    table = torch.full((S, maxb), -1, dtype=torch.int32)
+    perm = torch.randperm(pages, generator=g).tolist()
+    kc = torch.zeros(pages, nkv, page, d, dtype=dt)
+    vc = torch.zeros_like(kc)
+    for s, n in enumerate(lens):
+        for b in range(-(-n // page)):
+            pg = perm.pop()
+            table[s, b] = pg
+            m = min(page, n - b * page)
+            kc[pg, :, :m] = ks[s][b * page:b * page + m].transpose(0, 1)
+            vc[pg, :, :m] = vs[s][b * page:b * page + m].transpose(0, 1)
+    positions = torch.cat([torch.arange(n - m, n) for n, m in zip(lens, q_lens)]).int()
+    token_seq = torch.cat([torch.full((m,), s) for s, m in enumerate(q_lens)]).int()
+    return ks, vs, qs, table, kc, vc, positions, token_seq
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(6, 2, 48, 4, 0), (5, 5, 16, 16, 0), (8, 1, 128, 32, 0),
+                                                  (4, 2, 64, 8, 37), (3, 1, 256, 16, 5)])
+def test_attention_simt(ops, err, dt, nq, nkv, d, page, window):
+    lens, q_lens = [150, 1, 33, 64], [1, 1, 33, 7]
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, lens, q_lens)
+    q = torch.cat(qs).reshape(-1, nq * d).to(DEV)
+    out = torch.empty_like(q)
+    scale = 0.77 / math.sqrt(d)
+    ops.attention_simt(q, nq * d, out, kc.to(DEV), vc.to(DEV), table.to(DEV), positions.to(DEV),
+                       token_seq.to(DEV), nq, nkv, d, window, scale, err)
+    assert int(err.item()) == 0
+    off = 0
+    for s, (n, m) in enumerate(zip(lens, q_lens)):
+        want = pl.attention(qs[s].double(), ks[s].double(), vs[s].double(), torch.arange(n - m, n),
+                            window=window or None, scale=scale)
+        assert rel_err(out[off:off + m], want) <= tol(dt), (s, n, m)
+        off += m
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_attention_finds_one_far_key(ops, err, dt):
+    """One key among hundreds, at the far end of the context and at a page's
+    first row, is made to dominate: the output must be its value."""
+    nq, nkv, d, page = 4, 2, 32, 16
+    lens, q_lens = [700], [1]
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, lens, q_lens, seed=9)
+    for target in (0, 16, 15, 699, 400):
+        kc2 = kc.clone()
+        qq = qs[0].clone()
+        pg = int(table[0, target // page])
+        kc2[pg, :, target % page] = 0
+        kc2[pg, :, target % page, 0] = 30.0
+        qq[:, :, 0] = 30.0
+        q = qq.reshape(1, nq * d).to(DEV)
+        out = torch.empty_like(q)
+        ops.attention_simt(q, nq * d, out, kc2.to(DEV), vc.to(DEV), table.to(DEV), positions.to(DEV),
+                           token_seq.to(DEV), nq, nkv, d, 0, 1.0, err)
+        want = vs[0][target].repeat_interleave(nq // nkv, dim=0).reshape(1, nq * d)
+        assert rel_err(out, want) <= tol(dt), target
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 130, 72), (7, 389, 96), (64, 64, 16), (129, 200, 1000), (300, 17, 264)])
+def test_gemm_f32(ops, M, N, K):
+    torch.manual_seed(5)
+    a, w = torch.randn(M, K, device=DEV), torch.randn(N, K, device=DEV)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_f32(a, w, out)
+    assert rel_err(out, a.double().cpu() @ w.double().cpu().t()) <= 2e-6
+    # a row's result does not depend on what else is in the batch
+    out1 = torch.empty(1, N, device=DEV)
+    ops.gemm_f32(a[M // 2:M // 2 + 1], w, out1)
+    assert torch.equal(out1[0], out[M // 2])
+
+
+def test_sizes_that_kernels_refuse_raise(ops, err):
+    from rllm_b200.kernels.ops import KernelError
+    q = torch.zeros(1, 2 * 24, device=DEV)
+    kc = torch.zeros(4, 1, 16, 24, device=DEV)
+    table = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="no kernel"):
+        ops.attention_simt(q, 48, torch.empty_like(q), kc, kc, table, z, z, 2, 1, 24, 0, 1.0, err)
+    with pytest.raises(KernelError, match="CUDA tensors only"):
+        ops.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))

@@ -1,0 +1,139 @@
+"""The sampling kernels against the plain sampler (tests/plain_llama.py), on
+vocabularies that are no power of two."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+
+
+@pytest.fixture(scope="module")
+def sampler():
+    from rllm_b200.sampling import Sampler
+    return Sampler(DEV)
+
+
+def rows_for(params_list, seeds, gen_index, contexts=None, eos=()):
+    from rllm_b200.sampling import SamplingRow
+    return [SamplingRow(p, s, g, (contexts[i] if contexts else ()), eos)
+            for i, (p, s, g) in enumerate(zip(params_list, seeds, gen_index))]
+
+
+def plain_pick(logits_row, p, seed, gen_index, context=(), eos=()):
+    suppress = eos if (p.min_tokens > 0 and gen_index < p.min_tokens) else ()
+    x = pl.process_logits(logits_row, context=context, logit_bias=p.logit_bias,
+                          repetition_penalty=p.repetition_penalty, frequency_penalty=p.frequency_penalty,
+                          presence_penalty=p.presence_penalty, allowed_token_ids=p.allowed_token_ids,
+                          suppress=suppress, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
+                          min_p=p.min_p)
+    return pl.sample_row(x, p.temperature, p.top_k, pl.uniform_for(seed, gen_index))
+
+
+def test_greedy_is_argmax_with_lowest_index_on_ties(sampler):
+    from rllm_b200.sampling import SamplingParams
+    torch.manual_seed(0)
+    logits = torch.randn(5, 128256 + 3, device=DEV)
+    logits[2, 77] = logits[2, 90000] = 50.0
+    logits[3, 128258] = 60.0
+    p = SamplingParams(temperature=0.0)
+    got = sampler.sample(logits.clone(), rows_for([p] * 5, range(5), [0] * 5)).tolist()
+    assert got == logits.argmax(dim=1).tolist() and got[2] == 77 and got[3] == 128258
+    # top_k == 1 is greedy too (crates/rllm-sampling/src/sampler.rs:117)
+    p1 = SamplingParams(temperature=0.9, top_k=1)
+    assert sampler.sample(logits.clone(), rows_for([p1] * 5, range(5), [0] * 5)).tolist() == got
+
+
+@pytest.mark.parametrize("V", [389, 5003, 128256])
+def test_draws_match_the_plain_sampler(sampler, V):
+    from rllm_b200.sampling import SamplingParams
+    rng = np.random.default_rng(V)
+    variants = [SamplingParams(temperature=0.7), SamplingParams(temperature=1.3, top_k=40),
+                SamplingParams(temperature=1.0, top_p=0.8), SamplingParams(temperature=0.9, min_p=0.05),
+                SamplingParams(temperature=1.1, top_k=200, top_p=0.9, min_p=0.01),
+                SamplingParams(temperature=2.0, top_k=3)]
+    R = 48
+    logits = (rng.standard_normal((R, V)) * 3).astype(np.float32)
+    params = [variants[i % len(variants)] for i in range(R)]
+    seeds = [int(s) for s in rng.integers(0, 2 ** 62, size=R)]
+    gen = [int(g) for g in rng.integers(0, 5000, size=R)]
+    got = sampler.sample(torch.from_numpy(logits).to(DEV), rows_for(params, seeds, gen)).tolist()
+    want = [plain_pick(logits[r], params[r], seeds[r], gen[r]) for r in range(R)]
+    assert got == want
+
+
+def test_a_row_does_not_depend_on_its_batch(sampler):
+    from rllm_b200.sampling import SamplingParams
+    rng = np.random.default_rng(7)
+    V = 2000
+    logits = (rng.standard_normal((9, V)) * 2).astype(np.float32)
+    p = SamplingParams(temperature=0.8, top_p=0.95)
+    seeds, gen = list(range(100, 109)), list(range(9))
+    full = sampler.sample(torch.from_numpy(logits).to(DEV), rows_for([p] * 9, seeds, gen)).tolist()
+    for r in (0, 4, 8):
+        alone = sampler.sample(torch.from_numpy(logits[r:r + 1]).to(DEV), rows_for([p], [seeds[r]], [gen[r]]))
+        assert alone.tolist() == [full[r]]
+    # mixed with greedy rows
+    mixed = [p, SamplingParams(temperature=0.0)] * 4 + [p]
+    got = sampler.sample(torch.from_numpy(logits).to(DEV), rows_for(mixed, seeds, gen)).tolist()
+    assert got[0::2] == full[0::2] and got[1::2] == logits[1::2].argmax(axis=1).tolist()
+
+
+def test_draw_frequencies(sampler):
+    from rllm_b200.sampling import SamplingParams
+    probs = np.array([0.5, 0.25, 0.125, 0.125, 0.0], dtype=np.float64)
+    with np.errstate(divide="ignore"):
+        row = np.log(probs).astype(np.float32)
+    R = 4000
+    logits = torch.from_numpy(np.tile(row, (R, 1))).to(DEV)
+    p = SamplingParams(temperature=1.0)
+    got = sampler.sample(logits, rows_for([p] * R, [5] * R, list(range(R)))).cpu().numpy()
+    freq = np.bincount(got, minlength=5) / R
+    assert freq[4] == 0 and np.allclose(freq[:4], probs[:4], atol=0.03)
+    again = sampler.sample(logits, rows_for([p] * R, [5] * R, list(range(R)))).cpu().numpy()
+    assert (again == got).all()                      # same seed and index: same token
+
+
+def test_processors_match_the_plain_ones(sampler):
+    from rllm_b200.sampling import SamplingParams
+    rng = np.random.default_rng(3)
+    V, R = 777, 12
+    logits = (rng.standard_normal((R, V)) * 2).astype(np.float32)
+    contexts = [[int(t) for t in rng.integers(0, 50, size=rng.integers(1, 60))] for _ in range(R)]
+    eos = (5, 9)
+    ps = []
+    for r in range(R):
+        ps.append(SamplingParams(
+            temperature=[0.0, 0.8][r % 2], repetition_penalty=[1.0, 1.3, 0.7][r % 3],
+            frequency_penalty=[0.0, 0.4][(r // 2) % 2], presence_penalty=[0.0, 1.5][(r // 3) % 2],
+            logit_bias={3: 5.0, 700: -2.0} if r % 4 == 0 else {},
+            allowed_token_ids=list(range(0, V, 3)) if r % 5 == 0 else None,
+            min_tokens=4 if r % 2 else 0))
+    seeds, gen = list(range(R)), [r % 6 for r in range(R)]
+    dev = torch.from_numpy(logits).to(DEV)
+    got = sampler.sample(dev, rows_for(ps, seeds, gen, contexts, eos)).tolist()
+    want = [plain_pick(logits[r], ps[r], seeds[r], gen[r], contexts[r], eos) for r in range(R)]
+    assert got == want
+    # and the edited logits themselves
+    dev = torch.from_numpy(logits).to(DEV)
+    sampler.apply_processors(dev, rows_for(ps, seeds, gen, contexts, eos))
+    for r in range(R):
+        suppress = eos if (ps[r].min_tokens > 0 and gen[r] < ps[r].min_tokens) else ()
+        x = pl.process_logits(logits[r], context=contexts[r], logit_bias=ps[r].logit_bias,
+                              repetition_penalty=ps[r].repetition_penalty,
+                              frequency_penalty=ps[r].frequency_penalty,
+                              presence_penalty=ps[r].presence_penalty,
+                              allowed_token_ids=ps[r].allowed_token_ids, suppress=suppress, temperature=0.0)
+        np.testing.assert_allclose(dev[r].cpu().numpy(), x, rtol=1e-6, atol=1e-6)
+
+
+def test_params_are_validated():
+    from rllm_b200.sampling import InvalidSamplingParams, SamplingParams
+    SamplingParams().validate()
+    assert SamplingParams().max_tokens == 16 and SamplingParams().temperature == 1.0
+    for bad in (dict(temperature=-1.0), dict(top_p=1.5), dict(n=0), dict(n=2), dict(repetition_penalty=0.0),
+                dict(presence_penalty=3.0), dict(logprobs=5)):
+        with pytest.raises(InvalidSamplingParams):
+            SamplingParams(**bad).validate()
