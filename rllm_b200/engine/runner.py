@@ -47,14 +47,13 @@ _ERR_BITS = {1: "a token id outside the vocabulary", 2: "a cache write to a page
              4: "an attention read from a page the request does not hold"}
 
 
-class ModelRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager, storage: CacheStorage):
-        if model.device is None:
-            raise StepError("the model has no weights yet")
-        if model.device.type != "cuda":
+class BatchBuilder:
+    """Flattens entries into the device arrays of a ``StepContext``."""
+
+    def __init__(self, cache: CacheManager, device: torch.device, act_dtype: torch.dtype):
+        if device.type != "cuda":
             raise StepError("the engine runs on a CUDA device only; there is no CPU path")
-        self.model, self.cache, self.storage = model, cache, storage
-        self.device = model.device
+        self.cache, self.device, self.act_dtype = cache, device, act_dtype
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         # ring of pinned staging buffers; a buffer is reused only after its copy has run
         self._ring: List[list] = [[None, None] for _ in range(4)]
@@ -145,9 +144,22 @@ class ModelRunner:
             num_tokens=T, num_seqs=S, num_decode=num_decode, positions=d_pos, token_seq=d_tseq,
             q_start=d_qstart, seq_lens=d_seqlens, q_lens_host=q_lens,
             seq_lens_host=[int(x) for x in seq_lens], block_tables=block_tables, state_slots=d_slots,
-            state_slots_host=[int(x) for x in slots], err=self.err, act_dtype=self.model.dtype)
+            state_slots_host=[int(x) for x in slots], err=self.err, act_dtype=self.act_dtype)
         ctx.extras["starts_host"] = [entries[i].start for i in order]
         return ctx, d_tokens, d_rows
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cache: CacheManager, storage: CacheStorage):
+        if model.device is None:
+            raise StepError("the model has no weights yet")
+        self.model, self.cache, self.storage = model, cache, storage
+        self.device = model.device
+        self.builder = BatchBuilder(cache, self.device, model.dtype)
+        self.err = self.builder.err
+
+    def build_context(self, entries: Sequence[StepEntry]):
+        return self.builder.build_context(entries)
 
     # ------------------------------------------------------------------
     @torch.no_grad()

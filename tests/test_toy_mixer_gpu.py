@@ -1,0 +1,146 @@
+"""A toy mixer with state of its own, a toy feed-forward and a toy architecture
+are defined HERE, registered, written as a model folder, loaded, and stepped
+through trace replay - without a change to the framework's files.  The toy
+model mixes kinds layer by layer: its first layer keeps a running state per
+request, its second is the framework's attention."""
+import json
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as pl
+import replay_util as ru
+
+pytestmark = pytest.mark.gpu
+
+H, V, STATE = 40, 131, 24
+DECAY = 0.9
+
+
+def register_toy():
+    from rllm_b200.config import register_architecture
+    from rllm_b200.parts import (FeedForward, LayerSpec, Mixer, ModelSpec, PartSpec, Run, StateNeed,
+                                 TensorSpec, register_part)
+
+    @register_part("mixer", "toy_decay_state")
+    class DecayState(Mixer):
+        """s_t = decay * s_{t-1} + W_in x_t ;  y_t = W_out s_t, state float32 [STATE] per request."""
+
+        def __init__(self, spec, prefix=""):
+            super().__init__(spec, prefix)
+            self.hidden, self.size, self.decay = spec["hidden_size"], spec["state_size"], spec["decay"]
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "in.weight", (self.size, self.hidden), init=("normal", 0.2)),
+                    TensorSpec(self.prefix + "out.weight", (self.hidden, self.size), init=("normal", 0.2))]
+
+        def load(self, tensors):
+            self.w_in, self.w_out = tensors[self.prefix + "in.weight"], tensors[self.prefix + "out.weight"]
+
+        def cache_need(self):
+            return StateNeed((self.size,))
+
+        def forward(self, x, ctx, cache):
+            u = x.float() @ self.w_in.float().t()                      # [T, STATE]
+            out = torch.empty_like(u)
+            off = 0
+            for s, n in enumerate(ctx.q_lens_host):                    # a sequence's tokens in order
+                state = cache.state[ctx.state_slots_host[s]]
+                for t in range(off, off + n):
+                    state.mul_(self.decay).add_(u[t])
+                    out[t] = state
+                off += n
+            return (out @ self.w_out.float().t()).to(x.dtype)
+
+    @register_part("feed_forward", "toy_scale")
+    class Scale(FeedForward):
+        def __init__(self, spec, prefix=""):
+            super().__init__(spec, prefix)
+            self.hidden = spec["hidden_size"]
+
+        def tensor_specs(self):
+            return [TensorSpec(self.prefix + "scale", (self.hidden,), role="vector", init=("one_plus_normal", 0.3))]
+
+        def load(self, tensors):
+            self.scale = tensors[self.prefix + "scale"]
+
+        def forward(self, x):
+            return (x.float() * self.scale.float()).to(x.dtype)
+
+    def parse(raw):
+        return dict(raw)
+
+    def build(cfg):
+        norms = lambda: (PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="n0.weight"),
+                         PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="n1.weight"))
+        pos = PartSpec.of("rotary", head_dim=16, rotary_dim=16, theta=100.0, scaling=None)
+        layers = (
+            LayerSpec("pre_norm", PartSpec.of("toy_decay_state", hidden_size=H, state_size=STATE, decay=DECAY,
+                                              tensor_prefix="state."),
+                      PartSpec.of("toy_scale", hidden_size=H, tensor_prefix="ff."), norms(), "toy.0."),
+            LayerSpec("pre_norm", PartSpec.of("attention", hidden_size=H, num_heads=2, num_kv_heads=1, head_dim=16,
+                                              window=None, scale=None, position=pos),
+                      PartSpec.of("gated_mlp", hidden_size=H, intermediate_size=56), norms(), "toy.1."),
+        )
+        return ModelSpec(hidden_size=H, vocab_size=V,
+                         embedding=PartSpec.of("token_embedding", vocab_size=V, hidden_size=H, name="toy.embed"),
+                         layers=layers, order=(Run(0, 0), Run(1, 1)),
+                         final_norm=PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="toy.norm"),
+                         head=PartSpec.of("lm_head", vocab_size=V, hidden_size=H, name="toy.head", tied_to="toy.embed"),
+                         max_positions=512)
+
+    register_architecture("ToyStateForCausalLM", parse, build)
+
+
+def plain_toy(w, tokens, eps):
+    x = pl.embedding(w["toy.embed"], tokens)
+    t = len(tokens)
+    # layer 0: decaying state, scale feed-forward
+    xn = pl.rms_norm(x, w["toy.0.n0.weight"], eps)
+    u = xn @ w["toy.0.state.in.weight"].t()
+    s, outs = torch.zeros(STATE, dtype=torch.float64), []
+    for i in range(t):
+        s = DECAY * s + u[i]
+        outs.append(s)
+    x = x + torch.stack(outs) @ w["toy.0.state.out.weight"].t()
+    x = x + pl.rms_norm(x, w["toy.0.n1.weight"], eps) * w["toy.0.ff.scale"]
+    # layer 1: attention, gated mlp
+    xn = pl.rms_norm(x, w["toy.1.n0.weight"], eps)
+    inv = pl.rope_inv_freq(16, 100.0, None)
+    pos = torch.arange(t)
+    q = pl.apply_rope((xn @ w["toy.1.self_attn.q_proj.weight"].t()).reshape(t, 2, 16), pos, inv)
+    k = pl.apply_rope((xn @ w["toy.1.self_attn.k_proj.weight"].t()).reshape(t, 1, 16), pos, inv)
+    v = (xn @ w["toy.1.self_attn.v_proj.weight"].t()).reshape(t, 1, 16)
+    x = x + pl.attention(q, k, v, pos) @ w["toy.1.self_attn.o_proj.weight"].t()
+    xn = pl.rms_norm(x, w["toy.1.n1.weight"], eps)
+    x = x + pl.gated_mlp(xn, w["toy.1.mlp.gate_proj.weight"], w["toy.1.mlp.up_proj.weight"], w["toy.1.mlp.down_proj.weight"])
+    return pl.rms_norm(x, w["toy.norm"], eps) @ w["toy.embed"].t()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_is_registered_built_and_stepped(tmp_path, dtype):
+    from safetensors import safe_open
+    from rllm_b200.engine.loading import write_random_model
+    register_toy()
+    cfg = {"architectures": ["ToyStateForCausalLM"], "eps": 1e-4, "torch_dtype": "float32"}
+    d = str(tmp_path / "toy")
+    write_random_model(d, cfg, seed=3)
+    w = {}
+    with safe_open(os.path.join(d, "model.safetensors"), framework="pt") as f:
+        for n in f.keys():
+            t = f.get_tensor(n)
+            w[n] = (t.to(torch.bfloat16) if dtype == "bfloat16" and t.dim() == 2 else t).double()
+    assert "toy.0.state.in.weight" in w and "toy.head" not in w
+    rng = np.random.default_rng(5)
+    reqs = {f"r{i}": [int(t) for t in rng.integers(0, V, size=n)] for i, n in enumerate([40, 3, 77, 21, 64, 9])}
+    want = {r: plain_toy(w, toks, 1e-4).numpy() for r, toks in reqs.items()}
+    tol = 1e-4 if dtype == "float32" else 3e-2
+    for tb in (ru.trace_whole(reqs), ru.trace_portions(reqs, seed=1), ru.trace_mixed(reqs, seed=2, live=3, tail=5)):
+        got = ru.run_trace(d, dtype, tb, V, page_size=16)
+        for r, toks in reqs.items():
+            have = np.stack([got[(r, p)] for p in range(len(toks))])
+            err = np.abs(have - want[r]).max(axis=1) / np.abs(want[r]).max()
+            assert err.max() <= tol, (r, int(err.argmax()), float(err.max()))
