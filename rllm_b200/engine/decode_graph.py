@@ -1,0 +1,118 @@
+"""CUDA graphs for decode steps.
+
+A step in which every request brings exactly one token launches the same
+kernels with the same shapes whenever the number of requests and the width of
+the block table are the same; only the contents of a few small device arrays
+change.  Such a step is captured once per (number of requests, table width)
+and replayed: the host then issues one copy of the packed inputs and one graph
+launch instead of hundreds of kernel launches.  The kernels read lengths,
+positions and page ids from device memory, never from launch arguments, so a
+replay follows the step's own data.
+
+The first two steps of a given shape run eagerly on the graph's static buffers
+(their results are used, and they warm up the libraries); after the second the
+same work is captured for later steps.  A capture executes nothing, so the
+cache is not touched twice.
+
+The reference captures decode for batch sizes 1..64 in powers of two on the
+default stream (crates/rllm-worker/src/model_runner.rs:555-667, replay at
+crates/rllm-executor/src/uniproc.rs:81-106); here every batch size gets its own
+graph on first use, on a private stream, with no padding rows.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..parts.base import StepContext
+
+
+def table_width_bucket(blocks: int) -> int:
+    """Table widths are powers of two (at least 8) so that few graphs serve all lengths."""
+    w = 8
+    while w < blocks:
+        w *= 2
+    return w
+
+
+class DecodeGraph:
+    """Static buffers, context and (after the first step) the captured graph of
+    decode steps with S requests and block tables of ``width`` entries."""
+
+    def __init__(self, runner, S: int, width: int):
+        self.runner, self.S, self.width = runner, S, width
+        cache = runner.cache
+        self.paged = list(cache.paged)
+        n = 7 * S + 1 + len(self.paged) * S * width
+        self.static = torch.zeros(n, dtype=torch.int32, device=runner.device)
+        self.stage = torch.zeros(n, dtype=torch.int32, pin_memory=True)
+        self.host = self.stage.numpy()
+        self.copied = torch.cuda.Event()
+        self.copied.record()
+        o = [0]
+
+        def take(k):
+            v = (o[0], o[0] + k)
+            o[0] += k
+            return v
+        self.r_tokens, self.r_pos, self.r_tseq = take(S), take(S), take(S)
+        self.r_qstart, self.r_seqlens, self.r_slots, self.r_rows = take(S + 1), take(S), take(S), take(S)
+        self.r_tables = [take(S * width) for _ in self.paged]
+        # the parts that never change
+        self.host[self.r_tseq[0]:self.r_tseq[1]] = np.arange(S)
+        self.host[self.r_qstart[0]:self.r_qstart[1]] = np.arange(S + 1)
+        self.host[self.r_rows[0]:self.r_rows[1]] = np.arange(S)
+        sv = lambda r: self.static[r[0]:r[1]]
+        tables: List[Optional[torch.Tensor]] = [None] * len(cache.needs)
+        for g, r in zip(self.paged, self.r_tables):
+            tables[g] = sv(r).view(S, width)
+        self.token_ids = sv(self.r_tokens)
+        self.rows = sv(self.r_rows)
+        self.ctx = StepContext(
+            num_tokens=S, num_seqs=S, num_decode=S, positions=sv(self.r_pos), token_seq=sv(self.r_tseq),
+            q_start=sv(self.r_qstart), seq_lens=sv(self.r_seqlens), q_lens_host=[1] * S,
+            seq_lens_host=[width * cache.page_size] * S, block_tables=tables, state_slots=sv(self.r_slots),
+            state_slots_host=[], err=runner.err, act_dtype=runner.model.dtype)
+        self.ctx.extras["graph"] = True
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.uses = 0
+
+    def fill(self, entries) -> None:
+        """Pack the step's inputs into the pinned buffer and copy them over."""
+        cache, S, W = self.runner.cache, self.S, self.width
+        self.copied.synchronize()
+        h = self.host
+        for s, e in enumerate(entries):
+            h[self.r_tokens[0] + s] = e.tokens[0]
+            h[self.r_pos[0] + s] = e.start
+            h[self.r_seqlens[0] + s] = e.start + 1
+            h[self.r_slots[0] + s] = cache.slot(e.req)
+        for g, r in zip(self.paged, self.r_tables):
+            tab = h[r[0]:r[1]].reshape(S, W)
+            for s, e in enumerate(entries):
+                tb = cache.table(e.req, g)
+                n = min(len(tb), W)
+                tab[s, :n] = tb[:n]
+                tab[s, n:] = -1
+        self.static.copy_(self.stage, non_blocking=True)
+        self.copied.record()
+
+    def run(self) -> torch.Tensor:
+        """Logits float32 [S, vocab]; valid until the next run of this graph."""
+        r = self.runner
+        self.uses += 1
+        if self.graph is not None:
+            self.graph.replay()
+            return self.logits
+        logits = r.model.forward(self.token_ids, self.ctx, self.rows, r.storage)
+        if self.uses >= 2 and r.capture_graphs:
+            # capture the same work for the following steps (nothing executes during capture)
+            torch.cuda.synchronize(r.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=r.graph_pool):
+                self.logits = r.model.forward(self.token_ids, self.ctx, self.rows, r.storage)
+            self.graph = g
+        return logits

@@ -96,7 +96,7 @@ class EngineCore:
                                   self.args.max_num_seqs, self.args.enable_prefix_caching)
         self.storage = CacheStorage(model.layout, self.args.block_size, [pages] * n_paged,
                                     self.args.max_num_seqs, model.dtype, self.device)
-        self.runner = ModelRunner(model, self.cache, self.storage)
+        self.runner = ModelRunner(model, self.cache, self.storage, self.args.enable_cuda_graphs)
         self.sampler = Sampler(self.device)
         self.scheduler = Scheduler(SchedulerConfig(
             max_num_seqs=self.args.max_num_seqs, max_num_batched_tokens=self.args.max_num_batched_tokens,

@@ -37,14 +37,18 @@ def require_cuda(device: Optional[str] = None) -> torch.device:
 
 
 def load_model(model_dir: str, dtype: str = "auto", device: Optional[str] = None,
-               random_weights: bool = False, seed: int = 0) -> Tuple[Any, DecoderModel]:
-    """(typed configuration, model with weights on ``device``)."""
+               random_weights: bool = False, seed: int = 0,
+               draw_on_device: bool = False) -> Tuple[Any, DecoderModel]:
+    """(typed configuration, model with weights on ``device``).  With
+    ``random_weights`` the folder needs config.json only; ``draw_on_device``
+    draws them with the device's generator (fast for large models) instead of
+    the CPU's (the values a written model folder would hold)."""
     config, spec = load_model_description(model_dir)
     run_dtype = torch_dtype_of(EngineArgs(dtype=dtype).run_dtype(getattr(config, "torch_dtype", "bfloat16")))
     dev = require_cuda(device)
     model = DecoderModel(spec)
     if random_weights:
-        source = RandomSource(model.tensor_specs(), seed, torch.float32)
+        source = RandomSource(model.tensor_specs(), seed, torch.float32, str(dev) if draw_on_device else "cpu")
     else:
         source = FolderSource(model_dir)
     try:

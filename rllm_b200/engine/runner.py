@@ -150,13 +150,35 @@ class BatchBuilder:
 
 
 class ModelRunner:
-    def __init__(self, model: DecoderModel, cache: CacheManager, storage: CacheStorage):
+    MAX_GRAPHS = 96
+
+    def __init__(self, model: DecoderModel, cache: CacheManager, storage: CacheStorage,
+                 enable_cuda_graphs: bool = True):
         if model.device is None:
             raise StepError("the model has no weights yet")
         self.model, self.cache, self.storage = model, cache, storage
         self.device = model.device
         self.builder = BatchBuilder(cache, self.device, model.dtype)
         self.err = self.builder.err
+        # decode steps go through CUDA graphs if every mixer says its forward can be captured
+        self.capture_graphs = bool(enable_cuda_graphs) and all(
+            getattr(b.mixer, "graph_safe", False) for b in model.blocks)
+        self.graphs = {}
+        self.graph_pool = None
+
+    def _decode_graph(self, entries: Sequence[StepEntry]):
+        from .decode_graph import DecodeGraph, table_width_bucket
+        page = self.cache.page_size
+        blocks = max(-(-(e.start + 1) // page) for e in entries)
+        key = (len(entries), table_width_bucket(blocks))
+        g = self.graphs.get(key)
+        if g is None:
+            if len(self.graphs) >= self.MAX_GRAPHS:
+                return None
+            if self.graph_pool is None:
+                self.graph_pool = torch.cuda.graph_pool_handle()
+            g = self.graphs[key] = DecodeGraph(self, *key)
+        return g
 
     def build_context(self, entries: Sequence[StepEntry]):
         return self.builder.build_context(entries)
@@ -169,8 +191,50 @@ class ModelRunner:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
         with torch.cuda.device(self.device):
             self.storage.zero_slots(self.cache.take_fresh_slots())
+            if self.capture_graphs and all(len(e.tokens) == 1 for e in entries):
+                g = self._decode_graph(entries)
+                if g is not None:
+                    g.fill(entries)
+                    logits = g.run()
+                    wanted = [s for s, e in enumerate(entries) if len(e.want)]
+                    if len(wanted) == len(entries):
+                        return logits
+                    return logits[torch.tensor(wanted, dtype=torch.long, device=self.device)]
             ctx, token_ids, rows = self.build_context(entries)
             return self.model.forward(token_ids, ctx, rows, self.storage)
+
+    @torch.no_grad()
+    def greedy_decode_run(self, entries: Sequence[StepEntry], num_steps: int,
+                          timing: Optional[tuple] = None) -> torch.Tensor:
+        """``num_steps`` greedy decode steps that stay on the device: each step's
+        argmax token is the next step's input.  Every entry brings one token; the
+        caller has made sure of pages for ``start + num_steps`` tokens.  Returns
+        the generated tokens int32 [num_steps, S] (on the device).  ``timing`` =
+        (first timed step, start event, end event) records the two CUDA events
+        around the steps from the given one to the last."""
+        from ..kernels import ops
+        if not self.capture_graphs or any(len(e.tokens) != 1 for e in entries):
+            raise StepError("greedy_decode_run needs single-token entries and capturable mixers")
+        page = self.cache.page_size
+        with torch.cuda.device(self.device):
+            self.storage.zero_slots(self.cache.take_fresh_slots())
+            last = [StepEntry(e.req, e.tokens, e.start + num_steps - 1, e.want) for e in entries]
+            g = self._decode_graph(last)            # a table wide enough for the whole run
+            if g is None:
+                raise StepError("too many decode graphs")
+            g.fill(entries)
+            S = len(entries)
+            history = torch.empty((num_steps, S), dtype=torch.int32, device=self.device)
+            sampled = torch.empty(S, dtype=torch.int32, device=self.device)
+            for i in range(num_steps):
+                if timing is not None and i == timing[0]:
+                    timing[1].record()
+                logits = g.run()
+                ops.argmax(logits, sampled)
+                ops.decode_advance(g.token_ids, g.ctx.positions, g.ctx.seq_lens, sampled, history[i])
+            if timing is not None:
+                timing[2].record()
+            return history
 
     def check_errors(self) -> None:
         """Raise if a kernel of an earlier step flagged a bad index (synchronises)."""

@@ -235,3 +235,29 @@ RLLM_EXPORT int rllm_silu_mul(const void* gu, void* out, int dtype, int T, int I
   RLLM_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Between two decode steps that stay on the device: the sampled token becomes
+// the next input, positions and lengths grow by one, and the token is appended
+// to a history [max_steps, S] for the host to read later.
+// ---------------------------------------------------------------------------
+__global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
+                                      int* __restrict__ seq_lens, const int* __restrict__ sampled,
+                                      int* __restrict__ history_row, int S) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= S) return;
+  const int t = sampled[i];
+  token_ids[i] = t;
+  positions[i] += 1;
+  seq_lens[i] += 1;
+  if (history_row) history_row[i] = t;
+}
+
+RLLM_EXPORT int rllm_decode_advance(int* token_ids, int* positions, int* seq_lens, const int* sampled,
+                                    int* history_row, int S, cudaStream_t stream) {
+  if (S <= 0) return 0;
+  decode_advance_kernel<<<(S + 127) / 128, 128, 0, stream>>>(token_ids, positions, seq_lens, sampled,
+                                                            history_row, S);
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}

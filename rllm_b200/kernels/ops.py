@@ -39,7 +39,11 @@ def _stream() -> c_void_p:
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+LAUNCHES = [0]      # entry-point calls so far (each launches at least one kernel)
+
+
 def _check(code: int, what: str) -> None:
+    LAUNCHES[0] += 1
     if code == 0:
         return
     if code == -1:
@@ -216,3 +220,11 @@ def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: t
     kernel for the dtype and the shape of the batch (``ctx`` is a StepContext)."""
     attention_simt(q, q_stride, out, kcache, vcache, block_table, ctx.positions, ctx.token_seq,
                    nq, nkv, d, window, scale, ctx.err)
+
+
+def decode_advance(token_ids: torch.Tensor, positions: torch.Tensor, seq_lens: torch.Tensor,
+                   sampled: torch.Tensor, history_row: Optional[torch.Tensor]) -> None:
+    """token_ids = sampled; positions += 1; seq_lens += 1; history_row = sampled."""
+    lib = build.load_library("elementwise")
+    _check(lib.rllm_decode_advance(_ptr(token_ids), _ptr(positions), _ptr(seq_lens), _ptr(sampled),
+                                   _ptr(history_row), c_int(token_ids.numel()), _stream()), "decode_advance")

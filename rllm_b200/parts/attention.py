@@ -33,6 +33,8 @@ from .spec import KVPagesNeed, PartSpec, TensorSpec
 
 @register_part("mixer", "attention")
 class PagedAttention(Mixer):
+    graph_safe = True        # forward launches kernels only: a decode step can be captured in a CUDA graph
+
     def __init__(self, spec: PartSpec, prefix: str = ""):
         super().__init__(spec, prefix)
         p = spec.get()

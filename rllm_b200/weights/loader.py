@@ -99,31 +99,37 @@ def _fnv1a64(text: str) -> int:
     return h
 
 
-def draw_tensor(spec: TensorSpec, seed: int) -> torch.Tensor:
-    """The random tensor for ``spec`` under ``seed``, float32 (int64 for "int")."""
-    g = torch.Generator(device="cpu")
+def draw_tensor(spec: TensorSpec, seed: int, device: str = "cpu") -> torch.Tensor:
+    """The random tensor for ``spec`` under ``seed``, float32 (int64 for "int").
+    Drawn on the CPU by default, which is what a written model folder holds; a
+    CUDA ``device`` draws with that device's generator (other values, same
+    distribution), which is much faster for large models."""
+    g = torch.Generator(device=device)
     g.manual_seed(((seed * 0x9E3779B97F4A7C15) ^ _fnv1a64(spec.name)) & 0x7FFFFFFFFFFFFFFF)
     kind = spec.init[0]
+    kw = dict(generator=g, dtype=torch.float32, device=device)
     if kind == "normal":
-        return torch.randn(spec.shape, generator=g, dtype=torch.float32) * float(spec.init[1])
+        return torch.randn(spec.shape, **kw) * float(spec.init[1])
     if kind == "one_plus_normal":
-        return 1.0 + torch.randn(spec.shape, generator=g, dtype=torch.float32) * float(spec.init[1])
+        return 1.0 + torch.randn(spec.shape, **kw) * float(spec.init[1])
     if kind == "zeros":
-        return torch.zeros(spec.shape, dtype=torch.float32)
+        return torch.zeros(spec.shape, dtype=torch.float32, device=device)
     if kind == "ones":
-        return torch.ones(spec.shape, dtype=torch.float32)
+        return torch.ones(spec.shape, dtype=torch.float32, device=device)
     if kind == "randint":
-        return torch.randint(0, int(spec.init[1]), spec.shape, generator=g, dtype=torch.int64)
+        return torch.randint(0, int(spec.init[1]), spec.shape, generator=g, dtype=torch.int64, device=device)
     raise WeightsError(f"tensor {spec.name!r}: unknown init rule {spec.init!r}")
 
 
 class RandomSource(WeightSource):
     """Draws the tensors of ``specs`` from ``seed``; optional tensors are absent."""
 
-    def __init__(self, specs: Iterable[TensorSpec], seed: int, store_dtype: torch.dtype = torch.float32):
+    def __init__(self, specs: Iterable[TensorSpec], seed: int, store_dtype: torch.dtype = torch.float32,
+                 device: str = "cpu"):
         self.specs = {s.name: s for s in specs if not s.optional}
         self.seed = int(seed)
         self.store_dtype = store_dtype
+        self.device = device
 
     def names(self):
         return list(self.specs)
@@ -137,7 +143,7 @@ class RandomSource(WeightSource):
 
     def read(self, name):
         s = self.specs[name]
-        return draw_tensor(s, self.seed).to(self._dtype(s))
+        return draw_tensor(s, self.seed, self.device).to(self._dtype(s))
 
 
 def _held_dtype(spec: TensorSpec, stored: torch.dtype, run_dtype: torch.dtype) -> torch.dtype:
