@@ -213,11 +213,73 @@ def logit_mask(logits: torch.Tensor, allowed_start: Optional[torch.Tensor],
                                _ptr(sup_tokens), _stream()), "logit_mask")
 
 
+def attention_prefill_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
+                           vcache: torch.Tensor, block_table: torch.Tensor, q_start: torch.Tensor,
+                           seq_lens: torch.Tensor, seq_begin: int, seq_end: int, num_tokens: int, nq: int,
+                           nkv: int, d: int, window: int, scale: float, err: torch.Tensor) -> None:
+    """Tensor-core attention of the prompt portions of sequences seq_begin .. seq_end-1."""
+    lib = build.load_library("attention_mma")
+    _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
+    assert q.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
+    _check(lib.rllm_attention_prefill_bf16(_ptr(q), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
+                                           _ptr(block_table), c_int(block_table.shape[1]), _ptr(q_start),
+                                           _ptr(seq_lens), c_int(seq_begin), c_int(seq_end), c_int(num_tokens),
+                                           c_int(nq), c_int(nkv), c_int(d), c_int(kcache.shape[2]),
+                                           c_int(kcache.shape[0]), c_int(window), c_float(scale), _ptr(err),
+                                           _stream()), "attention_prefill_bf16")
+
+
+def attention_decode_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
+                          vcache: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
+                          num_seqs: int, max_seq_len: int, nq: int, nkv: int, d: int, window: int,
+                          scale: float, err: torch.Tensor, workspace: Optional[torch.Tensor] = None) -> None:
+    """Split-KV tensor-core attention of sequences 0 .. num_seqs-1, one query token
+    each (row s of q and out).  ``max_seq_len`` bounds every length.  The
+    workspace (float32, ``attention_decode_workspace`` elements) holds the
+    splits' partial results; it is allocated here if not given."""
+    lib = build.load_library("attention_mma")
+    _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
+    assert q.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
+    need = attention_decode_workspace(num_seqs, nq, d, max_seq_len)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.float32, device=q.device)
+    assert workspace.dtype is torch.float32 and workspace.numel() >= need
+    _check(lib.rllm_attention_decode_bf16(_ptr(q), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
+                                          _ptr(block_table), c_int(block_table.shape[1]), _ptr(seq_lens),
+                                          c_int(num_seqs), c_int(max_seq_len), c_int(nq), c_int(nkv), c_int(d),
+                                          c_int(kcache.shape[2]), c_int(kcache.shape[0]), c_int(window),
+                                          c_float(scale), _ptr(workspace), _ptr(err), _stream()),
+           "attention_decode_bf16")
+
+
+def attention_decode_workspace(num_seqs: int, nq: int, d: int, max_seq_len: int) -> int:
+    lib = build.load_library("attention_mma")
+    lib.rllm_attention_decode_workspace.restype = c_longlong
+    return int(lib.rllm_attention_decode_workspace(c_int(num_seqs), c_int(nq), c_int(d), c_int(max_seq_len)))
+
+
+def mma_attention_takes(nq: int, nkv: int, d: int) -> bool:
+    return d in (16, 32, 64, 128) and nq % nkv == 0 and nq // nkv <= 16
+
+
 def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
                     vcache: torch.Tensor, block_table: torch.Tensor, ctx, nq: int, nkv: int, d: int,
                     window: int, scale: float) -> None:
-    """Attention of all query tokens of a step over the paged cache; picks the
-    kernel for the dtype and the shape of the batch (``ctx`` is a StepContext)."""
+    """Attention of all query tokens of a step over the paged cache (``ctx`` is a
+    StepContext).  bfloat16 with a head size the tensor-core kernels take: the
+    sequences with one token go to the split-KV decode kernel, the others to the
+    prefill kernel.  float32, and other head sizes: the CUDA-core kernel."""
+    import os
+    if q.dtype is torch.bfloat16 and mma_attention_takes(nq, nkv, d) and os.environ.get("RLLM_ATTENTION") != "simt":
+        nd, S, T = ctx.num_decode, ctx.num_seqs, ctx.num_tokens
+        if nd > 0:
+            bound = max(ctx.seq_lens_host[:nd])
+            attention_decode_bf16(q, q_stride, out, kcache, vcache, block_table, ctx.seq_lens, nd, bound,
+                                  nq, nkv, d, window, scale, ctx.err)
+        if S > nd:
+            attention_prefill_bf16(q, q_stride, out, kcache, vcache, block_table, ctx.q_start, ctx.seq_lens,
+                                   nd, S, T - nd, nq, nkv, d, window, scale, ctx.err)
+        return
     attention_simt(q, q_stride, out, kcache, vcache, block_table, ctx.positions, ctx.token_seq,
                    nq, nkv, d, window, scale, ctx.err)
 

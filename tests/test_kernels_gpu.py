@@ -217,3 +217,93 @@ def test_sizes_that_kernels_refuse_raise(ops, err):
         ops.attention_simt(q, 48, torch.empty_like(q), kc, kc, table, z, z, 2, 1, 24, 0, 1.0, err)
     with pytest.raises(KernelError, match="CUDA tensors only"):
         ops.silu_mul(torch.zeros(2, 8), torch.zeros(2, 4))
+
+
+# ---------------------------------------------------------------------------
+# tensor-core attention (bfloat16): prefill and split-KV decode
+# ---------------------------------------------------------------------------
+MMA_CASES = [(8, 2, 64, 16, 0), (3, 1, 32, 8, 0), (4, 4, 128, 16, 0), (12, 2, 16, 4, 0), (32, 8, 64, 16, 0),
+             (8, 2, 64, 16, 300), (6, 2, 128, 32, 70), (5, 1, 32, 8, 17)]
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window", MMA_CASES)
+def test_attention_prefill_mma(ops, err, nq, nkv, d, page, window):
+    dt = torch.bfloat16
+    lens, q_lens = [700, 64, 65, 130, 2], [257, 64, 2, 129, 2]        # portions after earlier context, and whole prompts
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, lens, q_lens, pages=256)
+    q = torch.cat(qs).reshape(-1, nq * d).to(DEV)
+    out = torch.zeros_like(q)
+    q_start = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=DEV)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    ops.attention_prefill_bf16(q, nq * d, out, kc.to(DEV), vc.to(DEV), table.to(DEV), q_start, seq_lens,
+                               0, len(lens), sum(q_lens), nq, nkv, d, window, scale, err)
+    assert int(err.item()) == 0
+    off = 0
+    for s, (n, m) in enumerate(zip(lens, q_lens)):
+        want = pl.attention(qs[s].double(), ks[s].double(), vs[s].double(), torch.arange(n - m, n),
+                            window=window or None, scale=scale)
+        assert rel_err(out[off:off + m], want) <= tol(dt), (s, n, m)
+        off += m
+    # a subrange of the sequences leaves the other rows alone
+    out2 = torch.zeros_like(q)
+    ops.attention_prefill_bf16(q, nq * d, out2, kc.to(DEV), vc.to(DEV), table.to(DEV), q_start, seq_lens,
+                               2, 4, q_lens[2] + q_lens[3], nq, nkv, d, window, scale, err)
+    a, b = sum(q_lens[:2]), sum(q_lens[:4])
+    assert torch.equal(out2[a:b], out[a:b]) and float(out2[:a].abs().max()) == 0 and float(out2[b:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("nq,nkv,d,page,window", MMA_CASES)
+def test_attention_decode_mma(ops, err, nq, nkv, d, page, window):
+    dt = torch.bfloat16
+    lens = [1, 255, 256, 257, 1000, 64, 513]
+    q_lens = [1] * len(lens)
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, lens, q_lens, pages=1024)
+    q = torch.cat(qs).reshape(-1, nq * d).to(DEV)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    outs = []
+    for bound in (max(lens), 4096):          # the bound on the lengths (as under a CUDA graph) changes nothing
+        out = torch.zeros_like(q)
+        ops.attention_decode_bf16(q, nq * d, out, kc.to(DEV), vc.to(DEV), table.to(DEV), seq_lens, len(lens), bound,
+                                  nq, nkv, d, window, scale, err)
+        outs.append(out)
+    assert int(err.item()) == 0 and torch.equal(outs[0], outs[1])
+    for s, n in enumerate(lens):
+        want = pl.attention(qs[s].double(), ks[s].double(), vs[s].double(), torch.tensor([n - 1]),
+                            window=window or None, scale=scale)
+        assert rel_err(outs[0][s:s + 1], want) <= tol(dt), (s, n)
+    # a sequence's row does not depend on the batch it is in
+    alone = torch.zeros(1, nq * d, device=DEV, dtype=dt)
+    ops.attention_decode_bf16(q[4:5], nq * d, alone, kc.to(DEV), vc.to(DEV), table[4:5].contiguous().to(DEV),
+                              seq_lens[4:5], 1, 1000, nq, nkv, d, window, scale, err)
+    assert torch.equal(alone[0], outs[0][4])
+
+
+@pytest.mark.parametrize("kind", ["prefill", "decode"])
+def test_mma_attention_finds_one_far_key(ops, err, kind):
+    """One key among a thousand, at a tile's, split's or page's edge, is made to
+    dominate: the output must be its value."""
+    dt = torch.bfloat16
+    nq, nkv, d, page = 8, 2, 64, 16
+    n = 1100
+    m = 1 if kind == "decode" else 5
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, [n], [m], pages=128, seed=9)
+    seq_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
+    q_start = torch.tensor([0, m], dtype=torch.int32, device=DEV)
+    for target in (0, 63, 64, 255, 256, 511, 512, 1023, 1024, n - m - 1, n - m):
+        kc2, qq = kc.clone(), qs[0].clone()
+        pg = int(table[0, target // page])
+        kc2[pg, :, target % page] = 0
+        kc2[pg, :, target % page, 3] = 30.0
+        qq[:, :, 3] = 30.0
+        q = qq.reshape(m, nq * d).to(DEV)
+        out = torch.zeros_like(q)
+        if kind == "decode":
+            ops.attention_decode_bf16(q, nq * d, out, kc2.to(DEV), vc.to(DEV), table.to(DEV), seq_lens, 1, n,
+                                      nq, nkv, d, 0, 1.0, err)
+        else:
+            ops.attention_prefill_bf16(q, nq * d, out, kc2.to(DEV), vc.to(DEV), table.to(DEV), q_start, seq_lens,
+                                       0, 1, m, nq, nkv, d, 0, 1.0, err)
+        want = vs[0][target].repeat_interleave(nq // nkv, dim=0).reshape(1, nq * d).expand(m, -1)
+        assert rel_err(out, want) <= tol(dt), target
