@@ -21,6 +21,7 @@ graph on first use, on a private stream, with no padding rows.
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -110,9 +111,17 @@ class DecodeGraph:
         logits = r.model.forward(self.token_ids, self.ctx, self.rows, r.storage)
         if self.uses >= 2 and r.capture_graphs:
             # capture the same work for the following steps (nothing executes during capture)
+            # No garbage collection while capturing: freeing an older engine's graph in
+            # the middle of a capture is a CUDA call that invalidates the capture.
             torch.cuda.synchronize(r.device)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, pool=r.graph_pool):
-                self.logits = r.model.forward(self.token_ids, self.ctx, self.rows, r.storage)
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g, pool=r.graph_pool, capture_error_mode="thread_local"):
+                    self.logits = r.model.forward(self.token_ids, self.ctx, self.rows, r.storage)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.graph = g
         return logits
