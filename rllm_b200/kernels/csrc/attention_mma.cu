@@ -6,16 +6,18 @@
 //   prefill kernel  rows = (query token, head of the group); 4 warps x 16 rows;
 //                   key tiles of 64, double-buffered with cp.async; online
 //                   softmax in float32 (FlashAttention-2 schedule).
-//   decode kernel   one query token per sequence; CTA = (256-key split, kv
-//                   head, sequence); each of the 4 warps takes 64 keys of the
-//                   split; partial (max, sum, output) go to a workspace and a
-//                   combine kernel merges the splits in order.
+//   decode kernel   one query token per sequence; a warp walks a 128-key chunk
+//                   of one (sequence, kv head) in tiles of 32 with its own
+//                   cp.async pipeline and online softmax; partial (max, sum,
+//                   output) go to a workspace and the last warp of a sequence
+//                   merges its chunks in order.  The token's rotation and
+//                   cache write can be fused in.
 //
 // Contract as in attention_simt.cu: the query at position p of sequence s
 // sees keys max(0, p - window + 1) .. p (window 0: all), read from the cache
 // through the block table; kv head of head h is h / (nq / nkv); scores are
 // scaled by `scale`; softmax and both accumulations are float32.  Key tiles and
-// splits are aligned to absolute positions (multiples of 64 and 256), so a
+// splits are aligned to absolute positions (multiples of 32, 64 and 128), so a
 // row's arithmetic does not depend on the batch around it or on how its
 // sequence was cut into steps.
 //
@@ -26,7 +28,6 @@
 
 #define BM 64          // rows per CTA (prefill)
 #define BN 64          // keys per tile
-#define SPLIT 256      // keys per CTA (decode)
 #define NTHREADS 128
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
@@ -70,41 +71,57 @@ template <int D> __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, 
   return base + row * D + swz<D>(row, chunk) * 8;
 }
 
-// Copy `rows` keys (positions j0 .. j0+rows-1 of the sequence) of one kv head
-// from the paged cache into a tile; keys outside [lo, hi) are zero-filled.
+// Where the keys j0 .. j0+rows-1 of one kv head of a sequence lie in the paged
+// cache: element offset of each key's row (the same in the K and the V cache),
+// or -1 for keys outside [lo, hi) and for pages the sequence does not hold.
+// Called by `rows` threads (one key each); the caller synchronises before the
+// offsets are used.
+__device__ __forceinline__ void kv_row_offsets(long long* rowoff, const int* __restrict__ bt, int j0, int r,
+                                               int lo, int hi, int kvh, int nkv, int page_size, int page_shift,
+                                               int num_pages, int D, int* err) {
+  const int j = j0 + r;
+  long long off = -1;
+  if (j >= lo && j < hi) {
+    const int pi = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+    const int pr = page_shift >= 0 ? (j & (page_size - 1)) : (j - pi * page_size);
+    const int page = bt[pi];
+    if (page < 0 || page >= num_pages) atomicOr(err, 4);
+    else off = (((long long)page * nkv + kvh) * page_size + pr) * D;
+  }
+  rowoff[r] = off;
+}
+
+// Copy `rows` key rows of K and of V from the caches into two swizzled tiles;
+// rows with offset -1 are zero-filled.  A thread keeps one 16-byte column and
+// walks down the rows, rstep at a time; its swizzled column takes two values.
 template <int D>
-__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict__ cache,
-                                             const int* __restrict__ bt, int j0, int rows, int lo, int hi,
-                                             int kvh, int nkv, int page_size, int num_pages, int tid,
-                                             int nthreads, int* err) {
+__device__ __forceinline__ void copy_kv_pair(bf16* tile_k, bf16* tile_v, const bf16* __restrict__ kcache,
+                                             const bf16* __restrict__ vcache, const long long* rowoff,
+                                             int rows, int tid, int nthreads) {
   constexpr int C = D / 8;
-  for (int idx = tid; idx < rows * C; idx += nthreads) {
-    const int r = idx / C, c = idx - r * C;
-    const int j = j0 + r;
-    bool ok = j >= lo && j < hi;
-    const bf16* src = cache;
-    if (ok) {
-      const int page = bt[j / page_size];
-      if (page < 0 || page >= num_pages) {
-        atomicOr(err, 4);
-        ok = false;
-      } else {
-        src = cache + (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * D + c * 8;
-      }
-    }
-    cp_async16(tile_ptr<D>(tile, r, c), src, ok);
+  const int c = tid % C;
+  const int rstep = nthreads / C;          // nthreads is a multiple of C (C <= 16, nthreads >= 32)
+  const bf16* kcol = kcache + c * 8;
+  const bf16* vcol = vcache + c * 8;
+#pragma unroll 4
+  for (int r = tid / C; r < rows; r += rstep) {
+    const long long off = rowoff[r];
+    const bool ok = off >= 0;
+    const int d = r * D + swz<D>(r, c) * 8;
+    cp_async16(tile_k + d, ok ? kcol + off : kcache, ok);
+    cp_async16(tile_v + d, ok ? vcol + off : vcache, ok);
   }
 }
 
-// S[16 x 64] = Q_frag . K_tile^T for one warp; accumulators s[8 n-tiles][4].
-template <int D>
+// S[16 x 8 NT] = Q_frag . K_tile^T for one warp; accumulators s[NT n-tiles][4].
+template <int D, int NT>
 __device__ __forceinline__ void qk_tile(float (*s)[4], const unsigned (*qf)[4], bf16* sK, int lane) {
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+  for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
 #pragma unroll
-    for (int np = 0; np < 4; ++np) {   // two n-tiles (16 keys) per ldmatrix.x4
+    for (int np = 0; np < NT / 2; ++np) {   // two n-tiles (16 keys) per ldmatrix.x4
       const int mat = lane >> 3;
       const int key = np * 16 + (lane & 7) + (mat >> 1) * 8;
       const int chunk = kk * 2 + (mat & 1);
@@ -116,11 +133,11 @@ __device__ __forceinline__ void qk_tile(float (*s)[4], const unsigned (*qf)[4], 
   }
 }
 
-// O[16 x D] += P[16 x 64] . V_tile for one warp; p given as accumulators.
-template <int D>
+// O[16 x D] += P[16 x 8 NT] . V_tile for one warp; p given as accumulators.
+template <int D, int NT>
 __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*p)[4], bf16* sV, int lane) {
 #pragma unroll
-  for (int kk = 0; kk < 4; ++kk) {     // 16 keys per k-step
+  for (int kk = 0; kk < NT / 2; ++kk) {     // 16 keys per k-step
     unsigned a[4];
     a[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
     a[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
@@ -138,46 +155,57 @@ __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*p)[4], bf16
   }
 }
 
-// Online-softmax update of one warp's 16 x 64 score tile.  Thread holds rows
+// Online-softmax update of one warp's 16 x (8 NT) score tile.  Thread holds rows
 // r0 = lane/4 and r0 + 8; positions and key ranges per row are given.
 //   s: raw scores in, probabilities out;  m, l: running max (log2 domain) and sum.
-template <int DT>
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // ex2(-inf) = +0
+  return y;
+}
+
+template <int DT, int NT>
 __device__ __forceinline__ void softmax_tile(float (*s)[4], float (*o)[4], float* m, float* l, int j0,
                                              const int* row_lo, const int* row_hi, float scale_log2,
                                              int lane) {
-  const int col0 = (lane & 3) * 2;
+  const bool whole = j0 >= row_lo[0] && j0 + NT * 8 <= row_hi[0] && j0 >= row_lo[1] && j0 + NT * 8 <= row_hi[1];
+  if (!__all_sync(0xffffffffu, whole)) {     // some key of this tile is masked for some row of the warp
+    const int col0 = (lane & 3) * 2;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int hrow = e >> 1;
+        const int j = j0 + nt * 8 + col0 + (e & 1);
+        if (!(j >= row_lo[hrow] && j < row_hi[hrow])) s[nt][e] = -INFINITY;
+      }
+  }
   float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt)
+  for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int hrow = e >> 1;
-      const int j = j0 + nt * 8 + col0 + (e & 1);
-      const bool vis = j >= row_lo[hrow] && j < row_hi[hrow];
-      const float v = vis ? s[nt][e] * scale_log2 : -INFINITY;
-      s[nt][e] = v;
-      mx[hrow] = fmaxf(mx[hrow], v);
-    }
+    for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
     mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
   }
-  float corr[2], mnew[2];
+  // scores are scaled here (scale_log2 > 0): max of the raw scores times the scale
+  float corr[2], msafe[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    mnew[h] = fmaxf(m[h], mx[h]);
-    corr[h] = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - mnew[h]);
-    if (mnew[h] == -INFINITY) corr[h] = 1.f;   // nothing seen yet: keep zeros
-    m[h] = mnew[h];
+    const float mnew = fmaxf(m[h], mx[h] * scale_log2);
+    msafe[h] = (mnew == -INFINITY) ? 0.f : mnew;        // a row that has seen nothing yet
+    corr[h] = ex2_approx(m[h] - msafe[h]);              // m = -inf gives 0; its sums are 0 anyway
+    m[h] = mnew;
   }
   float sum[2] = {0.f, 0.f};
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt)
+  for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int hrow = e >> 1;
-      const float p = (s[nt][e] == -INFINITY) ? 0.f : exp2f(s[nt][e] - mnew[hrow]);
+      const float p = ex2_approx(fmaf(s[nt][e], scale_log2, -msafe[hrow]));   // a masked score gives 0
       s[nt][e] = p;
       sum[hrow] += p;
     }
@@ -187,10 +215,12 @@ __device__ __forceinline__ void softmax_tile(float (*s)[4], float (*o)[4], float
     sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
     l[h] = l[h] * corr[h] + sum[h];
   }
+  if (!__all_sync(0xffffffffu, corr[0] == 1.f && corr[1] == 1.f)) {   // the max of some row moved
 #pragma unroll
-  for (int nt = 0; nt < DT; ++nt) {
-    o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
-    o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+    for (int nt = 0; nt < DT; ++nt) {
+      o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
+      o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+    }
   }
 }
 
@@ -209,8 +239,10 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   bf16* sQ = (bf16*)smem_raw;          // [BM][D]
   bf16* sK = sQ + BM * D;              // 2 stages [BN][D]
   bf16* sV = sK + 2 * BN * D;          // 2 stages [BN][D]
+  long long* sOff = (long long*)(sV + 2 * BN * D);   // 2 stages [BN] row offsets
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = nq / nkv;
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
   const int bq = BM / g;               // query tokens per tile (rows beyond bq * g stay idle)
   const int kvh = blockIdx.y;
   // which (sequence, tile) is this CTA?
@@ -263,8 +295,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     }
   }
 
-  load_kv_tile<D>(sK, kcache, bt, tile_lo * BN, BN, kmin, kend, kvh, nkv, page_size, num_pages, tid, NTHREADS, err);
-  load_kv_tile<D>(sV, vcache, bt, tile_lo * BN, BN, kmin, kend, kvh, nkv, page_size, num_pages, tid, NTHREADS, err);
+  if (tid < BN) kv_row_offsets(sOff, bt, tile_lo * BN, tid, kmin, kend, kvh, nkv, page_size, page_shift, num_pages, D, err);
+  __syncthreads();
+  copy_kv_pair<D>(sK, sV, kcache, vcache, sOff, BN, tid, NTHREADS);
   cp_async_commit();
 
   cp_async_wait<1>();      // Q has landed
@@ -284,22 +317,22 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 
   for (int kt = tile_lo; kt < tile_hi; ++kt) {
     const int stage = (kt - tile_lo) & 1;
-    if (kt + 1 < tile_hi) {
-      bf16* nK = sK + (stage ^ 1) * BN * D;
-      bf16* nV = sV + (stage ^ 1) * BN * D;
-      load_kv_tile<D>(nK, kcache, bt, (kt + 1) * BN, BN, kmin, kend, kvh, nkv, page_size, num_pages, tid, NTHREADS, err);
-      load_kv_tile<D>(nV, vcache, bt, (kt + 1) * BN, BN, kmin, kend, kvh, nkv, page_size, num_pages, tid, NTHREADS, err);
+    const bool more = kt + 1 < tile_hi;
+    if (more && tid < BN)
+      kv_row_offsets(sOff + (stage ^ 1) * BN, bt, (kt + 1) * BN, tid, kmin, kend, kvh, nkv, page_size, page_shift,
+                     num_pages, D, err);
+    cp_async_wait<0>();
+    __syncthreads();       // this stage's K and V are in; the next stage's offsets are published
+    if (more) {            // the other stage was last read before the barrier that ended the previous iteration
+      copy_kv_pair<D>(sK + (stage ^ 1) * BN * D, sV + (stage ^ 1) * BN * D, kcache, vcache,
+                      sOff + (stage ^ 1) * BN, BN, tid, NTHREADS);
       cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
     }
-    __syncthreads();
     float sc[8][4];
-    qk_tile<D>(sc, qf, sK + stage * BN * D, lane);
-    softmax_tile<D / 8>(sc, o, m, l, kt * BN, row_lo, row_hi, scale_log2, lane);
-    pv_tile<D>(o, sc, sV + stage * BN * D, lane);
-    __syncthreads();       // the next iteration overwrites the other stage, which is this one's successor
+    qk_tile<D, 8>(sc, qf, sK + stage * BN * D, lane);
+    softmax_tile<D / 8, 8>(sc, o, m, l, kt * BN, row_lo, row_hi, scale_log2, lane);
+    pv_tile<D, 8>(o, sc, sV + stage * BN * D, lane);
+    __syncthreads();
   }
 
   // epilogue: O / l
@@ -319,61 +352,107 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 }
 
 // ---------------------------------------------------------------------------
-// decode: one query token per sequence, keys split over CTAs and warps
-// workspace per (sequence, head, split): D floats of unnormalised output, then
-// per (sequence, head, split) max (log2 domain) and sum.
+// decode: one query token per sequence.  The keys of a (sequence, kv head) are
+// cut into chunks of 128 at absolute positions; one warp takes one chunk and
+// walks it in tiles of 32 keys with its own cp.async pipeline and an online
+// softmax in registers.  Warps are independent; a CTA is just 1, 2 or 4 of
+// them.  Every chunk leaves its partial (max, sum, output) in the workspace; the
+// CTA that finds itself last for its (sequence, kv head) merges all chunks in
+// order, so the result does not depend on the CTA shape, the pipeline depth or
+// the batch.  Optionally fused in: the rotation of the token's q and k
+// (rotate-half over the first rotary_dim dims, angle position * f_i reduced in
+// float64, cosine and sine in float32) and the write of its k and v into their
+// cache page.
+// Workspace (floats): partial outputs [S, nq, max_chunks, D], then (max, sum)
+// pairs [S, nq, max_chunks, 2].  Counters: int [S * nkv], zero before the call;
+// the kernel leaves them zero.
 // ---------------------------------------------------------------------------
-template <int D>
-__global__ void __launch_bounds__(NTHREADS)
-attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ kcache,
-                        const bf16* __restrict__ vcache, const int* __restrict__ block_table,
-                        int max_blocks, const int* __restrict__ seq_lens, int nq, int nkv, int page_size,
-                        int num_pages, int window, float scale_log2, int max_splits,
-                        float* __restrict__ ws_o, float* __restrict__ ws_ml, int* __restrict__ err) {
+#define DEC_BN 32        // keys per tile
+#define DEC_TILES 4      // tiles per chunk
+#define CHUNK (DEC_BN * DEC_TILES)
+
+template <int D, int STAGES> __host__ __device__ constexpr int dec_warp_smem() {
+  return STAGES * 2 * DEC_BN * D * 2 + DEC_BN * 8 + (D < 32 ? 32 : D) * 4;
+}
+
+template <int D, int STAGES>
+__global__ void __launch_bounds__(128)
+attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
+                        bf16* __restrict__ kcache, bf16* __restrict__ vcache,
+                        const int* __restrict__ block_table, int max_blocks,
+                        const int* __restrict__ seq_lens, int nq, int nkv, int page_size, int num_pages,
+                        int window, float scale_log2, int max_chunks, const double* __restrict__ inv_freq,
+                        int rotary_dim, int write_kv, float* __restrict__ ws_o, float* __restrict__ ws_ml,
+                        int* __restrict__ counters, int* __restrict__ err) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  bf16* sQ = (bf16*)smem_raw;                        // [16][D]
-  bf16* sK = sQ + 16 * D + warp * 2 * BN * D;        // this warp's [BN][D]
-  bf16* sV = sK + BN * D;
-  float* sO = (float*)(sQ + 16 * D + 4 * 2 * BN * D);   // [4 warps][16][D] partial outputs
-  float* sML = sO + 4 * 16 * D;                          // [4][16][2]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned char* mine = smem_raw + (size_t)warp * dec_warp_smem<D, STAGES>();
+  bf16* sW = (bf16*)mine;                                          // STAGES x (K [32][D], V [32][D])
+  bf16* sQ = sW + (STAGES - 1) * 2 * DEC_BN * D;                   // [16][D], over the last stage's K tile: that
+                                                                   // stage is first filled after Q is in registers
+  long long* sOff = (long long*)(sW + STAGES * 2 * DEC_BN * D);    // [32] row offsets
+  float* sCS = (float*)(sOff + DEC_BN);                            // cos[D/2], sin[D/2]
   const int g = nq / nkv;
-  const int split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+  const int chunk = blockIdx.x * (blockDim.x >> 5) + warp, kvh = blockIdx.y, s = blockIdx.z;
   const int len = seq_lens[s];
   const int pos = len - 1;
   const int kmin = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int c0 = split * SPLIT;
-  if (c0 >= len || c0 + SPLIT <= kmin) return;      // this split holds no visible key
+  const int w0 = chunk * CHUNK;
+  const int nwarps = blockDim.x >> 5;
+  {  // a CTA none of whose chunks holds a visible key has nothing to do
+    const int first = blockIdx.x * nwarps * CHUNK;
+    if (first >= len || first + nwarps * CHUNK <= kmin) return;
+  }
+  const bool active = w0 < len && w0 + CHUNK > kmin;
   const int* bt = block_table + (size_t)s * max_blocks;
+  const int half = rotary_dim >> 1;
+  bf16* qrow = qkv + (size_t)s * q_stride;
+  // keys to read from the cache: with write_kv the token's own key comes from qkv, not from the cache
+  const int read_hi = write_kv ? pos : len;
+  const int t_lo = active ? (kmin > w0 ? (kmin - w0) / DEC_BN : 0) : 0;
+  const int t_hi = active ? min(DEC_TILES, (len - w0 + DEC_BN - 1) / DEC_BN) : 0;
 
-  // Q rows = heads of the group, rows >= g zero
-  {
-    constexpr int C = D / 8;
-    for (int idx = tid; idx < 16 * C; idx += NTHREADS) {
-      const int r = idx / C, c = idx - r * C;
-      const bool ok = r < g;
-      const bf16* src = ok ? q + (size_t)s * q_stride + (size_t)(kvh * g + r) * D + c * 8 : q;
-      cp_async16(tile_ptr<D>(sQ, r, c), src, ok);
+  auto issue = [&](int t) {
+    if (t < t_hi) {
+      bf16* st = sW + ((t - t_lo) % STAGES) * 2 * DEC_BN * D;
+      __syncwarp();
+      kv_row_offsets(sOff, bt, w0 + t * DEC_BN, lane, kmin, read_hi, kvh, nkv, page_size, page_shift, num_pages, D, err);
+      __syncwarp();
+      copy_kv_pair<D>(st, st + DEC_BN * D, kcache, vcache, sOff, DEC_BN, lane, 32);
     }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) issue(t_lo + i);
+
+  for (int i = lane; i < half; i += 32) rope_cos_sin(pos, inv_freq[i], &sCS[i], &sCS[half + i]);
+  __syncwarp();
+  // Q rows = heads of the group, rows >= g zero: 16-byte loads first, then the rotation in
+  // shared memory (a lane rotates the pairs (i, i + half) it owns)
+  for (int idx = lane; idx < 16 * (D / 8); idx += 32) {
+    const int r = idx / (D / 8), c = idx % (D / 8);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < g) v = *(const uint4*)(qrow + (size_t)(kvh * g + r) * D + c * 8);
+    *(uint4*)tile_ptr<D>(sQ, r, c) = v;
   }
-  const int j0 = c0 + warp * BN;
-  const bool active = j0 < len && j0 + BN > kmin;
-  if (active) {
-    load_kv_tile<D>(sK, kcache, bt, j0, BN, kmin, len, kvh, nkv, page_size, num_pages, lane, 32, err);
+  __syncwarp();
+  for (int idx = lane; idx < g * half; idx += 32) {
+    const int r = idx / half, i = idx - r * half;
+    bf16* pa = tile_ptr<D>(sQ, r, i >> 3) + (i & 7);
+    bf16* pb = tile_ptr<D>(sQ, r, (i + half) >> 3) + ((i + half) & 7);
+    const float a = to_f32(*pa), b = to_f32(*pb);
+    const float cs = sCS[i], sn = sCS[half + i];
+    *pa = from_f32<bf16>(a * cs - b * sn);
+    *pb = from_f32<bf16>(b * cs + a * sn);
   }
-  cp_async_commit();
-  if (active) {
-    load_kv_tile<D>(sV, vcache, bt, j0, BN, kmin, len, kvh, nkv, page_size, num_pages, lane, 32, err);
-  }
-  cp_async_commit();
-  cp_async_wait<1>();
-  __syncthreads();                                   // Q (all threads) and this warp's K are in
+  __syncwarp();
 
   float o[D / 8][4];
 #pragma unroll
   for (int nt = 0; nt < D / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-  if (active) {
+  {
     unsigned qf[D / 16][4];
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk)
@@ -385,73 +464,104 @@ attention_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __
       row_lo[h] = kmin;
       row_hi[h] = r < g ? len : 0;
     }
-    float sc[8][4];
-    qk_tile<D>(sc, qf, sK, lane);
-    softmax_tile<D / 8>(sc, o, m, l, j0, row_lo, row_hi, scale_log2, lane);
-    cp_async_wait<0>();
-    __syncwarp();
-    pv_tile<D>(o, sc, sV, lane);
-  } else {
-    cp_async_wait<0>();
+    for (int t = t_lo; t < t_hi; ++t) {
+      bf16* sK = sW + ((t - t_lo) % STAGES) * 2 * DEC_BN * D;
+      bf16* sV = sK + DEC_BN * D;
+      issue(t + STAGES - 1);
+      cp_async_wait<STAGES - 1>();
+      __syncwarp();
+      const int j0 = w0 + t * DEC_BN;
+      if (write_kv && pos >= j0 && pos < j0 + DEC_BN) {
+        // the token's own k (rotated) and v: into the cache page, and into this tile
+        const int pi = page_shift >= 0 ? (pos >> page_shift) : (pos / page_size);
+        const int page = bt[pi];
+        const bool okp = page >= 0 && page < num_pages;
+        if (!okp && lane == 0) atomicOr(err, 2);
+        const long long off = (((long long)(okp ? page : 0) * nkv + kvh) * page_size + (pos - pi * page_size)) * D;
+        const bf16* kx = qrow + (size_t)(nq + kvh) * D;
+        const bf16* vx = qrow + (size_t)(nq + nkv + kvh) * D;
+        const int r = pos - j0;
+        for (int i = lane; i < D; i += 32) {
+          float kv = to_f32(kx[i]);
+          if (i < half) kv = kv * sCS[i] - to_f32(kx[i + half]) * sCS[half + i];
+          else if (i < rotary_dim) kv = kv * sCS[i - half] + to_f32(kx[i - half]) * sCS[i];
+          const bf16 kb = from_f32<bf16>(kv), vb = vx[i];
+          tile_ptr<D>(sK, r, i >> 3)[i & 7] = kb;
+          tile_ptr<D>(sV, r, i >> 3)[i & 7] = vb;
+          if (okp) { kcache[off + i] = kb; vcache[off + i] = vb; }
+        }
+        __syncwarp();
+      }
+      float sc[DEC_BN / 8][4];
+      qk_tile<D, DEC_BN / 8>(sc, qf, sK, lane);
+      softmax_tile<D / 8, DEC_BN / 8>(sc, o, m, l, j0, row_lo, row_hi, scale_log2, lane);
+      pv_tile<D, DEC_BN / 8>(o, sc, sV, lane);
+    }
   }
-  // hand the warp's partial to shared memory
+  cp_async_wait<0>();
+  // this chunk's partial: rows < g, straight from the accumulators
+  if (active) {
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int r = (lane >> 2) + h * 8;
-    float* dst = sO + ((size_t)warp * 16 + r) * D + (lane & 3) * 2;
+    for (int h = 0; h < 2; ++h) {
+      const int r = (lane >> 2) + h * 8;
+      if (r >= g) continue;
+      const size_t slot = ((size_t)s * nq + kvh * g + r) * max_chunks + chunk;
+      float* dst = ws_o + slot * D + (lane & 3) * 2;
 #pragma unroll
-    for (int nt = 0; nt < D / 8; ++nt) {
-      dst[nt * 8] = o[nt][h * 2];
-      dst[nt * 8 + 1] = o[nt][h * 2 + 1];
+      for (int nt = 0; nt < D / 8; ++nt) *(float2*)(dst + nt * 8) = make_float2(o[nt][h * 2], o[nt][h * 2 + 1]);
+      if ((lane & 3) == 0) *(float2*)(ws_ml + slot * 2) = make_float2(m[h], l[h]);
     }
-    if ((lane & 3) == 0) {
-      sML[(warp * 16 + r) * 2] = m[h];
-      sML[(warp * 16 + r) * 2 + 1] = l[h];
-    }
+  }
+  // the last CTA of this (sequence, kv head) merges all chunks, in order
+  const int ch_lo = kmin / CHUNK, ch_hi = (len + CHUNK - 1) / CHUNK;
+  const int ncta = (ch_hi - 1) / nwarps - ch_lo / nwarps + 1;
+  __shared__ int s_last;
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(&counters[s * nkv + kvh], 1);
+    s_last = (done == ncta - 1);
+    if (s_last) counters[s * nkv + kvh] = 0;
   }
   __syncthreads();
-  // merge the four warps in order and write this split's partial
-  for (int idx = tid; idx < g * D; idx += NTHREADS) {
-    const int r = idx / D, dcol = idx - r * D;
+  if (!s_last) return;
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  float* sRow = (float*)smem_raw;                       // warp 0's Q tile: [16] common max per row
+  for (int r = tid; r < g; r += nthr) {
+    const size_t base = ((size_t)s * nq + kvh * g + r) * max_chunks;
     float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sML[(w * 16 + r) * 2]);
-    float acc = 0.f, ll = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float mw = sML[(w * 16 + r) * 2];
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
-      acc += sO[((size_t)w * 16 + r) * D + dcol] * f;
-      ll += sML[(w * 16 + r) * 2 + 1] * f;
-    }
-    const size_t slot = ((size_t)s * nq + kvh * g + r) * max_splits + split;
-    ws_o[slot * D + dcol] = acc;
-    if (dcol == 0) { ws_ml[slot * 2] = mm; ws_ml[slot * 2 + 1] = ll; }
+#pragma unroll 8
+    for (int c = ch_lo; c < ch_hi; ++c) mm = fmaxf(mm, __ldcg(&ws_ml[(base + c) * 2]));
+    sRow[r] = mm;
   }
-}
-
-// out[s, h, :] = sum over the sequence's splits, in order, rescaled to the common max
-template <int D>
-__global__ void attention_combine_kernel(bf16* __restrict__ out, const float* __restrict__ ws_o,
-                                         const float* __restrict__ ws_ml, const int* __restrict__ seq_lens,
-                                         int nq, int window, int max_splits) {
-  const int h = blockIdx.x, s = blockIdx.y;
-  const int len = seq_lens[s];
-  const int pos = len - 1;
-  const int kmin = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int sp_lo = kmin / SPLIT, sp_hi = (len + SPLIT - 1) / SPLIT;
-  const size_t base = ((size_t)s * nq + h) * max_splits;
-  float mm = -INFINITY;
-  for (int sp = sp_lo; sp < sp_hi; ++sp) mm = fmaxf(mm, ws_ml[(base + sp) * 2]);
-  for (int dcol = threadIdx.x; dcol < D; dcol += blockDim.x) {
+  __syncthreads();
+  // Output by output; the loads of 16 chunks are issued together (indices are clamped and
+  // the factor of a chunk past the end is 0, so that no load waits for a branch).
+  for (int idx = tid; idx < g * D; idx += nthr) {
+    const int r = idx / D, dcol = idx - r * D;
+    const float mm = sRow[r];
+    const size_t base = ((size_t)s * nq + kvh * g + r) * max_chunks;
     float acc = 0.f, ll = 0.f;
-    for (int sp = sp_lo; sp < sp_hi; ++sp) {
-      const float mw = ws_ml[(base + sp) * 2];
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
-      acc += ws_o[(base + sp) * D + dcol] * f;
-      ll += ws_ml[(base + sp) * 2 + 1] * f;
+    for (int c0 = ch_lo; c0 < ch_hi; c0 += 16) {
+      float v[16], f[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int c = min(c0 + j, ch_hi - 1);
+        v[j] = __ldcg(&ws_o[(base + c) * D + dcol]);
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int c = min(c0 + j, ch_hi - 1);
+        const float2 ml = __ldcg((const float2*)(ws_ml + (base + c) * 2));
+        const float fj = (c0 + j < ch_hi && ml.x != -INFINITY) ? exp2f(ml.x - mm) : 0.f;
+        f[j] = fj;
+        ll += ml.y * fj;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc += v[j] * f[j];
     }
-    out[((size_t)s * nq + h) * D + dcol] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    out[((size_t)s * nq + kvh * g + r) * D + dcol] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
   }
 }
 
@@ -464,11 +574,7 @@ static bool mma_supported(int nq, int nkv, int d) {
   return true;
 }
 
-template <int D> static size_t prefill_smem() { return (size_t)(BM + 4 * BN) * D * sizeof(bf16); }
-template <int D> static size_t decode_smem() {
-  return (size_t)(16 + 8 * BN) * D * sizeof(bf16) + (size_t)4 * 16 * D * sizeof(float) + 4 * 16 * 2 * sizeof(float);
-}
-
+template <int D> static size_t prefill_smem() { return (size_t)(BM + 4 * BN) * D * sizeof(bf16) + 2 * BN * sizeof(long long); }
 template <int D>
 static int launch_prefill(const bf16* q, int q_stride, bf16* out, const bf16* kc, const bf16* vc,
                           const int* bt, int max_blocks, const int* q_start, const int* seq_lens,
@@ -500,7 +606,8 @@ RLLM_EXPORT int rllm_attention_prefill_bf16(const void* q, int q_stride, void* o
                                             int num_pages, int window, float scale, int* err,
                                             cudaStream_t stream) {
   if (seq_end <= seq_begin || num_tokens <= 0) return 0;
-  if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0 || q_stride % 8) return RLLM_E_BADARG;
+  if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0 || q_stride % 8 || !(scale > 0.f))
+    return RLLM_E_BADARG;
   if (!mma_supported(nq, nkv, d) || nq / nkv > BM) return RLLM_E_UNSUPPORTED;
 #define RLLM_PREFILL(DD) return launch_prefill<DD>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache, \
       (const bf16*)vcache, block_table, max_blocks, q_start, seq_lens, seq_begin, seq_end, num_tokens, nq, nkv, \
@@ -516,52 +623,72 @@ RLLM_EXPORT int rllm_attention_prefill_bf16(const void* q, int q_stride, void* o
 
 // floats of workspace that a decode call with these sizes needs
 RLLM_EXPORT long long rllm_attention_decode_workspace(int num_seqs, int nq, int d, int max_seq_len) {
-  const long long splits = (max_seq_len + SPLIT - 1) / SPLIT;
-  return (long long)num_seqs * nq * splits * (d + 2);
+  const long long chunks = (max_seq_len + CHUNK - 1) / CHUNK;
+  return (long long)num_seqs * nq * chunks * (d + 2);
 }
 
-template <int D>
-static int launch_decode(const bf16* q, int q_stride, bf16* out, const bf16* kc, const bf16* vc, const int* bt,
-                         int max_blocks, const int* seq_lens, int num_seqs, int nq, int nkv, int page_size,
-                         int num_pages, int window, float scale, int max_splits, float* ws, int* err,
-                         cudaStream_t stream) {
-  const size_t smem = decode_smem<D>();
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+template <int D, int STAGES>
+static int launch_decode_cfg(int warps, bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc, const int* bt,
+                             int max_blocks, const int* seq_lens, int num_seqs, int nq, int nkv, int page_size,
+                             int num_pages, int window, float scale, int max_chunks, const double* inv_freq,
+                             int rotary_dim, int write_kv, float* ws, int* counters, int* err,
+                             cudaStream_t stream) {
+  const size_t smem = (size_t)warps * dec_warp_smem<D, STAGES>();
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured = smem;
   }
   float* ws_o = ws;
-  float* ws_ml = ws + (size_t)num_seqs * nq * max_splits * D;
-  dim3 grid(max_splits, nkv, num_seqs);
-  attention_decode_kernel<D><<<grid, NTHREADS, smem, stream>>>(q, q_stride, kc, vc, bt, max_blocks, seq_lens, nq, nkv,
-      page_size, num_pages, window, scale * 1.4426950408889634f, max_splits, ws_o, ws_ml, err);
-  RLLM_LAUNCH_CHECK();
-  dim3 cgrid(nq, num_seqs);
-  attention_combine_kernel<D><<<cgrid, D < 32 ? 32 : D, 0, stream>>>(out, ws_o, ws_ml, seq_lens, nq, window, max_splits);
+  float* ws_ml = ws + (size_t)num_seqs * nq * max_chunks * D;
+  dim3 grid((max_chunks + warps - 1) / warps, nkv, num_seqs);
+  attention_decode_kernel<D, STAGES><<<grid, 32 * warps, smem, stream>>>(qkv, q_stride, out, kc, vc, bt, max_blocks,
+      seq_lens, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, max_chunks, inv_freq, rotary_dim,
+      write_kv, ws_o, ws_ml, counters, err);
   RLLM_LAUNCH_CHECK();
   return 0;
 }
 
-// Decode: sequences 0 .. num_seqs-1 with one query token each (row s of q and
-// out).  max_seq_len bounds every seq_lens[s]; workspace holds
-// rllm_attention_decode_workspace(...) floats.
-RLLM_EXPORT int rllm_attention_decode_bf16(const void* q, int q_stride, void* out, const void* kcache,
-                                           const void* vcache, const int* block_table, int max_blocks,
-                                           const int* seq_lens, int num_seqs, int max_seq_len, int nq, int nkv,
-                                           int d, int page_size, int num_pages, int window, float scale,
-                                           float* workspace, int* err, cudaStream_t stream) {
+// Few chunks in all (small batch, short context): few warps per CTA and a deep
+// pipeline, to have enough loads in flight.  Many chunks: 4 warps per CTA and a
+// shallower pipeline, to keep more warps resident.  The choice changes no result.
+template <int D>
+static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc, const int* bt, int max_blocks,
+                         const int* seq_lens, int num_seqs, int nq, int nkv, int page_size, int num_pages,
+                         int window, float scale, int max_chunks, const double* inv_freq, int rotary_dim,
+                         int write_kv, float* ws, int* counters, int* err, cudaStream_t stream) {
+  const long long total = (long long)max_chunks * nkv * num_seqs;
+#define RLLM_DEC_ARGS qkv, q_stride, out, kc, vc, bt, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, \
+      window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream
+  if (total <= 148 * 6) return launch_decode_cfg<D, 4>(D >= 128 ? 1 : 2, RLLM_DEC_ARGS);
+  return launch_decode_cfg<D, 2>(4, RLLM_DEC_ARGS);
+}
+
+// Decode: sequences 0 .. num_seqs-1 with one query token each.  Row s of qkv
+// holds the token's q heads (and, with write_kv, its k and v heads behind them);
+// row s of out receives the result.  rotary_dim > 0 rotates q (and k) here with
+// the float64 frequency table inv_freq; write_kv stores the token's k and v into
+// the cache.  max_seq_len bounds every seq_lens[s]; workspace holds
+// rllm_attention_decode_workspace(...) floats; counters holds num_seqs * nkv
+// ints that are zero before the call (the kernel leaves them zero).
+RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, void* kcache, void* vcache,
+                                           const int* block_table, int max_blocks, const int* seq_lens,
+                                           int num_seqs, int max_seq_len, int nq, int nkv, int d, int page_size,
+                                           int num_pages, int window, float scale, const double* inv_freq,
+                                           int rotary_dim, int write_kv, float* workspace, int* counters,
+                                           int* err, cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
   if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0 || q_stride % 8 || max_seq_len <= 0 ||
-      !workspace)
+      !workspace || !counters || !(scale > 0.f) || rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim && !inv_freq))
     return RLLM_E_BADARG;
   if (!mma_supported(nq, nkv, d) || nq / nkv > 16) return RLLM_E_UNSUPPORTED;
-  const int max_splits = (max_seq_len + SPLIT - 1) / SPLIT;
-  if (max_splits > 65535 || num_seqs > 65535) return RLLM_E_UNSUPPORTED;
-#define RLLM_DECODE(DD) return launch_decode<DD>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache, \
-      (const bf16*)vcache, block_table, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, window, \
-      scale, max_splits, workspace, err, stream)
+  const int max_splits = (max_seq_len + CHUNK - 1) / CHUNK;
+  if (max_splits > 65535 * 4 || num_seqs > 65535) return RLLM_E_UNSUPPORTED;
+#define RLLM_DECODE(DD) return launch_decode<DD>((bf16*)qkv, q_stride, (bf16*)out, (bf16*)kcache, (bf16*)vcache, \
+      block_table, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, window, scale, max_splits, \
+      inv_freq, rotary_dim, write_kv, workspace, counters, err, stream)
   switch (d) {
     case 16: RLLM_DECODE(16);
     case 32: RLLM_DECODE(32);

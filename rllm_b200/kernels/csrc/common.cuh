@@ -56,6 +56,17 @@ __device__ __forceinline__ float block_sum(float v, float* smem32) {
   return t;
 }
 
+// cos and sin of position * inv_freq for the bfloat16 path: the angle is reduced
+// mod 2 pi in float64 (exact to ~1e-11 for positions up to 2^20), then cosine
+// and sine are taken in float32 (absolute error ~2e-7).  The float32 path of the
+// model uses float64 sincos instead.
+__device__ __forceinline__ void rope_cos_sin(int pos, double inv_freq, float* c, float* s) {
+  const double a = (double)pos * inv_freq;
+  const double n = rint(a * 0.15915494309189535);
+  const double r = fma(-n, 6.283185307179586, a) - n * 2.4492935982947064e-16;
+  sincosf((float)r, s, c);
+}
+
 // Dispatch helpers ---------------------------------------------------------
 #define RLLM_DISPATCH_DTYPE(code, T, ...)                    \
   do {                                                       \

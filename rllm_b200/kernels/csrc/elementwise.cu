@@ -131,9 +131,11 @@ RLLM_EXPORT int rllm_residual_add(float* x, const void* delta, int act_dtype, lo
 // (crates/rllm-model/src/rope.rs:57-82): for i < rd/2
 //   out[i]        = x[i] * cos(p f_i) - x[i + rd/2] * sin(p f_i)
 //   out[i + rd/2] = x[i + rd/2] * cos(p f_i) + x[i] * sin(p f_i)
-// The angle p * f_i and its cosine and sine are computed in float64 and then
-// rounded to float32, like the reference's table (rope.rs:13-31); the
-// rotation is float32.  rotary_dim 0 rotates nothing.
+// float32 activations: the angle p * f_i and its cosine and sine are computed in
+// float64 and then rounded to float32, like the reference's table
+// (rope.rs:13-31).  bfloat16 activations: the angle is reduced mod 2 pi in
+// float64 and cosine and sine are float32.  The rotation itself is float32.
+// rotary_dim 0 rotates nothing.
 // Cache layout per layer: K and V each [num_pages, nkv, page_size, d]; token
 // at position p of sequence s lies in page block_table[s][p / page_size] at
 // row p % page_size (slot rule of crates/rllm-worker/src/model_runner.rs:806-826).
@@ -151,11 +153,15 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   const int pos = positions[t];
   const int half = rotary_dim >> 1;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
-    double a = (double)pos * inv_freq[i];
-    double s, c;
-    sincos(a, &s, &c);
-    cs[i] = (float)c;
-    cs[half + i] = (float)s;
+    if (sizeof(T) == 4) {            // the true 32-bit path: float64 cosine and sine, rounded once
+      double a = (double)pos * inv_freq[i];
+      double s, c;
+      sincos(a, &s, &c);
+      cs[i] = (float)c;
+      cs[half + i] = (float)s;
+    } else {
+      rope_cos_sin(pos, inv_freq[i], &cs[i], &cs[half + i]);
+    }
   }
   __syncthreads();
   T* row = qkv + (size_t)t * (nq + 2 * nkv) * d;

@@ -229,27 +229,49 @@ def attention_prefill_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, kc
                                            _stream()), "attention_prefill_bf16")
 
 
-def attention_decode_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
+_decode_counters = {}
+
+
+def _counters_for(device: torch.device, n: int) -> torch.Tensor:
+    """Zeroed per-device counters of the decode kernel's split merge; the kernel
+    leaves them zero, so one buffer serves every call (also under CUDA graphs)."""
+    buf = _decode_counters.get(device)
+    if buf is None or buf.numel() < n:
+        buf = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
+        _decode_counters[device] = buf
+    return buf
+
+
+def attention_decode_bf16(qkv: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
                           vcache: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
                           num_seqs: int, max_seq_len: int, nq: int, nkv: int, d: int, window: int,
-                          scale: float, err: torch.Tensor, workspace: Optional[torch.Tensor] = None) -> None:
+                          scale: float, err: torch.Tensor, workspace: Optional[torch.Tensor] = None,
+                          inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0,
+                          write_kv: bool = False) -> None:
     """Split-KV tensor-core attention of sequences 0 .. num_seqs-1, one query token
-    each (row s of q and out).  ``max_seq_len`` bounds every length.  The
-    workspace (float32, ``attention_decode_workspace`` elements) holds the
-    splits' partial results; it is allocated here if not given."""
+    each: row s of ``qkv`` holds the token's q heads (and behind them its k and v
+    heads if ``write_kv``), row s of ``out`` gets the result.  ``rotary_dim`` > 0
+    rotates q (and the new k) in the kernel; ``write_kv`` stores the token's k and
+    v into the cache in the kernel.  ``max_seq_len`` bounds every length.  The
+    workspace (float32, ``attention_decode_workspace`` elements) holds the splits'
+    partial results; it is allocated here if not given."""
     lib = build.load_library("attention_mma")
     _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
-    assert q.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
+    assert qkv.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
     need = attention_decode_workspace(num_seqs, nq, d, max_seq_len)
     if workspace is None:
-        workspace = torch.empty(need, dtype=torch.float32, device=q.device)
+        workspace = torch.empty(need, dtype=torch.float32, device=qkv.device)
     assert workspace.dtype is torch.float32 and workspace.numel() >= need
-    _check(lib.rllm_attention_decode_bf16(_ptr(q), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
+    if rotary_dim:
+        assert inv_freq is not None and inv_freq.dtype is torch.float64 and inv_freq.numel() == rotary_dim // 2
+    counters = _counters_for(qkv.device, num_seqs * nkv)
+    _check(lib.rllm_attention_decode_bf16(_ptr(qkv), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
                                           _ptr(block_table), c_int(block_table.shape[1]), _ptr(seq_lens),
                                           c_int(num_seqs), c_int(max_seq_len), c_int(nq), c_int(nkv), c_int(d),
                                           c_int(kcache.shape[2]), c_int(kcache.shape[0]), c_int(window),
-                                          c_float(scale), _ptr(workspace), _ptr(err), _stream()),
-           "attention_decode_bf16")
+                                          c_float(scale), _ptr(inv_freq), c_int(rotary_dim),
+                                          c_int(1 if write_kv else 0), _ptr(workspace), _ptr(counters),
+                                          _ptr(err), _stream()), "attention_decode_bf16")
 
 
 def attention_decode_workspace(num_seqs: int, nq: int, d: int, max_seq_len: int) -> int:
@@ -262,26 +284,11 @@ def mma_attention_takes(nq: int, nkv: int, d: int) -> bool:
     return d in (16, 32, 64, 128) and nq % nkv == 0 and nq // nkv <= 16
 
 
-def paged_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
-                    vcache: torch.Tensor, block_table: torch.Tensor, ctx, nq: int, nkv: int, d: int,
-                    window: int, scale: float) -> None:
-    """Attention of all query tokens of a step over the paged cache (``ctx`` is a
-    StepContext).  bfloat16 with a head size the tensor-core kernels take: the
-    sequences with one token go to the split-KV decode kernel, the others to the
-    prefill kernel.  float32, and other head sizes: the CUDA-core kernel."""
+def use_mma_attention(dtype: torch.dtype, nq: int, nkv: int, d: int) -> bool:
+    """bfloat16 with a head size the tensor-core attention kernels take; other
+    cases (float32, other head sizes) go to the CUDA-core kernel."""
     import os
-    if q.dtype is torch.bfloat16 and mma_attention_takes(nq, nkv, d) and os.environ.get("RLLM_ATTENTION") != "simt":
-        nd, S, T = ctx.num_decode, ctx.num_seqs, ctx.num_tokens
-        if nd > 0:
-            bound = max(ctx.seq_lens_host[:nd])
-            attention_decode_bf16(q, q_stride, out, kcache, vcache, block_table, ctx.seq_lens, nd, bound,
-                                  nq, nkv, d, window, scale, ctx.err)
-        if S > nd:
-            attention_prefill_bf16(q, q_stride, out, kcache, vcache, block_table, ctx.q_start, ctx.seq_lens,
-                                   nd, S, T - nd, nq, nkv, d, window, scale, ctx.err)
-        return
-    attention_simt(q, q_stride, out, kcache, vcache, block_table, ctx.positions, ctx.token_seq,
-                   nq, nkv, d, window, scale, ctx.err)
+    return dtype is torch.bfloat16 and mma_attention_takes(nq, nkv, d) and os.environ.get("RLLM_ATTENTION") != "simt"
 
 
 def decode_advance(token_ids: torch.Tensor, positions: torch.Tensor, seq_lens: torch.Tensor,

@@ -95,9 +95,24 @@ class PagedAttention(Mixer):
             self.position.apply(q, k, ctx.positions)
             fused = (None, 0)
         inv_freq, rd = fused
-        ops.rope_kv_write(qkv, ctx.positions, ctx.token_seq, inv_freq, rd, table, cache.k, cache.v,
-                          self.nq, nkv_here, self.d, ctx.err, write_kv=writes)
         out = torch.empty((T, self.nq * self.d), dtype=x.dtype, device=x.device)
-        ops.paged_attention(qkv, qkv.shape[1], out, cache.k, cache.v, table, ctx, self.nq, self.nkv,
-                            self.d, int(self.window or 0), self.scale)
+        window = int(self.window or 0)
+        stride = qkv.shape[1]
+        use_mma = ops.use_mma_attention(x.dtype, self.nq, self.nkv, self.d)
+        # sequences with one token: rotation, cache write and attention in one kernel
+        nd = ctx.num_decode if use_mma else 0
+        if nd:
+            ops.attention_decode_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.seq_lens, nd,
+                                      max(ctx.seq_lens_host[:nd]), self.nq, self.nkv, self.d, window, self.scale,
+                                      ctx.err, inv_freq=inv_freq, rotary_dim=rd, write_kv=writes)
+        if T > nd:
+            ops.rope_kv_write(qkv[nd:], ctx.positions[nd:], ctx.token_seq[nd:], inv_freq, rd, table, cache.k,
+                              cache.v, self.nq, nkv_here, self.d, ctx.err, write_kv=writes)
+            if use_mma:
+                ops.attention_prefill_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.q_start, ctx.seq_lens,
+                                           nd, ctx.num_seqs, T - nd, self.nq, self.nkv, self.d, window,
+                                           self.scale, ctx.err)
+            else:
+                ops.attention_simt(qkv, stride, out, cache.k, cache.v, table, ctx.positions, ctx.token_seq,
+                                   self.nq, self.nkv, self.d, window, self.scale, ctx.err)
         return linear(out, self.w_o)

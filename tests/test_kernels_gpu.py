@@ -307,3 +307,45 @@ def test_mma_attention_finds_one_far_key(ops, err, kind):
                                        0, 1, m, nq, nkv, d, 0, 1.0, err)
         want = vs[0][target].repeat_interleave(nq // nkv, dim=0).reshape(1, nq * d).expand(m, -1)
         assert rel_err(out, want) <= tol(dt), target
+
+
+@pytest.mark.parametrize("nq,nkv,d,rd,page,window", [(8, 2, 64, 64, 16, 0), (3, 1, 32, 16, 8, 0), (4, 4, 128, 128, 16, 40),
+                                                     (12, 2, 16, 16, 4, 0)])
+def test_decode_with_fused_rotation_and_cache_write(ops, err, nq, nkv, d, rd, page, window):
+    """The decode kernel that also rotates the token's q and k and stores k and v
+    gives what the separate rotation-and-write kernel followed by attention gives."""
+    dt = torch.bfloat16
+    lens = [1, 32, 33, 256, 257, 700, 1025]
+    S = len(lens)
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, lens, [1] * S, pages=1024)
+    torch.manual_seed(7)
+    qkv = torch.randn(S, (nq + 2 * nkv) * d, device=DEV).to(dt)
+    inv = torch.tensor([50000.0 ** (-(2 * i) / rd) for i in range(rd // 2)], dtype=torch.float64, device=DEV)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    pos, tseq, tab = positions.to(DEV), token_seq.to(DEV), table.to(DEV)
+    scale = 1.0 / math.sqrt(d)
+    # separate kernels
+    qa, ka, va = qkv.clone(), kc.to(DEV), vc.to(DEV)
+    ops.rope_kv_write(qa, pos, tseq, inv, rd, tab, ka, va, nq, nkv, d, err)
+    out_a = torch.zeros(S, nq * d, device=DEV, dtype=dt)
+    ops.attention_decode_bf16(qa, qa.shape[1], out_a, ka, va, tab, seq_lens, S, max(lens), nq, nkv, d, window, scale, err)
+    # one kernel
+    qb, kb, vb = qkv.clone(), kc.to(DEV), vc.to(DEV)
+    out_b = torch.zeros_like(out_a)
+    ops.attention_decode_bf16(qb, qb.shape[1], out_b, kb, vb, tab, seq_lens, S, max(lens), nq, nkv, d, window, scale, err,
+                              inv_freq=inv, rotary_dim=rd, write_kv=True)
+    assert int(err.item()) == 0
+    assert torch.equal(ka, kb) and torch.equal(va, vb)
+    assert torch.equal(out_a, out_b)
+    assert torch.equal(qb, qkv)                         # the fused kernel leaves its input alone
+    # and against the plain formulation, with the new key and value in place
+    x = qkv.double().cpu().view(S, nq + 2 * nkv, d)
+    for s, n in enumerate(lens):
+        def rot(h):
+            o = h.clone()
+            o[..., :rd] = pl.apply_rope(h[..., :rd], torch.tensor([n - 1]), inv.cpu())
+            return o
+        k_all = torch.cat([ks[s][:n - 1].double(), rot(x[s:s + 1, nq:nq + nkv])])
+        v_all = torch.cat([vs[s][:n - 1].double(), x[s:s + 1, nq + nkv:]])
+        want = pl.attention(rot(x[s:s + 1, :nq]), k_all, v_all, torch.tensor([n - 1]), window=window or None, scale=scale)
+        assert rel_err(out_b[s:s + 1], want) <= tol(dt), (s, n)
