@@ -171,6 +171,47 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                              c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), _stream()), "gemm_f32")
 
 
+SMALL_M_MAX = 8       # up to here the weight-streaming GEMM beats the library's on a B200 (it takes 16)
+
+
+def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: str = "store") -> None:
+    """out = x . w^T for M <= 16 rows of bfloat16, bound by one read of w.
+    epilogue "store": out [M, N] bfloat16 or float32.  "silu_mul": w = [gate rows;
+    up rows] stacked (2 N rows), out [M, N] bfloat16 = silu(x gate^T) * (x up^T)."""
+    lib = build.load_library("gemm_small_m")
+    M, K = x.shape
+    assert x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and w.shape[1] == K
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if epilogue == "silu_mul":
+        N = w.shape[0] // 2
+        assert out.dtype is torch.bfloat16 and out.shape == (M, N) and w.shape[0] == 2 * N
+        code = 2
+    else:
+        N = w.shape[0]
+        assert out.shape == (M, N)
+        code = 1 if out.dtype is torch.float32 else 0
+        assert out.dtype in (torch.float32, torch.bfloat16)
+    _check(lib.rllm_gemm_small_m(_ptr(x), c_int(x.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out),
+                                 c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(code), _stream()),
+           "gemm_small_m")
+
+
+def small_m_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
+    import os
+    return (x.dtype is torch.bfloat16 and 0 < x.shape[0] <= SMALL_M_MAX and x.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and os.environ.get("RLLM_GEMM") != "library")
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
+    """x . w^T through this engine's own bfloat16 kernels, or None if none of them
+    takes the shape (the caller then uses the library's matrix product)."""
+    if small_m_takes(x, w) and w.shape[0] <= 65536:     # the library's kernel is ahead on very tall weights
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+        gemm_small_m(x, w, out)
+        return out
+    return None
+
+
 # ---------------------------------------------------------------------------
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     lib = build.load_library("sampling")

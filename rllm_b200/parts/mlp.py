@@ -42,7 +42,11 @@ class GatedMLP(FeedForward):
         self.w_down = tensors[d]
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        gate_up = linear(x, self.w_gate_up)                       # [T, 2I]
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        ops.silu_mul(gate_up, act)
+        if ops.small_m_takes(x, self.w_gate_up):
+            # few rows: one kernel streams [Wgate; Wup] once and applies silu(gate) * up to its accumulators
+            ops.gemm_small_m(x, self.w_gate_up, act, "silu_mul")
+        else:
+            gate_up = linear(x, self.w_gate_up)                   # [T, 2I]
+            ops.silu_mul(gate_up, act)
         return linear(act, self.w_down)

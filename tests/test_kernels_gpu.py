@@ -349,3 +349,39 @@ def test_decode_with_fused_rotation_and_cache_write(ops, err, nq, nkv, d, rd, pa
         v_all = torch.cat([vs[s][:n - 1].double(), x[s:s + 1, nq + nkv:]])
         want = pl.attention(rot(x[s:s + 1, :nq]), k_all, v_all, torch.tensor([n - 1]), window=window or None, scale=scale)
         assert rel_err(out_b[s:s + 1], want) <= tol(dt), (s, n)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(389, 96), (3072, 2048), (17, 264), (256, 64), (2048, 8192)])
+def test_gemm_small_m(ops, M, N, K):
+    torch.manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    want = x.double().cpu() @ w.double().cpu().t()
+    for dt in (torch.float32, torch.bfloat16):
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=dt)
+        ops.gemm_small_m(x, w, out)
+        assert rel_err(out, want) <= (1e-5 if dt is torch.float32 else 1e-2)
+    # a row's result does not depend on the rows around it
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_small_m(x, w, out)
+    one = torch.empty(1, N, device=DEV)
+    ops.gemm_small_m(x[M // 2:M // 2 + 1], w, one)
+    assert torch.equal(one[0], out[M // 2])
+    # rows of a wider buffer (a view with a row stride)
+    wide = torch.randn(M, K + 24, device=DEV).bfloat16()
+    ops.gemm_small_m(wide[:, 8:8 + K], w, out)
+    assert rel_err(out, wide[:, 8:8 + K].double().cpu() @ w.double().cpu().t()) <= 1e-5
+
+
+@pytest.mark.parametrize("M", [1, 8, 11, 16])
+@pytest.mark.parametrize("I,K", [(176, 64), (264, 96), (8192, 2048), (50, 72)])
+def test_gemm_small_m_silu(ops, M, I, K):
+    torch.manual_seed(I + M)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV) * 0.1).bfloat16()
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_small_m(x, w, out, "silu_mul")
+    xd, wd = x.double().cpu(), w.double().cpu()
+    want = pl.silu(xd @ wd[:I].t()) * (xd @ wd[I:].t())
+    assert rel_err(out, want) <= 1e-2
