@@ -238,6 +238,8 @@ class ModelRunner:
 
     def check_errors(self) -> None:
         """Raise if a kernel of an earlier step flagged a bad index (synchronises)."""
+        from ..kernels import ops
+        ops.check_gemm_errors(self.device)
         code = int(self.err.item())
         if code:
             self.err.zero_()

@@ -59,27 +59,54 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
   const TD* dr = delta ? delta + (size_t)src * H : nullptr;
   TO* o = out + (size_t)r * H;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = xr[i];
-    if (dr) {
-      v += to_f32(dr[i]);
-      if (writeback) xr[i] = v;
+  const bool vec = (H & 3) == 0 && ((((uintptr_t)xr | (uintptr_t)o | (uintptr_t)w) & 15) == 0) &&
+                   (!dr || (((uintptr_t)dr) & 7) == 0) && sizeof(TO) <= 4;
+  if (vec) {
+    // 4 values a thread and step: the sums of a row keep the same order for every batch
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 v = *(const float4*)(xr + i);
+      if (dr) {
+        v.x += to_f32(dr[i]); v.y += to_f32(dr[i + 1]); v.z += to_f32(dr[i + 2]); v.w += to_f32(dr[i + 3]);
+        if (writeback) *(float4*)(xr + i) = v;
+      }
+      ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
     }
-    ss += v * v;
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = xr[i];
+      if (dr) {
+        v += to_f32(dr[i]);
+        if (writeback) xr[i] = v;
+      }
+      ss += v * v;
+    }
   }
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)H + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = xr[i];
-    if (dr && !writeback) v += to_f32(dr[i]);
-    o[i] = from_f32<TO>(v * inv * to_f32(w[i]));
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      float4 v = *(const float4*)(xr + i);
+      if (dr && !writeback) {
+        v.x += to_f32(dr[i]); v.y += to_f32(dr[i + 1]); v.z += to_f32(dr[i + 2]); v.w += to_f32(dr[i + 3]);
+      }
+      o[i] = from_f32<TO>(v.x * inv * to_f32(w[i]));
+      o[i + 1] = from_f32<TO>(v.y * inv * to_f32(w[i + 1]));
+      o[i + 2] = from_f32<TO>(v.z * inv * to_f32(w[i + 2]));
+      o[i + 3] = from_f32<TO>(v.w * inv * to_f32(w[i + 3]));
+    }
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float v = xr[i];
+      if (dr && !writeback) v += to_f32(dr[i]);
+      o[i] = from_f32<TO>(v * inv * to_f32(w[i]));
+    }
   }
 }
 
 template <typename TD, typename TO>
 static int rmsnorm_launch_w(float* x, const void* delta, const int* rows, const void* w, int w_dtype,
                             void* out, int R, int H, float eps, int writeback, cudaStream_t stream) {
-  int threads = H >= 4096 ? 1024 : (H >= 1024 ? 512 : (H >= 256 ? 128 : 64));
+  int threads = H >= 8192 ? 1024 : (H >= 2048 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64)));
   if (w_dtype == RLLM_DT_F32)
     rmsnorm_kernel<TD, float, TO><<<R, threads, 0, stream>>>(x, (const TD*)delta, rows, (const float*)w,
                                                             (TO*)out, H, eps, writeback);
@@ -231,9 +258,35 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
   out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// bfloat16 with I a multiple of 8: 16-byte loads and stores, 8 values a thread
+__global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I8, size_t n8) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n8) return;
+  const size_t t = idx / I8;
+  const int i = (int)(idx - t * I8);
+  const uint4 g = *(const uint4*)(gu + (t * 2 * I8 + i) * 8);
+  const uint4 u = *(const uint4*)(gu + (t * 2 * I8 + I8 + i) * 8);
+  const __nv_bfloat162* gp = (const __nv_bfloat162*)&g;
+  const __nv_bfloat162* up = (const __nv_bfloat162*)&u;
+  uint4 o;
+  __nv_bfloat162* op = (__nv_bfloat162*)&o;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 gf = __bfloat1622float2(gp[k]), uf = __bfloat1622float2(up[k]);
+    op[k] = __floats2bfloat162_rn(gf.x / (1.0f + expf(-gf.x)) * uf.x, gf.y / (1.0f + expf(-gf.y)) * uf.y);
+  }
+  *(uint4*)(out + idx * 8) = o;
+}
+
 RLLM_EXPORT int rllm_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (I <= 0) return RLLM_E_BADARG;
+  if (dtype == RLLM_DT_BF16 && I % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0) {
+    const size_t n8 = (size_t)T * (I / 8);
+    silu_mul_bf16x8_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>((const bf16*)gu, (bf16*)out, I / 8, n8);
+    RLLM_LAUNCH_CHECK();
+    return 0;
+  }
   size_t n = (size_t)T * I;
   unsigned blocks = (unsigned)((n + 255) / 256);
   RLLM_DISPATCH_DTYPE(dtype, T_,

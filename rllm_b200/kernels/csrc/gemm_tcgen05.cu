@@ -1,0 +1,313 @@
+// C[M, N] = A[M, K] . W[N, K]^T in bfloat16 on the 5th-generation tensor cores
+// of sm_100a: the projections of prompt portions (M > 16 rows).
+//
+//   * operands come from global memory by TMA (cp.async.bulk.tensor, 128-byte
+//     swizzle) into a ring of shared-memory stages, signalled by mbarriers;
+//   * one elected thread issues tcgen05.mma (128 x BN x 16 per instruction,
+//     operands described by shared-memory matrix descriptors), accumulating in
+//     float32 in tensor memory (TMEM, BN columns of the 512);
+//   * tcgen05.commit hands a stage back to the TMA producer when the MMAs that
+//     read it are done, and at the end tells the epilogue warps that the
+//     accumulator is complete;
+//   * four epilogue warps read their 32 TMEM lanes with tcgen05.ld, round to
+//     bfloat16 (or keep float32) and store; with the SiLU-gate epilogue the tile
+//     holds 128 gate and 128 up features of [Wgate; Wup] side by side and
+//     silu(gate) * up is applied to the accumulators
+//     (crates/rllm-model/src/layers.rs:214-220), so the [T, 2I] intermediate
+//     never exists.
+// Warp 0: TMA producer.  Warp 1: TMEM allocation and MMA issue.  Warps 2-5:
+// epilogue.  One output tile per CTA.  No cluster, no multicast.
+//
+// Every wait on an mbarrier is bounded: after the limit the thread sets bit 16
+// of the error word and the CTA winds down (gives its TMEM columns back) instead
+// of hanging.
+//
+// The reference computes these products with a library call
+// (crates/rllm-model/src/layers.rs:162-175).
+#include "common.cuh"
+#include <cuda.h>
+
+#define TG_BM 128
+#define TG_BK 64
+#define TG_THREADS 192
+#define TG_EPI_BF16 0
+#define TG_EPI_F32 1
+#define TG_EPI_SILU 2
+#define TG_SPIN_LIMIT (1u << 22)
+
+__device__ __forceinline__ unsigned tg_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(void* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tg_smem(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tg_smem(bar)), "r"(bytes) : "memory");
+}
+// true when the phase with this parity has completed; false after the spin limit
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* err) {
+  const unsigned addr = tg_smem(bar);
+  for (unsigned spin = 0; spin < TG_SPIN_LIMIT; ++spin) {
+    unsigned done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  atomicOr(err, 16);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(tg_smem(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(tg_smem(bar)) : "memory");
+}
+// K-major operand tile of rows x 64 bf16 with 128-byte swizzle: rows are 128 bytes, groups
+// of 8 rows are 1024 bytes apart.  Fields: start address >> 4; leading byte offset 1
+// (unused with swizzle); stride byte offset 1024 >> 4; version 1; layout type 2 (128B swizzle).
+__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((tg_smem(tile) >> 4) & 0x3FFF);
+  d |= (unsigned long long)1 << 16;
+  d |= (unsigned long long)(1024 >> 4) << 32;
+  d |= (unsigned long long)1 << 46;
+  d |= (unsigned long long)2 << 61;
+  return d;
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long da, unsigned long long db,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+               : "memory");
+}
+__device__ __forceinline__ void umma_commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tg_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned* r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr) : "memory");
+}
+
+template <int BN> constexpr int tg_stages() { return BN == 256 ? 4 : 6; }
+template <int BN> constexpr int tg_stage_bytes() { return (TG_BM + BN) * TG_BK * 2; }
+template <int BN> constexpr int tg_smem_bytes() { return tg_stages<BN>() * tg_stage_bytes<BN>() + 1024 + 256; }
+
+// EPI: 0 bfloat16 out, 1 float32 out, 2 SiLU-gate (BN must be 256; W rows n and up_offset + n pair up).
+template <int BN, int EPI>
+__global__ void __launch_bounds__(TG_THREADS)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    void* __restrict__ out, int ldo, int M, int N, int K, int up_offset, int* __restrict__ err) {
+  constexpr int STAGES = tg_stages<BN>();
+  constexpr int NOUT = (EPI == TG_EPI_SILU) ? BN / 2 : BN;     // output columns of a tile
+  extern __shared__ unsigned char tg_raw[];
+  unsigned char* base = (unsigned char*)(((uintptr_t)tg_raw + 1023) & ~(uintptr_t)1023);
+  unsigned char* stage_mem = base;
+  unsigned long long* bars = (unsigned long long*)(base + STAGES * tg_stage_bytes<BN>());
+  unsigned long long* full = bars;               // [STAGES]
+  unsigned long long* empty = bars + STAGES;     // [STAGES]
+  unsigned long long* acc_done = bars + 2 * STAGES;
+  unsigned* tmem_slot = (unsigned*)(bars + 2 * STAGES + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * TG_BM, n0 = blockIdx.y * NOUT;
+  const int num_kb = (K + TG_BK - 1) / TG_BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    mbar_init(acc_done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_w) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tg_smem(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % STAGES;
+        const unsigned phase = (kb / STAGES) & 1;
+        if (!mbar_wait(&empty[s], phase ^ 1, err)) break;       // a fresh barrier passes the wait for parity 1
+        unsigned char* sa = stage_mem + s * tg_stage_bytes<BN>();
+        unsigned char* sb = sa + TG_BM * TG_BK * 2;
+        mbar_expect_tx(&full[s], (unsigned)tg_stage_bytes<BN>());
+        tma_load_2d(sa, &map_a, kb * TG_BK, m0, &full[s]);
+        if (EPI == TG_EPI_SILU) {
+          tma_load_2d(sb, &map_w, kb * TG_BK, n0, &full[s]);
+          tma_load_2d(sb + (BN / 2) * TG_BK * 2, &map_w, kb * TG_BK, up_offset + n0, &full[s]);
+        } else {
+          tma_load_2d(sb, &map_w, kb * TG_BK, n0, &full[s]);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptor: float32 accumulate, bfloat16 A and B, both K-major, N = BN, M = 128
+      const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TG_BM >> 4) << 24);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % STAGES;
+        const unsigned phase = (kb / STAGES) & 1;
+        ok = mbar_wait(&full[s], phase, err);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned char* sa = stage_mem + s * tg_stage_bytes<BN>();
+        unsigned char* sb = sa + TG_BM * TG_BK * 2;
+        const unsigned long long da = umma_desc(sa), db = umma_desc(sb);
+#pragma unroll
+        for (int k = 0; k < TG_BK / 16; ++k)     // 16 bf16 = 32 bytes further along K: + 2 in the address field
+          umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+        umma_commit(&empty[s]);                  // the stage is free once these MMAs have read it
+      }
+      umma_commit(acc_done);                     // the accumulator is complete once all MMAs are done
+    }
+    __syncwarp();
+  } else {
+    // epilogue: warp w reads TMEM lanes 32 (w % 4) .. + 31 = rows of the tile
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int m = m0 + row;
+    const bool ok = mbar_wait(acc_done, 0, err);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const unsigned lane_addr = tmem_acc + ((unsigned)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < NOUT; c0 += 32) {
+        unsigned r[32];
+        tmem_ld32(lane_addr + c0, r);
+        if (EPI == TG_EPI_SILU) {
+          unsigned u[32];
+          tmem_ld32(lane_addr + NOUT + c0, u);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float g = __uint_as_float(r[j]);
+            r[j] = __float_as_uint(g / (1.0f + expf(-g)) * __uint_as_float(u[j]));
+          }
+        } else {
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        }
+        if (m < M) {
+          const int n = n0 + c0;
+          if (EPI == TG_EPI_F32) {
+            float* o = (float*)out + (size_t)m * ldo + n;
+            if (n + 32 <= N && (((uintptr_t)o) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *(float4*)(o + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+              for (int j = 0; j < 32; ++j) if (n + j < N) o[j] = __uint_as_float(r[j]);
+            }
+          } else {
+            bf16* o = (bf16*)out + (size_t)m * ldo + n;
+            if (n + 32 <= N && (((uintptr_t)o) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 v;
+                __nv_bfloat162* p = (__nv_bfloat162*)&v;
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  p[q] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * q]), __uint_as_float(r[j + 2 * q + 1]));
+                *(uint4*)(o + j) = v;
+              }
+            } else {
+              for (int j = 0; j < 32; ++j) if (n + j < N) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*tg_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static tg_encode_fn tg_get_encode() {
+  static tg_encode_fn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (tg_encode_fn)p;
+  }
+  return fn;
+}
+
+// [rows, K] bf16 row-major with row stride ld (elements); box = 64 (K) x box_rows; out-of-range reads give 0
+static int tg_make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+  tg_encode_fn enc = tg_get_encode();
+  if (!enc) return RLLM_E_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {TG_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : RLLM_E_BADARG;
+}
+
+template <int BN, int EPI>
+static int tg_launch(const void* a, int lda, const void* w, int ldw, int w_rows, void* out, int ldo, int M, int N,
+                     int K, int up_offset, int* err, cudaStream_t stream) {
+  constexpr int NOUT = (EPI == TG_EPI_SILU) ? BN / 2 : BN;
+  CUtensorMap ma, mw;
+  int rc = tg_make_map(&ma, a, M, K, lda, TG_BM);
+  if (rc) return rc;
+  rc = tg_make_map(&mw, w, w_rows, K, ldw, NOUT);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         tg_smem_bytes<BN>());
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((M + TG_BM - 1) / TG_BM, (N + NOUT - 1) / NOUT);
+  if (grid.y > 65535) return RLLM_E_UNSUPPORTED;
+  gemm_tcgen05_kernel<BN, EPI><<<grid, TG_THREADS, tg_smem_bytes<BN>(), stream>>>(ma, mw, out, ldo, M, N, K, up_offset, err);
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+// epilogue 0: out bfloat16 [M, N]; 1: out float32 [M, N]; 2: W = [gate rows (N); up rows (N)] stacked,
+// out bfloat16 [M, N] = silu(A . gate^T) * (A . up^T).  err: the engine's error word (bit 16: a wait ran out).
+RLLM_EXPORT int rllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw, void* out, int ldo, int M, int N,
+                                  int K, int epilogue, int* err, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || lda < K || ldw < K || ldo < N || !err) return RLLM_E_BADARG;
+  // TMA: 16-byte aligned bases and row strides
+  if (K % 8 || lda % 8 || ldw % 8 || (((uintptr_t)a | (uintptr_t)w) & 15)) return RLLM_E_UNSUPPORTED;
+  switch (epilogue) {
+    case TG_EPI_BF16:
+      if (N > 128) return tg_launch<256, TG_EPI_BF16>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
+      return tg_launch<128, TG_EPI_BF16>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
+    case TG_EPI_F32:
+      if (N > 128) return tg_launch<256, TG_EPI_F32>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
+      return tg_launch<128, TG_EPI_F32>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
+    case TG_EPI_SILU:
+      return tg_launch<256, TG_EPI_SILU>(a, lda, w, ldw, 2 * N, out, ldo, M, N, K, N, err, stream);
+  }
+  return RLLM_E_BADARG;
+}

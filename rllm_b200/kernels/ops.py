@@ -202,12 +202,79 @@ def small_m_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and os.environ.get("RLLM_GEMM") != "library")
 
 
+_gemm_err = {}
+
+
+def gemm_error_word(device: torch.device) -> torch.Tensor:
+    """The per-device error word of the tcgen05 GEMM (bit 16: a bounded wait ran out)."""
+    t = _gemm_err.get(device)
+    if t is None:
+        t = _gemm_err[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return t
+
+
+def check_gemm_errors(device: torch.device) -> None:
+    t = _gemm_err.get(device)
+    if t is not None and int(t.item()):
+        t.zero_()
+        raise KernelError("gemm_tcgen05: a wait on an mbarrier ran out; the result of that product is undefined")
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: str = "store") -> None:
+    """out = x . w^T for bfloat16 on the tcgen05 tensor cores (TMA in, TMEM accumulators).
+    epilogue "store": out [M, N] bfloat16 or float32.  "silu_mul": w = [gate rows;
+    up rows] stacked (2 N rows), out [M, N] bfloat16 = silu(x gate^T) * (x up^T)."""
+    lib = build.load_library("gemm_tcgen05")
+    M, K = x.shape
+    assert x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and w.shape[1] == K
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if epilogue == "silu_mul":
+        N = w.shape[0] // 2
+        assert out.dtype is torch.bfloat16 and out.shape == (M, N) and w.shape[0] == 2 * N
+        code = 2
+    else:
+        N = w.shape[0]
+        assert out.shape == (M, N) and out.dtype in (torch.float32, torch.bfloat16)
+        code = 1 if out.dtype is torch.float32 else 0
+    _check(lib.rllm_gemm_tcgen05(_ptr(x), c_int(x.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(out),
+                                 c_int(out.stride(0)), c_int(M), c_int(N), c_int(K), c_int(code),
+                                 _ptr(gemm_error_word(x.device)), _stream()), "gemm_tcgen05")
+
+
+TCGEN05_MIN_TILES = 96    # below this many 128 x 256 output tiles the GPU is not filled: the library's
+                          # small-tile kernels read the weight faster
+
+
+def tcgen05_takes(x: torch.Tensor, w: torch.Tensor, silu: bool = False) -> bool:
+    """Whether the tcgen05 kernel should compute x . w^T.  ``silu``: w is [gate; up] stacked and the
+    output has half of w's rows.  With the environment variable RLLM_GEMM=tcgen05 every shape it can
+    take goes to it (used by tests, so that tiny models run through it)."""
+    import os
+    mode = os.environ.get("RLLM_GEMM", "")
+    if mode in ("library", "no_tcgen05"):
+        return False
+    ok = (x.dtype is torch.bfloat16 and x.shape[0] > 0 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+          and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+    if not ok or mode == "tcgen05":
+        return ok
+    n_out = w.shape[0] // 2 if silu else w.shape[0]
+    tiles = -(-x.shape[0] // 128) * -(-n_out // (128 if silu else 256))
+    return tiles >= TCGEN05_MIN_TILES
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> Optional[torch.Tensor]:
     """x . w^T through this engine's own bfloat16 kernels, or None if none of them
-    takes the shape (the caller then uses the library's matrix product)."""
-    if small_m_takes(x, w) and w.shape[0] <= 65536:     # the library's kernel is ahead on very tall weights
+    takes the shape (the caller then uses the library's matrix product).  Few rows:
+    the weight-streaming kernel; more: the tcgen05 kernel."""
+    if small_m_takes(x, w):
+        if w.shape[0] > 65536:          # very tall weights (the vocabulary): the library's kernel is ahead
+            return None
         out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
         gemm_small_m(x, w, out)
+        return out
+    if tcgen05_takes(x, w):
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+        gemm_tcgen05(x, w, out)
         return out
     return None
 

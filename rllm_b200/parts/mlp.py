@@ -46,6 +46,9 @@ class GatedMLP(FeedForward):
         if ops.small_m_takes(x, self.w_gate_up):
             # few rows: one kernel streams [Wgate; Wup] once and applies silu(gate) * up to its accumulators
             ops.gemm_small_m(x, self.w_gate_up, act, "silu_mul")
+        elif ops.tcgen05_takes(x, self.w_gate_up, silu=True):
+            # many rows: tensor-core tiles of 128 gate and 128 up features, silu(gate) * up in the epilogue
+            ops.gemm_tcgen05(x, self.w_gate_up, act, "silu_mul")
         else:
             gate_up = linear(x, self.w_gate_up)                   # [T, 2I]
             ops.silu_mul(gate_up, act)

@@ -385,3 +385,35 @@ def test_gemm_small_m_silu(ops, M, I, K):
     xd, wd = x.double().cpu(), w.double().cpu()
     want = pl.silu(xd @ wd[:I].t()) * (xd @ wd[I:].t())
     assert rel_err(out, want) <= 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(17, 96, 64), (128, 128, 64), (129, 389, 96), (200, 300, 264), (300, 3072, 2048),
+                                   (2048, 2048, 8192), (64, 128256, 2048), (1000, 72, 1000)])
+def test_gemm_tcgen05(ops, M, N, K):
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(N, K, device=DEV) * 0.05).bfloat16()
+    want = x.double().cpu() @ w.double().cpu().t() if M * N * K < 2e10 else (x.float() @ w.float().t()).double().cpu()
+    for dt in (torch.float32, torch.bfloat16):
+        out = torch.full((M, N), float("nan"), device=DEV, dtype=dt)
+        ops.gemm_tcgen05(x, w, out)
+        ops.check_gemm_errors(torch.device(DEV))
+        assert rel_err(out, want) <= (2e-5 if dt is torch.float32 else 1e-2)
+    # rows of a wider buffer (a view with a row stride), as the attention output is read
+    wide = torch.randn(M, K + 24, device=DEV).bfloat16()
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_tcgen05(wide[:, 8:8 + K], w, out)
+    assert rel_err(out, (wide[:, 8:8 + K].float() @ w.float().t())) <= 2e-5
+
+
+@pytest.mark.parametrize("M,I,K", [(33, 176, 64), (130, 264, 96), (2048, 8192, 2048), (257, 50, 72)])
+def test_gemm_tcgen05_silu(ops, M, I, K):
+    torch.manual_seed(I + M)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(2 * I, K, device=DEV) * 0.1).bfloat16()
+    out = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tcgen05(x, w, out, "silu_mul")
+    ops.check_gemm_errors(torch.device(DEV))
+    xf, wf = x.float(), w.float()
+    want = pl.silu((xf @ wf[:I].t()).double().cpu()) * (xf @ wf[I:].t()).double().cpu()
+    assert rel_err(out, want) <= 1e-2

@@ -106,3 +106,16 @@ def test_too_few_pages_is_an_error(model_dirs):
     tb = ru.trace_whole(reqs)
     with pytest.raises(AssertionError):
         ru.run_trace(model_dirs["A"], "float32", tb, cfg["vocab_size"], page_size=page, max_tokens=64)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("mode", ["whole", "mixed"])
+def test_replay_through_the_tcgen05_gemm(model_dirs, name, mode, monkeypatch):
+    """Tiny models are too small for the tcgen05 GEMM to be chosen by itself (it
+    wants enough tiles to fill the GPU); RLLM_GEMM=tcgen05 sends every product of
+    more than 8 rows through it, tails in all three dimensions included."""
+    monkeypatch.setenv("RLLM_GEMM", "tcgen05")
+    cfg, _, page = TINY[name]
+    reqs = make_requests(name)
+    got = ru.run_trace(model_dirs[name], "bfloat16", MODES[mode](reqs), cfg["vocab_size"], page_size=page)
+    compare(got, plain_logits(model_dirs, name, "bfloat16"), reqs, "bfloat16", f"{name}/tcgen05/{mode}")
