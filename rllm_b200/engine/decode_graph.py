@@ -80,6 +80,9 @@ class DecodeGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.uses = 0
+        # what the pinned buffer holds per row: (request, number of table entries written), so that an
+        # unchanged block table is not written again
+        self.row_state: List[Optional[tuple]] = [None] * S
 
     def fill(self, entries) -> None:
         """Pack the step's inputs into the pinned buffer and copy them over."""
@@ -91,10 +94,15 @@ class DecodeGraph:
             h[self.r_pos[0] + s] = e.start
             h[self.r_seqlens[0] + s] = e.start + 1
             h[self.r_slots[0] + s] = cache.slot(e.req)
-        for g, r in zip(self.paged, self.r_tables):
-            tab = h[r[0]:r[1]].reshape(S, W)
-            for s, e in enumerate(entries):
-                tb = cache.table(e.req, g)
+        windowed = any(cache.needs[g].window is not None for g in self.paged)
+        for s, e in enumerate(entries):
+            tbs = [cache.table(e.req, g) for g in self.paged]
+            state = (e.req, tuple((id(tb), len(tb)) for tb in tbs))
+            if self.row_state[s] == state and not windowed:
+                continue                      # same request, tables only grow: nothing new to write
+            self.row_state[s] = state
+            for (g, r), tb in zip(zip(self.paged, self.r_tables), tbs):
+                tab = h[r[0]:r[1]].reshape(S, W)
                 n = min(len(tb), W)
                 tab[s, :n] = tb[:n]
                 tab[s, n:] = -1

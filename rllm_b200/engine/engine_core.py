@@ -141,7 +141,7 @@ class EngineCore:
         entries, rows, sampled_reqs = [], [], []
         for s in sched.scheduled:
             req = s.request
-            toks = req.all_token_ids[s.start:s.start + s.num_tokens]
+            toks = req.tokens(s.start, s.num_tokens)
             entries.append(StepEntry(req.request_id, toks, s.start, [s.num_tokens - 1] if s.want_logits else []))
             if s.want_logits:
                 ctx_needed = req.params.edits_logits

@@ -74,6 +74,15 @@ class Request:
     def num_tokens(self) -> int:
         return len(self.prompt_token_ids) + len(self.output_token_ids)
 
+    def tokens(self, start: int, n: int) -> List[int]:
+        """Tokens start .. start + n - 1 of prompt + generated, without joining the two lists."""
+        p = len(self.prompt_token_ids)
+        if start >= p:
+            return self.output_token_ids[start - p:start - p + n]
+        if start + n <= p:
+            return self.prompt_token_ids[start:start + n]
+        return self.prompt_token_ids[start:] + self.output_token_ids[:start + n - p]
+
 
 @dataclass
 class Scheduled:
@@ -224,8 +233,11 @@ class Scheduler:
         """The step ran: its tokens' keys and values are in the cache."""
         for s in out.scheduled:
             req = s.request
+            before = req.num_computed
             req.num_computed = s.start + s.num_tokens
-            self.cache.register_computed(req.request_id, req.all_token_ids, req.num_computed)
+            # content hashes only when a page was completed by this step
+            if self.cache.prefix_caching and req.num_computed // self.cache.page_size > before // self.cache.page_size:
+                self.cache.register_computed(req.request_id, req.all_token_ids, req.num_computed)
 
     def finish(self, req: Request, status: RequestStatus) -> None:
         """Take a request out and give back what it holds."""

@@ -385,6 +385,7 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
                         int rotary_dim, int write_kv, float* __restrict__ ws_o, float* __restrict__ ws_ml,
                         int* __restrict__ counters, int* __restrict__ err) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned char* mine = smem_raw + (size_t)warp * dec_warp_smem<D, STAGES>();
   bf16* sW = (bf16*)mine;                                          // STAGES x (K [32][D], V [32][D])
@@ -499,6 +500,7 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
     }
   }
   cp_async_wait<0>();
+  pdl_launch();                  // the stream's next kernel may start coming in now
   // this chunk's partial: rows < g, straight from the accumulators
   if (active) {
 #pragma unroll
@@ -644,11 +646,10 @@ static int launch_decode_cfg(int warps, bf16* qkv, int q_stride, bf16* out, bf16
   float* ws_o = ws;
   float* ws_ml = ws + (size_t)num_seqs * nq * max_chunks * D;
   dim3 grid((max_chunks + warps - 1) / warps, nkv, num_seqs);
-  attention_decode_kernel<D, STAGES><<<grid, 32 * warps, smem, stream>>>(qkv, q_stride, out, kc, vc, bt, max_blocks,
-      seq_lens, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, max_chunks, inv_freq, rotary_dim,
-      write_kv, ws_o, ws_ml, counters, err);
-  RLLM_LAUNCH_CHECK();
-  return 0;
+  cudaError_t e = rllm_launch_pdl(attention_decode_kernel<D, STAGES>, grid, dim3(32 * warps), smem, stream, qkv,
+      q_stride, out, kc, vc, bt, max_blocks, seq_lens, nq, nkv, page_size, num_pages, window,
+      scale * 1.4426950408889634f, max_chunks, inv_freq, rotary_dim, write_kv, ws_o, ws_ml, counters, err);
+  return (int)e;
 }
 
 // Few chunks in all (small batch, short context): few warps per CTA and a deep

@@ -67,6 +67,38 @@ __device__ __forceinline__ void rope_cos_sin(int pos, double inv_freq, float* c,
   sincosf((float)r, s, c);
 }
 
+// Programmatic dependent launch: a kernel lets the next kernel of the stream start
+// (pdl_launch) while it is still running, and itself waits for the kernel before it
+// (pdl_wait) only when it first touches memory that kernel may have written.  What a
+// kernel does before pdl_wait (index arithmetic, loads of weights that no kernel
+// writes) overlaps the tail of its predecessor.  pdl_wait returns when the
+// predecessor has completed and its writes are visible; without a predecessor that
+// was launched this way both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Launch `kernel` so that it may start before the kernel ahead of it in the stream has
+// finished (the kernel must call pdl_wait before it reads that kernel's output).
+// RLLM_PDL=0 in the environment turns this into an ordinary launch.
+#include <stdlib.h>
+static inline bool rllm_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("RLLM_PDL"); on = (e && e[0] == '0') ? 0 : 1; }
+  return on == 1;
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t rllm_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                          cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = rllm_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Dispatch helpers ---------------------------------------------------------
 #define RLLM_DISPATCH_DTYPE(code, T, ...)                    \
   do {                                                       \

@@ -15,6 +15,8 @@
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                  float* __restrict__ out, int H, int V, int* __restrict__ err) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * H;
@@ -32,10 +34,10 @@ RLLM_EXPORT int rllm_embedding(const int* ids, const void* table, int table_dtyp
   if (T <= 0) return 0;
   if (H <= 0 || V <= 0) return RLLM_E_BADARG;
   int threads = H >= 1024 ? 256 : 128;
+  cudaError_t e = cudaErrorInvalidValue;
   RLLM_DISPATCH_DTYPE(table_dtype, TW,
-    (embedding_kernel<TW><<<T, threads, 0, stream>>>(ids, (const TW*)table, out, H, V, err)));
-  RLLM_LAUNCH_CHECK();
-  return 0;
+    (e = rllm_launch_pdl(embedding_kernel<TW>, dim3(T), dim3(threads), 0, stream, ids, (const TW*)table, out, H, V, err)));
+  return (int)e;
 }
 
 // ---------------------------------------------------------------------------
@@ -53,6 +55,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
                                const int* __restrict__ rows, const TW* __restrict__ w,
                                TO* __restrict__ out, int H, float eps, int writeback) {
   __shared__ float red[32];
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* xr = x + (size_t)src * H;
@@ -81,6 +84,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
       ss += v * v;
     }
   }
+  pdl_launch();
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)H + eps);
   if (vec) {
@@ -107,16 +111,16 @@ template <typename TD, typename TO>
 static int rmsnorm_launch_w(float* x, const void* delta, const int* rows, const void* w, int w_dtype,
                             void* out, int R, int H, float eps, int writeback, cudaStream_t stream) {
   int threads = H >= 8192 ? 1024 : (H >= 2048 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64)));
+  cudaError_t e;
   if (w_dtype == RLLM_DT_F32)
-    rmsnorm_kernel<TD, float, TO><<<R, threads, 0, stream>>>(x, (const TD*)delta, rows, (const float*)w,
-                                                            (TO*)out, H, eps, writeback);
+    e = rllm_launch_pdl(rmsnorm_kernel<TD, float, TO>, dim3(R), dim3(threads), 0, stream, x, (const TD*)delta, rows,
+                        (const float*)w, (TO*)out, H, eps, writeback);
   else if (w_dtype == RLLM_DT_BF16)
-    rmsnorm_kernel<TD, bf16, TO><<<R, threads, 0, stream>>>(x, (const TD*)delta, rows, (const bf16*)w,
-                                                           (TO*)out, H, eps, writeback);
+    e = rllm_launch_pdl(rmsnorm_kernel<TD, bf16, TO>, dim3(R), dim3(threads), 0, stream, x, (const TD*)delta, rows,
+                        (const bf16*)w, (TO*)out, H, eps, writeback);
   else
     return RLLM_E_BADARG;
-  RLLM_LAUNCH_CHECK();
-  return 0;
+  return (int)e;
 }
 
 // act_dtype is the dtype of delta and of out.
@@ -303,6 +307,8 @@ RLLM_EXPORT int rllm_silu_mul(const void* gu, void* out, int dtype, int T, int I
 __global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
                                       int* __restrict__ seq_lens, const int* __restrict__ sampled,
                                       int* __restrict__ history_row, int S) {
+  pdl_launch();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= S) return;
   const int t = sampled[i];
@@ -315,8 +321,6 @@ __global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restri
 RLLM_EXPORT int rllm_decode_advance(int* token_ids, int* positions, int* seq_lens, const int* sampled,
                                     int* history_row, int S, cudaStream_t stream) {
   if (S <= 0) return 0;
-  decode_advance_kernel<<<(S + 127) / 128, 128, 0, stream>>>(token_ids, positions, seq_lens, sampled,
-                                                            history_row, S);
-  RLLM_LAUNCH_CHECK();
-  return 0;
+  return (int)rllm_launch_pdl(decode_advance_kernel, dim3((S + 127) / 128), dim3(128), 0, stream, token_ids, positions,
+                              seq_lens, sampled, history_row, S);
 }

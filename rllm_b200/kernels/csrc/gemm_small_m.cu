@@ -69,8 +69,10 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
   // a warp takes a contiguous range of k blocks, so that its loads walk along the rows of W
   const int per_warp = (nblocks + nwarps - 1) / nwarps;
   const int b_end = min(nblocks, (warp + 1) * per_warp);
+  bool waited = false;
   for (int b0 = warp * per_warp; b0 < b_end; b0 += U) {
     uint4 a[U], v[U], xb[U][MT];
+    // the weight first (no kernel writes it: these loads may run ahead of the kernel before this one) ...
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = (b0 + u) * 32;
@@ -78,6 +80,13 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
       a[u] = make_uint4(0u, 0u, 0u, 0u);
       v[u] = a[u];
       if (in) { a[u] = ld_stream16(w_lo + k); v[u] = ld_stream16(w_hi + k); }
+    }
+    // ... then x, which the kernel before this one wrote
+    if (!waited) { pdl_wait(); waited = true; }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int k = (b0 + u) * 32;
+      const bool in = b0 + u < b_end && k + t * 8 < K;
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         xb[u][i] = make_uint4(0u, 0u, 0u, 0u);
@@ -92,6 +101,8 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
         mma16816(c[i], a[u].z, v[u].z, a[u].w, v[u].w, xb[u][i].z, xb[u][i].w);
       }
   }
+  pdl_launch();                  // the stream's next kernel may start coming in now
+  if (!waited) pdl_wait();       // a warp without k blocks: nothing was read, but the stores below must wait too
   // partial sums of the warps -> shared memory; c[i]: rows gq, gq + 8; batch columns i*8 + 2t, 2t + 1
   float* mine = red + (size_t)warp * 16 * 8 * MT;
 #pragma unroll
@@ -140,8 +151,9 @@ static int launch_small_m(const bf16* x, int ldx, const bf16* W, int ldw, void* 
   while (warps > 1 && warps > nblocks) warps /= 2;
   while (warps > 1 && (size_t)warps * 16 * 8 * MT * sizeof(float) > 48 * 1024) warps /= 2;
   const size_t smem = (size_t)warps * 16 * 8 * MT * sizeof(float);
-  gemm_small_m_kernel<MT, EPI><<<tiles, 32 * warps, smem, stream>>>(x, ldx, W, ldw, out, ldo, M, N, K, up_offset);
-  RLLM_LAUNCH_CHECK();
+  cudaError_t e = rllm_launch_pdl(gemm_small_m_kernel<MT, EPI>, dim3(tiles), dim3(32 * warps), smem, stream,
+                                  x, ldx, W, ldw, out, ldo, M, N, K, up_offset);
+  if (e != cudaSuccess) return (int)e;
   return 0;
 }
 

@@ -240,6 +240,8 @@ RLLM_EXPORT int rllm_sample(const float* logits, int R, int V, int ld, const flo
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out_tokens) {
   __shared__ ArgMax sm_arg[32];
+  pdl_launch();
+  pdl_wait();
   const float* x = logits + (size_t)blockIdx.x * ld;
   ArgMax best; best.v = -INFINITY; best.i = 0x7fffffff;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
@@ -254,9 +256,7 @@ RLLM_EXPORT int rllm_argmax(const float* logits, int R, int V, int ld, int* out_
                             cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0 || ld < V) return RLLM_E_BADARG;
-  argmax_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, ld, out_tokens);
-  RLLM_LAUNCH_CHECK();
-  return 0;
+  return (int)rllm_launch_pdl(argmax_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, V, ld, out_tokens);
 }
 
 // ---------------------------------------------------------------------------
