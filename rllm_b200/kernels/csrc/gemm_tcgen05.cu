@@ -16,7 +16,9 @@
 //     (crates/rllm-model/src/layers.rs:214-220), so the [T, 2I] intermediate
 //     never exists.
 // Warp 0: TMA producer.  Warp 1: TMEM allocation and MMA issue.  Warps 2-5:
-// epilogue.  One output tile per CTA.  No cluster, no multicast.
+// epilogue.  The kernel is persistent (one CTA per SM walks over output tiles) and
+// keeps two accumulators in TMEM, so that the epilogue of a tile overlaps the
+// MMAs of the next.  No cluster, no multicast.
 //
 // Every wait on an mbarrier is bounded: after the limit the thread sets bit 16
 // of the error word and the CTA winds down (gives its TMEM columns back) instead
@@ -95,56 +97,70 @@ template <int BN> constexpr int tg_stages() { return BN == 256 ? 4 : 6; }
 template <int BN> constexpr int tg_stage_bytes() { return (TG_BM + BN) * TG_BK * 2; }
 template <int BN> constexpr int tg_smem_bytes() { return tg_stages<BN>() * tg_stage_bytes<BN>() + 1024 + 256; }
 
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tg_smem(bar)) : "memory");
+}
+
 // EPI: 0 bfloat16 out, 1 float32 out, 2 SiLU-gate (BN must be 256; W rows n and up_offset + n pair up).
+// Persistent: CTA b takes the output tiles b, b + gridDim.x, ... (rows of tiles first, so that CTAs
+// running side by side share a weight tile in L2).  Two accumulators in TMEM: the epilogue of a
+// tile runs while the tensor cores work on the next.
 template <int BN, int EPI>
 __global__ void __launch_bounds__(TG_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    void* __restrict__ out, int ldo, int M, int N, int K, int up_offset, int* __restrict__ err) {
+                    void* __restrict__ out, int ldo, int M, int N, int K, int up_offset, int tiles_m,
+                    int num_tiles, int* __restrict__ err) {
   constexpr int STAGES = tg_stages<BN>();
   constexpr int NOUT = (EPI == TG_EPI_SILU) ? BN / 2 : BN;     // output columns of a tile
   extern __shared__ unsigned char tg_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)tg_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* stage_mem = base;
   unsigned long long* bars = (unsigned long long*)(base + STAGES * tg_stage_bytes<BN>());
-  unsigned long long* full = bars;               // [STAGES]
-  unsigned long long* empty = bars + STAGES;     // [STAGES]
-  unsigned long long* acc_done = bars + 2 * STAGES;
-  unsigned* tmem_slot = (unsigned*)(bars + 2 * STAGES + 1);
+  unsigned long long* full = bars;                   // [STAGES]  TMA -> MMA
+  unsigned long long* empty = bars + STAGES;         // [STAGES]  MMA -> TMA
+  unsigned long long* acc_full = bars + 2 * STAGES;  // [2]       MMA -> epilogue
+  unsigned long long* acc_empty = acc_full + 2;      // [2]       epilogue -> MMA
+  unsigned* tmem_slot = (unsigned*)(acc_empty + 2);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * TG_BM, n0 = blockIdx.y * NOUT;
   const int num_kb = (K + TG_BK - 1) / TG_BK;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    mbar_init(acc_done, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_a) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_w) : "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tg_smem(tmem_slot)), "r"(BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tg_smem(tmem_slot)), "r"(2 * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const unsigned tmem_acc = *tmem_slot;
+  const unsigned tmem_base = *tmem_slot;
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % STAGES;
-        const unsigned phase = (kb / STAGES) & 1;
-        if (!mbar_wait(&empty[s], phase ^ 1, err)) break;       // a fresh barrier passes the wait for parity 1
-        unsigned char* sa = stage_mem + s * tg_stage_bytes<BN>();
-        unsigned char* sb = sa + TG_BM * TG_BK * 2;
-        mbar_expect_tx(&full[s], (unsigned)tg_stage_bytes<BN>());
-        tma_load_2d(sa, &map_a, kb * TG_BK, m0, &full[s]);
-        if (EPI == TG_EPI_SILU) {
-          tma_load_2d(sb, &map_w, kb * TG_BK, n0, &full[s]);
-          tma_load_2d(sb + (BN / 2) * TG_BK * 2, &map_w, kb * TG_BK, up_offset + n0, &full[s]);
-        } else {
-          tma_load_2d(sb, &map_w, kb * TG_BK, n0, &full[s]);
+      unsigned it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * NOUT;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const unsigned phase = (it / STAGES) & 1;
+          ok = mbar_wait(&empty[s], phase ^ 1, err);       // a fresh barrier passes the wait for parity 1
+          if (!ok) break;
+          unsigned char* sa = stage_mem + s * tg_stage_bytes<BN>();
+          unsigned char* sb = sa + TG_BM * TG_BK * 2;
+          mbar_expect_tx(&full[s], (unsigned)tg_stage_bytes<BN>());
+          tma_load_2d(sa, &map_a, kb * TG_BK, m0, &full[s]);
+          if (EPI == TG_EPI_SILU) {
+            tma_load_2d(sb, &map_w, kb * TG_BK, n0, &full[s]);
+            tma_load_2d(sb + (BN / 2) * TG_BK * 2, &map_w, kb * TG_BK, up_offset + n0, &full[s]);
+          } else {
+            tma_load_2d(sb, &map_w, kb * TG_BK, n0, &full[s]);
+          }
         }
       }
     }
@@ -153,33 +169,46 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {
       // instruction descriptor: float32 accumulate, bfloat16 A and B, both K-major, N = BN, M = 128
       const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(TG_BM >> 4) << 24);
+      unsigned it = 0, ti = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % STAGES;
-        const unsigned phase = (kb / STAGES) & 1;
-        ok = mbar_wait(&full[s], phase, err);
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti) {
+        const unsigned buf = ti & 1, use = ti >> 1;
+        ok = mbar_wait(&acc_empty[buf], (use & 1) ^ 1, err);   // the epilogue has drained this accumulator
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        unsigned char* sa = stage_mem + s * tg_stage_bytes<BN>();
-        unsigned char* sb = sa + TG_BM * TG_BK * 2;
-        const unsigned long long da = umma_desc(sa), db = umma_desc(sb);
+        const unsigned tmem_acc = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const unsigned phase = (it / STAGES) & 1;
+          ok = mbar_wait(&full[s], phase, err);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          unsigned char* sa = stage_mem + s * tg_stage_bytes<BN>();
+          unsigned char* sb = sa + TG_BM * TG_BK * 2;
+          const unsigned long long da = umma_desc(sa), db = umma_desc(sb);
 #pragma unroll
-        for (int k = 0; k < TG_BK / 16; ++k)     // 16 bf16 = 32 bytes further along K: + 2 in the address field
-          umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
-        umma_commit(&empty[s]);                  // the stage is free once these MMAs have read it
+          for (int k = 0; k < TG_BK / 16; ++k)     // 16 bf16 = 32 bytes further along K: + 2 in the address field
+            umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+          umma_commit(&empty[s]);                  // the stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(&acc_full[buf]);       // the accumulator is complete once all MMAs are done
       }
-      umma_commit(acc_done);                     // the accumulator is complete once all MMAs are done
     }
     __syncwarp();
   } else {
     // epilogue: warp w reads TMEM lanes 32 (w % 4) .. + 31 = rows of the tile
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const int m = m0 + row;
-    const bool ok = mbar_wait(acc_done, 0, err);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      const unsigned lane_addr = tmem_acc + ((unsigned)(quarter * 32) << 16);
+    unsigned ti = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti) {
+      const int m0 = (tile % tiles_m) * TG_BM, n0 = (tile / tiles_m) * NOUT;
+      const unsigned buf = ti & 1, use = ti >> 1;
+      const int m = m0 + quarter * 32 + lane;
+      ok = mbar_wait(&acc_full[buf], use & 1, err);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const unsigned lane_addr = tmem_base + buf * BN + ((unsigned)(quarter * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < NOUT; c0 += 32) {
         unsigned r[32];
@@ -191,7 +220,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const float g = __uint_as_float(r[j]);
-            r[j] = __float_as_uint(g / (1.0f + expf(-g)) * __uint_as_float(u[j]));
+            r[j] = __float_as_uint(__fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(u[j]));
           }
         } else {
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -226,12 +255,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
         }
       }
+      // this warp has read its lanes of the accumulator: hand it back to the MMA warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
   }
 }
 
@@ -284,9 +317,19 @@ static int tg_launch(const void* a, int lda, const void* w, int ldw, int w_rows,
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((M + TG_BM - 1) / TG_BM, (N + NOUT - 1) / NOUT);
-  if (grid.y > 65535) return RLLM_E_UNSUPPORTED;
-  gemm_tcgen05_kernel<BN, EPI><<<grid, TG_THREADS, tg_smem_bytes<BN>(), stream>>>(ma, mw, out, ldo, M, N, K, up_offset, err);
+  const int tiles_m = (M + TG_BM - 1) / TG_BM;
+  const long long num_tiles = (long long)tiles_m * ((N + NOUT - 1) / NOUT);
+  if (num_tiles > (1ll << 30)) return RLLM_E_UNSUPPORTED;
+  static int num_sms = 0;
+  if (!num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (num_sms <= 0) num_sms = 148;
+  }
+  const int grid = (int)(num_tiles < num_sms ? num_tiles : num_sms);
+  gemm_tcgen05_kernel<BN, EPI><<<grid, TG_THREADS, tg_smem_bytes<BN>(), stream>>>(ma, mw, out, ldo, M, N, K, up_offset,
+                                                                                  tiles_m, (int)num_tiles, err);
   RLLM_LAUNCH_CHECK();
   return 0;
 }
@@ -299,12 +342,21 @@ RLLM_EXPORT int rllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
   if (K <= 0 || lda < K || ldw < K || ldo < N || !err) return RLLM_E_BADARG;
   // TMA: 16-byte aligned bases and row strides
   if (K % 8 || lda % 8 || ldw % 8 || (((uintptr_t)a | (uintptr_t)w) & 15)) return RLLM_E_UNSUPPORTED;
+  // 128 x 256 tiles unless 128 x 128 tiles fill the SMs' last round better
+  bool wide = N > 128;
+  if (wide) {
+    const long long tm = (M + TG_BM - 1) / TG_BM, sms = 148;
+    const long long t256 = tm * ((N + 255) / 256), t128 = tm * ((N + 127) / 128);
+    const double e256 = (double)t256 / (double)(((t256 + sms - 1) / sms) * sms);
+    const double e128 = (double)t128 / (double)(((t128 + sms - 1) / sms) * sms);
+    if (e128 > e256 * 1.6) wide = false;     // the narrow tile re-reads A twice as often: only for a big gain
+  }
   switch (epilogue) {
     case TG_EPI_BF16:
-      if (N > 128) return tg_launch<256, TG_EPI_BF16>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
+      if (wide) return tg_launch<256, TG_EPI_BF16>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
       return tg_launch<128, TG_EPI_BF16>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
     case TG_EPI_F32:
-      if (N > 128) return tg_launch<256, TG_EPI_F32>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
+      if (wide) return tg_launch<256, TG_EPI_F32>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
       return tg_launch<128, TG_EPI_F32>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
     case TG_EPI_SILU:
       return tg_launch<256, TG_EPI_SILU>(a, lda, w, ldw, 2 * N, out, ldo, M, N, K, N, err, stream);
