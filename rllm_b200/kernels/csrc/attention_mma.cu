@@ -698,3 +698,55 @@ RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, v
   }
   return RLLM_E_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------
+// The same decode attention for callers that cannot allocate: the scratch lives
+// in this library's own device memory.  See attention_decode_static.h for who
+// needs this and for the rules; nothing like it exists in the reference.
+// ---------------------------------------------------------------------------
+#include "attention_decode_static.h"
+
+// partial results first, then the counters; fixed size, one per GPU that loads the library
+static __device__ __align__(256) float rllm_decode_static_scratch[RLLM_DECODE_STATIC_FLOATS + RLLM_DECODE_STATIC_COUNTERS];
+
+// Device address of the scratch array on the current device.  In host code the
+// array's name is only a stand-in; a kernel must be given the address that
+// cudaGetSymbolAddress reports.  Looked up once per device.
+static int decode_static_address(float** ptr) {
+  static float* cached[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return RLLM_E_UNSUPPORTED;
+  if (!cached[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, rllm_decode_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    cached[dev] = (float*)p;
+  }
+  *ptr = cached[dev];
+  return 0;
+}
+
+RLLM_EXPORT int rllm_attention_decode_bf16_static(void* qkv, int q_stride, void* out, void* kcache, void* vcache,
+                                                  const int* block_table, int max_blocks, const int* seq_lens,
+                                                  int num_seqs, int max_seq_len, int nq, int nkv, int d,
+                                                  int page_size, int num_pages, int window, float scale,
+                                                  const double* inv_freq, int rotary_dim, int write_kv, int* err,
+                                                  cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || d <= 0 || max_seq_len <= 0) return RLLM_E_BADARG;
+  const long long need = rllm_attention_decode_workspace(num_seqs, nq, d, max_seq_len);
+  if (need > RLLM_DECODE_STATIC_FLOATS || (long long)num_seqs * nkv > RLLM_DECODE_STATIC_COUNTERS)
+    return RLLM_E_STATIC_TOO_LARGE;
+  float* scratch = nullptr;
+  int rc = decode_static_address(&scratch);
+  if (rc) return rc;
+  int* counters = (int*)(scratch + RLLM_DECODE_STATIC_FLOATS);
+  // the merge counters must start at zero; an earlier call that was cut short may have left them set
+  cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)num_seqs * nkv * sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
+  return rllm_attention_decode_bf16(qkv, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs,
+                                    max_seq_len, nq, nkv, d, page_size, num_pages, window, scale, inv_freq,
+                                    rotary_dim, write_kv, scratch, counters, err, stream);
+}
