@@ -106,6 +106,7 @@ class EngineCore:
         self.eos_token_ids = tuple(spec.eos_token_ids)
         self._arrivals = itertools.count()
         self.num_steps = 0
+        self._unchecked = 0
         self.last_schedule: Optional[SchedulerOutput] = None
 
     # ------------------------------------------------------------------
@@ -138,19 +139,31 @@ class EngineCore:
         self.num_steps += 1
         if not sched.scheduled:
             return []
-        entries, rows, sampled_reqs = [], [], []
+        entries, sampled_reqs = [], []
+        plain_greedy = True            # every sampled row: argmax of untouched logits
         for s in sched.scheduled:
             req = s.request
             toks = req.tokens(s.start, s.num_tokens)
             entries.append(StepEntry(req.request_id, toks, s.start, [s.num_tokens - 1] if s.want_logits else []))
             if s.want_logits:
-                ctx_needed = req.params.edits_logits
-                rows.append(SamplingRow(req.params, req.seed, len(req.output_token_ids),
-                                        req.all_token_ids if ctx_needed else (), self.eos_token_ids))
                 sampled_reqs.append(req)
+                p = req.params
+                plain_greedy = plain_greedy and p.greedy and not p.edits_logits
         logits = self.runner.step(entries)
-        tokens = self.sampler.sample(logits, rows).tolist() if rows else []
-        self.runner.check_errors()
+        if not sampled_reqs:
+            tokens = []
+        elif plain_greedy:
+            tokens = self.sampler.greedy(logits).tolist()
+        else:
+            rows = [SamplingRow(r.params, r.seed, len(r.output_token_ids),
+                                r.all_token_ids if r.params.edits_logits else (), self.eos_token_ids)
+                    for r in sampled_reqs]
+            tokens = self.sampler.sample(logits, rows).tolist()
+        # the kernels' error words cost a device read each: every step of a prompt, every 32nd decode step
+        self._unchecked += 1
+        if self._unchecked >= 32 or sched.num_prefill_tokens or any(t < 0 for t in tokens):
+            self.runner.check_errors()
+            self._unchecked = 0
         self.scheduler.after_step(sched)
         outputs = []
         for req, tok in zip(sampled_reqs, tokens):

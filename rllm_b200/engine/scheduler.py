@@ -124,6 +124,7 @@ class Scheduler:
         self.requests: Dict[Hashable, Request] = {}
         self.num_preemptions = 0
         self.prefix_hit_tokens = 0
+        self._windowed = any(getattr(cache.needs[g], "window", None) is not None for g in cache.paged)
 
     # ------------------------------------------------------------------
     def add_request(self, req: Request) -> None:
@@ -184,6 +185,12 @@ class Scheduler:
             if n <= 0:
                 continue
             if n < req.num_tokens - req.num_computed and not self.config.enable_chunked_prefill:
+                continue
+            # a decoding request needs a new page only when its next token opens one (and a window, if any
+            # group has one, gives pages back on the way): skip the page bookkeeping otherwise
+            if n == 1 and not self._windowed and req.num_computed % self.cache.page_size != 0:
+                out.scheduled.append(Scheduled(req, req.num_computed, 1, req.num_computed + 1 == req.num_tokens))
+                budget -= 1
                 continue
             while not self.cache.ensure(req.request_id, req.num_computed, req.num_computed + n):
                 victim = max(self.running, key=lambda r: r.arrival)

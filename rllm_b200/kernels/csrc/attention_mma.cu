@@ -228,7 +228,7 @@ __device__ __forceinline__ void softmax_tile(float (*s)[4], float (*o)[4], float
 // prefill
 // ---------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(NTHREADS)
+__global__ void __launch_bounds__(NTHREADS, (D <= 64 ? 4 : 2))
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                          const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                          const int* __restrict__ block_table, int max_blocks,
@@ -246,12 +246,14 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   const int bq = BM / g;               // query tokens per tile (rows beyond bq * g stay idle)
   const int kvh = blockIdx.y;
   // which (sequence, tile) is this CTA?
+  // CTAs are handed out in order of blockIdx: the last tiles of a sequence see the most keys, so
+  // they get the lowest indices and start first
   int s = -1, tile = 0;
   {
     int left = blockIdx.x;
     for (int i = seq_begin; i < seq_end; ++i) {
       const int n = (q_start[i + 1] - q_start[i] + bq - 1) / bq;
-      if (left < n) { s = i; tile = left; break; }
+      if (left < n) { s = i; tile = n - 1 - left; break; }
       left -= n;
     }
   }
@@ -652,9 +654,9 @@ static int launch_decode_cfg(int warps, bf16* qkv, int q_stride, bf16* out, bf16
   return (int)e;
 }
 
-// Few chunks in all (small batch, short context): few warps per CTA and a deep
-// pipeline, to have enough loads in flight.  Many chunks: 4 warps per CTA and a
-// shallower pipeline, to keep more warps resident.  The choice changes no result.
+// Head sizes up to 64: 4 warps a CTA with two stages each (12 warps resident per SM) measured best
+// from batch 1 to 64.  Head size 128: a stage is twice as large; few chunks in all get one warp a
+// CTA and a deep pipeline, many get 2 warps and 3 stages.  The choice changes no result.
 template <int D>
 static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc, const int* bt, int max_blocks,
                          const int* seq_lens, int num_seqs, int nq, int nkv, int page_size, int num_pages,
@@ -663,8 +665,9 @@ static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc,
   const long long total = (long long)max_chunks * nkv * num_seqs;
 #define RLLM_DEC_ARGS qkv, q_stride, out, kc, vc, bt, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, \
       window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream
-  if (total <= 148 * 6) return launch_decode_cfg<D, 4>(D >= 128 ? 1 : 2, RLLM_DEC_ARGS);
-  return launch_decode_cfg<D, 2>(4, RLLM_DEC_ARGS);
+  if (D < 128) return launch_decode_cfg<D, 2>(4, RLLM_DEC_ARGS);
+  if (total <= 148 * 6) return launch_decode_cfg<D, 4>(1, RLLM_DEC_ARGS);
+  return launch_decode_cfg<D, 3>(2, RLLM_DEC_ARGS);
 }
 
 // Decode: sequences 0 .. num_seqs-1 with one query token each.  Row s of qkv

@@ -85,6 +85,13 @@ class Sampler:
                            self._dev(np.asarray(sup_rows, np.int32)) if sup_rows else None,
                            self._dev(np.asarray(sup_tok, np.int32)) if sup_rows else None)
 
+    def greedy(self, logits: torch.Tensor) -> torch.Tensor:
+        """int32 [R]: the lowest index of the largest logit of every row."""
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=self.device)
+        if logits.shape[0]:
+            ops.argmax(logits, out)
+        return out
+
     @torch.no_grad()
     def sample(self, logits: torch.Tensor, rows: Sequence[SamplingRow]) -> torch.Tensor:
         """int32 [R] next tokens on the device.  ``logits`` float32 [R, V] may be
