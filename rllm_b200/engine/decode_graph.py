@@ -86,6 +86,21 @@ class DecodeGraph:
 
     def fill(self, entries) -> None:
         """Pack the step's inputs into the pinned buffer and copy them over."""
+        self.fill_host(entries)
+        self.commit()
+
+    def patch_tokens(self, tokens: Sequence[int]) -> None:
+        """Set the input token of every row in the pinned buffer (after fill_host, before commit)."""
+        self.host[self.r_tokens[0]:self.r_tokens[1]] = tokens
+
+    def commit(self) -> None:
+        """Copy the pinned buffer to the device buffer the graph reads."""
+        self.static.copy_(self.stage, non_blocking=True)
+        self.copied.record()
+
+    def fill_host(self, entries) -> None:
+        """Pack the step's inputs into the pinned buffer.  May run while the graph of the step before is
+        still executing: that one reads the device buffer, and the copy that fed it has completed."""
         cache, S, W = self.runner.cache, self.S, self.width
         self.copied.synchronize()
         h = self.host
@@ -106,8 +121,6 @@ class DecodeGraph:
                 n = min(len(tb), W)
                 tab[s, :n] = tb[:n]
                 tab[s, n:] = -1
-        self.static.copy_(self.stage, non_blocking=True)
-        self.copied.record()
 
     def run(self) -> torch.Tensor:
         """Logits float32 [S, vocab]; valid until the next run of this graph."""

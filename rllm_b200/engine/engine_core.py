@@ -107,6 +107,7 @@ class EngineCore:
         self._arrivals = itertools.count()
         self.num_steps = 0
         self._unchecked = 0
+        self._prepared = None          # (schedule, requests, plain_greedy, graph) of the next step, made ahead
         self.last_schedule: Optional[SchedulerOutput] = None
 
     # ------------------------------------------------------------------
@@ -124,9 +125,11 @@ class EngineCore:
         max_tokens = params.max_tokens if params.max_tokens is not None else self.max_model_len - len(prompt)
         seed = params.seed if params.seed is not None else (self.args.seed * 1000003 + arrival)
         self.scheduler.add_request(Request(rid, prompt, params, arrival, seed, max_tokens))
+        self._prepared = None          # a step prepared ahead did not know of this request
         return rid
 
     def abort_request(self, request_id: Hashable) -> bool:
+        self._prepared = None
         return self.scheduler.abort_request(request_id)
 
     def has_work(self) -> bool:
@@ -134,49 +137,99 @@ class EngineCore:
 
     # ------------------------------------------------------------------
     def step(self) -> List[RequestOutput]:
-        sched = self.scheduler.schedule()
-        self.last_schedule = sched
-        self.num_steps += 1
-        if not sched.scheduled:
-            return []
-        entries, sampled_reqs = [], []
-        plain_greedy = True            # every sampled row: argmax of untouched logits
-        for s in sched.scheduled:
-            req = s.request
-            toks = req.tokens(s.start, s.num_tokens)
-            entries.append(StepEntry(req.request_id, toks, s.start, [s.num_tokens - 1] if s.want_logits else []))
-            if s.want_logits:
-                sampled_reqs.append(req)
-                p = req.params
-                plain_greedy = plain_greedy and p.greedy and not p.edits_logits
-        logits = self.runner.step(entries)
+        prepared, self._prepared = self._prepared, None
+        if prepared is not None:
+            # the schedule and the packed inputs of this step were made while the GPU ran the last one
+            sched, sampled_reqs, plain_greedy, graph = prepared
+            self.last_schedule = sched
+            self.num_steps += 1
+            logits = self.runner.run_prepared(graph)
+        else:
+            sched = self.scheduler.schedule()
+            self.last_schedule = sched
+            self.num_steps += 1
+            if not sched.scheduled:
+                return []
+            entries, sampled_reqs = [], []
+            plain_greedy = True            # every sampled row: argmax of untouched logits
+            for s in sched.scheduled:
+                req = s.request
+                toks = req.tokens(s.start, s.num_tokens)
+                entries.append(StepEntry(req.request_id, toks, s.start, [s.num_tokens - 1] if s.want_logits else []))
+                if s.want_logits:
+                    sampled_reqs.append(req)
+                    p = req.params
+                    plain_greedy = plain_greedy and p.greedy and not p.edits_logits
+            logits = self.runner.step(entries)
         if not sampled_reqs:
-            tokens = []
+            sampled = None
         elif plain_greedy:
-            tokens = self.sampler.greedy(logits).tolist()
+            sampled = self.sampler.greedy(logits)
         else:
             rows = [SamplingRow(r.params, r.seed, len(r.output_token_ids),
                                 r.all_token_ids if r.params.edits_logits else (), self.eos_token_ids)
                     for r in sampled_reqs]
-            tokens = self.sampler.sample(logits, rows).tolist()
+            sampled = self.sampler.sample(logits, rows)
+        # The GPU is busy now.  What does not depend on the sampled tokens is done meanwhile: the
+        # bookkeeping of this step and, if the next step is sure to be a plain decode step of the same
+        # requests, its schedule and its packed inputs.
+        self.scheduler.after_step(sched)
+        nxt = self._prepare_next(sched, sampled_reqs, plain_greedy)
+        tokens = sampled.tolist() if sampled is not None else []
         # the kernels' error words cost a device read each: every step of a prompt, every 32nd decode step
         self._unchecked += 1
-        if self._unchecked >= 32 or sched.num_prefill_tokens or any(t < 0 for t in tokens):
+        if self._unchecked >= 32 or sched.num_prefill_tokens:
             self.runner.check_errors()
             self._unchecked = 0
-        self.scheduler.after_step(sched)
         outputs = []
+        any_finished = False
         for req, tok in zip(sampled_reqs, tokens):
             req.output_token_ids.append(int(tok))
             reason = self._finish_reason(req, int(tok))
             if reason is not None:
+                any_finished = True
                 self.scheduler.finish(req, RequestStatus.FINISHED_STOPPED if reason == "stop"
                                       else RequestStatus.FINISHED_LENGTH)
             n_prompt, n_out = len(req.prompt_token_ids), len(req.output_token_ids)
             outputs.append(RequestOutput(req.request_id, req.prompt_token_ids,
                                          [CompletionOutput(0, [int(tok)], reason)], reason is not None,
                                          Usage(n_prompt, n_out, n_prompt + n_out)))
+        if nxt is not None and not any_finished and not self.scheduler.waiting:
+            by_req = {r.request_id: t for r, t in zip(sampled_reqs, tokens)}
+            nxt[3].patch_tokens([by_req[s.request.request_id] for s in nxt[0].scheduled])
+            self._prepared = nxt
         return outputs
+
+    def _prepare_next(self, sched: SchedulerOutput, sampled_reqs, plain_greedy):
+        """Schedule and pack the next step ahead of time, if it is certain to be a decode step of exactly
+        the requests that were just sampled (unless one of them stops on the token being sampled, which
+        the caller finds out).  Returns (schedule, requests, plain_greedy, graph) or None."""
+        sch = self.scheduler
+        if (not self.args.enable_cuda_graphs or sch.waiting or not sampled_reqs
+                or len(sampled_reqs) != len(sched.scheduled) or len(sampled_reqs) != len(sch.running)
+                or self.cache.num_free_pages() < len(sampled_reqs)):
+            return None
+        for s in sched.scheduled:
+            r = s.request
+            if (s.num_tokens != 1 or len(r.output_token_ids) + 2 > r.max_tokens
+                    or r.num_tokens + 2 > self.max_model_len):
+                return None
+        for r in sampled_reqs:
+            r.output_token_ids.append(-1)          # stands for the token being sampled right now
+        try:
+            nsched = sch.schedule()
+            ok = (not nsched.preempted and len(nsched.scheduled) == len(sampled_reqs)
+                  and all(s.num_tokens == 1 and s.want_logits for s in nsched.scheduled))
+            graph = None
+            if ok:
+                entries = [StepEntry(s.request.request_id, [0], s.start, [0]) for s in nsched.scheduled]
+                graph = self.runner.prepare_decode(entries)
+        finally:
+            for r in sampled_reqs:
+                r.output_token_ids.pop()
+        if graph is None:
+            return None
+        return nsched, [s.request for s in nsched.scheduled], plain_greedy, graph
 
     def _finish_reason(self, req: Request, token: int) -> Optional[str]:
         p = req.params

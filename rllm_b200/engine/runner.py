@@ -203,6 +203,27 @@ class ModelRunner:
             ctx, token_ids, rows = self.build_context(entries)
             return self.model.forward(token_ids, ctx, rows, self.storage)
 
+    def prepare_decode(self, entries: Sequence[StepEntry]):
+        """Get the next decode step ready on the host while the GPU is still busy with the current one:
+        picks the captured graph of this shape and packs the inputs into its pinned buffer.  Returns the
+        graph (to be given to ``run_prepared``, after ``patch_tokens`` if the tokens were not known yet),
+        or None if this step cannot go through an already captured graph."""
+        if not self.capture_graphs or not entries or any(len(e.tokens) != 1 or len(e.want) != 1 for e in entries):
+            return None
+        if self.cache.fresh_slots:
+            return None
+        g = self._decode_graph(entries)
+        if g is None or g.graph is None:
+            return None
+        g.fill_host(entries)
+        return g
+
+    @torch.no_grad()
+    def run_prepared(self, g) -> torch.Tensor:
+        with torch.cuda.device(self.device):
+            g.commit()
+            return g.run()
+
     @torch.no_grad()
     def greedy_decode_run(self, entries: Sequence[StepEntry], num_steps: int,
                           timing: Optional[tuple] = None) -> torch.Tensor:
