@@ -378,7 +378,7 @@ template <int D, int STAGES> __host__ __device__ constexpr int dec_warp_smem() {
 }
 
 template <int D, int STAGES>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, (STAGES == 1 && D <= 64 ? 5 : 1))
 attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
                         bf16* __restrict__ kcache, bf16* __restrict__ vcache,
                         const int* __restrict__ block_table, int max_blocks,
@@ -654,8 +654,9 @@ static int launch_decode_cfg(int warps, bf16* qkv, int q_stride, bf16* out, bf16
   return (int)e;
 }
 
-// Head sizes up to 64: 4 warps a CTA with two stages each (12 warps resident per SM) measured best
-// from batch 1 to 64.  Head size 128: a stage is twice as large; few chunks in all get one warp a
+// Head sizes up to 64, 4 warps a CTA: with many chunks in all, one stage a warp, so that 20 warps are
+// resident per SM and hide each other's loads (measured best at batch 8 and 64); with few chunks, two
+// stages a warp (best at batch 1).  Head size 128: a stage is twice as large; few chunks get one warp a
 // CTA and a deep pipeline, many get 2 warps and 3 stages.  The choice changes no result.
 template <int D>
 static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc, const int* bt, int max_blocks,
@@ -665,7 +666,10 @@ static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc,
   const long long total = (long long)max_chunks * nkv * num_seqs;
 #define RLLM_DEC_ARGS qkv, q_stride, out, kc, vc, bt, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, \
       window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream
-  if (D < 128) return launch_decode_cfg<D, 2>(4, RLLM_DEC_ARGS);
+  if (D < 128) {
+    if (total >= 1024) return launch_decode_cfg<D, 1>(4, RLLM_DEC_ARGS);
+    return launch_decode_cfg<D, 2>(4, RLLM_DEC_ARGS);
+  }
   if (total <= 148 * 6) return launch_decode_cfg<D, 4>(1, RLLM_DEC_ARGS);
   return launch_decode_cfg<D, 3>(2, RLLM_DEC_ARGS);
 }

@@ -50,6 +50,26 @@ RLLM_EXPORT int rllm_embedding(const int* ids, const void* table, int table_dtyp
 // One block per output row.  The order of the additions of a row depends on
 // H and the block size only.
 // ---------------------------------------------------------------------------
+// four consecutive values, as one 16-byte (float) or 8-byte (bfloat16) access
+__device__ __forceinline__ void load4(const float* p, float* o) {
+  const float4 v = *(const float4*)p;
+  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float* o) {
+  const uint2 v = *(const uint2*)p;
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&v.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&v.y);
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+  *(float4*)p = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float d) {
+  uint2 v;
+  *(__nv_bfloat162*)&v.x = __floats2bfloat162_rn(a, b);
+  *(__nv_bfloat162*)&v.y = __floats2bfloat162_rn(c, d);
+  *(uint2*)p = v;
+}
+
 template <typename TD, typename TW, typename TO>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                const int* __restrict__ rows, const TW* __restrict__ w,
@@ -63,13 +83,36 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
   TO* o = out + (size_t)r * H;
   float ss = 0.f;
   const bool vec = (H & 3) == 0 && ((((uintptr_t)xr | (uintptr_t)o | (uintptr_t)w) & 15) == 0) &&
-                   (!dr || (((uintptr_t)dr) & 7) == 0) && sizeof(TO) <= 4;
-  if (vec) {
-    // 4 values a thread and step: the sums of a row keep the same order for every batch
+                   (!dr || (((uintptr_t)dr) & 15) == 0);
+  constexpr int KEEP = 4;                           // float4 values a thread keeps in registers
+  const bool resident = vec && H <= 4 * KEEP * (int)blockDim.x;
+  float4 kept[KEEP];
+  if (resident) {
+    // the row stays in registers between the two passes; 4 values a thread and step, so the
+    // sums of a row keep the same order for every batch
+#pragma unroll
+    for (int slot = 0; slot < KEEP; ++slot) {
+      const int i = (threadIdx.x + slot * blockDim.x) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < H) {
+        v = *(const float4*)(xr + i);
+        if (dr) {
+          float d4[4];
+          load4(dr + i, d4);
+          v.x += d4[0]; v.y += d4[1]; v.z += d4[2]; v.w += d4[3];
+          if (writeback) *(float4*)(xr + i) = v;
+        }
+        ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
+      }
+      kept[slot] = v;
+    }
+  } else if (vec) {
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
       float4 v = *(const float4*)(xr + i);
       if (dr) {
-        v.x += to_f32(dr[i]); v.y += to_f32(dr[i + 1]); v.z += to_f32(dr[i + 2]); v.w += to_f32(dr[i + 3]);
+        float d4[4];
+        load4(dr + i, d4);
+        v.x += d4[0]; v.y += d4[1]; v.z += d4[2]; v.w += d4[3];
         if (writeback) *(float4*)(xr + i) = v;
       }
       ss += v.x * v.x; ss += v.y * v.y; ss += v.z * v.z; ss += v.w * v.w;
@@ -87,16 +130,28 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
   pdl_launch();
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)H + eps);
-  if (vec) {
+  if (resident) {
+#pragma unroll
+    for (int slot = 0; slot < KEEP; ++slot) {
+      const int i = (threadIdx.x + slot * blockDim.x) * 4;
+      if (i < H) {
+        const float4 v = kept[slot];
+        float w4[4];
+        load4(w + i, w4);
+        store4(o + i, v.x * inv * w4[0], v.y * inv * w4[1], v.z * inv * w4[2], v.w * inv * w4[3]);
+      }
+    }
+  } else if (vec) {
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
       float4 v = *(const float4*)(xr + i);
       if (dr && !writeback) {
-        v.x += to_f32(dr[i]); v.y += to_f32(dr[i + 1]); v.z += to_f32(dr[i + 2]); v.w += to_f32(dr[i + 3]);
+        float d4[4];
+        load4(dr + i, d4);
+        v.x += d4[0]; v.y += d4[1]; v.z += d4[2]; v.w += d4[3];
       }
-      o[i] = from_f32<TO>(v.x * inv * to_f32(w[i]));
-      o[i + 1] = from_f32<TO>(v.y * inv * to_f32(w[i + 1]));
-      o[i + 2] = from_f32<TO>(v.z * inv * to_f32(w[i + 2]));
-      o[i + 3] = from_f32<TO>(v.w * inv * to_f32(w[i + 3]));
+      float w4[4];
+      load4(w + i, w4);
+      store4(o + i, v.x * inv * w4[0], v.y * inv * w4[1], v.z * inv * w4[2], v.w * inv * w4[3]);
     }
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
