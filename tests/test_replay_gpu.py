@@ -119,3 +119,61 @@ def test_replay_through_the_tcgen05_gemm(model_dirs, name, mode, monkeypatch):
     reqs = make_requests(name)
     got = ru.run_trace(model_dirs[name], "bfloat16", MODES[mode](reqs), cfg["vocab_size"], page_size=page)
     compare(got, plain_logits(model_dirs, name, "bfloat16"), reqs, "bfloat16", f"{name}/tcgen05/{mode}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decoding(model_dirs, name, dtype):
+    """A short prompt, then one token a step for as long as the model allows: over many pages, past
+    split and chunk edges of the decode kernels and (tiny-B) far past the rotary scaling's original
+    context.  Two more requests decode beside it, starting at other steps."""
+    cfg, _, page = TINY[name]
+    n = cfg["max_position_embeddings"] - 1
+    rng = np.random.default_rng(17)
+    reqs = {"long": [int(t) for t in rng.integers(0, cfg["vocab_size"], size=n)],
+            "mid": [int(t) for t in rng.integers(0, cfg["vocab_size"], size=n // 3)],
+            "late": [int(t) for t in rng.integers(0, cfg["vocab_size"], size=n // 5)]}
+    tb = ru.TraceBuilder()
+    fed = {k: 0 for k in reqs}
+    tb.step([("long", reqs["long"][:3])])
+    fed["long"] = 3
+    step = 0
+    while any(fed[k] < len(v) for k, v in reqs.items()):
+        entries, end = [], []
+        for k, v in reqs.items():
+            if k == "mid" and step < 10 or k == "late" and step < n // 2:
+                continue
+            if fed[k] < len(v):
+                entries.append((k, v[fed[k]:fed[k] + 1]))
+                fed[k] += 1
+                if fed[k] == len(v):
+                    end.append(k)
+        tb.step(entries, end=end)
+        step += 1
+    got = ru.run_trace(model_dirs[name], dtype, tb, cfg["vocab_size"], page_size=page)
+    model = plain_llama.read_model_dir(model_dirs[name], round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+    want = {k: model.logits(v).numpy() for k, v in reqs.items()}
+    compare(got, want, reqs, dtype, f"{name}/{dtype}/long decoding")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
+    """Sequences of 1 to 5 tokens, whole and token by token: position 0 sees only itself, and the
+    first page is only partly filled."""
+    cfg, _, page = TINY[name]
+    rng = np.random.default_rng(23)
+    reqs = {f"s{n}": [int(t) for t in rng.integers(0, cfg["vocab_size"], size=n)] for n in range(1, 6)}
+    model = plain_llama.read_model_dir(model_dirs[name], round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+    want = {k: model.logits(v).numpy() for k, v in reqs.items()}
+    whole = ru.run_trace(model_dirs[name], dtype, ru.trace_whole(reqs), cfg["vocab_size"], page_size=page)
+    compare(whole, want, reqs, dtype, f"{name}/{dtype}/first tokens whole")
+    single = ru.run_trace(model_dirs[name], dtype, ru.trace_tail_decode(reqs, tail=8), cfg["vocab_size"], page_size=page)
+    compare(single, want, reqs, dtype, f"{name}/{dtype}/first tokens one by one")
+    # all five first tokens in one step, as a batch of single-token prompts
+    tb = ru.TraceBuilder()
+    tb.step([(k, v[:1]) for k, v in reqs.items()], end=list(reqs))
+    batch = ru.run_trace(model_dirs[name], dtype, tb, cfg["vocab_size"], page_size=page)
+    for k in reqs:
+        err = np.abs(batch[(k, 0)] - want[k][0]).max() / np.abs(want[k]).max()
+        assert err <= TOL[dtype], (k, err)
