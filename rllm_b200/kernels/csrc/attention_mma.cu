@@ -244,13 +244,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   const int g = nq / nkv;
   const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
   const int bq = BM / g;               // query tokens per tile (rows beyond bq * g stay idle)
-  const int kvh = blockIdx.y;
+  const int kvh = blockIdx.x % nkv;
   // which (sequence, tile) is this CTA?
   // CTAs are handed out in order of blockIdx: the last tiles of a sequence see the most keys, so
-  // they get the lowest indices and start first
+  // they get the lowest indices (for every kv head) and start first
   int s = -1, tile = 0;
   {
-    int left = blockIdx.x;
+    int left = blockIdx.x / nkv;
     for (int i = seq_begin; i < seq_end; ++i) {
       const int n = (q_start[i + 1] - q_start[i] + bq - 1) / bq;
       if (left < n) { s = i; tile = n - 1 - left; break; }
@@ -594,7 +594,8 @@ static int launch_prefill(const bf16* q, int q_stride, bf16* out, const bf16* kc
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid(tiles, nkv);
+  if ((long long)tiles * nkv > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;
+  dim3 grid(tiles * nkv);
   attention_prefill_kernel<D><<<grid, NTHREADS, smem, stream>>>(q, q_stride, out, kc, vc, bt, max_blocks, q_start,
       seq_lens, seq_begin, seq_end, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
   RLLM_LAUNCH_CHECK();

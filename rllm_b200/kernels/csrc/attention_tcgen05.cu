@@ -1,0 +1,438 @@
+// Paged causal attention over prompt portions for bfloat16 on the tcgen05
+// tensor cores (head size 64): both products of attention, S = Q K^T and P V,
+// run as tcgen05.mma with accumulators in tensor memory.
+//
+// One CTA per (tile of 128 rows, kv head, sequence); a row is a (query token,
+// head of the kv head's group) pair, so 128 / g tokens share every K/V tile.
+//   warp 0     TMA producer: Q once (a 3-D box: 64 dims x g heads x 128/g tokens),
+//              then per 128-key tile the K and V rows of its cache pages (one 2-D
+//              box per page), into a two-stage ring; pages a sequence does not
+//              hold are skipped.
+//   warp 1     allocates TMEM (S: 128 columns, PV: 64) and issues the MMAs:
+//              S = Q K^T (128 x 128 x 64, both operands K-major), then, when the
+//              softmax warps have left P in shared memory, PV = P V (128 x 64 x
+//              128; V is the MN-major operand, straight from its cache layout).
+//   warps 2-5  softmax: thread r owns row r (= TMEM lane r): reads its 128 scores
+//              with tcgen05.ld, masks (causal, window), keeps the running max and
+//              sum in float32, writes P as bfloat16 into the swizzled A-operand
+//              layout, and adds each tile's PV to its float32 output row, rescaled
+//              when the max moved.  No shuffles: a row never leaves its thread.
+// Contract and tile alignment as in attention_mma.cu (keys in tiles of 128 at
+// absolute positions; a row's arithmetic does not depend on the batch).
+// Every mbarrier wait is bounded (bit 16 of the error word, then wind-down).
+// No cluster, no multicast.
+#include "tcgen05.cuh"
+#include <math.h>
+
+#define AT_BM 128
+#define AT_BN 128
+#define AT_D 64
+#define AT_THREADS 320
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, void* bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(tg_smem(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(z), "r"(tg_smem(bar)) : "memory");
+}
+__device__ __forceinline__ float at_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Q, two stages of K and of V, P, barriers: two CTAs fit one SM, so that one CTA's
+// softmax runs beside the other's products.
+// The two threads of a row (one in warp w, one in warp w + 4, same TMEM lane) swap one value:
+// each stores its own into column `half` of a pair of columns and reads the other's after the
+// pair's mbarrier (two arrivals, one a warp; exchange n completes phase n).  A pair of columns is
+// used again two exchanges later at the earliest, when the partner, having passed the barrier
+// between, has read it.  False if the wait ran out.
+__device__ __forceinline__ bool pair_exchange(unsigned taddr, int half, void* bar, int n, float mine, float* theirs, int* err) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr + half), "r"(__float_as_uint(mine)) : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+  if (!__all_sync(0xffffffffu, mbar_wait(bar, n & 1, err))) return false;
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  unsigned other;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(other) : "r"(taddr + (half ^ 1)) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  *theirs = __uint_as_float(other);
+  return true;
+}
+
+#define AT_SMEM_BYTES (16384 + 2 * 16384 + 2 * 16384 + 32768 + 256)
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                         const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
+                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
+                         const int* __restrict__ seq_lens, int seq_begin, int seq_end, int nq, int nkv,
+                         int page_size, int num_pages, int window, float scale_log2, int* __restrict__ err) {
+  extern __shared__ __align__(1024) unsigned char at_raw[];
+  unsigned char* base = at_raw;
+  if (tg_smem(base) & 1023u) {                    // the swizzled tiles need 1024-byte alignment
+    if (threadIdx.x == 0) atomicOr(err, 32);
+    return;
+  }
+  unsigned char* sQ = base;                       // [128 rows][64] bf16, 128B swizzle
+  unsigned char* sK = sQ + 16384;                 // 2 stages x [128 keys][64]
+  unsigned char* sV = sK + 2 * 16384;             // 2 stages x [128 keys][64]
+  unsigned char* sP = sV + 2 * 16384;             // 2 panels x [128 rows][64 keys] bf16
+  unsigned long long* bars = (unsigned long long*)(sP + 32768);
+  unsigned long long* q_full = bars;              // TMA -> MMA
+  unsigned long long* k_full = bars + 1;          // [2] TMA -> MMA
+  unsigned long long* k_empty = bars + 3;         // [2] MMA -> TMA: the scores that read the stage are done
+  unsigned long long* v_full = bars + 5;          // [2] TMA -> MMA (and the softmax warps, for the last tile)
+  unsigned long long* v_empty = bars + 7;         // [2] MMA -> TMA: the product that read the stage is done
+  unsigned long long* s_full = bars + 9;          // MMA -> softmax
+  unsigned long long* p_full = bars + 10;         // softmax (8 warps) -> MMA
+  unsigned long long* pv_full = bars + 11;        // MMA -> softmax
+  unsigned long long* s_free = bars + 12;         // softmax (8 warps) -> MMA
+  unsigned long long* xbar = bars + 13;           // [4] the two warps of a row quarter, one another
+  unsigned* tmem_slot = (unsigned*)(bars + 17);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = nq / nkv;
+  const int bq = AT_BM / g;                        // query tokens per tile
+  const int kvh = blockIdx.x % nkv;
+  // which (sequence, tile): the tiles that see the most keys get the lowest block indices, for every kv head
+  int s = -1, tile = 0;
+  {
+    int left = blockIdx.x / nkv;
+    for (int i = seq_begin; i < seq_end; ++i) {
+      const int n = (q_start[i + 1] - q_start[i] + bq - 1) / bq;
+      if (left < n) { s = i; tile = n - 1 - left; break; }
+      left -= n;
+    }
+  }
+  if (s < 0) return;
+  const int qs = q_start[s], qlen = q_start[s + 1] - qs;
+  const int pos0 = seq_lens[s] - qlen;
+  const int t0 = tile * bq;
+  const int ntok = min(bq, qlen - t0);
+  const int first_pos = pos0 + t0, last_pos = pos0 + t0 + ntok - 1;
+  const int kmin = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+  const int kend = last_pos + 1;
+  const int tile_lo = kmin / AT_BN, tile_hi = (kend + AT_BN - 1) / AT_BN;
+  const int* bt = block_table + (size_t)s * max_blocks;
+
+  // stale rows of K and V (pages that are skipped) must hold finite numbers: clear the ring once
+  for (int i = threadIdx.x; i < 4 * 16384 / 16; i += AT_THREADS) ((uint4*)sK)[i] = make_uint4(0u, 0u, 0u, 0u);
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 8);
+    mbar_init(pv_full, 1);
+    mbar_init(s_free, 8);
+    for (int i = 0; i < 4; ++i) mbar_init(&xbar[i], 2);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_v) : "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tg_smem(tmem_slot)), "r"(256) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the cleared ring, before TMA writes into it
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + AT_BN, tmem_x = tmem_o + AT_D;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 16384u);
+      tma_load_3d(sQ, &map_q, 0, kvh * g, qs + t0, q_full);
+    }
+    // Lanes 0-7 fetch the boxes of a tile (one page each).  K and V have rings of their own: a K stage is
+    // free once the scores that read it are done, a V stage once its product is, so K runs a tile further
+    // ahead.  Lane 0 polls both rings; the pages of the next tile of each are looked up ahead of time.
+    const int boxes = AT_BN / page_size;            // page_size divides 128
+    const int ntiles = tile_hi - tile_lo;
+    auto lookup = [&](int it) {
+      // the page of this lane's box in tile it, if the sequence holds it and it holds keys below kend
+      const int j = (tile_lo + it) * AT_BN + lane * page_size;
+      int page = -1;
+      if (lane < boxes && it < ntiles && j < kend) {
+        page = bt[j / page_size];
+        if (page < 0 || page >= num_pages) {
+          page = -1;
+          if (j + page_size > kmin) atomicOr(err, 4);   // a page with visible keys is missing
+        }
+      }
+      return page;
+    };
+    auto issue = [&](unsigned char* ring, const CUtensorMap* map, unsigned long long* full, int it, int page) {
+      const int st = it & 1;
+      const unsigned have = __ballot_sync(0xffffffffu, page >= 0);
+      if (lane == 0) mbar_expect_tx(&full[st], (unsigned)(__popc(have) * page_size * 128));
+      __syncwarp();
+      if (page >= 0)
+        tma_load_2d(ring + st * 16384 + lane * page_size * 128, map, 0, (page * nkv + kvh) * page_size, &full[st]);
+    };
+    int nk = 0, nv = 0;                              // tiles whose K, V have been asked for
+    int page_k = lookup(0), page_v = page_k;
+    unsigned spin = 0;
+    while (nk < ntiles || nv < ntiles) {
+      unsigned ready = 0;
+      if (lane == 0) {
+        if (nk < ntiles && mbar_test(&k_empty[nk & 1], ((nk >> 1) & 1) ^ 1)) ready |= 1u;
+        if (nv < ntiles && mbar_test(&v_empty[nv & 1], ((nv >> 1) & 1) ^ 1)) ready |= 2u;
+      }
+      ready = __shfl_sync(0xffffffffu, ready, 0);
+      if (!ready) {
+        if (++spin > TG_SPIN_LIMIT) { if (lane == 0) atomicOr(err, 16); break; }
+        continue;
+      }
+      spin = 0;
+      if (ready & 1u) { issue(sK, &map_k, k_full, nk, page_k); ++nk; page_k = lookup(nk); }
+      if (ready & 2u) { issue(sV, &map_v, v_full, nv, page_v); ++nv; page_v = lookup(nv); }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // S: float32 accumulate, bf16 x bf16, A and B K-major, M 128, N 128.
+      // PV: the same with N 64 and B (V) MN-major.
+      const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_BN >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
+      const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(AT_D >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
+      const int ntiles = tile_hi - tile_lo;
+      const unsigned long long dq = umma_desc(sQ);
+      bool ok = mbar_wait(q_full, 0, err) && mbar_wait(&k_full[0], 0, err);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned long long dk = umma_desc(sK);
+#pragma unroll
+        for (int k = 0; k < AT_D / 16; ++k) umma_bf16(tmem_s, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);
+        umma_commit(s_full);
+        umma_commit(&k_empty[0]);
+      }
+      for (int it = 0; it < ntiles && ok; ++it) {
+        const int st = it & 1;
+        if (it + 1 < ntiles) {
+          // the next tile's scores, as soon as its keys are here and the softmax warps hold this tile's scores
+          const int sn = (it + 1) & 1;
+          ok = mbar_wait(&k_full[sn], ((it + 1) >> 1) & 1, err) && mbar_wait(s_free, it & 1, err);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const unsigned long long dk = umma_desc(sK + sn * 16384);
+#pragma unroll
+          for (int k = 0; k < AT_D / 16; ++k) umma_bf16(tmem_s, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);
+          umma_commit(s_full);
+          umma_commit(&k_empty[sn]);
+        }
+        ok = mbar_wait(&v_full[st], (it >> 1) & 1, err) && mbar_wait(p_full, it & 1, err);   // P is in shared memory, O is rescaled
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned long long dv = umma_desc(sV + st * 16384);
+#pragma unroll
+        for (int kk = 0; kk < AT_BN / 16; ++kk) {     // 16 keys a step: P along K inside a 64-key panel, V two row groups on
+          const unsigned long long dp = umma_desc(sP + (kk >> 2) * 16384) + 2 * (kk & 3);
+          umma_bf16(tmem_o, dp, dv + (unsigned long long)(kk * (2048 >> 4)), idesc_pv, (it != 0) || (kk != 0));
+        }
+        umma_commit(pv_full);
+        umma_commit(&v_empty[st]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // Two threads a row: warps 2-5 take the tile's keys 0-63 (and output dims 0-31), warps 6-9
+    // keys 64-127 (dims 32-63); warp w and warp w + 4 own the same 32 rows (TMEM lanes) and
+    // exchange the row's max and sum through four spare TMEM columns (shared memory is full:
+    // two CTAs share an SM), under a barrier of their own.
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;               // this thread's row of the tile
+    const int tl = r / g, hl = r - tl * g;
+    const bool live = tl < ntok;
+    // rows behind the portion's last token compute like the others; their result is not stored
+    const int pos = pos0 + t0 + tl;
+    const int row_hi = pos + 1;
+    const int row_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    // tiles all of whose keys every row sees need no mask
+    const int clear_lo = (window > 0 && pos0 + t0 + bq - window > 0) ? pos0 + t0 + bq - window : 0;
+    const int clear_hi = first_pos + 1;
+    float m_ref = -INFINITY, l = 0.f;
+    const unsigned lane_sel = (unsigned)(quarter * 32) << 16;
+    const int ntiles = tile_hi - tile_lo;
+    constexpr int HC = AT_BN / 2;                    // keys a thread
+    bool ok = true;
+    for (int it = 0; it < ntiles; ++it) {
+      const int j0 = (tile_lo + it) * AT_BN;
+      ok = __all_sync(0xffffffffu, mbar_wait(s_full, it & 1, err));
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      float sc[HC];
+#pragma unroll
+      for (int c0 = 0; c0 < HC; c0 += 32) tmem_ld32(tmem_s + lane_sel + half * HC + c0, (unsigned*)(sc + c0));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free);
+      if (!(j0 >= clear_lo && j0 + AT_BN <= clear_hi)) {
+        const unsigned lo_rel = (unsigned)(row_lo - j0 - half * HC), span = (unsigned)(row_hi - row_lo);
+#pragma unroll
+        for (int j = 0; j < HC; ++j)
+          if (!((unsigned)j - lo_rel < span)) sc[j] = -INFINITY;
+      }
+      float mx0 = sc[0], mx1 = sc[1], mx2 = sc[2], mx3 = sc[3];
+#pragma unroll
+      for (int j = 4; j < HC; j += 4) {
+        mx0 = fmaxf(mx0, sc[j]); mx1 = fmaxf(mx1, sc[j + 1]); mx2 = fmaxf(mx2, sc[j + 2]); mx3 = fmaxf(mx3, sc[j + 3]);
+      }
+      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      float mx_other;
+      ok = pair_exchange(tmem_x + lane_sel + (it & 1) * 2, half, &xbar[quarter], it, mx, &mx_other, err);
+      if (!ok) break;
+      mx = fmaxf(mx, mx_other) * scale_log2;
+      // The reference point of the exponentials moves only when the max has grown by more than 2^8: until
+      // then the old one serves (probabilities up to 256, the sum and the output scale alike), and the
+      // output accumulated so far needs no rescaling.  The rule looks at this row's scores only.
+      const bool moves = mx > m_ref + 8.0f;
+      float corr = 1.0f;
+      if (moves) {
+        corr = at_ex2(m_ref - mx);                    // from -inf: 0, and nothing has been summed yet
+        m_ref = mx;
+        l *= corr;
+      }
+      const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
+      unsigned pk[HC / 2];
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+      for (int j = 0; j < HC; j += 4) {
+        const float p0 = at_ex2(fmaf(sc[j], scale_log2, -m_safe)), p1 = at_ex2(fmaf(sc[j + 1], scale_log2, -m_safe));
+        const float p2 = at_ex2(fmaf(sc[j + 2], scale_log2, -m_safe)), p3 = at_ex2(fmaf(sc[j + 3], scale_log2, -m_safe));
+        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+        pk[j / 2] = *(unsigned*)&h0;
+        pk[j / 2 + 1] = *(unsigned*)&h1;
+      }
+      l += (sum0 + sum1) + (sum2 + sum3);
+      // the product of the tile before has to be through: it read P, and it wrote the output that is rescaled here
+      if (it > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (it - 1) & 1, err));
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, moves)) {
+          unsigned v[32];
+          tmem_ld32(tmem_o + lane_sel + half * 32, v);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+          tmem_st32(tmem_o + lane_sel + half * 32, v);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+      unsigned char* prow = sP + half * 16384 + r * 128;   // this thread's keys are one 64-key panel
+#pragma unroll
+      for (int c = 0; c < HC / 8; ++c)                 // 8 keys = one 16-byte chunk of the row's 128 bytes
+        *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      // rows of V at and behind the last visible key were never written by this sequence: whatever
+      // they hold must not reach the product (0 x inf), so they are cleared before P V is issued
+      if (it == ntiles - 1) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&v_full[it & 1], (it >> 1) & 1, err));   // V has landed: nothing overwrites the zeros
+        if (!ok) break;
+      }
+      if (it == ntiles - 1 && j0 + r >= kend) {
+        uint4* vrow = (uint4*)(sV + (it & 1) * 16384 + r * 128 + half * 64);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      // hand P to the MMA warp: make the shared-memory writes visible to the async proxy first
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (ntiles - 1) & 1, err));
+    // the row's sum is the two halves' sums (an exchange slot no tile is using: the pair's last
+    // exchange was for tile ntiles-1, this one takes the other parity)
+    float lother = 0.f;
+    if (ok) ok = pair_exchange(tmem_x + lane_sel + (ntiles & 1) * 2, half, &xbar[quarter], ntiles, l, &lother, err);
+    const float lsum = half == 0 ? l + lother : lother + l;
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
+      bf16* orow = out + ((size_t)(qs + t0 + tl) * nq + kvh * g + hl) * AT_D + half * 32;
+      unsigned v[32];
+      tmem_ld32(tmem_o + lane_sel + half * 32, v);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (live) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+          uint4 w;
+          __nv_bfloat162* h = (__nv_bfloat162*)&w;
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            h[q] = __floats2bfloat162_rn(__uint_as_float(v[c + 2 * q]) * inv, __uint_as_float(v[c + 2 * q + 1]) * inv);
+          *(uint4*)(orow + c) = w;
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(256) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+static int at_encode(CUtensorMap* map, int rank, const void* ptr, const cuuint64_t* dims, const cuuint64_t* strides,
+                     const cuuint32_t* box) {
+  tg_encode_fn enc = tg_get_encode();
+  if (!enc) return RLLM_E_UNSUPPORTED;
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(ptr), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : RLLM_E_BADARG;
+}
+
+// Sequences seq_begin .. seq_end-1 of the step; q rows q_start[s] .. q_start[s+1]-1 (num_q_rows rows of
+// q exist in all); head size 64; page size 16, 32, 64 or 128; nq / nkv a power of two up to 128.
+RLLM_EXPORT int rllm_attention_prefill_tcgen05(const void* q, int q_stride, int num_q_rows, void* out,
+                                               const void* kcache, const void* vcache, const int* block_table,
+                                               int max_blocks, const int* q_start, const int* seq_lens,
+                                               int seq_begin, int seq_end, int num_tokens, int nq, int nkv, int d,
+                                               int page_size, int num_pages, int window, float scale, int* err,
+                                               cudaStream_t stream) {
+  if (seq_end <= seq_begin || num_tokens <= 0) return 0;
+  if (nq <= 0 || nkv <= 0 || nq % nkv || num_pages <= 0 || max_blocks <= 0 || window < 0 || !(scale > 0.f) || !err)
+    return RLLM_E_BADARG;
+  const int g = nq / nkv;
+  if (d != AT_D || !(page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128) ||
+      (g & (g - 1)) || g > AT_BM || q_stride % 8 || (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache) & 15))
+    return RLLM_E_UNSUPPORTED;
+  CUtensorMap mq, mk, mv;
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)AT_D, (cuuint64_t)nq, (cuuint64_t)num_q_rows};
+    cuuint64_t strides[2] = {(cuuint64_t)AT_D * 2, (cuuint64_t)q_stride * 2};
+    cuuint32_t box[3] = {AT_D, (cuuint32_t)g, (cuuint32_t)(AT_BM / g)};
+    int rc = at_encode(&mq, 3, q, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)AT_D, (cuuint64_t)num_pages * nkv * page_size};
+    cuuint64_t strides[1] = {(cuuint64_t)AT_D * 2};
+    cuuint32_t box[2] = {AT_D, (cuuint32_t)page_size};
+    int rc = at_encode(&mk, 2, kcache, dims, strides, box);
+    if (rc) return rc;
+    rc = at_encode(&mv, 2, vcache, dims, strides, box);
+    if (rc) return rc;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int bq = AT_BM / g;
+  const long long tiles = (num_tokens + bq - 1) / bq + (seq_end - seq_begin);
+  if (tiles * nkv > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;
+  dim3 grid((unsigned)(tiles * nkv));
+  attention_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(mq, mk, mv, (bf16*)out, block_table, max_blocks,
+      q_start, seq_lens, seq_begin, seq_end, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}

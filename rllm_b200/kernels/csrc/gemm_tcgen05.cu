@@ -26,8 +26,7 @@
 //
 // The reference computes these products with a library call
 // (crates/rllm-model/src/layers.rs:162-175).
-#include "common.cuh"
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 #define TG_BM 128
 #define TG_BK 64
@@ -35,71 +34,9 @@
 #define TG_EPI_BF16 0
 #define TG_EPI_F32 1
 #define TG_EPI_SILU 2
-#define TG_SPIN_LIMIT (1u << 22)
-
-__device__ __forceinline__ unsigned tg_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(void* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tg_smem(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tg_smem(bar)), "r"(bytes) : "memory");
-}
-// true when the phase with this parity has completed; false after the spin limit
-__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* err) {
-  const unsigned addr = tg_smem(bar);
-  for (unsigned spin = 0; spin < TG_SPIN_LIMIT; ++spin) {
-    unsigned done;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  atomicOr(err, 16);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, void* bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(tg_smem(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(tg_smem(bar)) : "memory");
-}
-// K-major operand tile of rows x 64 bf16 with 128-byte swizzle: rows are 128 bytes, groups
-// of 8 rows are 1024 bytes apart.  Fields: start address >> 4; leading byte offset 1
-// (unused with swizzle); stride byte offset 1024 >> 4; version 1; layout type 2 (128B swizzle).
-__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((tg_smem(tile) >> 4) & 0x3FFF);
-  d |= (unsigned long long)1 << 16;
-  d |= (unsigned long long)(1024 >> 4) << 32;
-  d |= (unsigned long long)1 << 46;
-  d |= (unsigned long long)2 << 61;
-  return d;
-}
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long da, unsigned long long db,
-                                          unsigned idesc, unsigned accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-               : "memory");
-}
-__device__ __forceinline__ void umma_commit(void* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tg_smem(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned* r) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-               "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                 "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                 "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-               : "r"(taddr) : "memory");
-}
-
 template <int BN> constexpr int tg_stages() { return BN == 256 ? 4 : 6; }
 template <int BN> constexpr int tg_stage_bytes() { return (TG_BM + BN) * TG_BK * 2; }
 template <int BN> constexpr int tg_smem_bytes() { return tg_stages<BN>() * tg_stage_bytes<BN>() + 1024 + 256; }
-
-__device__ __forceinline__ void mbar_arrive(void* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tg_smem(bar)) : "memory");
-}
 
 // EPI: 0 bfloat16 out, 1 float32 out, 2 SiLU-gate (BN must be 256; W rows n and up_offset + n pair up).
 // Persistent: CTA b takes the output tiles b, b + gridDim.x, ... (rows of tiles first, so that CTAs
@@ -271,22 +208,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
-typedef CUresult (*tg_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static tg_encode_fn tg_get_encode() {
-  static tg_encode_fn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (tg_encode_fn)p;
-  }
-  return fn;
-}
-
 // [rows, K] bf16 row-major with row stride ld (elements); box = 64 (K) x box_rows; out-of-range reads give 0
 static int tg_make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
   tg_encode_fn enc = tg_get_encode();

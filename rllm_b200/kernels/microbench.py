@@ -1,7 +1,7 @@
 """Timing of single kernels at the sizes of a model, for profiling.
 
     python -m rllm_b200.kernels.microbench attention_decode --batch 8 --context 4096
-    python -m rllm_b200.kernels.microbench attention_prefill --tokens 2048
+    python -m rllm_b200.kernels.microbench attention_prefill --tokens 2048 [--impl tcgen05]
     python -m rllm_b200.kernels.microbench gemm_small_m --rows 8
     python -m rllm_b200.kernels.microbench gemm_tcgen05 --rows 2048
 
@@ -95,11 +95,15 @@ def attention_prefill(args) -> None:
     q_start = torch.tensor([0, T], dtype=torch.int32, device=DEV)
     scale = 1 / math.sqrt(d)
 
+    fn = ops.attention_prefill_tcgen05 if args.impl == "tcgen05" else ops.attention_prefill_bf16
+
     def run(i):
-        ops.attention_prefill_bf16(q, nq * d, out, k, v, table, q_start, seq_lens, 0, 1, T, nq, nkv, d, 0, scale, err)
+        fn(q, nq * d, out, k, v, table, q_start, seq_lens, 0, 1, T, nq, nkv, d, 0, scale, err)
     us = time_us(run, args.iters)
     flops = 4 * d * nq * T * (T + 1) // 2
-    print(f"attention_prefill tokens {T}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s (causal)")
+    print(f"attention_prefill ({args.impl}) tokens {T}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s (causal)")
+    if int(err.item()):
+        print(f"error word {int(err.item())}", file=sys.stderr)
 
 
 def _shapes(args):
@@ -154,6 +158,8 @@ def main(argv=None) -> int:
     p.add_argument("--hidden", type=int, default=2048)
     p.add_argument("--intermediate", type=int, default=8192)
     p.add_argument("--page", type=int, default=16)
+    p.add_argument("--impl", choices=["mma", "tcgen05"], default="mma",
+                   help="attention_prefill: the mma.sync kernel or the tcgen05 kernel")
     args = p.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)

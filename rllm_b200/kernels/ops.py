@@ -337,6 +337,31 @@ def attention_prefill_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, kc
                                            _stream()), "attention_prefill_bf16")
 
 
+def attention_prefill_tcgen05_supported(nq: int, nkv: int, d: int, page_size: int) -> bool:
+    """The sizes the tcgen05 prompt attention takes: head size 64, pages of 16 to
+    128 keys, a power-of-two group of query heads per kv head."""
+    g = nq // nkv if nkv else 0
+    return d == 64 and page_size in (16, 32, 64, 128) and g >= 1 and nq % nkv == 0 and g & (g - 1) == 0 and g <= 128
+
+
+def attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
+                              vcache: torch.Tensor, block_table: torch.Tensor, q_start: torch.Tensor,
+                              seq_lens: torch.Tensor, seq_begin: int, seq_end: int, num_tokens: int, nq: int,
+                              nkv: int, d: int, window: int, scale: float, err: torch.Tensor) -> None:
+    """Attention of the prompt portions of sequences seq_begin .. seq_end-1 on the
+    tcgen05 tensor cores (same contract as ``attention_prefill_bf16``; ``q`` is the
+    first of ``q.shape[0]`` rows of ``q_stride`` elements)."""
+    lib = build.load_library("attention_tcgen05")
+    _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
+    assert q.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
+    _check(lib.rllm_attention_prefill_tcgen05(_ptr(q), c_int(q_stride), c_int(q.shape[0]), _ptr(out), _ptr(kcache),
+                                              _ptr(vcache), _ptr(block_table), c_int(block_table.shape[1]),
+                                              _ptr(q_start), _ptr(seq_lens), c_int(seq_begin), c_int(seq_end),
+                                              c_int(num_tokens), c_int(nq), c_int(nkv), c_int(d),
+                                              c_int(kcache.shape[2]), c_int(kcache.shape[0]), c_int(window),
+                                              c_float(scale), _ptr(err), _stream()), "attention_prefill_tcgen05")
+
+
 _decode_counters = {}
 
 
@@ -397,6 +422,14 @@ def use_mma_attention(dtype: torch.dtype, nq: int, nkv: int, d: int) -> bool:
     cases (float32, other head sizes) go to the CUDA-core kernel."""
     import os
     return dtype is torch.bfloat16 and mma_attention_takes(nq, nkv, d) and os.environ.get("RLLM_ATTENTION") != "simt"
+
+
+def use_tcgen05_attention(dtype: torch.dtype, nq: int, nkv: int, d: int, page_size: int) -> bool:
+    """Prompt portions go to the tcgen05 attention kernel when it takes the sizes;
+    RLLM_ATTENTION=mma (or simt) keeps them on the older kernels."""
+    import os
+    return (dtype is torch.bfloat16 and attention_prefill_tcgen05_supported(nq, nkv, d, page_size)
+            and os.environ.get("RLLM_ATTENTION") not in ("simt", "mma"))
 
 
 def decode_advance(token_ids: torch.Tensor, positions: torch.Tensor, seq_lens: torch.Tensor,

@@ -108,7 +108,11 @@ class PagedAttention(Mixer):
         if T > nd:
             ops.rope_kv_write(qkv[nd:], ctx.positions[nd:], ctx.token_seq[nd:], inv_freq, rd, table, cache.k,
                               cache.v, self.nq, nkv_here, self.d, ctx.err, write_kv=writes)
-            if use_mma:
+            if ops.use_tcgen05_attention(x.dtype, self.nq, self.nkv, self.d, cache.k.shape[2]):
+                ops.attention_prefill_tcgen05(qkv, stride, out, cache.k, cache.v, table, ctx.q_start, ctx.seq_lens,
+                                              nd, ctx.num_seqs, T - nd, self.nq, self.nkv, self.d, window,
+                                              self.scale, ctx.err)
+            elif use_mma:
                 ops.attention_prefill_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.q_start, ctx.seq_lens,
                                            nd, ctx.num_seqs, T - nd, self.nq, self.nkv, self.d, window,
                                            self.scale, ctx.err)

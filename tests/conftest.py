@@ -1,4 +1,4 @@
-"""Shared fixtures: two tiny Llama configurations that differ in every size and
+"""Shared fixtures: tiny Llama configurations that differ in every size and
 option, written as model folders (random weights) into a temporary folder.
 
 tiny-A: 2 layers, hidden 64, 4 heads / 2 kv heads, head_dim 16, intermediate
@@ -8,6 +8,10 @@ tiny-B: 3 layers, hidden 96, 3 heads / 1 kv head, head_dim 32, intermediate
 (no power of two, odd), theta 5e5 with llama3 scaling (factor 4, low 1, high 4,
 original 32: its 16 frequencies hit all three branches), eps 1e-6, untied
 head, pages of 8.
+tiny-C: head_dim 64 (the size the tcgen05 attention kernel takes), 2 layers,
+hidden 256, 4 heads / 2 kv heads, intermediate 200,
+vocab 311, theta 1e6, eps 1e-5, untied head, pages of 16, contexts of several
+128-key tiles.
 """
 from __future__ import annotations
 
@@ -43,7 +47,15 @@ TINY_B = {
     "max_position_embeddings": 512, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
     "hidden_act": "silu", "torch_dtype": "float32", "bos_token_id": 0, "eos_token_id": [3, 7],
 }
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8)}     # name -> (config, weight seed, page size)
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 200, "vocab_size": 311, "rope_theta": 1000000.0,
+    "rope_scaling": None, "max_position_embeddings": 640, "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "float32",
+    "bos_token_id": 1, "eos_token_id": 2,
+}
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16)}   # name -> (config, weight seed, page size)
 
 
 @pytest.fixture(scope="session")

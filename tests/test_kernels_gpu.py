@@ -253,6 +253,77 @@ def test_attention_prefill_mma(ops, err, nq, nkv, d, page, window):
     assert torch.equal(out2[a:b], out[a:b]) and float(out2[:a].abs().max()) == 0 and float(out2[b:].abs().max()) == 0
 
 
+TCGEN05_CASES = [(8, 2, 16, 0), (32, 8, 16, 0), (4, 4, 32, 0), (16, 1, 64, 0), (8, 2, 128, 300), (2, 1, 16, 70),
+                 (64, 1, 16, 0), (6, 3, 32, 129)]
+
+
+@pytest.mark.parametrize("nq,nkv,page,window", TCGEN05_CASES)
+def test_attention_prefill_tcgen05(ops, err, nq, nkv, page, window):
+    """The tcgen05 kernel for prompt portions (head size 64): portions after earlier context and whole
+    prompts, from 2 tokens to several 128-key tiles, strided q rows as in the engine.  Pages that no
+    sequence holds, and the rows of a last page behind a sequence's end, hold NaN: nothing of them
+    may reach a result."""
+    dt, d = torch.bfloat16, 64
+    lens, q_lens = [700, 64, 65, 130, 2, 385], [257, 64, 2, 129, 2, 384]
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, lens, q_lens, pages=256)
+    held = torch.zeros(256, dtype=torch.bool)
+    held[table[table >= 0].long()] = True
+    kc[~held] = float("nan")
+    vc[~held] = float("nan")
+    for s, n in enumerate(lens):
+        if n % page:
+            kc[int(table[s, n // page]), :, n % page:] = float("nan")
+            vc[int(table[s, n // page]), :, n % page:] = float("inf")
+    T = sum(q_lens)
+    stride = (nq + 2 * nkv) * d
+    qkv = torch.randn(T, stride).to(dt).to(DEV)
+    qkv[:, : nq * d] = torch.cat(qs).reshape(T, nq * d).to(DEV)
+    out = torch.zeros(T, nq * d, dtype=dt, device=DEV)
+    q_start = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=DEV)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 0.9 / math.sqrt(d)
+    assert ops.attention_prefill_tcgen05_supported(nq, nkv, d, page)
+    ops.attention_prefill_tcgen05(qkv, stride, out, kc.to(DEV), vc.to(DEV), table.to(DEV), q_start, seq_lens,
+                                  0, len(lens), T, nq, nkv, d, window, scale, err)
+    assert int(err.item()) == 0
+    off = 0
+    for s, (n, m) in enumerate(zip(lens, q_lens)):
+        want = pl.attention(qs[s].double(), ks[s].double(), vs[s].double(), torch.arange(n - m, n),
+                            window=window or None, scale=scale)
+        assert rel_err(out[off:off + m], want) <= tol(dt), (s, n, m)
+        off += m
+    # a subrange of the sequences leaves the other rows alone, and a sequence's rows do not depend on the batch
+    out2 = torch.zeros_like(out)
+    ops.attention_prefill_tcgen05(qkv, stride, out2, kc.to(DEV), vc.to(DEV), table.to(DEV), q_start, seq_lens,
+                                  2, 4, q_lens[2] + q_lens[3], nq, nkv, d, window, scale, err)
+    a, b = sum(q_lens[:2]), sum(q_lens[:4])
+    assert torch.equal(out2[a:b], out[a:b]) and float(out2[:a].abs().max()) == 0 and float(out2[b:].abs().max()) == 0
+    # a portion cut in two gives the same rows: the second half alone, after the first as context
+    s, cut = 0, 100
+    a = 0
+    q_start2 = torch.tensor([0, q_lens[s] - cut], dtype=torch.int32, device=DEV)
+    out3 = torch.zeros(q_lens[s] - cut, nq * d, dtype=dt, device=DEV)
+    ops.attention_prefill_tcgen05(qkv[a + cut:a + q_lens[s]], stride, out3, kc.to(DEV), vc.to(DEV),
+                                  table[s:s + 1].contiguous().to(DEV), q_start2, seq_lens[s:s + 1], 0, 1,
+                                  q_lens[s] - cut, nq, nkv, d, window, scale, err)
+    assert int(err.item()) == 0
+    assert rel_err(out3, out[a + cut:a + q_lens[s]].double().cpu()) <= 2e-3    # other tiles of rows: rounding only
+
+
+def test_tcgen05_attention_refuses_other_sizes(ops, err):
+    from rllm_b200.kernels.ops import KernelError
+    assert not ops.attention_prefill_tcgen05_supported(8, 2, 128, 16)
+    assert not ops.attention_prefill_tcgen05_supported(6, 2, 64, 16)      # groups of 3
+    assert not ops.attention_prefill_tcgen05_supported(8, 2, 64, 8)
+    q = torch.zeros(4, 6 * 64, device=DEV, dtype=torch.bfloat16)
+    kc = torch.zeros(4, 2, 16, 64, device=DEV, dtype=torch.bfloat16)
+    table = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
+    qs = torch.tensor([0, 4], dtype=torch.int32, device=DEV)
+    sl = torch.tensor([4], dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="no kernel"):
+        ops.attention_prefill_tcgen05(q, 6 * 64, torch.empty_like(q), kc, kc, table, qs, sl, 0, 1, 4, 6, 2, 64, 0, 1.0, err)
+
+
 @pytest.mark.parametrize("nq,nkv,d,page,window", MMA_CASES)
 def test_attention_decode_mma(ops, err, nq, nkv, d, page, window):
     dt = torch.bfloat16
@@ -280,18 +351,18 @@ def test_attention_decode_mma(ops, err, nq, nkv, d, page, window):
     assert torch.equal(alone[0], outs[0][4])
 
 
-@pytest.mark.parametrize("kind", ["prefill", "decode"])
+@pytest.mark.parametrize("kind", ["prefill", "decode", "tcgen05"])
 def test_mma_attention_finds_one_far_key(ops, err, kind):
     """One key among a thousand, at a tile's, split's or page's edge, is made to
     dominate: the output must be its value."""
     dt = torch.bfloat16
     nq, nkv, d, page = 8, 2, 64, 16
     n = 1100
-    m = 1 if kind == "decode" else 5
+    m = {"decode": 1, "prefill": 5, "tcgen05": 40}[kind]
     ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, [n], [m], pages=128, seed=9)
     seq_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
     q_start = torch.tensor([0, m], dtype=torch.int32, device=DEV)
-    for target in (0, 63, 64, 255, 256, 511, 512, 1023, 1024, n - m - 1, n - m):
+    for target in (0, 63, 64, 127, 128, 255, 256, 511, 512, 1023, 1024, n - m - 1, n - m):
         kc2, qq = kc.clone(), qs[0].clone()
         pg = int(table[0, target // page])
         kc2[pg, :, target % page] = 0
@@ -303,8 +374,9 @@ def test_mma_attention_finds_one_far_key(ops, err, kind):
             ops.attention_decode_bf16(q, nq * d, out, kc2.to(DEV), vc.to(DEV), table.to(DEV), seq_lens, 1, n,
                                       nq, nkv, d, 0, 1.0, err)
         else:
-            ops.attention_prefill_bf16(q, nq * d, out, kc2.to(DEV), vc.to(DEV), table.to(DEV), q_start, seq_lens,
-                                       0, 1, m, nq, nkv, d, 0, 1.0, err)
+            fn = ops.attention_prefill_tcgen05 if kind == "tcgen05" else ops.attention_prefill_bf16
+            fn(q, nq * d, out, kc2.to(DEV), vc.to(DEV), table.to(DEV), q_start, seq_lens,
+               0, 1, m, nq, nkv, d, 0, 1.0, err)
         want = vs[0][target].repeat_interleave(nq // nkv, dim=0).reshape(1, nq * d).expand(m, -1)
         assert rel_err(out, want) <= tol(dt), target
 

@@ -18,12 +18,13 @@ pytestmark = pytest.mark.gpu
 # max |engine - plain| over a request's logits, relative to max |plain|
 TOL = {"float32": 1e-4, "bfloat16": 2e-2}
 
-LENGTHS = {"A": [5, 12, 17, 70, 100, 33, 64, 49], "B": [1, 31, 70, 150, 300, 97, 2, 210]}
+LENGTHS = {"A": [5, 12, 17, 70, 100, 33, 64, 49], "B": [1, 31, 70, 150, 300, 97, 2, 210],
+           "C": [3, 130, 257, 400, 129, 64, 500, 33]}
 
 
 def make_requests(name: str):
     cfg, _, _ = TINY[name]
-    rng = np.random.default_rng(1 if name == "A" else 3)
+    rng = np.random.default_rng({"A": 1, "B": 3, "C": 8}[name])
     return {f"r{i}": [int(t) for t in rng.integers(0, cfg["vocab_size"], size=n)]
             for i, n in enumerate(LENGTHS[name])}
 
@@ -119,6 +120,30 @@ def test_replay_through_the_tcgen05_gemm(model_dirs, name, mode, monkeypatch):
     reqs = make_requests(name)
     got = ru.run_trace(model_dirs[name], "bfloat16", MODES[mode](reqs), cfg["vocab_size"], page_size=page)
     compare(got, plain_logits(model_dirs, name, "bfloat16"), reqs, "bfloat16", f"{name}/tcgen05/{mode}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", list(MODES))
+def test_replay_with_head_size_64(model_dirs, dtype, mode):
+    """tiny-C has the head size of the tcgen05 attention kernel: in bfloat16 its prompt portions
+    run there, over several 128-key tiles, in every way of cutting."""
+    cfg, _, page = TINY["C"]
+    reqs = make_requests("C")
+    got = ru.run_trace(model_dirs["C"], dtype, MODES[mode](reqs), cfg["vocab_size"], page_size=page)
+    compare(got, plain_logits(model_dirs, "C", dtype), reqs, dtype, f"C/{dtype}/{mode}")
+
+
+def test_attention_kernels_agree_through_replay(model_dirs, monkeypatch):
+    """RLLM_ATTENTION=mma keeps prompt portions on the mma.sync kernel: the same trace through
+    both kernels gives logits that differ by bfloat16 rounding only."""
+    cfg, _, page = TINY["C"]
+    reqs = make_requests("C")
+    a = ru.run_trace(model_dirs["C"], "bfloat16", MODES["portions"](reqs), cfg["vocab_size"], page_size=page)
+    monkeypatch.setenv("RLLM_ATTENTION", "mma")
+    b = ru.run_trace(model_dirs["C"], "bfloat16", MODES["portions"](reqs), cfg["vocab_size"], page_size=page)
+    compare(b, plain_logits(model_dirs, "C", "bfloat16"), reqs, "bfloat16", "C/mma/portions")
+    worst = max(float(np.abs(a[k] - b[k]).max() / np.abs(b[k]).max()) for k in a)
+    assert 0 < worst <= TOL["bfloat16"], worst       # not the same kernel, and close
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
