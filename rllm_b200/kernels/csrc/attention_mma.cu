@@ -373,8 +373,30 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 #define DEC_TILES 4      // tiles per chunk
 #define CHUNK (DEC_BN * DEC_TILES)
 
+// a warp's shared memory: STAGES x (K tile, V tile), the Q tile [16][D], the cache row of each of the
+// chunk's keys, cosines and sines
 template <int D, int STAGES> __host__ __device__ constexpr int dec_warp_smem() {
-  return STAGES * 2 * DEC_BN * D * 2 + DEC_BN * 8 + (D < 32 ? 32 : D) * 4;
+  return STAGES * 2 * DEC_BN * D * 2 + 16 * D * 2 + CHUNK * 4 + (D < 32 ? 32 : D) * 4;
+}
+
+// Copy `rows` key rows of K and of V (cache row numbers in rowidx, -1: zero-fill) into two swizzled tiles.
+template <int D>
+__device__ __forceinline__ void copy_kv_rows(bf16* tile_k, bf16* tile_v, const bf16* __restrict__ kcache,
+                                             const bf16* __restrict__ vcache, const int* rowidx, int rows, int lane) {
+  constexpr int C = D / 8;
+  const int c = lane % C;
+  constexpr int rstep = 32 / C;
+  const bf16* kcol = kcache + c * 8;
+  const bf16* vcol = vcache + c * 8;
+#pragma unroll 4
+  for (int r = lane / C; r < rows; r += rstep) {
+    const int row = rowidx[r];
+    const bool ok = row >= 0;
+    const long long off = (long long)row * D;
+    const int d = r * D + swz<D>(r, c) * 8;
+    cp_async16(tile_k + d, ok ? kcol + off : kcache, ok);
+    cp_async16(tile_v + d, ok ? vcol + off : vcache, ok);
+  }
 }
 
 template <int D, int STAGES>
@@ -387,14 +409,18 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
                         int rotary_dim, int write_kv, float* __restrict__ ws_o, float* __restrict__ ws_ml,
                         int* __restrict__ counters, int* __restrict__ err) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned char* mine = smem_raw + (size_t)warp * dec_warp_smem<D, STAGES>();
   bf16* sW = (bf16*)mine;                                          // STAGES x (K [32][D], V [32][D])
-  bf16* sQ = sW + (STAGES - 1) * 2 * DEC_BN * D;                   // [16][D], over the last stage's K tile: that
-                                                                   // stage is first filled after Q is in registers
-  long long* sOff = (long long*)(sW + STAGES * 2 * DEC_BN * D);    // [32] row offsets
-  float* sCS = (float*)(sOff + DEC_BN);                            // cos[D/2], sin[D/2]
+  bf16* sQ = sW + STAGES * 2 * DEC_BN * D;                         // [16][D]
+  int* sRowIdx = (int*)(sQ + 16 * D);                              // [CHUNK] cache row of each key of the chunk
+  float* sCS = (float*)(sRowIdx + CHUNK);                          // cos[D/2], sin[D/2]
+  // With write_kv nothing that this kernel reads before the wait below was written by the kernel
+  // before it in the stream: lengths and block tables are inputs of the step, the cache rows of
+  // earlier positions are from earlier steps (the token's own key and value come from qkv, after
+  // the wait).  So the first tiles are on their way while that kernel finishes.  Without write_kv
+  // the token's key was stored by the kernel before this one: wait first.
+  if (!write_kv) pdl_wait();
   const int g = nq / nkv;
   const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
   const int chunk = blockIdx.x * (blockDim.x >> 5) + warp, kvh = blockIdx.y, s = blockIdx.z;
@@ -416,18 +442,33 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
   const int t_lo = active ? (kmin > w0 ? (kmin - w0) / DEC_BN : 0) : 0;
   const int t_hi = active ? min(DEC_TILES, (len - w0 + DEC_BN - 1) / DEC_BN) : 0;
 
+  // where the chunk's keys lie: all block-table lookups at once
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < CHUNK / 32; ++i) {
+      const int j = w0 + i * 32 + lane;
+      int row = -1;
+      if (j >= kmin && j < read_hi) {
+        const int pi = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
+        const int pr = page_shift >= 0 ? (j & (page_size - 1)) : (j - pi * page_size);
+        const int page = bt[pi];
+        if (page < 0 || page >= num_pages) atomicOr(err, 4);
+        else row = (page * nkv + kvh) * page_size + pr;
+      }
+      sRowIdx[i * 32 + lane] = row;
+    }
+  }
+  __syncwarp();
   auto issue = [&](int t) {
     if (t < t_hi) {
       bf16* st = sW + ((t - t_lo) % STAGES) * 2 * DEC_BN * D;
-      __syncwarp();
-      kv_row_offsets(sOff, bt, w0 + t * DEC_BN, lane, kmin, read_hi, kvh, nkv, page_size, page_shift, num_pages, D, err);
-      __syncwarp();
-      copy_kv_pair<D>(st, st + DEC_BN * D, kcache, vcache, sOff, DEC_BN, lane, 32);
+      copy_kv_rows<D>(st, st + DEC_BN * D, kcache, vcache, sRowIdx + t * DEC_BN, DEC_BN, lane);
     }
     cp_async_commit();
   };
 #pragma unroll
-  for (int i = 0; i < STAGES - 1; ++i) issue(t_lo + i);
+  for (int i = 0; i < STAGES; ++i) issue(t_lo + i);
+  if (write_kv) pdl_wait();
 
   for (int i = lane; i < half; i += 32) rope_cos_sin(pos, inv_freq[i], &sCS[i], &sCS[half + i]);
   __syncwarp();
@@ -470,7 +511,6 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
     for (int t = t_lo; t < t_hi; ++t) {
       bf16* sK = sW + ((t - t_lo) % STAGES) * 2 * DEC_BN * D;
       bf16* sV = sK + DEC_BN * D;
-      issue(t + STAGES - 1);
       cp_async_wait<STAGES - 1>();
       __syncwarp();
       const int j0 = w0 + t * DEC_BN;
@@ -499,6 +539,8 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
       qk_tile<D, DEC_BN / 8>(sc, qf, sK, lane);
       softmax_tile<D / 8, DEC_BN / 8>(sc, o, m, l, j0, row_lo, row_hi, scale_log2, lane);
       pv_tile<D, DEC_BN / 8>(o, sc, sV, lane);
+      __syncwarp();                // every lane is through with this stage
+      issue(t + STAGES);
     }
   }
   cp_async_wait<0>();
@@ -695,6 +737,7 @@ RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, v
   if (!mma_supported(nq, nkv, d) || nq / nkv > 16) return RLLM_E_UNSUPPORTED;
   const int max_splits = (max_seq_len + CHUNK - 1) / CHUNK;
   if (max_splits > 65535 * 4 || num_seqs > 65535) return RLLM_E_UNSUPPORTED;
+  if ((long long)num_pages * nkv * page_size > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;   // cache rows are counted in an int
 #define RLLM_DECODE(DD) return launch_decode<DD>((bf16*)qkv, q_stride, (bf16*)out, (bf16*)kcache, (bf16*)vcache, \
       block_table, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, window, scale, max_splits, \
       inv_freq, rotary_dim, write_kv, workspace, counters, err, stream)
