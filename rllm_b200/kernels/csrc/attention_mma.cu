@@ -407,7 +407,7 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
                         const int* __restrict__ seq_lens, int nq, int nkv, int page_size, int num_pages,
                         int window, float scale_log2, int max_chunks, const double* __restrict__ inv_freq,
                         int rotary_dim, int write_kv, float* __restrict__ ws_o, float* __restrict__ ws_ml,
-                        int* __restrict__ counters, int* __restrict__ err) {
+                        int* __restrict__ counters, int* __restrict__ err, int tail_from) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned char* mine = smem_raw + (size_t)warp * dec_warp_smem<D, STAGES>();
@@ -469,6 +469,8 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
 #pragma unroll
   for (int i = 0; i < STAGES; ++i) issue(t_lo + i);
   if (write_kv) pdl_wait();
+  // no CTA of this grid is still to come once its last wave runs: the stream's next kernel may come in
+  if ((int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) >= tail_from) pdl_launch();
 
   for (int i = lane; i < half; i += 32) rope_cos_sin(pos, inv_freq[i], &sCS[i], &sCS[half + i]);
   __syncwarp();
@@ -691,9 +693,13 @@ static int launch_decode_cfg(int warps, bf16* qkv, int q_stride, bf16* out, bf16
   float* ws_o = ws;
   float* ws_ml = ws + (size_t)num_seqs * nq * max_chunks * D;
   dim3 grid((max_chunks + warps - 1) / warps, nkv, num_seqs);
+  static int resident[5];        // by number of warps
+  if (!resident[warps]) resident[warps] = rllm_resident_ctas(attention_decode_kernel<D, STAGES>, 32 * warps, smem) + 1;
+  const long long ctas = (long long)grid.x * grid.y * grid.z;
+  const int tail_from = (int)(ctas > resident[warps] - 1 ? ctas - (resident[warps] - 1) : 0);
   cudaError_t e = rllm_launch_pdl(attention_decode_kernel<D, STAGES>, grid, dim3(32 * warps), smem, stream, qkv,
       q_stride, out, kc, vc, bt, max_blocks, seq_lens, nq, nkv, page_size, num_pages, window,
-      scale * 1.4426950408889634f, max_chunks, inv_freq, rotary_dim, write_kv, ws_o, ws_ml, counters, err);
+      scale * 1.4426950408889634f, max_chunks, inv_freq, rotary_dim, write_kv, ws_o, ws_ml, counters, err, tail_from);
   return (int)e;
 }
 

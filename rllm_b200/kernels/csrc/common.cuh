@@ -74,6 +74,9 @@ __device__ __forceinline__ void rope_cos_sin(int pos, double inv_freq, float* c,
 // writes) overlaps the tail of its predecessor.  pdl_wait returns when the
 // predecessor has completed and its writes are visible; without a predecessor that
 // was launched this way both are no-ops.
+// Rule of this code base: a kernel calls pdl_launch only after its own pdl_wait.  Then,
+// when a kernel starts, every kernel but the one directly ahead of it has completed, and
+// what it reads before its own pdl_wait may include what those earlier kernels wrote.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -97,6 +100,19 @@ static inline cudaError_t rllm_launch_pdl(void (*kernel)(KArgs...), dim3 grid, d
   cfg.attrs = attr;
   cfg.numAttrs = rllm_pdl_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// How many CTAs of `kernel` the GPU holds at once.  CTAs are handed out in order of block
+// index, so once the last that-many CTAs of a grid have started, no CTA of it is still to
+// come: such a CTA may let the next kernel in (pdl_launch) early, since that kernel's CTAs
+// can only take room that this grid no longer needs.
+template <typename K>
+static inline int rllm_resident_ctas(K kernel, int threads, size_t smem) {
+  int per_sm = 0, dev = 0, sms = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess) return 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  return per_sm * sms;
 }
 
 // Dispatch helpers ---------------------------------------------------------

@@ -15,8 +15,8 @@
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                  float* __restrict__ out, int H, int V, int* __restrict__ err) {
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + (size_t)t * H;
@@ -73,9 +73,10 @@ __device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float
 template <typename TD, typename TW, typename TO>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ delta,
                                const int* __restrict__ rows, const TW* __restrict__ w,
-                               TO* __restrict__ out, int H, float eps, int writeback) {
+                               TO* __restrict__ out, int H, float eps, int writeback, int early_launch) {
   __shared__ float red[32];
   pdl_wait();
+  if (early_launch) pdl_launch();      // a small grid: the next kernel's CTAs find room beside it
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* xr = x + (size_t)src * H;
@@ -166,13 +167,14 @@ template <typename TD, typename TO>
 static int rmsnorm_launch_w(float* x, const void* delta, const int* rows, const void* w, int w_dtype,
                             void* out, int R, int H, float eps, int writeback, cudaStream_t stream) {
   int threads = H >= 8192 ? 1024 : (H >= 2048 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64)));
+  const int early = R <= 4 * 148 ? 1 : 0;      // all of the grid's CTAs are resident at once
   cudaError_t e;
   if (w_dtype == RLLM_DT_F32)
     e = rllm_launch_pdl(rmsnorm_kernel<TD, float, TO>, dim3(R), dim3(threads), 0, stream, x, (const TD*)delta, rows,
-                        (const float*)w, (TO*)out, H, eps, writeback);
+                        (const float*)w, (TO*)out, H, eps, writeback, early);
   else if (w_dtype == RLLM_DT_BF16)
     e = rllm_launch_pdl(rmsnorm_kernel<TD, bf16, TO>, dim3(R), dim3(threads), 0, stream, x, (const TD*)delta, rows,
-                        (const bf16*)w, (TO*)out, H, eps, writeback);
+                        (const bf16*)w, (TO*)out, H, eps, writeback, early);
   else
     return RLLM_E_BADARG;
   return (int)e;
@@ -362,8 +364,8 @@ RLLM_EXPORT int rllm_silu_mul(const void* gu, void* out, int dtype, int T, int I
 __global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
                                       int* __restrict__ seq_lens, const int* __restrict__ sampled,
                                       int* __restrict__ history_row, int S) {
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= S) return;
   const int t = sampled[i];

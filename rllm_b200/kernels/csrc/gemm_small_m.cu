@@ -43,7 +43,7 @@ __device__ __forceinline__ void mma16816(float* c, unsigned a0, unsigned a1, uns
 template <int MT, int EPI>
 __global__ void __launch_bounds__(512)
 gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ W, int ldw,
-                    void* __restrict__ out, int ldo, int M, int N, int K, int up_offset) {
+                    void* __restrict__ out, int ldo, int M, int N, int K, int up_offset, int tail_from) {
   extern __shared__ float red[];                 // [warps][16][8 MT]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int gq = lane >> 2, t = lane & 3;
@@ -82,7 +82,13 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
       if (in) { a[u] = ld_stream16(w_lo + k); v[u] = ld_stream16(w_hi + k); }
     }
     // ... then x, which the kernel before this one wrote
-    if (!waited) { pdl_wait(); waited = true; }
+    if (!waited) {
+      pdl_wait();
+      waited = true;
+      // no CTA of this grid is still to come once its last wave runs: the stream's next kernel may
+      // come in and fetch its own weights while this one works
+      if ((int)blockIdx.x >= tail_from) pdl_launch();
+    }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int k = (b0 + u) * 32;
@@ -101,8 +107,8 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
         mma16816(c[i], a[u].z, v[u].z, a[u].w, v[u].w, xb[u][i].z, xb[u][i].w);
       }
   }
-  pdl_launch();                  // the stream's next kernel may start coming in now
   if (!waited) pdl_wait();       // a warp without k blocks: nothing was read, but the stores below must wait too
+  pdl_launch();                  // the stream's next kernel may start coming in now
   // partial sums of the warps -> shared memory; c[i]: rows gq, gq + 8; batch columns i*8 + 2t, 2t + 1
   float* mine = red + (size_t)warp * 16 * 8 * MT;
 #pragma unroll
@@ -151,8 +157,11 @@ static int launch_small_m(const bf16* x, int ldx, const bf16* W, int ldw, void* 
   while (warps > 1 && warps > nblocks) warps /= 2;
   while (warps > 1 && (size_t)warps * 16 * 8 * MT * sizeof(float) > 48 * 1024) warps /= 2;
   const size_t smem = (size_t)warps * 16 * 8 * MT * sizeof(float);
+  static int resident[17];       // by number of warps
+  if (!resident[warps]) resident[warps] = rllm_resident_ctas(gemm_small_m_kernel<MT, EPI>, 32 * warps, smem) + 1;
+  const int tail_from = resident[warps] > 1 ? tiles - (resident[warps] - 1) : tiles;
   cudaError_t e = rllm_launch_pdl(gemm_small_m_kernel<MT, EPI>, dim3(tiles), dim3(32 * warps), smem, stream,
-                                  x, ldx, W, ldw, out, ldo, M, N, K, up_offset);
+                                  x, ldx, W, ldw, out, ldo, M, N, K, up_offset, tail_from);
   if (e != cudaSuccess) return (int)e;
   return 0;
 }

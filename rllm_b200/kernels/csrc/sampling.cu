@@ -240,8 +240,8 @@ RLLM_EXPORT int rllm_sample(const float* logits, int R, int V, int ld, const flo
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out_tokens) {
   __shared__ ArgMax sm_arg[32];
-  pdl_launch();
   pdl_wait();
+  pdl_launch();
   const float* x = logits + (size_t)blockIdx.x * ld;
   ArgMax best; best.v = -INFINITY; best.i = 0x7fffffff;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
