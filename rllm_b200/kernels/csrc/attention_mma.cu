@@ -468,12 +468,12 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
   };
 #pragma unroll
   for (int i = 0; i < STAGES; ++i) issue(t_lo + i);
+  // the rotation's angles depend on the position alone
+  for (int i = lane; i < half; i += 32) rope_cos_sin(pos, inv_freq[i], &sCS[i], &sCS[half + i]);
   if (write_kv) pdl_wait();
   // no CTA of this grid is still to come once its last wave runs: the stream's next kernel may come in
   if ((int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) >= tail_from) pdl_launch();
 
-  for (int i = lane; i < half; i += 32) rope_cos_sin(pos, inv_freq[i], &sCS[i], &sCS[half + i]);
-  __syncwarp();
   // Q rows = heads of the group, rows >= g zero: 16-byte loads first, then the rotation in
   // shared memory (a lane rotates the pairs (i, i + half) it owns)
   for (int idx = lane; idx < 16 * (D / 8); idx += 32) {
@@ -575,41 +575,71 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
   if (!s_last) return;
   asm volatile("fence.acq_rel.gpu;" ::: "memory");
   const int tid = threadIdx.x, nthr = blockDim.x;
-  float* sRow = (float*)smem_raw;                       // warp 0's Q tile: [16] common max per row
-  for (int r = tid; r < g; r += nthr) {
+  float* sRow = (float*)smem_raw;                       // [16] common max per row (warp 0's tiles are done with)
+  // the rows' common max: a warp takes a row, its lanes the chunks, four loads a lane in flight
+  for (int r = warp; r < g; r += nwarps) {
     const size_t base = ((size_t)s * nq + kvh * g + r) * max_chunks;
     float mm = -INFINITY;
-#pragma unroll 8
-    for (int c = ch_lo; c < ch_hi; ++c) mm = fmaxf(mm, __ldcg(&ws_ml[(base + c) * 2]));
-    sRow[r] = mm;
+    for (int c0 = ch_lo; c0 < ch_hi; c0 += 128) {
+      float v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + j * 32 + lane;
+        v[j] = c < ch_hi ? __ldcg(&ws_ml[(base + c) * 2]) : -INFINITY;
+      }
+      mm = fmaxf(fmaxf(mm, fmaxf(v[0], v[1])), fmaxf(v[2], v[3]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    if (lane == 0) sRow[r] = mm;
   }
   __syncthreads();
-  // Output by output; the loads of 16 chunks are issued together (indices are clamped and
-  // the factor of a chunk past the end is 0, so that no load waits for a branch).
-  for (int idx = tid; idx < g * D; idx += nthr) {
-    const int r = idx / D, dcol = idx - r * D;
+  // Four outputs of a row and one half of its chunks a thread (neighbouring lanes hold the two halves):
+  // the loads of 8 chunks are issued together (indices are clamped and the factor of a chunk past the
+  // end is 0, so that no load waits for a branch); a half is summed in chunk order, then first half +
+  // second half.  The order depends on the sequence's own length only.
+  const int nch = ch_hi - ch_lo, half_n = (nch + 1) >> 1;
+  const int items = g * (D / 4) * 2;
+  for (int it0 = 0; it0 < items; it0 += nthr) {
+    const int item = it0 + tid;
+    const bool valid = item < items;
+    const int h = item & 1, q4 = (item >> 1) % (D / 4), r = valid ? (item >> 1) / (D / 4) : 0;
     const float mm = sRow[r];
     const size_t base = ((size_t)s * nq + kvh * g + r) * max_chunks;
-    float acc = 0.f, ll = 0.f;
-    for (int c0 = ch_lo; c0 < ch_hi; c0 += 16) {
-      float v[16], f[16];
+    const int c_begin = ch_lo + h * half_n, c_end = valid ? min(ch_hi, c_begin + half_n) : c_begin;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float ll = 0.f;
+    for (int c0 = c_begin; c0 < c_end; c0 += 8) {
+      float4 v[8];
+      float2 ml[8];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int c = min(c0 + j, ch_hi - 1);
-        v[j] = __ldcg(&ws_o[(base + c) * D + dcol]);
+      for (int j = 0; j < 8; ++j) {
+        const int c = min(c0 + j, c_end - 1);
+        v[j] = __ldcg((const float4*)(ws_o + (base + c) * D + q4 * 4));
+        ml[j] = __ldcg((const float2*)(ws_ml + (base + c) * 2));
       }
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int c = min(c0 + j, ch_hi - 1);
-        const float2 ml = __ldcg((const float2*)(ws_ml + (base + c) * 2));
-        const float fj = (c0 + j < ch_hi && ml.x != -INFINITY) ? exp2f(ml.x - mm) : 0.f;
-        f[j] = fj;
-        ll += ml.y * fj;
+      for (int j = 0; j < 8; ++j) {
+        const float f = (c0 + j < c_end && ml[j].x != -INFINITY) ? exp2f(ml[j].x - mm) : 0.f;
+        ll += ml[j].y * f;
+        acc.x += v[j].x * f; acc.y += v[j].y * f; acc.z += v[j].z * f; acc.w += v[j].w * f;
       }
-#pragma unroll
-      for (int j = 0; j < 16; ++j) acc += v[j] * f[j];
     }
-    out[((size_t)s * nq + kvh * g + r) * D + dcol] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    // lane pairs (h = 0, 1) are neighbours: every lane of the warp takes part in the exchange
+    float4 oth;
+    oth.x = __shfl_xor_sync(0xffffffffu, acc.x, 1); oth.y = __shfl_xor_sync(0xffffffffu, acc.y, 1);
+    oth.z = __shfl_xor_sync(0xffffffffu, acc.z, 1); oth.w = __shfl_xor_sync(0xffffffffu, acc.w, 1);
+    const float llo = __shfl_xor_sync(0xffffffffu, ll, 1);
+    if (valid && h == 0) {
+      const float lt = ll + llo;
+      const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+      bf16* o = out + ((size_t)s * nq + kvh * g + r) * D + q4 * 4;
+      __nv_bfloat162 lo = __floats2bfloat162_rn((acc.x + oth.x) * inv, (acc.y + oth.y) * inv);
+      __nv_bfloat162 hi = __floats2bfloat162_rn((acc.z + oth.z) * inv, (acc.w + oth.w) * inv);
+      uint2 w;
+      w.x = *(unsigned*)&lo; w.y = *(unsigned*)&hi;
+      *(uint2*)o = w;
+    }
   }
 }
 
