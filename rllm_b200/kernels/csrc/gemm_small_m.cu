@@ -13,13 +13,26 @@
 //
 // Epilogues: plain store (bfloat16 or float32), or SiLU-gate: with W = [gate
 // rows; up rows], a CTA takes 8 gate rows and the 8 up rows of the same
-// features and stores silu(gate) * up (crates/rllm-model/src/layers.rs:214-220).
+// features and stores silu(gate) * up (crates/rllm-model/src/layers.rs:214-220),
+// or residual: the float32 accumulators are added to the float32 residual
+// stream h in place (a CTA owns its 16 columns).
+//
+// The residual epilogue also prepares the RMSNorm that reads h next
+// (crates/rllm-model/src/layers.rs:133-140: y = h / sqrt(mean(h^2) + eps) * w,
+// float32), so that no norm kernel stands between this product and the one
+// after the norm (up to 8 rows): it stores scaled[m][n] = bfloat16(h[m][n] *
+// w[n]) and, for every row, the sum of squares of the CTA's 16 new values of h.
+// The product that follows takes `scaled` as its operand and, told so (RSTD),
+// adds up a row's partial sums in a fixed order and multiplies row m of its
+// result by 1 / sqrt(mean(h[m]^2) + eps).
 #include "common.cuh"
 #include <stdlib.h>
 
 #define EPI_BF16 0
 #define EPI_F32 1
 #define EPI_SILU 2
+#define EPI_RESID 3
+#define RLLM_NO_EARLY_LAUNCH 0x7fffffff     // tail_from: no CTA calls pdl_launch; the next kernel starts when this one ends
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 v;
@@ -40,11 +53,45 @@ __device__ __forceinline__ void mma16816(float* c, unsigned a0, unsigned a1, uns
 
 // MT: batch tiles of 8 rows.  blockDim.x = 32 * warps; warp w takes a contiguous
 // range of 32-wide k blocks.  K is a multiple of 8; the last block may be partial.
-template <int MT, int EPI>
+// RSTD: the rows' partial sums of squares; EPI_RESID: where the partial sums and the scaled copy of h go
+struct NormSide {
+  const float* parts; int P; float eps; int width;      // in:  [P, M]; the row's mean is over `width` values
+  float* parts_out;                                     // out: [gridDim.x, M]
+  const void* w_next; int w_is_f32;                     // out: weight [N] of the norm that reads h next (or null)
+  bf16* scaled; int lds;                                // out: [M, N] = bfloat16(h * w_next)
+};
+
+// The parts of row m = tid % 8 that fall to this thread's slice tid / 8, added in order; the loads are
+// independent of one another.  Rows past M repeat the last row.
+__device__ __forceinline__ float rows_sumsq_slice(const float* __restrict__ parts, int P, int M) {
+  const int m = min((int)(threadIdx.x & 7), M - 1), slice = threadIdx.x >> 3, nslices = blockDim.x >> 3;
+  float v[4] = {0.f, 0.f, 0.f, 0.f}, acc = 0.f;
+  for (int p0 = slice; p0 < P; p0 += 4 * nslices) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { const int pp = p0 + j * nslices; v[j] = pp < P ? parts[(size_t)pp * M + m] : 0.f; }
+    acc += v[0]; acc += v[1]; acc += v[2]; acc += v[3];
+  }
+  return acc;
+}
+
+// Element idx = tid of the CTA's [16 columns][8 MT rows] tile of h, fetched long before it is needed.
+__device__ __forceinline__ float resid_old(const void* h, int ldh, int n0, int M, int N, int MT) {
+  const int cols = 8 * MT, idx = threadIdx.x;
+  if (idx >= 16 * cols) return 0.f;
+  const int r = idx / cols, m = idx - r * cols, n = n0 + r;
+  return (m < M && n < N) ? ((const float*)h)[(size_t)m * ldh + n] : 0.f;
+}
+
+// 104 registers a thread: a CTA of 512 threads then leaves room for one CTA of the decode attention kernel
+// on its SM (and two CTAs of 256 threads likewise), so that kernels that follow one another overlap
+template <int MT, int EPI, bool RSTD>
 __global__ void __launch_bounds__(512)
 gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ W, int ldw,
-                    void* __restrict__ out, int ldo, int M, int N, int K, int up_offset, int tail_from) {
+                    void* __restrict__ out, int ldo, int M, int N, int K, int up_offset, int tail_from,
+                    NormSide ns) {
   extern __shared__ float red[];                 // [warps][16][8 MT]
+  __shared__ float s_rstd[8];
+  __shared__ float s_part[RSTD ? 64 : 1][8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int gq = lane >> 2, t = lane & 3;
   const int rows_per_cta = (EPI == EPI_SILU) ? 8 : 16;
@@ -70,6 +117,10 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
   const int per_warp = (nblocks + nwarps - 1) / nwarps;
   const int b_end = min(nblocks, (warp + 1) * per_warp);
   bool waited = false;
+  // RSTD: thread (slice, m) = (tid / 8, tid % 8) adds the parts slice, slice + nslices, ... of row m
+  float psum = 0.f;
+  // EPI_RESID: the old value of the element of h that this thread will update (threads 0 .. 16 * 8 MT - 1)
+  float h_old = 0.f;
   for (int b0 = warp * per_warp; b0 < b_end; b0 += U) {
     uint4 a[U], v[U], xb[U][MT];
     // the weight first (no kernel writes it: these loads may run ahead of the kernel before this one) ...
@@ -85,6 +136,8 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     if (!waited) {
       pdl_wait();
       waited = true;
+      if (RSTD) psum = rows_sumsq_slice(ns.parts, ns.P, M);
+      if (EPI == EPI_RESID) h_old = resid_old(out, ldo, n0, M, N, MT);
       // no CTA of this grid is still to come once its last wave runs: the stream's next kernel may
       // come in and fetch its own weights while this one works
       if ((int)blockIdx.x >= tail_from) pdl_launch();
@@ -107,8 +160,11 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
         mma16816(c[i], a[u].z, v[u].z, a[u].w, v[u].w, xb[u][i].z, xb[u][i].w);
       }
   }
-  if (!waited) pdl_wait();       // a warp without k blocks: nothing was read, but the stores below must wait too
-  pdl_launch();                  // the stream's next kernel may start coming in now
+  if (!waited) {                 // a warp without k blocks: nothing was read, but what follows must wait too
+    pdl_wait();
+    if (EPI == EPI_RESID) h_old = resid_old(out, ldo, n0, M, N, MT);
+  }
+  if (tail_from != RLLM_NO_EARLY_LAUNCH) pdl_launch();   // the stream's next kernel may start coming in now
   // partial sums of the warps -> shared memory; c[i]: rows gq, gq + 8; batch columns i*8 + 2t, 2t + 1
   float* mine = red + (size_t)warp * 16 * 8 * MT;
 #pragma unroll
@@ -118,9 +174,46 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     mine[(gq + 8) * 8 * MT + i * 8 + 2 * t] = c[i][2];
     mine[(gq + 8) * 8 * MT + i * 8 + 2 * t + 1] = c[i][3];
   }
+  if (RSTD) {
+    if (!waited) psum = rows_sumsq_slice(ns.parts, ns.P, M);
+    s_part[threadIdx.x >> 3][threadIdx.x & 7] = psum;
+    __syncthreads();
+    if (threadIdx.x < 8) {
+      float ss = 0.f;
+      for (int sl = 0; sl < (int)(blockDim.x >> 3); ++sl) ss += s_part[sl][threadIdx.x];
+      s_rstd[threadIdx.x] = 1.0f / sqrtf(ss / (float)ns.width + ns.eps);     // eps inside the root
+    }
+  }
   __syncthreads();
   const int cols = 8 * MT;
-  if (EPI == EPI_SILU) {
+  if (EPI == EPI_RESID) {
+    // h[m][n] += acc for the CTA's 16 columns n; the scaled copy; then, row by row, the sum of squares
+    float* tile = red + (size_t)nwarps * 16 * cols;          // [8 MT][16] new values of h (0 outside the matrix)
+    for (int idx = threadIdx.x; idx < 16 * cols; idx += blockDim.x) {
+      const int r = idx / cols, m = idx - r * cols;
+      float acc = 0.f;
+      for (int w = 0; w < nwarps; ++w) acc += red[((size_t)w * 16 + r) * cols + m];
+      const int n = n0 + r;
+      float hv = 0.f;
+      if (m < M && n < N) {
+        float* hp = (float*)out + (size_t)m * ldo + n;
+        hv = (idx == (int)threadIdx.x ? h_old : *hp) + acc;      // blocks of fewer than 16 * cols threads: later elements are read here
+        *hp = hv;
+        if (ns.scaled) {
+          const float wv = ns.w_is_f32 ? ((const float*)ns.w_next)[n] : __bfloat162float(((const bf16*)ns.w_next)[n]);
+          ns.scaled[(size_t)m * ns.lds + n] = __float2bfloat16_rn(hv * wv);
+        }
+      }
+      tile[m * 16 + r] = hv;
+    }
+    __syncthreads();
+    if (threadIdx.x < cols && threadIdx.x < M) {
+      float ss = 0.f;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) { const float v = tile[threadIdx.x * 16 + r]; ss += v * v; }
+      ns.parts_out[(size_t)blockIdx.x * M + threadIdx.x] = ss;
+    }
+  } else if (EPI == EPI_SILU) {
     for (int idx = threadIdx.x; idx < 8 * cols; idx += blockDim.x) {
       const int r = idx / cols, m = idx - r * cols;
       float g = 0.f, u = 0.f;
@@ -129,6 +222,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
         u += red[((size_t)w * 16 + r + 8) * cols + m];
       }
       const int n = n0 + r;
+      if (RSTD) { g *= s_rstd[m]; u *= s_rstd[m]; }
       if (m < M && n < N) ((bf16*)out)[(size_t)m * ldo + n] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
     }
   } else {
@@ -137,6 +231,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
       float acc = 0.f;
       for (int w = 0; w < nwarps; ++w) acc += red[((size_t)w * 16 + r) * cols + m];
       const int n = n0 + r;
+      if (RSTD) acc *= s_rstd[m];
       if (m < M && n < N) {
         if (EPI == EPI_F32) ((float*)out)[(size_t)m * ldo + n] = acc;
         else ((bf16*)out)[(size_t)m * ldo + n] = __float2bfloat16_rn(acc);
@@ -145,23 +240,28 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
   }
 }
 
-template <int MT, int EPI>
+template <int MT, int EPI, bool RSTD>
 static int launch_small_m(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, int M, int N, int K,
-                          int up_offset, cudaStream_t stream) {
+                          int up_offset, NormSide ns, cudaStream_t stream) {
   const int rows_per_cta = (EPI == EPI_SILU) ? 8 : 16;
   const int tiles = (N + rows_per_cta - 1) / rows_per_cta;
   const int nblocks = (K + 31) / 32;
   int warps = 4;
   while (warps < 16 && (long long)tiles * warps < 1536) warps *= 2;
-  if (const char* e = getenv("RLLM_SMALLM_WARPS")) warps = atoi(e);
   while (warps > 1 && warps > nblocks) warps /= 2;
-  while (warps > 1 && (size_t)warps * 16 * 8 * MT * sizeof(float) > 48 * 1024) warps /= 2;
-  const size_t smem = (size_t)warps * 16 * 8 * MT * sizeof(float);
+  while (warps > 1 && (size_t)warps * 16 * 8 * MT * sizeof(float) > 40 * 1024) warps /= 2;
+  // EPI_RESID keeps the CTA's new values of h behind the warps' partial sums
+  const size_t smem = ((size_t)warps * 16 * 8 * MT + (EPI == EPI_RESID ? 16 * 8 * MT : 0)) * sizeof(float);
   static int resident[17];       // by number of warps
-  if (!resident[warps]) resident[warps] = rllm_resident_ctas(gemm_small_m_kernel<MT, EPI>, 32 * warps, smem) + 1;
-  const int tail_from = resident[warps] > 1 ? tiles - (resident[warps] - 1) : tiles;
-  cudaError_t e = rllm_launch_pdl(gemm_small_m_kernel<MT, EPI>, dim3(tiles), dim3(32 * warps), smem, stream,
-                                  x, ldx, W, ldw, out, ldo, M, N, K, up_offset, tail_from);
+  if (!resident[warps]) resident[warps] = rllm_resident_ctas(gemm_small_m_kernel<MT, EPI, RSTD>, 32 * warps, smem) + 1;
+  int tail_from = resident[warps] > 1 ? tiles - (resident[warps] - 1) : tiles;
+  // A product with a small weight (the o projection of a small model) is over in a few microseconds, all
+  // of them latency.  Measured at 3 to 8 rows: when it lets the large product behind it in while it runs,
+  // the step takes 13 % longer than when that product starts at its end; so it lets nothing in early.
+  const size_t weight_bytes = (size_t)(EPI == EPI_SILU ? 2 : 1) * N * K * sizeof(bf16);
+  if (weight_bytes < ((size_t)12 << 20) && M > 2) tail_from = RLLM_NO_EARLY_LAUNCH;
+  cudaError_t e = rllm_launch_pdl(gemm_small_m_kernel<MT, EPI, RSTD>, dim3(tiles), dim3(32 * warps), smem, stream,
+                                  x, ldx, W, ldw, out, ldo, M, N, K, up_offset, tail_from, ns);
   if (e != cudaSuccess) return (int)e;
   return 0;
 }
@@ -169,8 +269,9 @@ static int launch_small_m(const bf16* x, int ldx, const bf16* W, int ldw, void* 
 template <int EPI>
 static int dispatch_mt(const bf16* x, int ldx, const bf16* W, int ldw, void* out, int ldo, int M, int N, int K,
                        int up_offset, cudaStream_t stream) {
-  if (M <= 8) return launch_small_m<1, EPI>(x, ldx, W, ldw, out, ldo, M, N, K, up_offset, stream);
-  if (M <= 16) return launch_small_m<2, EPI>(x, ldx, W, ldw, out, ldo, M, N, K, up_offset, stream);
+  NormSide none = {};
+  if (M <= 8) return launch_small_m<1, EPI, false>(x, ldx, W, ldw, out, ldo, M, N, K, up_offset, none, stream);
+  if (M <= 16) return launch_small_m<2, EPI, false>(x, ldx, W, ldw, out, ldo, M, N, K, up_offset, none, stream);
   return RLLM_E_UNSUPPORTED;
 }
 
@@ -189,5 +290,43 @@ RLLM_EXPORT int rllm_gemm_small_m(const void* x, int ldx, const void* W, int ldw
     case EPI_F32: return dispatch_mt<EPI_F32>(xp, ldx, wp, ldw, out, ldo, M, N, K, 0, stream);
     case EPI_SILU: return dispatch_mt<EPI_SILU>(xp, ldx, wp, ldw, out, ldo, M, N, K, N, stream);
   }
+  return RLLM_E_BADARG;
+}
+
+// How many partial sums a row gets from rllm_gemm_small_m_residual with N columns.
+RLLM_EXPORT int rllm_gemm_small_m_parts(int N) { return (N + 15) / 16; }
+
+// h[M, N] (float32, in place) += x[M, K] . W[N, K]^T for M <= 8 rows.  parts_out
+// [rllm_gemm_small_m_parts(N), M] receives, part by part, the sums of squares of 16 new values of each
+// row; with w_next (weight [N] of the norm that reads h next, float32 or bfloat16), scaled [M, N] receives
+// bfloat16(h * w_next).
+RLLM_EXPORT int rllm_gemm_small_m_residual(const void* x, int ldx, const void* W, int ldw, float* h, int ldh,
+                                           float* parts_out, const void* w_next, int w_is_f32, void* scaled,
+                                           int lds, int M, int N, int K, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || ldx < K || ldw < K || ldh < N || !parts_out || (scaled && (!w_next || lds < N))) return RLLM_E_BADARG;
+  if (K % 8 || ldx % 8 || ldw % 8 || M > 8) return RLLM_E_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)W) & 15) return RLLM_E_BADARG;
+  NormSide ns = {};
+  ns.parts_out = parts_out; ns.w_next = w_next; ns.w_is_f32 = w_is_f32; ns.scaled = (bf16*)scaled; ns.lds = lds;
+  return launch_small_m<1, EPI_RESID, false>((const bf16*)x, ldx, (const bf16*)W, ldw, h, ldh, M, N, K, 0, ns, stream);
+}
+
+// out = (x . W^T) with row m scaled by 1 / sqrt(sum_p parts[p][m] / K + eps), for M <= 8 rows: x is the
+// `scaled` output of rllm_gemm_small_m_residual and parts [P, M] its partial sums, so that out is the
+// product of the RMS-normalised h with W.  epilogue 0 (bfloat16 out) or 2 (SiLU-gate), as above.
+RLLM_EXPORT int rllm_gemm_small_m_rstd(const void* x, int ldx, const float* parts, int P, float eps, const void* W,
+                                       int ldw, void* out, int ldo, int M, int N, int K, int epilogue,
+                                       cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || ldx < K || ldw < K || ldo < N || P <= 0 || !parts || !(eps > 0.f)) return RLLM_E_BADARG;
+  if (K % 8 || ldx % 8 || ldw % 8 || M > 8) return RLLM_E_UNSUPPORTED;
+  if (((uintptr_t)x | (uintptr_t)W) & 15) return RLLM_E_BADARG;
+  NormSide ns = {};
+  ns.parts = parts; ns.P = P; ns.eps = eps; ns.width = K;
+  const bf16* xp = (const bf16*)x;
+  const bf16* wp = (const bf16*)W;
+  if (epilogue == EPI_BF16) return launch_small_m<1, EPI_BF16, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, 0, ns, stream);
+  if (epilogue == EPI_SILU) return launch_small_m<1, EPI_SILU, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, N, ns, stream);
   return RLLM_E_BADARG;
 }

@@ -196,6 +196,59 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: 
            "gemm_small_m")
 
 
+def gemm_small_m_residual(x: torch.Tensor, w: torch.Tensor, h: torch.Tensor,
+                          w_next: Optional[torch.Tensor]):
+    """h += x . w^T (h float32, in place) for M <= 8 rows of bfloat16.  Returns
+    (parts, scaled): parts float32 [P, M], whose sum over P is each row's new sum of
+    squares; scaled = bfloat16(h * w_next) [M, N] if the weight ``w_next`` of the norm
+    that reads h next is given, else None."""
+    lib = build.load_library("gemm_small_m")
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and w.shape[1] == K
+    assert h.dtype is torch.float32 and h.shape == (M, N) and h.stride(1) == 1
+    assert x.stride(1) == 1 and w.stride(1) == 1
+    P = int(lib.rllm_gemm_small_m_parts(c_int(N)))
+    parts = torch.empty((P, M), dtype=torch.float32, device=x.device)
+    scaled = None
+    if w_next is not None:
+        assert w_next.numel() == N and w_next.is_contiguous() and w_next.dtype in (torch.float32, torch.bfloat16)
+        scaled = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    _check(lib.rllm_gemm_small_m_residual(_ptr(x), c_int(x.stride(0)), _ptr(w), c_int(w.stride(0)), _ptr(h),
+                                          c_int(h.stride(0)), _ptr(parts), _ptr(w_next),
+                                          c_int(1 if w_next is not None and w_next.dtype is torch.float32 else 0),
+                                          _ptr(scaled), c_int(N), c_int(M), c_int(N), c_int(K), _stream()),
+           "gemm_small_m_residual")
+    return parts, scaled
+
+
+def gemm_small_m_rstd(x: torch.Tensor, parts: torch.Tensor, eps: float, w: torch.Tensor, out: torch.Tensor,
+                      epilogue: str = "store") -> None:
+    """out = (x . w^T) with row m scaled by 1 / sqrt(sum(parts[:, m]) / K + eps): with
+    x and parts from ``gemm_small_m_residual`` this is rmsnorm(h) . w^T.  Epilogues
+    as in ``gemm_small_m`` (bfloat16 out)."""
+    lib = build.load_library("gemm_small_m")
+    M, K = x.shape
+    assert x.dtype is torch.bfloat16 and w.dtype is torch.bfloat16 and w.shape[1] == K and out.dtype is torch.bfloat16
+    assert parts.dtype is torch.float32 and parts.is_contiguous() and parts.shape[1] == M
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    if epilogue == "silu_mul":
+        N, code = w.shape[0] // 2, 2
+        assert w.shape[0] == 2 * N
+    else:
+        N, code = w.shape[0], 0
+    assert out.shape == (M, N)
+    _check(lib.rllm_gemm_small_m_rstd(_ptr(x), c_int(x.stride(0)), _ptr(parts), c_int(parts.shape[0]), c_float(eps),
+                                      _ptr(w), c_int(w.stride(0)), _ptr(out), c_int(out.stride(0)), c_int(M),
+                                      c_int(N), c_int(K), c_int(code), _stream()), "gemm_small_m_rstd")
+
+
+def small_m_rows(num_rows: int, dtype: torch.dtype) -> bool:
+    """Whether a step of this many rows goes through the weight-streaming kernels."""
+    import os
+    return dtype is torch.bfloat16 and 0 < num_rows <= SMALL_M_MAX and os.environ.get("RLLM_GEMM") != "library"
+
+
 def small_m_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
     import os
     return (x.dtype is torch.bfloat16 and 0 < x.shape[0] <= SMALL_M_MAX and x.shape[1] % 8 == 0

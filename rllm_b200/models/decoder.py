@@ -123,10 +123,19 @@ class DecoderModel:
         cache view."""
         h = self.embedding.forward(token_ids, ctx.err)
         pending = None
-        for i, run in enumerate(self.spec.order):
-            h, pending = self.blocks[run.layer].forward(h, pending, ctx, storage.view(i))
+        order = self.spec.order
+        for i, run in enumerate(order):
+            block = self.blocks[run.layer]
+            if getattr(block, "takes_next_norm", False) and i + 1 < len(order):
+                # the norm that reads the stream after this block: the block may prepare its input
+                nxt = getattr(self.blocks[order[i + 1].layer], "norms", None)
+                h, pending = block.forward(h, pending, ctx, storage.view(i), next_norm=nxt[0] if nxt else None)
+            else:
+                h, pending = block.forward(h, pending, ctx, storage.view(i))
         if logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
+        if not isinstance(pending, torch.Tensor):
+            pending = None                      # a block that adds into the stream itself left it complete
         xn = self.final_norm.gather_forward(h, pending, logit_rows, ctx.act_dtype)
         return self.head.forward(xn)
 

@@ -26,7 +26,7 @@ import torch
 
 from ..kernels import ops
 from .base import KVCacheView, Mixer, StepContext
-from .linear import linear
+from .linear import fused_residual_takes, linear
 from .registry import build_part, register_part
 from .spec import KVPagesNeed, PartSpec, TensorSpec
 
@@ -81,7 +81,10 @@ class PagedAttention(Mixer):
         return KVPagesNeed(self.nkv, self.d, self.window)
 
     # -- compute ----------------------------------------------------------
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: KVCacheView) -> torch.Tensor:
+    def fused_residual(self, num_rows: int, dtype: torch.dtype) -> bool:
+        return fused_residual_takes(num_rows, dtype, self.w_qkv, self.w_o)
+
+    def forward(self, x, ctx: StepContext, cache: KVCacheView, residual=None):
         T = x.shape[0]
         nkv_here = 0 if self.shares_kv else self.nkv
         qkv = linear(x, self.w_qkv)                                   # [T, (nq + 2 nkv) d]
@@ -119,4 +122,4 @@ class PagedAttention(Mixer):
             else:
                 ops.attention_simt(qkv, stride, out, cache.k, cache.v, table, ctx.positions, ctx.token_seq,
                                    self.nq, self.nkv, self.d, window, self.scale, ctx.err)
-        return linear(out, self.w_o)
+        return linear(out, self.w_o, residual=residual)

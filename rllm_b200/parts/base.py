@@ -20,6 +20,19 @@ FeedForward     forward(x act[T,H]) -> act[T,H]
 Block           forward(h_f32[T,H], pending act[T,H]|None, ctx, cache) -> (h_f32, pending)
                 where the true hidden state is h + pending (the last add is
                 left to the next norm, which fuses it)
+
+Few rows (decoding): the residual stream without norm kernels
+-------------------------------------------------------------
+A mixer or feed-forward that sets ``fused_residual`` takes two more forms of
+its arguments.  ``residual=(h, norm)``: it adds its result into h itself (float32,
+in place) and returns a ``RowSumsq``: per row, partial sums of squares of the new
+h, and, if ``norm`` is given, h times that norm's weight.  And its input ``x`` may
+be a ``ScaledRows`` made from such a ``RowSumsq`` by the norm (``scaled_input``):
+the product that reads it multiplies each row of its result by the row's
+1 / sqrt(mean(h^2) + eps), which makes it the product of the normalised h.  A
+block that finds all this in its parts runs a layer as five kernels; ``pending``
+between blocks is then a ``RowSumsq``, and a block that cannot use it reads h,
+which is complete.
 """
 from __future__ import annotations
 
@@ -66,6 +79,41 @@ class StepContext:
     @property
     def max_seq_len(self) -> int:
         return max(self.seq_lens_host) if self.seq_lens_host else 0
+
+
+@dataclass
+class RowSumsq:
+    """h is complete.  ``parts`` float32 [P, T]: the sum over P (in the consumer's fixed
+    order) is the sum of squares of row t of h.  ``scaled`` [T, H]: h times the weight
+    ``scaled_by`` of the norm that is expected to read h next, rounded to the
+    activation dtype; None if no such norm was named."""
+
+    parts: torch.Tensor
+    scaled: Optional[torch.Tensor] = None
+    scaled_by: Optional[torch.Tensor] = None
+
+
+@dataclass
+class ScaledRows:
+    """An RMS-normalised activation that has not been divided by its rows' root mean
+    square yet: ``x`` = h * weight, ``parts`` and ``eps`` give the rows' factors
+    1 / sqrt(sum(parts[:, t]) / H + eps).  Stands where an activation [T, H] stands."""
+
+    x: torch.Tensor
+    parts: torch.Tensor
+    eps: float
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    @property
+    def device(self):
+        return self.x.device
 
 
 @dataclass

@@ -13,7 +13,8 @@ import torch
 
 from ..kernels import ops
 from .base import FeedForward
-from .linear import linear
+from .base import ScaledRows
+from .linear import fused_residual_takes, linear
 from .registry import register_part
 from .spec import PartSpec, TensorSpec
 
@@ -41,9 +42,15 @@ class GatedMLP(FeedForward):
         self.w_gate_up = torch.cat([tensors[g], tensors[u]], dim=0).contiguous()
         self.w_down = tensors[d]
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def fused_residual(self, num_rows: int, dtype: torch.dtype) -> bool:
+        return fused_residual_takes(num_rows, dtype, self.w_gate_up, self.w_down)
+
+    def forward(self, x, residual=None):
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        if ops.small_m_takes(x, self.w_gate_up):
+        if isinstance(x, ScaledRows):
+            # the rows' 1 / rms is applied to gate and up before the SiLU
+            ops.gemm_small_m_rstd(x.x, x.parts, x.eps, self.w_gate_up, act, "silu_mul")
+        elif ops.small_m_takes(x, self.w_gate_up):
             # few rows: one kernel streams [Wgate; Wup] once and applies silu(gate) * up to its accumulators
             ops.gemm_small_m(x, self.w_gate_up, act, "silu_mul")
         elif ops.tcgen05_takes(x, self.w_gate_up, silu=True):
@@ -52,4 +59,4 @@ class GatedMLP(FeedForward):
         else:
             gate_up = linear(x, self.w_gate_up)                   # [T, 2I]
             ops.silu_mul(gate_up, act)
-        return linear(act, self.w_down)
+        return linear(act, self.w_down, residual=residual)

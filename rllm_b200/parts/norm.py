@@ -12,7 +12,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from .base import Norm
+from .base import Norm, RowSumsq, ScaledRows
 from .registry import register_part
 from .spec import PartSpec, TensorSpec
 
@@ -43,6 +43,13 @@ class RMSNorm(Norm):
         out = torch.empty(x.shape, dtype=delta.dtype, device=x.device)
         ops.rmsnorm(x, self.weight, self.eps, out, delta=delta, writeback=True)
         return out
+
+    def scaled_input(self, stats: RowSumsq) -> Optional[ScaledRows]:
+        """The normalised stream for a product that applies the rows' factors itself, if
+        ``stats`` was prepared with this norm's weight."""
+        if stats.scaled is None or stats.scaled_by is not self.weight:
+            return None
+        return ScaledRows(stats.scaled, stats.parts, self.eps)
 
     def gather_forward(self, x, delta, rows, act_dtype):
         out = torch.empty((rows.numel(), x.shape[1]), dtype=act_dtype, device=x.device)

@@ -459,6 +459,49 @@ def test_gemm_small_m_silu(ops, M, I, K):
     assert rel_err(out, want) <= 1e-2
 
 
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,H,K,N2", [(1, 136, 264, 200), (3, 2048, 8192, 3072), (8, 72, 40, 50), (5, 96, 264, 389)])
+def test_gemm_small_m_residual_then_rstd(ops, M, H, K, N2, wdt):
+    """The pair of products that stands for 'add into the residual stream, RMSNorm, next product':
+    h += x W1^T with the rows' partial sums of squares and h * w_norm on the side, then
+    (h w_norm) W2^T scaled by the rows' 1 / rms, compared with the plain formulas."""
+    torch.manual_seed(M + H)
+    eps = 3e-4
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w1 = (torch.randn(H, K, device=DEV) * 0.1).bfloat16()
+    h0 = torch.randn(M, H, device=DEV) * 3
+    wn = (1 + 0.1 * torch.randn(H, device=DEV)).to(wdt)
+    h = h0.clone()
+    parts, scaled = ops.gemm_small_m_residual(x, w1, h, wn)
+    want_h = h0.double().cpu() + x.double().cpu() @ w1.double().cpu().t()
+    assert rel_err(h, want_h) <= 2e-6
+    assert rel_err(parts.sum(dim=0), (h.double().cpu() ** 2).sum(dim=1)) <= 1e-6
+    assert torch.equal(scaled, (h * wn.float()).bfloat16())
+    # without a norm named: no scaled copy, the same h
+    h2 = h0.clone()
+    parts2, none = ops.gemm_small_m_residual(x, w1, h2, None)
+    assert none is None and torch.equal(h2, h) and torch.equal(parts2, parts)
+    # the product after the norm: plain, and with the SiLU gate
+    want_x = pl.rms_norm(h.double().cpu(), wn.double().cpu(), eps)
+    w2 = (torch.randn(N2, H, device=DEV) * 0.1).bfloat16()
+    out = torch.full((M, N2), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_small_m_rstd(scaled, parts, eps, w2, out)
+    assert rel_err(out, want_x @ w2.double().cpu().t()) <= 1e-2
+    I = N2 // 2
+    act = torch.full((M, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_small_m_rstd(scaled, parts, eps, w2[:2 * I], act, "silu_mul")
+    w2d = w2.double().cpu()
+    assert rel_err(act, pl.silu(want_x @ w2d[:I].t()) * (want_x @ w2d[I:2 * I].t())) <= 1e-2
+    # a row's results do not depend on the rows beside it
+    if M > 1:
+        h1 = h0[M - 1:].clone()
+        p1, s1 = ops.gemm_small_m_residual(x[M - 1:], w1, h1, wn)
+        assert torch.equal(h1[0], h[M - 1]) and torch.equal(p1[:, 0], parts[:, M - 1]) and torch.equal(s1[0], scaled[M - 1])
+        o1 = torch.empty(1, N2, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_small_m_rstd(s1, p1, eps, w2, o1)
+        assert torch.equal(o1[0], out[M - 1])
+
+
 @pytest.mark.parametrize("M,N,K", [(17, 96, 64), (128, 128, 64), (129, 389, 96), (200, 300, 264), (300, 3072, 2048),
                                    (2048, 2048, 8192), (64, 128256, 2048), (1000, 72, 1000)])
 def test_gemm_tcgen05(ops, M, N, K):

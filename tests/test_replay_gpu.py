@@ -146,6 +146,25 @@ def test_attention_kernels_agree_through_replay(model_dirs, monkeypatch):
     assert 0 < worst <= TOL["bfloat16"], worst       # not the same kernel, and close
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_decoding_with_and_without_norm_kernels(model_dirs, name, monkeypatch):
+    """Steps of up to 8 tokens run a layer without norm kernels (the products carry the RMSNorm);
+    RLLM_FUSED_NORM=0 runs the same steps with them.  Both match the plain implementation, and
+    they differ from each other (so both ways were taken) by rounding only."""
+    cfg, _, page = TINY[name]
+    reqs = make_requests(name)
+    tb = ru.trace_mixed(reqs, seed=6, live=3, tail=32)
+    a = ru.run_trace(model_dirs[name], "bfloat16", tb, cfg["vocab_size"], page_size=page)
+    monkeypatch.setenv("RLLM_FUSED_NORM", "0")
+    b = ru.run_trace(model_dirs[name], "bfloat16", ru.trace_mixed(reqs, seed=6, live=3, tail=32), cfg["vocab_size"],
+                     page_size=page)
+    want = plain_logits(model_dirs, name, "bfloat16")
+    compare(a, want, reqs, "bfloat16", f"{name}/fused norm")
+    compare(b, want, reqs, "bfloat16", f"{name}/norm kernels")
+    worst = max(float(np.abs(a[k] - b[k]).max() / np.abs(b[k]).max()) for k in a)
+    assert 0 < worst <= TOL["bfloat16"], worst
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_long_decoding(model_dirs, name, dtype):
