@@ -108,6 +108,10 @@ class EngineCore:
         self.num_steps = 0
         self._unchecked = 0
         self._prepared = None          # (schedule, requests, plain_greedy, graph) of the next step, made ahead
+        self._inflight = None          # (schedule, requests, plain_greedy, sampled, read-back) of a step already on the GPU
+        self._readback = [None, None]  # pinned buffers and events for the sampled tokens, used in turn
+        self._readback_next = 0
+        self.num_steps_ahead = 0       # steps that were put on the GPU before the tokens of the step before were read
         self.last_schedule: Optional[SchedulerOutput] = None
 
     # ------------------------------------------------------------------
@@ -137,13 +141,21 @@ class EngineCore:
 
     # ------------------------------------------------------------------
     def step(self) -> List[RequestOutput]:
+        inflight, self._inflight = self._inflight, None
         prepared, self._prepared = self._prepared, None
-        if prepared is not None:
+        if inflight is not None and not any(r.status is RequestStatus.RUNNING for r in inflight[1]):
+            inflight = None            # every request of the step in flight has ended: nothing of it is wanted
+        if inflight is not None:
+            # this step was put on the GPU during the last call, behind the step before it
+            sched, sampled_reqs, plain_greedy, sampled, pending = inflight
+            self.last_schedule = sched
+        elif prepared is not None:
             # the schedule and the packed inputs of this step were made while the GPU ran the last one
             sched, sampled_reqs, plain_greedy, graph = prepared
             self.last_schedule = sched
             self.num_steps += 1
-            logits = self.runner.run_prepared(graph)
+            sampled = self._sample(self.runner.run_prepared(graph), sampled_reqs, plain_greedy, 0)
+            pending = self._read_back(sampled)
         else:
             sched = self.scheduler.schedule()
             self.last_schedule = sched
@@ -160,22 +172,20 @@ class EngineCore:
                     sampled_reqs.append(req)
                     p = req.params
                     plain_greedy = plain_greedy and p.greedy and not p.edits_logits
-            logits = self.runner.step(entries)
-        if not sampled_reqs:
-            sampled = None
-        elif plain_greedy:
-            sampled = self.sampler.greedy(logits)
-        else:
-            rows = [SamplingRow(r.params, r.seed, len(r.output_token_ids),
-                                r.all_token_ids if r.params.edits_logits else (), self.eos_token_ids)
-                    for r in sampled_reqs]
-            sampled = self.sampler.sample(logits, rows)
+            sampled = self._sample(self.runner.step(entries), sampled_reqs, plain_greedy, 0)
+            pending = self._read_back(sampled)
+        # requests that ended (or were aborted) after this step went to the GPU: their rows are dropped
+        live = [r.status is RequestStatus.RUNNING for r in sampled_reqs]
         # The GPU is busy now.  What does not depend on the sampled tokens is done meanwhile: the
         # bookkeeping of this step and, if the next step is sure to be a plain decode step of the same
-        # requests, its schedule and its packed inputs.
+        # requests, its schedule and its packed inputs; and that step is launched at once, behind this
+        # one, with this step's tokens as its input on the device, unless a request wants its logits
+        # edited by what it has generated.
         self.scheduler.after_step(sched)
-        nxt = self._prepare_next(sched, sampled_reqs, plain_greedy)
-        tokens = sampled.tolist() if sampled is not None else []
+        nxt = self._prepare_next(sched, sampled_reqs, plain_greedy) if all(live) else None
+        if nxt is not None and self._launch_ahead(nxt, sampled_reqs, sampled):
+            nxt = None
+        tokens = self._tokens_of(pending)
         # the kernels' error words cost a device read each: every step of a prompt, every 32nd decode step
         self._unchecked += 1
         if self._unchecked >= 32 or sched.num_prefill_tokens:
@@ -183,7 +193,9 @@ class EngineCore:
             self._unchecked = 0
         outputs = []
         any_finished = False
-        for req, tok in zip(sampled_reqs, tokens):
+        for req, tok, alive in zip(sampled_reqs, tokens, live):
+            if not alive:
+                continue
             req.output_token_ids.append(int(tok))
             reason = self._finish_reason(req, int(tok))
             if reason is not None:
@@ -199,6 +211,63 @@ class EngineCore:
             nxt[3].patch_tokens([by_req[s.request.request_id] for s in nxt[0].scheduled])
             self._prepared = nxt
         return outputs
+
+    def _read_back(self, sampled):
+        """Start the copy of a step's sampled tokens to pinned host memory, right behind the sampling
+        kernel in the stream; returns what ``_tokens_of`` waits for.  A plain ``tolist`` would wait for
+        everything queued since, a step launched ahead included."""
+        if sampled is None:
+            return None
+        n = sampled.numel()
+        slot = self._readback[self._readback_next]
+        self._readback_next ^= 1
+        if slot is None or slot[0].numel() < n:
+            slot = (torch.empty(max(n, self.args.max_num_seqs), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
+            self._readback[self._readback_next ^ 1] = slot
+        with torch.cuda.device(self.device):
+            slot[0][:n].copy_(sampled, non_blocking=True)
+            slot[1].record()
+        return slot[0], slot[1], n
+
+    @staticmethod
+    def _tokens_of(pending) -> List[int]:
+        if pending is None:
+            return []
+        buf, event, n = pending
+        event.synchronize()
+        return buf[:n].tolist()
+
+    def _sample(self, logits, sampled_reqs, plain_greedy: bool, ahead: int):
+        """The next tokens int32 [R] on the device; ``ahead``: tokens that the requests will have
+        generated by then beyond those the host knows (1 for a step launched ahead)."""
+        if not sampled_reqs:
+            return None
+        if plain_greedy:
+            return self.sampler.greedy(logits)
+        rows = [SamplingRow(r.params, r.seed, len(r.output_token_ids) + ahead,
+                            r.all_token_ids if r.params.edits_logits else (), self.eos_token_ids)
+                for r in sampled_reqs]
+        return self.sampler.sample(logits, rows)
+
+    def _launch_ahead(self, nxt, sampled_reqs, sampled) -> bool:
+        """Put the prepared next step on the GPU now.  Its rows are the same requests in the same order,
+        so the tokens being sampled are copied into its input on the device.  If one of the requests
+        turns out to end on this step's token, its row of the step in flight is computed for nothing and
+        dropped; the others' rows do not depend on it."""
+        nsched, nreqs, plain_greedy, graph = nxt
+        if sampled is None or len(nreqs) != len(sampled_reqs) or any(a is not b for a, b in zip(nreqs, sampled_reqs)):
+            return False
+        if any(r.params.edits_logits for r in nreqs):
+            return False
+        self.num_steps += 1
+        self.num_steps_ahead += 1
+        with torch.cuda.device(self.device), torch.no_grad():
+            graph.commit()
+            graph.token_ids.copy_(sampled, non_blocking=True)
+            logits = graph.run()
+        ahead = self._sample(logits, nreqs, plain_greedy, 1)
+        self._inflight = (nsched, nreqs, plain_greedy, ahead, self._read_back(ahead))
+        return True
 
     def _prepare_next(self, sched: SchedulerOutput, sampled_reqs, plain_greedy):
         """Schedule and pack the next step ahead of time, if it is certain to be a decode step of exactly
@@ -242,4 +311,4 @@ class EngineCore:
         return None
 
     def stats(self) -> dict:
-        return dict(self.scheduler.stats(), num_steps=self.num_steps)
+        return dict(self.scheduler.stats(), num_steps=self.num_steps, num_steps_ahead=self.num_steps_ahead)

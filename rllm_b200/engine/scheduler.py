@@ -240,6 +240,8 @@ class Scheduler:
         """The step ran: its tokens' keys and values are in the cache."""
         for s in out.scheduled:
             req = s.request
+            if req.status is not RequestStatus.RUNNING:
+                continue                 # ended while the step was on the GPU: it holds nothing any more
             before = req.num_computed
             req.num_computed = s.start + s.num_tokens
             # content hashes only when a page was completed by this step

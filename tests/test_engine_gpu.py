@@ -106,6 +106,59 @@ def test_stop_conditions(model_dirs):
     shutil.rmtree(d)
 
 
+@pytest.mark.parametrize("dtype,temperature", [("fp32", 0.0), ("fp32", 0.8)])
+def test_steps_launched_ahead_keep_every_request_right(model_dirs, dtype, temperature):
+    """Decode steps go to the GPU before the tokens of the step before them are read.  Requests that
+    end at different steps (length, a stop token), one that is aborted and one that arrives in the
+    middle each leave a step in flight that holds a row to drop or forces a fresh schedule: every
+    request's tokens are those of the plain implementation, and all pages come back."""
+    from rllm_b200 import SamplingParams
+    name = "A"
+    prompts = prompts_for(name, [9, 14, 6, 11, 7], 21)
+    plain = pl.read_model_dir(model_dirs[name])
+    llm = make_llm(model_dirs, name, dtype=dtype, enable_prefix_caching=False)
+    free = llm.engine.cache.num_free_pages()
+
+    def sp(i, n, **kw):
+        return SamplingParams(temperature=temperature, max_tokens=n, seed=40 + i, ignore_eos=True, **kw)
+
+    def want(i, n):
+        if temperature == 0.0:
+            return plain.greedy(prompts[i], n)
+        toks = list(prompts[i])
+        for j in range(n):
+            x = pl.process_logits(plain.logits(toks)[-1].numpy(), temperature=temperature)
+            toks.append(pl.sample_row(x, temperature, -1, pl.uniform_for(40 + i, j)))
+        return toks[len(prompts[i]):]
+    full1 = want(1, 40)
+    stop_tok = full1[17]
+    n_stop = full1.index(stop_tok) + 1
+    ids = [llm.add_request(prompts[0], sp(0, 40)), llm.add_request(prompts[1], sp(1, 40, stop_token_ids=[stop_tok])),
+           llm.add_request(prompts[2], sp(2, 23)), llm.add_request(prompts[3], sp(3, 40))]
+    got = {i: [] for i in ids}
+    reasons = {}
+    steps = 0
+    late = None
+    while llm.has_work():
+        for out in llm.step():
+            got.setdefault(out.request_id, []).extend(out.outputs[0].token_ids)
+            if out.finished:
+                reasons[out.request_id] = out.outputs[0].finish_reason
+        steps += 1
+        if steps == 12:
+            assert llm.abort_request(ids[3])
+        if steps == 27:
+            late = llm.add_request(prompts[4], sp(4, 15))
+    assert got[ids[0]] == want(0, 40) and reasons[ids[0]] == "length"
+    assert got[ids[1]] == full1[:n_stop] and reasons[ids[1]] == "stop"
+    assert got[ids[2]] == want(2, 23) and reasons[ids[2]] == "length"
+    assert got[ids[3]] == want(3, 40)[:len(got[ids[3]])] and 0 < len(got[ids[3]]) < 40
+    assert got[late] == want(4, 15)
+    assert llm.engine.stats()["num_steps_ahead"] > 10
+    llm.engine.cache.check()
+    assert llm.engine.cache.num_free_pages() == free and llm.engine.cache.usage()["num_requests"] == 0
+
+
 def test_preemption_does_not_change_outputs(model_dirs):
     from rllm_b200 import SamplingParams
     name = "B"
