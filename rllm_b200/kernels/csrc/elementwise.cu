@@ -285,6 +285,72 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
   }
 }
 
+// bfloat16 with head sizes and rotary sizes that are multiples of 16: a thread takes 8 consecutive dims of
+// the first half of a head's rotated part and the 8 dims that pair with them, 16 bytes a load and a store;
+// the unrotated dims of k and all of v are copied 16 bytes at a time.  Same arithmetic as above.
+__global__ void rope_kv_write_bf16x8_kernel(bf16* __restrict__ qkv, const int* __restrict__ positions,
+                                            const int* __restrict__ token_seq,
+                                            const double* __restrict__ inv_freq, int rotary_dim,
+                                            const int* __restrict__ block_table, int max_blocks,
+                                            bf16* __restrict__ kcache, bf16* __restrict__ vcache, int nq, int nkv,
+                                            int d, int page_size, int num_pages, int write_kv,
+                                            int* __restrict__ err) {
+  extern __shared__ float cs[];  // cos[rd/2], sin[rd/2]
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rotary_dim >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) rope_cos_sin(pos, inv_freq[i], &cs[i], &cs[half + i]);
+  __syncthreads();
+  bf16* row = qkv + (size_t)t * (nq + 2 * nkv) * d;
+  long long kdst = -1;
+  if (write_kv) {
+    const int seq = token_seq[t];
+    const int page = block_table[(size_t)seq * max_blocks + pos / page_size];
+    if (page < 0 || page >= num_pages) {
+      if (threadIdx.x == 0) atomicOr(err, 2);
+    } else {
+      kdst = ((long long)page * nkv * page_size + pos % page_size) * d;     // head 0; a head further: page_size * d
+    }
+  }
+  const int hc = half >> 3;                    // 16-byte chunks in half a rotated part
+  const int heads = nq + (write_kv ? nkv : 0);
+  for (int idx = threadIdx.x; idx < heads * hc; idx += blockDim.x) {
+    const int h = idx / hc, c = idx - h * hc;
+    bf16* x = row + (size_t)h * d + c * 8;
+    const uint4 lo = *(const uint4*)x, hi = *(const uint4*)(x + half);
+    const __nv_bfloat162* lp = (const __nv_bfloat162*)&lo;
+    const __nv_bfloat162* hp = (const __nv_bfloat162*)&hi;
+    uint4 olo, ohi;
+    __nv_bfloat162* ol = (__nv_bfloat162*)&olo;
+    __nv_bfloat162* oh = (__nv_bfloat162*)&ohi;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 a = __bfloat1622float2(lp[k]), b = __bfloat1622float2(hp[k]);
+      const float c0 = cs[c * 8 + 2 * k], c1 = cs[c * 8 + 2 * k + 1];
+      const float s0 = cs[half + c * 8 + 2 * k], s1 = cs[half + c * 8 + 2 * k + 1];
+      ol[k] = __floats2bfloat162_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+      oh[k] = __floats2bfloat162_rn(b.x * c0 + a.x * s0, b.y * c1 + a.y * s1);
+    }
+    if (h < nq) {
+      *(uint4*)x = olo;
+      *(uint4*)(x + half) = ohi;
+    } else if (kdst >= 0) {
+      bf16* kd = kcache + kdst + (size_t)(h - nq) * page_size * d + c * 8;
+      *(uint4*)kd = olo;
+      *(uint4*)(kd + half) = ohi;
+    }
+  }
+  if (kdst < 0) return;
+  // the dims of k behind the rotated part, and v
+  const int dc = d >> 3, rc = rotary_dim >> 3;
+  for (int idx = threadIdx.x; idx < nkv * dc; idx += blockDim.x) {
+    const int h = idx / dc, c = idx - h * dc;
+    const size_t dst = (size_t)kdst + (size_t)h * page_size * d + c * 8;
+    *(uint4*)(vcache + dst) = *(const uint4*)(row + (size_t)(nq + nkv + h) * d + c * 8);
+    if (c >= rc) *(uint4*)(kcache + dst) = *(const uint4*)(row + (size_t)(nq + h) * d + c * 8);
+  }
+}
+
 RLLM_EXPORT int rllm_rope_kv_write(void* qkv, int dtype, const int* positions, const int* token_seq,
                                    const double* inv_freq, int rotary_dim, const int* block_table,
                                    int max_blocks, void* kcache, void* vcache, int T, int nq, int nkv,
@@ -296,6 +362,13 @@ RLLM_EXPORT int rllm_rope_kv_write(void* qkv, int dtype, const int* positions, c
   if (write_kv && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0)) return RLLM_E_BADARG;
   size_t smem = (size_t)rotary_dim * sizeof(float);
   if (smem > 48 * 1024) return RLLM_E_UNSUPPORTED;
+  if (dtype == RLLM_DT_BF16 && d % 16 == 0 && rotary_dim % 16 == 0 && rotary_dim > 0 &&
+      (((uintptr_t)qkv | (uintptr_t)kcache | (uintptr_t)vcache) & 15) == 0) {
+    rope_kv_write_bf16x8_kernel<<<T, 128, smem, stream>>>((bf16*)qkv, positions, token_seq, inv_freq, rotary_dim,
+        block_table, max_blocks, (bf16*)kcache, (bf16*)vcache, nq, nkv, d, page_size, num_pages, write_kv, err);
+    RLLM_LAUNCH_CHECK();
+    return 0;
+  }
   RLLM_DISPATCH_DTYPE(dtype, T_,
     (rope_kv_write_kernel<T_><<<T, 128, smem, stream>>>((T_*)qkv, positions, token_seq, inv_freq,
         rotary_dim, block_table, max_blocks, (T_*)kcache, (T_*)vcache, nq, nkv, d, page_size,
