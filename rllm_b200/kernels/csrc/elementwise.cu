@@ -166,7 +166,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
 template <typename TD, typename TO>
 static int rmsnorm_launch_w(float* x, const void* delta, const int* rows, const void* w, int w_dtype,
                             void* out, int R, int H, float eps, int writeback, cudaStream_t stream) {
-  int threads = H >= 8192 ? 1024 : (H >= 2048 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64)));
+  int threads = H >= 8192 ? 1024 : (H >= 4096 ? 512 : (H >= 1024 ? 256 : (H >= 256 ? 128 : 64)));
   const int early = R <= 4 * 148 ? 1 : 0;      // all of the grid's CTAs are resident at once
   cudaError_t e;
   if (w_dtype == RLLM_DT_F32)
