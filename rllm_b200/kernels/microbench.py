@@ -2,7 +2,7 @@
 
     python -m rllm_b200.kernels.microbench attention_decode --batch 8 --context 4096
     python -m rllm_b200.kernels.microbench attention_prefill --tokens 2048 [--impl tcgen05]
-    python -m rllm_b200.kernels.microbench gemm_small_m --rows 8
+    python -m rllm_b200.kernels.microbench gemm_small_m --rows 8 [--variant residual|rstd]
     python -m rllm_b200.kernels.microbench gemm_tcgen05 --rows 2048
 
 Sizes default to the Llama-3.2-1B shape (32 heads, 8 kv heads, head 64, hidden
@@ -113,18 +113,32 @@ def _shapes(args):
 
 
 def gemm_small_m(args) -> None:
+    """--variant plain: the four projections.  residual: o and down adding into a float32 stream and
+    preparing the next norm.  rstd: qkv and gate_up applying the norm's row factors."""
     M = args.rows
     for name, N, K in _shapes(args):
+        silu = name == "gate_up"
+        if args.variant == "residual" and name not in ("o_proj", "down"):
+            continue
+        if args.variant == "rstd" and name not in ("qkv", "gate_up"):
+            continue
         nw = max(2, int(300e6 // (N * K * 2)) + 1)
         ws = [(torch.randn(N, K, device=DEV) * 0.02).bfloat16() for _ in range(nw)]
         x = torch.randn(M, K, device=DEV).bfloat16()
-        silu = name == "gate_up"
         out = torch.empty(M, N // 2 if silu else N, device=DEV, dtype=torch.bfloat16)
+        h = torch.randn(M, N, device=DEV)
+        wn = torch.ones(N, device=DEV)
+        parts = torch.ones(128, M, device=DEV)
 
         def run(i):
-            ops.gemm_small_m(x, ws[i % nw], out, "silu_mul" if silu else "store")
+            if args.variant == "residual":
+                ops.gemm_small_m_residual(x, ws[i % nw], h, wn)
+            elif args.variant == "rstd":
+                ops.gemm_small_m_rstd(x, parts, 1e-5, ws[i % nw], out, "silu_mul" if silu else "store")
+            else:
+                ops.gemm_small_m(x, ws[i % nw], out, "silu_mul" if silu else "store")
         us = time_graph_us(run, args.iters)
-        print(f"gemm_small_m rows {M} {name}{' +silu' if silu else ''} [{N} x {K}]: {us:.1f} us, "
+        print(f"gemm_small_m ({args.variant}) rows {M} {name}{' +silu' if silu else ''} [{N} x {K}]: {us:.1f} us, "
               f"{N * K * 2 / us / 1e3:.0f} GB/s of weight")
 
 
@@ -158,6 +172,8 @@ def main(argv=None) -> int:
     p.add_argument("--hidden", type=int, default=2048)
     p.add_argument("--intermediate", type=int, default=8192)
     p.add_argument("--page", type=int, default=16)
+    p.add_argument("--variant", choices=["plain", "residual", "rstd"], default="plain",
+                   help="gemm_small_m: which epilogue / operand form")
     p.add_argument("--impl", choices=["mma", "tcgen05"], default="mma",
                    help="attention_prefill: the mma.sync kernel or the tcgen05 kernel")
     args = p.parse_args(argv)
