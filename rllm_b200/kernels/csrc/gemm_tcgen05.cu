@@ -34,7 +34,9 @@
 #define TG_EPI_BF16 0
 #define TG_EPI_F32 1
 #define TG_EPI_SILU 2
-template <int BN> constexpr int tg_stages() { return BN == 256 ? 4 : 6; }
+template <int BN> constexpr int tg_stages() { return BN == 256 ? 4 : (BN == 192 ? 5 : 6); }
+// TMEM columns for two accumulators of BN columns: a power of two
+template <int BN> constexpr int tg_tmem_cols() { return BN > 128 ? 512 : 256; }
 template <int BN> constexpr int tg_stage_bytes() { return (TG_BM + BN) * TG_BK * 2; }
 template <int BN> constexpr int tg_smem_bytes() { return tg_stages<BN>() * tg_stage_bytes<BN>() + 1024 + 256; }
 
@@ -69,7 +71,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_w) : "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tg_smem(tmem_slot)), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tg_smem(tmem_slot)), "r"(tg_tmem_cols<BN>()) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -201,7 +203,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tg_tmem_cols<BN>()) : "memory");
   }
 }
 
@@ -263,22 +265,27 @@ RLLM_EXPORT int rllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
   if (K <= 0 || lda < K || ldw < K || ldo < N || !err) return RLLM_E_BADARG;
   // TMA: 16-byte aligned bases and row strides
   if (K % 8 || lda % 8 || ldw % 8 || (((uintptr_t)a | (uintptr_t)w) & 15)) return RLLM_E_UNSUPPORTED;
-  // 128 x 256 tiles unless 128 x 128 tiles fill the SMs' last round better
-  bool wide = N > 128;
-  if (wide) {
+  // Tile width 256, 192 or 128: the one with the least estimated time = rounds of the persistent CTAs x
+  // width x a factor for what a narrower tile costs (A is read again more often, the epilogue overlaps less).
+  int bn = N > 192 ? 256 : (N > 128 ? 192 : 128);
+  if (N > 128) {
     const long long tm = (M + TG_BM - 1) / TG_BM, sms = 148;
-    const long long t256 = tm * ((N + 255) / 256), t128 = tm * ((N + 127) / 128);
-    const double e256 = (double)t256 / (double)(((t256 + sms - 1) / sms) * sms);
-    const double e128 = (double)t128 / (double)(((t128 + sms - 1) / sms) * sms);
-    if (e128 > e256 * 1.6) wide = false;     // the narrow tile re-reads A twice as often: only for a big gain
+    double best = 1e30;
+    const int widths[3] = {256, 192, 128};
+    const double factor[3] = {1.0, 1.05, 1.3};
+    for (int i = 0; i < 3; ++i) {
+      const long long tiles = tm * ((N + widths[i] - 1) / widths[i]);
+      const double cost = (double)((tiles + sms - 1) / sms) * widths[i] * factor[i];
+      if (cost < best * 0.999) { best = cost; bn = widths[i]; }
+    }
   }
+#define TG_BY_WIDTH(EPI_)                                                                                      \
+  if (bn == 256) return tg_launch<256, EPI_>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);            \
+  if (bn == 192) return tg_launch<192, EPI_>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);            \
+  return tg_launch<128, EPI_>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream)
   switch (epilogue) {
-    case TG_EPI_BF16:
-      if (wide) return tg_launch<256, TG_EPI_BF16>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
-      return tg_launch<128, TG_EPI_BF16>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
-    case TG_EPI_F32:
-      if (wide) return tg_launch<256, TG_EPI_F32>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
-      return tg_launch<128, TG_EPI_F32>(a, lda, w, ldw, N, out, ldo, M, N, K, 0, err, stream);
+    case TG_EPI_BF16: TG_BY_WIDTH(TG_EPI_BF16);
+    case TG_EPI_F32: TG_BY_WIDTH(TG_EPI_F32);
     case TG_EPI_SILU:
       return tg_launch<256, TG_EPI_SILU>(a, lda, w, ldw, 2 * N, out, ldo, M, N, K, N, err, stream);
   }
