@@ -236,27 +236,90 @@ RLLM_EXPORT int rllm_sample(const float* logits, int R, int V, int ld, const flo
   return 0;
 }
 
-// Greedy only: out[r] = lowest index of the largest logit of row r.
+// Greedy only: out[r] = lowest index of the largest logit of row r.  A row is cut into `split` ranges,
+// one CTA each (a vocabulary of 128k in one CTA is all latency); a range's (max, index) goes to
+// `partials`, and the CTA that finds itself last for its row (a counter that the kernel leaves at zero)
+// takes the best of the ranges.  Ties go to the lowest index at every level, so the cut changes nothing.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out_tokens) {
+argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__ out_tokens,
+              ArgMax* __restrict__ partials, int* __restrict__ counters, int split) {
   __shared__ ArgMax sm_arg[32];
+  __shared__ int s_last;
   pdl_wait();
   pdl_launch();
-  const float* x = logits + (size_t)blockIdx.x * ld;
+  const int r = blockIdx.y, part = blockIdx.x;
+  const float* x = logits + (size_t)r * ld;
+  const int per = (((V + split - 1) / split) + 3) & ~3;
+  const int lo = part * per, hi = min(V, lo + per);
   ArgMax best; best.v = -INFINITY; best.i = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    ArgMax c; c.v = x[i]; c.i = i;
-    best = argmax_better(best, c);
+  if ((((uintptr_t)x) & 15) == 0) {
+    // lo is a multiple of 4: 16-byte loads, then the tail
+    const int n4 = hi > lo ? (hi - lo) >> 2 : 0;
+    const float4* x4 = (const float4*)(x + lo);
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 v = x4[i];
+      const int j = lo + 4 * i;
+      ArgMax c;
+      c.v = v.x; c.i = j; best = argmax_better(best, c);
+      c.v = v.y; c.i = j + 1; best = argmax_better(best, c);
+      c.v = v.z; c.i = j + 2; best = argmax_better(best, c);
+      c.v = v.w; c.i = j + 3; best = argmax_better(best, c);
+    }
+    for (int i = lo + 4 * n4 + threadIdx.x; i < hi; i += blockDim.x) {
+      ArgMax c; c.v = x[i]; c.i = i;
+      best = argmax_better(best, c);
+    }
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      ArgMax c; c.v = x[i]; c.i = i;
+      best = argmax_better(best, c);
+    }
   }
   best = block_argmax(best, sm_arg);
-  if (threadIdx.x == 0) out_tokens[blockIdx.x] = best.i == 0x7fffffff ? 0 : best.i;
+  if (split == 1) {
+    if (threadIdx.x == 0) out_tokens[r] = best.i == 0x7fffffff ? 0 : best.i;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    partials[(size_t)r * split + part] = best;
+    asm volatile("fence.acq_rel.gpu;" ::: "memory");
+    const int done = atomicAdd(&counters[r], 1);
+    s_last = done == split - 1;
+    if (s_last) counters[r] = 0;
+  }
+  __syncthreads();
+  if (!s_last || threadIdx.x >= 32) return;
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+  ArgMax a; a.v = -INFINITY; a.i = 0x7fffffff;
+  for (int p = threadIdx.x; p < split; p += 32) {
+    ArgMax c;
+    c.v = __ldcg(&partials[(size_t)r * split + p].v);
+    c.i = __ldcg(&partials[(size_t)r * split + p].i);
+    a = argmax_better(a, c);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax c; c.v = __shfl_xor_sync(0xffffffffu, a.v, o); c.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+    a = argmax_better(a, c);
+  }
+  if (threadIdx.x == 0) out_tokens[r] = a.i == 0x7fffffff ? 0 : a.i;
 }
 
-RLLM_EXPORT int rllm_argmax(const float* logits, int R, int V, int ld, int* out_tokens,
-                            cudaStream_t stream) {
+// How a row of V logits is cut for rllm_argmax, and the scratch it needs: R * split (max, index) pairs of
+// 8 bytes and R counters that are zero before the call (the kernel leaves them zero).
+RLLM_EXPORT int rllm_argmax_split(int V) {
+  const int s = (V + 4095) / 4096;
+  return s < 1 ? 1 : (s > 64 ? 64 : s);
+}
+
+RLLM_EXPORT int rllm_argmax(const float* logits, int R, int V, int ld, int* out_tokens, void* partials,
+                            int* counters, cudaStream_t stream) {
   if (R <= 0) return 0;
-  if (V <= 0 || ld < V) return RLLM_E_BADARG;
-  return (int)rllm_launch_pdl(argmax_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, V, ld, out_tokens);
+  if (V <= 0 || ld < V || R > 65535) return RLLM_E_BADARG;
+  const int split = rllm_argmax_split(V);
+  if (split > 1 && (!partials || !counters)) return RLLM_E_BADARG;
+  return (int)rllm_launch_pdl(argmax_kernel, dim3(split, R), dim3(SAMPLE_THREADS), 0, stream, logits, V, ld,
+                              out_tokens, (ArgMax*)partials, counters, split);
 }
 
 // ---------------------------------------------------------------------------

@@ -333,12 +333,23 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> Optio
 
 
 # ---------------------------------------------------------------------------
+_argmax_scratch = {}
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = lowest index of the largest value of row r (float32 rows)."""
     lib = build.load_library("sampling")
     R, V = logits.shape
     assert logits.dtype is torch.float32 and out.dtype is torch.int32 and logits.stride(1) == 1
+    split = int(lib.rllm_argmax_split(c_int(V)))
+    scratch = _argmax_scratch.get(logits.device)
+    if scratch is None or scratch[1].numel() < R:
+        rows = max(R, 256)
+        scratch = (torch.empty(rows * 64 * 2, dtype=torch.int32, device=logits.device),
+                   torch.zeros(rows, dtype=torch.int32, device=logits.device))
+        _argmax_scratch[logits.device] = scratch
     _check(lib.rllm_argmax(_ptr(logits), c_int(R), c_int(V), c_int(logits.stride(0)), _ptr(out),
-                           _stream()), "argmax")
+                           _ptr(scratch[0]), _ptr(scratch[1]), _stream()), "argmax")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,

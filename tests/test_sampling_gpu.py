@@ -32,6 +32,30 @@ def plain_pick(logits_row, p, seed, gen_index, context=(), eos=()):
     return pl.sample_row(x, p.temperature, p.top_k, pl.uniform_for(seed, gen_index))
 
 
+@pytest.mark.parametrize("V", [1, 255, 4096, 4097, 128256, 128259, 300001])
+def test_argmax_kernel_at_any_width(V):
+    """Rows are cut into ranges for several CTAs: the largest value wins wherever it lies, ties go to
+    the lowest index also across the ranges' edges, and a row of -inf gives token 0."""
+    from rllm_b200.kernels import ops
+    torch.manual_seed(V)
+    R = 7
+    logits = torch.randn(R, V, device=DEV)
+    if V > 4:
+        logits[1, V - 1] = 40.0                       # the last element
+        logits[2, 0] = logits[2, V - 1] = 41.0        # a tie between the first and the last range
+        logits[3, V // 2] = logits[3, V // 2 + 1] = 42.0
+        logits[4] = -float("inf")
+        logits[5, min(V - 1, 4096)] = logits[5, min(V - 1, 4095)] = 43.0   # a tie across an edge between ranges
+    out = torch.full((R,), -1, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, out)
+    want = logits.argmax(dim=1).tolist()
+    if V > 4:
+        want[2], want[3], want[4], want[5] = 0, V // 2, 0, min(V - 1, 4095)
+    assert out.tolist() == want
+    ops.argmax(logits[:, : V - V // 3], out)           # a view: rows are not contiguous
+    assert out.tolist()[0] == int(logits[0, : V - V // 3].argmax())
+
+
 def test_greedy_is_argmax_with_lowest_index_on_ties(sampler):
     from rllm_b200.sampling import SamplingParams
     torch.manual_seed(0)
