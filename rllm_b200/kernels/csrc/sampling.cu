@@ -88,12 +88,27 @@ __device__ unsigned radix_select(const float* __restrict__ x, int V, float inv_t
     const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
     for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0ull;
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float y = x[i] * inv_t;
-      const unsigned key = f2key(y);
-      if (key < floor_key || (key & himask) != prefix) continue;
-      const unsigned long long w = by_mass ? fx_mass(y, mx) : 1ull;
-      if (w) atomicAdd(&hist[(key >> shift) & 0xffu], w);
+    // The keys of a row crowd into a few bins: the lanes of a warp that hit the same bin add their
+    // weights up among themselves (two 32-bit sums of the halves of weights below 2^41), and one of
+    // them adds the sum to the bin.  Integer sums: the order does not matter.
+    const int lane = threadIdx.x & 31;
+    const int iters = (V + (int)blockDim.x - 1) / (int)blockDim.x;
+    for (int it = 0; it < iters; ++it) {
+      const int i = it * (int)blockDim.x + (int)threadIdx.x;
+      unsigned long long w = 0;
+      unsigned key = 0;
+      if (i < V) {
+        const float y = x[i] * inv_t;
+        key = f2key(y);
+        if (!(key < floor_key || (key & himask) != prefix)) w = by_mass ? fx_mass(y, mx) : 1ull;
+      }
+      const unsigned bin = w ? ((key >> shift) & 0xffu) : 256u + (unsigned)lane;   // lanes without weight stay alone
+      const unsigned m = __match_any_sync(0xffffffffu, bin);
+      if (w) {
+        const unsigned lo = __reduce_add_sync(m, (unsigned)(w & 0xfffffull));
+        const unsigned hi = __reduce_add_sync(m, (unsigned)(w >> 20));
+        if (lane == __ffs(m) - 1) atomicAdd(&hist[bin], ((unsigned long long)hi << 20) + lo);
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -320,6 +335,190 @@ RLLM_EXPORT int rllm_argmax(const float* logits, int R, int V, int ld, int* out_
   if (split > 1 && (!partials || !counters)) return RLLM_E_BADARG;
   return (int)rllm_launch_pdl(argmax_kernel, dim3(split, R), dim3(SAMPLE_THREADS), 0, stream, logits, V, ld,
                               out_tokens, (ArgMax*)partials, counters, split);
+}
+
+// ---------------------------------------------------------------------------
+// The same draw with a row cut into `split` ranges, one CTA each, for rows without top-k and top-p
+// (temperature and min-p only; greedy rows too): three small kernels instead of one CTA that walks a
+// 128k vocabulary three times.  The mass is the same exact 64-bit fixed point, the target the same
+// floor(total * u), the token the first index whose running sum exceeds it: the result is the one of
+// sample_kernel, bit for bit.
+//   1. sample_split_max:  (max of x / t, its lowest index) of every range
+//   2. sample_split_mass: the row's max from the ranges'; the mass of every range (a greedy row is
+//      finished here)
+//   3. sample_split_draw: the range the target falls into, then the token inside it
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ ArgMax row_best(const ArgMax* __restrict__ partials, int split, ArgMax* sm) {
+  ArgMax a; a.v = -INFINITY; a.i = 0x7fffffff;
+  for (int p = threadIdx.x; p < split; p += blockDim.x) a = argmax_better(a, partials[p]);
+  return block_argmax(a, sm);
+}
+__device__ __forceinline__ void split_range(int V, int split, int part, int* lo, int* hi) {
+  const int per = (((V + split - 1) / split) + 3) & ~3;
+  *lo = min(V, part * per);
+  *hi = min(V, *lo + per);
+}
+
+__global__ void __launch_bounds__(256)
+sample_split_max_kernel(const float* __restrict__ logits, int V, int ld, const float* __restrict__ temperature,
+                        const int* __restrict__ top_k, ArgMax* __restrict__ partials, int split) {
+  __shared__ ArgMax sm_arg[32];
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.y, part = blockIdx.x;
+  const float* x = logits + (size_t)r * ld;
+  const float temp = temperature[r];
+  const float inv_t = (!(temp > 0.f) || top_k[r] == 1) ? 1.0f : 1.0f / temp;
+  int lo, hi;
+  split_range(V, split, part, &lo, &hi);
+  ArgMax best; best.v = -INFINITY; best.i = 0x7fffffff;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    ArgMax c; c.v = x[i] * inv_t; c.i = i;
+    best = argmax_better(best, c);
+  }
+  best = block_argmax(best, sm_arg);
+  if (threadIdx.x == 0) partials[(size_t)r * split + part] = best;
+}
+
+__global__ void __launch_bounds__(256)
+sample_split_mass_kernel(const float* __restrict__ logits, int V, int ld, const float* __restrict__ temperature,
+                         const int* __restrict__ top_k, const float* __restrict__ min_p,
+                         const ArgMax* __restrict__ partials, unsigned long long* __restrict__ psum, int split,
+                         int* __restrict__ out_tokens) {
+  __shared__ ArgMax sm_arg[32];
+  __shared__ unsigned long long sm_sum[8];
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.y, part = blockIdx.x;
+  const float* x = logits + (size_t)r * ld;
+  const float temp = temperature[r];
+  const bool greedy = !(temp > 0.f) || top_k[r] == 1;
+  const ArgMax best = row_best(partials + (size_t)r * split, split, sm_arg);
+  if (greedy || best.v == -INFINITY) {
+    if (part == 0 && threadIdx.x == 0) out_tokens[r] = best.i == 0x7fffffff ? 0 : best.i;
+    return;
+  }
+  const float inv_t = 1.0f / temp, mx = best.v, mp = min_p[r];
+  const unsigned thr_key = mp > 0.f ? f2key(logf(mp) + mx) : 0u;
+  int lo, hi;
+  split_range(V, split, part, &lo, &hi);
+  unsigned long long mine = 0;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float y = x[i] * inv_t;
+    if (f2key(y) >= thr_key) mine += fx_mass(y, mx);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+  if ((threadIdx.x & 31) == 0) sm_sum[threadIdx.x >> 5] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long t = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sm_sum[w];
+    psum[(size_t)r * split + part] = t;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+sample_split_draw_kernel(const float* __restrict__ logits, int V, int ld, const float* __restrict__ temperature,
+                         const int* __restrict__ top_k, const float* __restrict__ min_p,
+                         const unsigned long long* __restrict__ seeds, const long long* __restrict__ gen_index,
+                         const ArgMax* __restrict__ partials, const unsigned long long* __restrict__ psum,
+                         int split, int* __restrict__ out_tokens) {
+  __shared__ ArgMax sm_arg[32];
+  __shared__ unsigned long long seg_sum[256];
+  __shared__ int sh_pick;
+  __shared__ unsigned long long sh_rest;
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.x;
+  const float* x = logits + (size_t)r * ld;
+  const float temp = temperature[r];
+  if (!(temp > 0.f) || top_k[r] == 1) return;                 // greedy: done by the kernel before
+  const ArgMax best = row_best(partials + (size_t)r * split, split, sm_arg);
+  if (best.v == -INFINITY) return;
+  const float inv_t = 1.0f / temp, mx = best.v, mp = min_p[r];
+  const unsigned thr_key = mp > 0.f ? f2key(logf(mp) + mx) : 0u;
+  if (threadIdx.x == 0) {
+    const unsigned long long* ps = psum + (size_t)r * split;
+    unsigned long long total = 0;
+    for (int p = 0; p < split; ++p) total += ps[p];
+    unsigned w[4];
+    const unsigned long long seed = seeds[r];
+    const unsigned long long ctr = (unsigned long long)gen_index[r];
+    philox4x32_10((unsigned)ctr, (unsigned)(ctr >> 32), 0u, 0u, (unsigned)seed, (unsigned)(seed >> 32), w);
+    const unsigned long long u24 = w[0] >> 8;  // u = u24 / 2^24 in [0, 1)
+    const unsigned long long thi = __umul64hi(total, u24), tlo = total * u24;
+    const unsigned long long target = (thi << 40) | (tlo >> 24);  // floor(total * u)
+    unsigned long long c = 0;
+    int pick = split - 1;
+    for (int p = 0; p < split; ++p) {
+      if (c + ps[p] > target) { pick = p; break; }
+      c += ps[p];
+    }
+    sh_pick = pick;
+    sh_rest = target - c;                // what is left to pass inside the picked range
+  }
+  __syncthreads();
+  int rlo, rhi;
+  split_range(V, split, sh_pick, &rlo, &rhi);
+  // inside the range: a contiguous segment a thread, exact integer prefix sums
+  const int seg = (rhi - rlo + blockDim.x - 1) / blockDim.x;
+  const int lo = min(rhi, rlo + (int)threadIdx.x * seg), hi = min(rhi, lo + seg);
+  unsigned long long mine = 0;
+  for (int i = lo; i < hi; ++i) {
+    const float y = x[i] * inv_t;
+    if (f2key(y) >= thr_key) mine += fx_mass(y, mx);
+  }
+  seg_sum[threadIdx.x] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long c = 0;
+    const unsigned long long rest = sh_rest;
+    int pick = blockDim.x - 1;
+    for (int i = 0; i < (int)blockDim.x; ++i) {
+      if (c + seg_sum[i] > rest) { pick = i; break; }
+      c += seg_sum[i];
+    }
+    sh_pick = pick;
+    sh_rest = rest - c;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x == sh_pick) {
+    const unsigned long long rest = sh_rest;
+    unsigned long long c = 0;
+    int tok = -1, last_kept = -1;
+    for (int i = lo; i < hi; ++i) {
+      const float y = x[i] * inv_t;
+      if (f2key(y) < thr_key) continue;
+      const unsigned long long w = fx_mass(y, mx);
+      if (w) last_kept = i;
+      c += w;
+      if (c > rest) { tok = i; break; }
+    }
+    if (tok < 0) tok = last_kept >= 0 ? last_kept : best.i;
+    out_tokens[r] = tok;
+  }
+}
+
+// Rows with top_k not in {0, 1, >= V} or top_p in (0, 1) are not for this entry point (the caller checks).
+// partials: R * split (max, index) pairs; psum: R * split 64-bit sums; split = rllm_argmax_split(V).
+RLLM_EXPORT int rllm_sample_split(const float* logits, int R, int V, int ld, const float* temperature,
+                                  const int* top_k, const float* min_p, const unsigned long long* seeds,
+                                  const long long* gen_index, int* out_tokens, void* partials, void* psum,
+                                  cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0 || ld < V || R > 65535 || !partials || !psum) return RLLM_E_BADARG;
+  const int split = rllm_argmax_split(V);
+  cudaError_t e = rllm_launch_pdl(sample_split_max_kernel, dim3(split, R), dim3(256), 0, stream, logits, V, ld,
+                                  temperature, top_k, (ArgMax*)partials, split);
+  if (e != cudaSuccess) return (int)e;
+  e = rllm_launch_pdl(sample_split_mass_kernel, dim3(split, R), dim3(256), 0, stream, logits, V, ld, temperature,
+                      top_k, min_p, (const ArgMax*)partials, (unsigned long long*)psum, split, out_tokens);
+  if (e != cudaSuccess) return (int)e;
+  e = rllm_launch_pdl(sample_split_draw_kernel, dim3(R), dim3(256), 0, stream, logits, V, ld, temperature, top_k,
+                      min_p, seeds, gen_index, (const ArgMax*)partials, (const unsigned long long*)psum, split,
+                      out_tokens);
+  return (int)e;
 }
 
 // ---------------------------------------------------------------------------

@@ -365,6 +365,29 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
                            _ptr(out), _stream()), "sample")
 
 
+_sample_scratch = {}
+
+
+def sample_split(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, min_p: torch.Tensor,
+                 seeds: torch.Tensor, gen_index: torch.Tensor, out: torch.Tensor) -> None:
+    """``sample`` for rows without top-k and top-p (top_k 0 or 1, top_p outside (0, 1)): a row is worked on
+    by several CTAs; the same tokens as ``sample``."""
+    lib = build.load_library("sampling")
+    R, V = logits.shape
+    assert logits.dtype is torch.float32 and logits.stride(1) == 1
+    assert temperature.dtype is torch.float32 and top_k.dtype is torch.int32 and min_p.dtype is torch.float32
+    assert seeds.dtype is torch.int64 and gen_index.dtype is torch.int64 and out.dtype is torch.int32
+    scratch = _sample_scratch.get(logits.device)
+    if scratch is None or scratch[0].numel() < R * 64 * 2:
+        rows = max(R, 256)
+        scratch = (torch.empty(rows * 64 * 2, dtype=torch.int32, device=logits.device),
+                   torch.empty(rows * 64, dtype=torch.int64, device=logits.device))
+        _sample_scratch[logits.device] = scratch
+    _check(lib.rllm_sample_split(_ptr(logits), c_int(R), c_int(V), c_int(logits.stride(0)), _ptr(temperature),
+                                 _ptr(top_k), _ptr(min_p), _ptr(seeds), _ptr(gen_index), _ptr(out),
+                                 _ptr(scratch[0]), _ptr(scratch[1]), _stream()), "sample_split")
+
+
 def logit_edits(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor, counts: torch.Tensor,
                 bias: torch.Tensor, rep: torch.Tensor, freq: torch.Tensor, pres: torch.Tensor) -> None:
     lib = build.load_library("sampling")

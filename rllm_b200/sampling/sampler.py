@@ -37,6 +37,18 @@ class Sampler:
     def __init__(self, device: torch.device):
         self.device = device
 
+    def _option_buffers(self, R: int):
+        """(numpy view of a pinned int32 buffer, device buffer, event of the last copy from it); pinned
+        buffers are used in turn so that filling one does not wait for the copy of the call before."""
+        if not hasattr(self, "_pinned") or self._pinned[0][0].numel() < 8 * R:
+            n = max(8 * R, 8 * 256)
+            self._pinned = [(torch.zeros(n, dtype=torch.int32, pin_memory=True), torch.cuda.Event()) for _ in range(4)]
+            self._devbuf = [torch.zeros(n, dtype=torch.int32, device=self.device) for _ in range(4)]
+            self._slot = 0
+        self._slot = (self._slot + 1) % 4
+        t, ev = self._pinned[self._slot]
+        return t.numpy(), self._devbuf[self._slot], ev
+
     def _dev(self, arr: np.ndarray) -> torch.Tensor:
         return torch.from_numpy(arr).to(self.device, non_blocking=False)
 
@@ -106,15 +118,30 @@ class Sampler:
         if all(row.params.greedy for row in rows):
             ops.argmax(logits, out)
             return out
-        f = np.empty((3, R), dtype=np.float32)
-        k = np.empty(R, dtype=np.int32)
-        s = np.empty((2, R), dtype=np.int64)
+        # all per-row options in one pinned buffer and one copy: int64 first (seeds, token indices),
+        # then float32 bits (temperature, top_p, min_p) and int32 (top_k)
+        host, dev, copied = self._option_buffers(R)
+        copied.synchronize()                      # the copy that last read this pinned buffer is through
+        s = host[: 4 * R].view(np.int64).reshape(2, R)
+        f = host[4 * R: 7 * R].view(np.float32).reshape(3, R)
+        k = host[7 * R: 8 * R]
         for r, row in enumerate(rows):
             p = row.params
             f[0, r], f[1, r], f[2, r] = p.temperature, p.top_p, p.min_p
             k[r] = p.top_k
             s[0, r] = np.int64(np.uint64(row.seed & 0xFFFFFFFFFFFFFFFF).astype(np.int64))
             s[1, r] = row.gen_index
-        fd, kd, sd = self._dev(f), self._dev(k), self._dev(s)
-        ops.sample(logits, fd[0], kd, fd[1], fd[2], sd[0], sd[1], out)
+        with torch.cuda.device(self.device):
+            dev[: 8 * R].copy_(self._pinned[self._slot][0][: 8 * R], non_blocking=True)
+            copied.record()
+        sd = dev[: 4 * R].view(torch.int64).view(2, R)
+        fd = dev[4 * R: 7 * R].view(torch.float32).view(3, R)
+        kd = dev[7 * R: 8 * R]
+        V = logits.shape[1]
+        if all((row.params.top_k <= 1 or row.params.top_k >= V) and not (0.0 < row.params.top_p < 1.0)
+               for row in rows):
+            # temperature (and min-p) only: several CTAs a row
+            ops.sample_split(logits, fd[0], kd, fd[2], sd[0], sd[1], out)
+        else:
+            ops.sample(logits, fd[0], kd, fd[1], fd[2], sd[0], sd[1], out)
         return out

@@ -56,6 +56,31 @@ def test_argmax_kernel_at_any_width(V):
     assert out.tolist()[0] == int(logits[0, : V - V // 3].argmax())
 
 
+@pytest.mark.parametrize("V", [7, 256, 4097, 128256, 300001])
+def test_split_sampling_draws_the_same_tokens(V):
+    """Rows without top-k and top-p are sampled by several CTAs a row: the same tokens as the one-CTA
+    kernel, for every temperature, min-p, seed and step, for greedy rows and for a row of -inf."""
+    from rllm_b200.kernels import ops
+    torch.manual_seed(V)
+    R = 12
+    logits = torch.randn(R, V, device=DEV) * 4
+    logits[3] = -float("inf")
+    logits[4, : V // 2] = -float("inf")
+    temperature = torch.tensor([0.7, 1.3, 0.0, 0.9, 0.5, 2.0, 0.8, 1.0, 0.3, 1.0, 0.8, 5.0], device=DEV)
+    top_k = torch.tensor([-1, 0, -1, -1, -1, 1, -1, V + 5, -1, -1, -1, -1], dtype=torch.int32, device=DEV)
+    top_p = torch.ones(R, device=DEV)
+    min_p = torch.tensor([0, 0, 0, 0, 0.1, 0, 0.3, 0, 0, 0.01, 0, 0], dtype=torch.float32, device=DEV)
+    for step in range(6):
+        seeds = torch.arange(R, dtype=torch.int64, device=DEV) * 7919 + step
+        gen = torch.full((R,), step * 3, dtype=torch.int64, device=DEV)
+        a = torch.full((R,), -1, dtype=torch.int32, device=DEV)
+        b = torch.full((R,), -2, dtype=torch.int32, device=DEV)
+        ops.sample(logits, temperature, top_k, top_p, min_p, seeds, gen, a)
+        ops.sample_split(logits, temperature, top_k, min_p, seeds, gen, b)
+        assert a.tolist() == b.tolist(), step
+    assert len(set(a.tolist())) > 3
+
+
 def test_greedy_is_argmax_with_lowest_index_on_ties(sampler):
     from rllm_b200.sampling import SamplingParams
     torch.manual_seed(0)
