@@ -53,6 +53,12 @@ __device__ void philox4x32_10(unsigned c0, unsigned c1, unsigned c2, unsigned c3
 }
 
 struct ArgMax { float v; int i; };
+// a row's radix descent in the several-CTAs pipeline (top-k by count, then top-p by mass)
+struct SelectState {
+  unsigned prefix, thr_key;
+  unsigned long long cum, target, total;
+  int counter, active;
+};
 __device__ __forceinline__ ArgMax argmax_better(ArgMax a, ArgMax b) {
   if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
   return a;
@@ -239,10 +245,10 @@ sample_kernel(const float* __restrict__ logits, int V, int ld, const float* __re
   }
 }
 
-RLLM_EXPORT int rllm_sample(const float* logits, int R, int V, int ld, const float* temperature,
-                            const int* top_k, const float* top_p, const float* min_p,
-                            const unsigned long long* seeds, const long long* gen_index,
-                            int* out_tokens, cudaStream_t stream) {
+RLLM_EXPORT int rllm_sample_one_cta(const float* logits, int R, int V, int ld, const float* temperature,
+                                    const int* top_k, const float* top_p, const float* min_p,
+                                    const unsigned long long* seeds, const long long* gen_index,
+                                    int* out_tokens, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0 || ld < V) return RLLM_E_BADARG;
   sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, V, ld, temperature, top_k, top_p, min_p,
@@ -384,7 +390,7 @@ __global__ void __launch_bounds__(256)
 sample_split_mass_kernel(const float* __restrict__ logits, int V, int ld, const float* __restrict__ temperature,
                          const int* __restrict__ top_k, const float* __restrict__ min_p,
                          const ArgMax* __restrict__ partials, unsigned long long* __restrict__ psum, int split,
-                         int* __restrict__ out_tokens) {
+                         int* __restrict__ out_tokens, const SelectState* __restrict__ states) {
   __shared__ ArgMax sm_arg[32];
   __shared__ unsigned long long sm_sum[8];
   pdl_wait();
@@ -399,7 +405,8 @@ sample_split_mass_kernel(const float* __restrict__ logits, int V, int ld, const 
     return;
   }
   const float inv_t = 1.0f / temp, mx = best.v, mp = min_p[r];
-  const unsigned thr_key = mp > 0.f ? f2key(logf(mp) + mx) : 0u;
+  unsigned thr_key = mp > 0.f ? f2key(logf(mp) + mx) : 0u;
+  if (states) thr_key = max(thr_key, states[r].thr_key);
   int lo, hi;
   split_range(V, split, part, &lo, &hi);
   unsigned long long mine = 0;
@@ -423,7 +430,7 @@ sample_split_draw_kernel(const float* __restrict__ logits, int V, int ld, const 
                          const int* __restrict__ top_k, const float* __restrict__ min_p,
                          const unsigned long long* __restrict__ seeds, const long long* __restrict__ gen_index,
                          const ArgMax* __restrict__ partials, const unsigned long long* __restrict__ psum,
-                         int split, int* __restrict__ out_tokens) {
+                         int split, int* __restrict__ out_tokens, const SelectState* __restrict__ states) {
   __shared__ ArgMax sm_arg[32];
   __shared__ unsigned long long seg_sum[256];
   __shared__ int sh_pick;
@@ -437,7 +444,8 @@ sample_split_draw_kernel(const float* __restrict__ logits, int V, int ld, const 
   const ArgMax best = row_best(partials + (size_t)r * split, split, sm_arg);
   if (best.v == -INFINITY) return;
   const float inv_t = 1.0f / temp, mx = best.v, mp = min_p[r];
-  const unsigned thr_key = mp > 0.f ? f2key(logf(mp) + mx) : 0u;
+  unsigned thr_key = mp > 0.f ? f2key(logf(mp) + mx) : 0u;
+  if (states) thr_key = max(thr_key, states[r].thr_key);
   if (threadIdx.x == 0) {
     const unsigned long long* ps = psum + (size_t)r * split;
     unsigned long long total = 0;
@@ -500,24 +508,208 @@ sample_split_draw_kernel(const float* __restrict__ logits, int V, int ld, const 
   }
 }
 
-// Rows with top_k not in {0, 1, >= V} or top_p in (0, 1) are not for this entry point (the caller checks).
-// partials: R * split (max, index) pairs; psum: R * split 64-bit sums; split = rllm_argmax_split(V).
-RLLM_EXPORT int rllm_sample_split(const float* logits, int R, int V, int ld, const float* temperature,
-                                  const int* top_k, const float* min_p, const unsigned long long* seeds,
-                                  const long long* gen_index, int* out_tokens, void* partials, void* psum,
-                                  cudaStream_t stream) {
+// ---------------------------------------------------------------------------
+// Top-k and top-p with a row cut into ranges: the radix descent of radix_select, one kernel a pass.
+// Every CTA adds the histogram of its range to the row's (integer sums: any order), and the CTA that
+// finds itself last for the row takes the descent's next step.  Per row a SelectState and 256 bins.
+//   select_begin   state for the top-k descent (or none)
+//   select_pass x4 by count
+//   select_total   the mass of what top-k left; state for the top-p descent (or none)
+//   select_pass x4 by mass
+//   then the ranges' masses and the draw, as above, with the state's threshold
+// ---------------------------------------------------------------------------
+__global__ void select_begin_kernel(int V, const float* __restrict__ temperature, const int* __restrict__ top_k,
+                                    SelectState* __restrict__ states, unsigned long long* __restrict__ hist) {
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.x;
+  for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[(size_t)r * 256 + b] = 0ull;
+  if (threadIdx.x == 0) {
+    const float temp = temperature[r];
+    const int k = top_k[r];
+    SelectState st;
+    st.prefix = 0u; st.thr_key = 0u; st.cum = 0ull; st.total = 0ull; st.counter = 0;
+    st.active = (temp > 0.f && k > 1 && k < V) ? 1 : 0;
+    st.target = (unsigned long long)(k > 0 ? k : 0);
+    states[r] = st;
+  }
+}
+
+// pass 0..3 of a descent; by_mass: weights are masses, else every element weighs 1
+__global__ void __launch_bounds__(256)
+select_pass_kernel(const float* __restrict__ logits, int V, int ld, const float* __restrict__ temperature,
+                   const ArgMax* __restrict__ partials, int split, SelectState* __restrict__ states,
+                   unsigned long long* __restrict__ hist, int pass, int by_mass) {
+  __shared__ ArgMax sm_arg[32];
+  __shared__ unsigned long long sh[256];
+  __shared__ int s_last;
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.y, part = blockIdx.x;
+  SelectState* st = states + r;
+  if (!st->active) return;
+  const float* x = logits + (size_t)r * ld;
+  const float inv_t = 1.0f / temperature[r];
+  const float mx = by_mass ? row_best(partials + (size_t)r * split, split, sm_arg).v : 0.f;
+  const unsigned prefix = st->prefix, floor_key = st->thr_key;
+  const int shift = 24 - 8 * pass;
+  const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+  for (int b = threadIdx.x; b < 256; b += blockDim.x) sh[b] = 0ull;
+  __syncthreads();
+  int lo, hi;
+  split_range(V, split, part, &lo, &hi);
+  const int lane = threadIdx.x & 31;
+  const int iters = (hi - lo + (int)blockDim.x - 1) / (int)blockDim.x;
+  for (int it = 0; it < iters; ++it) {
+    const int i = lo + it * (int)blockDim.x + (int)threadIdx.x;
+    unsigned long long w = 0;
+    unsigned key = 0;
+    if (i < hi) {
+      const float y = x[i] * inv_t;
+      key = f2key(y);
+      if (!(key < floor_key || (key & himask) != prefix)) w = by_mass ? fx_mass(y, mx) : 1ull;
+    }
+    const unsigned bin = w ? ((key >> shift) & 0xffu) : 256u + (unsigned)lane;
+    const unsigned m = __match_any_sync(0xffffffffu, bin);
+    if (w) {
+      const unsigned wl = __reduce_add_sync(m, (unsigned)(w & 0xfffffull));
+      const unsigned wh = __reduce_add_sync(m, (unsigned)(w >> 20));
+      if (lane == __ffs(m) - 1) atomicAdd(&sh[bin], ((unsigned long long)wh << 20) + wl);
+    }
+  }
+  __syncthreads();
+  unsigned long long* rh = hist + (size_t)r * 256;
+  for (int b = threadIdx.x; b < 256; b += blockDim.x)
+    if (sh[b]) atomicAdd(&rh[b], sh[b]);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    asm volatile("fence.acq_rel.gpu;" ::: "memory");
+    const int done = atomicAdd(&st->counter, 1);
+    s_last = done == split - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+  for (int b = threadIdx.x; b < 256; b += blockDim.x) { sh[b] = __ldcg(&rh[b]); rh[b] = 0ull; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long c = st->cum;
+    const unsigned long long target = st->target;
+    int b = 255;
+    for (; b > 0; --b) {
+      if (c + sh[b] >= target) break;
+      c += sh[b];
+    }
+    const unsigned np = prefix | ((unsigned)b << shift);
+    st->cum = c;
+    st->counter = 0;
+    if (pass == 3) {
+      st->thr_key = max(st->thr_key, np);
+      st->prefix = 0u;
+      st->cum = 0ull;
+      st->active = 0;
+    } else {
+      st->prefix = np;
+    }
+  }
+}
+
+// the mass of what the top-k threshold left, and the state of the top-p descent
+__global__ void __launch_bounds__(256)
+select_total_kernel(const float* __restrict__ logits, int V, int ld, const float* __restrict__ temperature,
+                    const int* __restrict__ top_k, const float* __restrict__ top_p,
+                    const ArgMax* __restrict__ partials, int split, SelectState* __restrict__ states) {
+  __shared__ ArgMax sm_arg[32];
+  __shared__ unsigned long long sm_sum[8];
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.y, part = blockIdx.x;
+  SelectState* st = states + r;
+  const float temp = temperature[r], p = top_p[r];
+  if (!(temp > 0.f) || top_k[r] == 1 || !(p > 0.f && p < 1.f)) return;
+  const ArgMax best = row_best(partials + (size_t)r * split, split, sm_arg);
+  if (best.v == -INFINITY) return;
+  const float* x = logits + (size_t)r * ld;
+  const float inv_t = 1.0f / temp, mx = best.v;
+  const unsigned thr_key = st->thr_key;
+  int lo, hi;
+  split_range(V, split, part, &lo, &hi);
+  unsigned long long mine = 0;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float y = x[i] * inv_t;
+    if (f2key(y) >= thr_key) mine += fx_mass(y, mx);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+  if ((threadIdx.x & 31) == 0) sm_sum[threadIdx.x >> 5] = mine;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long t = 0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += sm_sum[w];
+    atomicAdd(&st->total, t);
+    asm volatile("fence.acq_rel.gpu;" ::: "memory");
+    const int done = atomicAdd(&st->counter, 1);
+    if (done == split - 1) {
+      asm volatile("fence.acq_rel.gpu;" ::: "memory");
+      const unsigned long long total = *(volatile unsigned long long*)&st->total;
+      unsigned long long target = (unsigned long long)((double)total * (double)p);
+      if (target < 1ull) target = 1ull;
+      st->target = target;
+      st->prefix = 0u;
+      st->cum = 0ull;
+      st->counter = 0;
+      st->active = 1;
+    }
+  }
+}
+
+// Bytes of scratch that rllm_sample needs: R * split (max, index) pairs and 64-bit sums, R states, R * 256 bins.
+RLLM_EXPORT long long rllm_sample_scratch_bytes(int R, int V) {
+  const long long split = rllm_argmax_split(V);
+  return (long long)R * (split * 16 + (long long)sizeof(SelectState) + 256 * 8) + 256;
+}
+
+// The whole pipeline for any mix of rows (greedy, temperature, top-k, top-p, min-p): the same tokens as
+// rllm_sample_one_cta, with every row worked on by `split` CTAs.
+RLLM_EXPORT int rllm_sample(const float* logits, int R, int V, int ld, const float* temperature,
+                            const int* top_k, const float* top_p, const float* min_p,
+                            const unsigned long long* seeds, const long long* gen_index, int* out_tokens,
+                            void* scratch, int with_select, cudaStream_t stream) {
   if (R <= 0) return 0;
-  if (V <= 0 || ld < V || R > 65535 || !partials || !psum) return RLLM_E_BADARG;
+  if (V <= 0 || ld < V || R > 65535 || !scratch || (((uintptr_t)scratch) & 15)) return RLLM_E_BADARG;
   const int split = rllm_argmax_split(V);
-  cudaError_t e = rllm_launch_pdl(sample_split_max_kernel, dim3(split, R), dim3(256), 0, stream, logits, V, ld,
-                                  temperature, top_k, (ArgMax*)partials, split);
+  ArgMax* partials = (ArgMax*)scratch;
+  unsigned long long* psum = (unsigned long long*)(partials + (size_t)R * split);
+  unsigned long long* hist = psum + (size_t)R * split;
+  SelectState* states = (SelectState*)(hist + (size_t)R * 256);
+  const dim3 g2(split, R), b(256);
+  cudaError_t e = rllm_launch_pdl(sample_split_max_kernel, g2, b, 0, stream, logits, V, ld, temperature, top_k,
+                                  partials, split);
   if (e != cudaSuccess) return (int)e;
-  e = rllm_launch_pdl(sample_split_mass_kernel, dim3(split, R), dim3(256), 0, stream, logits, V, ld, temperature,
-                      top_k, min_p, (const ArgMax*)partials, (unsigned long long*)psum, split, out_tokens);
+  if (with_select) {
+    e = rllm_launch_pdl(select_begin_kernel, dim3(R), b, 0, stream, V, temperature, top_k, states, hist);
+    if (e != cudaSuccess) return (int)e;
+    for (int pass = 0; pass < 4; ++pass) {
+      e = rllm_launch_pdl(select_pass_kernel, g2, b, 0, stream, logits, V, ld, temperature, (const ArgMax*)partials,
+                          split, states, hist, pass, 0);
+      if (e != cudaSuccess) return (int)e;
+    }
+    e = rllm_launch_pdl(select_total_kernel, g2, b, 0, stream, logits, V, ld, temperature, top_k, top_p,
+                        (const ArgMax*)partials, split, states);
+    if (e != cudaSuccess) return (int)e;
+    for (int pass = 0; pass < 4; ++pass) {
+      e = rllm_launch_pdl(select_pass_kernel, g2, b, 0, stream, logits, V, ld, temperature, (const ArgMax*)partials,
+                          split, states, hist, pass, 1);
+      if (e != cudaSuccess) return (int)e;
+    }
+  }
+  const SelectState* sts = with_select ? states : nullptr;
+  e = rllm_launch_pdl(sample_split_mass_kernel, g2, b, 0, stream, logits, V, ld, temperature, top_k, min_p,
+                      (const ArgMax*)partials, psum, split, out_tokens, sts);
   if (e != cudaSuccess) return (int)e;
-  e = rllm_launch_pdl(sample_split_draw_kernel, dim3(R), dim3(256), 0, stream, logits, V, ld, temperature, top_k,
-                      min_p, seeds, gen_index, (const ArgMax*)partials, (const unsigned long long*)psum, split,
-                      out_tokens);
+  e = rllm_launch_pdl(sample_split_draw_kernel, dim3(R), b, 0, stream, logits, V, ld, temperature, top_k, min_p,
+                      seeds, gen_index, (const ArgMax*)partials, (const unsigned long long*)psum, split, out_tokens,
+                      sts);
   return (int)e;
 }
 

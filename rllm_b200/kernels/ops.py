@@ -352,40 +352,46 @@ def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
                            _ptr(scratch[0]), _ptr(scratch[1]), _stream()), "argmax")
 
 
-def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           min_p: torch.Tensor, seeds: torch.Tensor, gen_index: torch.Tensor, out: torch.Tensor) -> None:
-    lib = build.load_library("sampling")
-    R, V = logits.shape
+def _sample_asserts(logits, temperature, top_k, top_p, min_p, seeds, gen_index, out):
     assert logits.dtype is torch.float32 and logits.stride(1) == 1
     assert temperature.dtype is torch.float32 and top_k.dtype is torch.int32
     assert top_p.dtype is torch.float32 and min_p.dtype is torch.float32
     assert seeds.dtype is torch.int64 and gen_index.dtype is torch.int64 and out.dtype is torch.int32
-    _check(lib.rllm_sample(_ptr(logits), c_int(R), c_int(V), c_int(logits.stride(0)), _ptr(temperature),
-                           _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(seeds), _ptr(gen_index),
-                           _ptr(out), _stream()), "sample")
 
 
 _sample_scratch = {}
 
 
-def sample_split(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, min_p: torch.Tensor,
-                 seeds: torch.Tensor, gen_index: torch.Tensor, out: torch.Tensor) -> None:
-    """``sample`` for rows without top-k and top-p (top_k 0 or 1, top_p outside (0, 1)): a row is worked on
-    by several CTAs; the same tokens as ``sample``."""
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, seeds: torch.Tensor, gen_index: torch.Tensor, out: torch.Tensor,
+           with_select: bool = True) -> None:
+    """out[r] = the next token of row r: argmax for greedy rows, else a draw after temperature, top-k,
+    top-p and min-p.  Every row is worked on by several CTAs, in a chain of small kernels.
+    ``with_select=False`` leaves the top-k / top-p kernels out (the caller knows that no row uses them)."""
     lib = build.load_library("sampling")
     R, V = logits.shape
-    assert logits.dtype is torch.float32 and logits.stride(1) == 1
-    assert temperature.dtype is torch.float32 and top_k.dtype is torch.int32 and min_p.dtype is torch.float32
-    assert seeds.dtype is torch.int64 and gen_index.dtype is torch.int64 and out.dtype is torch.int32
+    _sample_asserts(logits, temperature, top_k, top_p, min_p, seeds, gen_index, out)
+    lib.rllm_sample_scratch_bytes.restype = c_longlong
+    need = int(lib.rllm_sample_scratch_bytes(c_int(R), c_int(V)))
     scratch = _sample_scratch.get(logits.device)
-    if scratch is None or scratch[0].numel() < R * 64 * 2:
-        rows = max(R, 256)
-        scratch = (torch.empty(rows * 64 * 2, dtype=torch.int32, device=logits.device),
-                   torch.empty(rows * 64, dtype=torch.int64, device=logits.device))
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=logits.device)
         _sample_scratch[logits.device] = scratch
-    _check(lib.rllm_sample_split(_ptr(logits), c_int(R), c_int(V), c_int(logits.stride(0)), _ptr(temperature),
-                                 _ptr(top_k), _ptr(min_p), _ptr(seeds), _ptr(gen_index), _ptr(out),
-                                 _ptr(scratch[0]), _ptr(scratch[1]), _stream()), "sample_split")
+    _check(lib.rllm_sample(_ptr(logits), c_int(R), c_int(V), c_int(logits.stride(0)), _ptr(temperature),
+                           _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(seeds), _ptr(gen_index), _ptr(out),
+                           _ptr(scratch), c_int(1 if with_select else 0), _stream()), "sample")
+
+
+def sample_one_cta(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                   min_p: torch.Tensor, seeds: torch.Tensor, gen_index: torch.Tensor, out: torch.Tensor) -> None:
+    """The same sampling with one CTA a row in one kernel (slow for large vocabularies; kept as the
+    simple form that the chain of kernels is checked against)."""
+    lib = build.load_library("sampling")
+    R, V = logits.shape
+    _sample_asserts(logits, temperature, top_k, top_p, min_p, seeds, gen_index, out)
+    _check(lib.rllm_sample_one_cta(_ptr(logits), c_int(R), c_int(V), c_int(logits.stride(0)), _ptr(temperature),
+                                   _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(seeds), _ptr(gen_index),
+                                   _ptr(out), _stream()), "sample_one_cta")
 
 
 def logit_edits(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor, counts: torch.Tensor,

@@ -138,10 +138,7 @@ class Sampler:
         fd = dev[4 * R: 7 * R].view(torch.float32).view(3, R)
         kd = dev[7 * R: 8 * R]
         V = logits.shape[1]
-        if all((row.params.top_k <= 1 or row.params.top_k >= V) and not (0.0 < row.params.top_p < 1.0)
-               for row in rows):
-            # temperature (and min-p) only: several CTAs a row
-            ops.sample_split(logits, fd[0], kd, fd[2], sd[0], sd[1], out)
-        else:
-            ops.sample(logits, fd[0], kd, fd[1], fd[2], sd[0], sd[1], out)
+        # the top-k / top-p kernels are left out when no row uses them
+        select = any(1 < row.params.top_k < V or 0.0 < row.params.top_p < 1.0 for row in rows)
+        ops.sample(logits, fd[0], kd, fd[1], fd[2], sd[0], sd[1], out, with_select=select)
         return out

@@ -57,27 +57,36 @@ def test_argmax_kernel_at_any_width(V):
 
 
 @pytest.mark.parametrize("V", [7, 256, 4097, 128256, 300001])
-def test_split_sampling_draws_the_same_tokens(V):
-    """Rows without top-k and top-p are sampled by several CTAs a row: the same tokens as the one-CTA
-    kernel, for every temperature, min-p, seed and step, for greedy rows and for a row of -inf."""
+def test_sampling_by_several_ctas_a_row_draws_the_same_tokens(V):
+    """The chain of kernels that cuts a row into ranges draws the tokens of the one-CTA kernel: every
+    mix of temperature, top-k, top-p and min-p, seeds and steps, greedy rows, rows of -inf, ties."""
     from rllm_b200.kernels import ops
     torch.manual_seed(V)
-    R = 12
+    R = 16
     logits = torch.randn(R, V, device=DEV) * 4
     logits[3] = -float("inf")
     logits[4, : V // 2] = -float("inf")
-    temperature = torch.tensor([0.7, 1.3, 0.0, 0.9, 0.5, 2.0, 0.8, 1.0, 0.3, 1.0, 0.8, 5.0], device=DEV)
-    top_k = torch.tensor([-1, 0, -1, -1, -1, 1, -1, V + 5, -1, -1, -1, -1], dtype=torch.int32, device=DEV)
-    top_p = torch.ones(R, device=DEV)
-    min_p = torch.tensor([0, 0, 0, 0, 0.1, 0, 0.3, 0, 0, 0.01, 0, 0], dtype=torch.float32, device=DEV)
-    for step in range(6):
-        seeds = torch.arange(R, dtype=torch.int64, device=DEV) * 7919 + step
-        gen = torch.full((R,), step * 3, dtype=torch.int64, device=DEV)
-        a = torch.full((R,), -1, dtype=torch.int32, device=DEV)
-        b = torch.full((R,), -2, dtype=torch.int32, device=DEV)
-        ops.sample(logits, temperature, top_k, top_p, min_p, seeds, gen, a)
-        ops.sample_split(logits, temperature, top_k, min_p, seeds, gen, b)
-        assert a.tolist() == b.tolist(), step
+    logits[13] = torch.round(logits[13])              # many equal values: ties at every threshold
+    temperature = torch.tensor([0.7, 1.3, 0.0, 0.9, 0.5, 2.0, 0.8, 1.0, 0.3, 1.0, 0.8, 5.0, 1.0, 1.0, 0.6, 1.5],
+                               device=DEV)
+    top_k = torch.tensor([-1, 0, -1, 5, -1, 1, 3, V + 5, 50, -1, 2, -1, 40, 7, V - 1, 1000], dtype=torch.int32,
+                         device=DEV)
+    top_p = torch.tensor([1, 1, 1, 0.9, 1, 1, 1, 0.5, 0.95, 0.3, 1, 0.999, 0.8, 0.9, 0.7, 0.6], dtype=torch.float32,
+                         device=DEV)
+    min_p = torch.tensor([0, 0, 0, 0, 0.1, 0, 0.3, 0, 0, 0.01, 0, 0, 0.05, 0, 0, 0.2], dtype=torch.float32,
+                         device=DEV)
+    for select in (True, False):
+        if not select:
+            top_k = torch.where((top_k > 1) & (top_k < V), torch.full_like(top_k, -1), top_k)
+            top_p = torch.ones_like(top_p)
+        for step in range(5):
+            seeds = torch.arange(R, dtype=torch.int64, device=DEV) * 7919 + step
+            gen = torch.full((R,), step * 3, dtype=torch.int64, device=DEV)
+            a = torch.full((R,), -1, dtype=torch.int32, device=DEV)
+            b = torch.full((R,), -2, dtype=torch.int32, device=DEV)
+            ops.sample_one_cta(logits, temperature, top_k, top_p, min_p, seeds, gen, a)
+            ops.sample(logits, temperature, top_k, top_p, min_p, seeds, gen, b, with_select=select)
+            assert a.tolist() == b.tolist(), (select, step)
     assert len(set(a.tolist())) > 3
 
 
