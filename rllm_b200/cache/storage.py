@@ -9,6 +9,10 @@ Inside a page the tokens of one kv head are contiguous rows of head_dim, so a
 [blocks, heads, head_dim, block_size], spec.rs:63-68, strides the hot axis).
 State group: every owning run gets float32 [max_seqs, *shape], indexed by a
 request's state slot.  All storage is allocated once, here.
+
+Every paged buffer has one page more than the manager hands out: page
+``spare_page(group)`` belongs to no request.  The rows that pad a decode step to
+a captured batch size read and write there.
 """
 from __future__ import annotations
 
@@ -34,10 +38,11 @@ class CacheStorage:
         self.state: Dict[int, torch.Tensor] = {}
         paged = [g for g, n in enumerate(layout.groups) if isinstance(n, KVPagesNeed)]
         pages_of = dict(zip(paged, num_pages))
+        self._pages_of = pages_of
         for g, need in enumerate(layout.groups):
             for run in layout.owners[g]:
                 if isinstance(need, KVPagesNeed):
-                    shape = (pages_of[g], need.num_kv_heads, page_size, need.head_dim)
+                    shape = (pages_of[g] + 1, need.num_kv_heads, page_size, need.head_dim)
                     self.kv[run] = (torch.zeros(shape, dtype=dtype, device=device),
                                     torch.zeros(shape, dtype=dtype, device=device))
                 elif isinstance(need, StateNeed):
@@ -45,6 +50,10 @@ class CacheStorage:
                                                   device=device)
                 else:
                     raise TypeError(f"unknown cache need {need!r}")
+
+    def spare_page(self, group: int) -> int:
+        """The id of the page of this paged group that no request ever holds."""
+        return self._pages_of[group]
 
     def view(self, run_index: int):
         g = self.layout.run_group[run_index]

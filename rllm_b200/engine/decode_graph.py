@@ -16,8 +16,13 @@ cache is not touched twice.
 
 The reference captures decode for batch sizes 1..64 in powers of two on the
 default stream (crates/rllm-worker/src/model_runner.rs:555-667, replay at
-crates/rllm-executor/src/uniproc.rs:81-106); here every batch size gets its own
-graph on first use, on a private stream, with no padding rows.
+crates/rllm-executor/src/uniproc.rs:81-106).  Here a graph is captured on first
+use, on a private stream; batches of up to 8 get a graph of their own size,
+larger ones are padded to the next size of ``batch_bucket`` (steps of 4, 8, 16,
+...), so that a batch that shrinks request by request keeps finding captured
+graphs.  A padding row is a request of one token at position 0 whose block
+table names only the storage's spare page: it reads and writes nothing that a
+request holds, and its logits are dropped.
 """
 from __future__ import annotations
 
@@ -36,6 +41,15 @@ def table_width_bucket(blocks: int) -> int:
     while w < blocks:
         w *= 2
     return w
+
+
+def batch_bucket(n: int) -> int:
+    """The captured batch size for n requests: n itself up to 8, then the next multiple of 4 up to 32,
+    of 8 up to 64, of 16 up to 128, of 32 beyond."""
+    if n <= 8:
+        return n
+    step = 4 if n <= 32 else (8 if n <= 64 else (16 if n <= 128 else 32))
+    return -(-n // step) * step
 
 
 class DecodeGraph:
@@ -80,6 +94,7 @@ class DecodeGraph:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.uses = 0
+        self.live = S                  # rows that are requests; the rest pads the batch
         # what the pinned buffer holds per row: (request, number of table entries written), so that an
         # unchanged block table is not written again
         self.row_state: List[Optional[tuple]] = [None] * S
@@ -90,8 +105,8 @@ class DecodeGraph:
         self.commit()
 
     def patch_tokens(self, tokens: Sequence[int]) -> None:
-        """Set the input token of every row in the pinned buffer (after fill_host, before commit)."""
-        self.host[self.r_tokens[0]:self.r_tokens[1]] = tokens
+        """Set the input token of every request's row in the pinned buffer (after fill_host, before commit)."""
+        self.host[self.r_tokens[0]:self.r_tokens[0] + len(tokens)] = tokens
 
     def commit(self) -> None:
         """Copy the pinned buffer to the device buffer the graph reads."""
@@ -104,6 +119,20 @@ class DecodeGraph:
         cache, S, W = self.runner.cache, self.S, self.width
         self.copied.synchronize()
         h = self.host
+        self.live = len(entries)
+        for s in range(len(entries), S):
+            # a padding row: one token at position 0 of the spare page
+            if self.row_state[s] == "pad":
+                continue
+            self.row_state[s] = "pad"
+            h[self.r_tokens[0] + s] = 0
+            h[self.r_pos[0] + s] = 0
+            h[self.r_seqlens[0] + s] = 1
+            h[self.r_slots[0] + s] = 0
+            for g, r in zip(self.paged, self.r_tables):
+                tab = h[r[0]:r[1]].reshape(S, W)
+                tab[s, :] = -1
+                tab[s, 0] = self.runner.storage.spare_page(g)
         for s, e in enumerate(entries):
             h[self.r_tokens[0] + s] = e.tokens[0]
             h[self.r_pos[0] + s] = e.start
@@ -123,13 +152,13 @@ class DecodeGraph:
                 tab[s, n:] = -1
 
     def run(self) -> torch.Tensor:
-        """Logits float32 [S, vocab]; valid until the next run of this graph."""
+        """Logits float32 [live rows, vocab]; valid until the next run of this graph."""
         r = self.runner
         self.uses += 1
         if self.graph is not None:
             self.graph.replay()
-            return self.logits
-        logits = r.model.forward(self.token_ids, self.ctx, self.rows, r.storage)
+            return self.logits[: self.live]
+        logits = r.model.forward(self.token_ids, self.ctx, self.rows, r.storage)[: self.live]
         if self.uses >= 2 and r.capture_graphs:
             # capture the same work for the following steps (nothing executes during capture)
             # No garbage collection while capturing: freeing an older engine's graph in

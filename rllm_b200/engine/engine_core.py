@@ -106,7 +106,6 @@ class EngineCore:
         self.eos_token_ids = tuple(spec.eos_token_ids)
         self._arrivals = itertools.count()
         self.num_steps = 0
-        self._unchecked = 0
         self._prepared = None          # (schedule, requests, plain_greedy, graph) of the next step, made ahead
         self._inflight = None          # (schedule, requests, plain_greedy, sampled, read-back) of a step already on the GPU
         self._readback = [None, None]  # pinned buffers and events for the sampled tokens, used in turn
@@ -186,11 +185,8 @@ class EngineCore:
         if nxt is not None and self._launch_ahead(nxt, sampled_reqs, sampled):
             nxt = None
         tokens = self._tokens_of(pending)
-        # the kernels' error words cost a device read each: every step of a prompt, every 32nd decode step
-        self._unchecked += 1
-        if self._unchecked >= 32 or sched.num_prefill_tokens:
-            self.runner.check_errors()
-            self._unchecked = 0
+        # the kernels' error words are read without waiting for the GPU; a bad index shows a step or two late
+        self.runner.poll_errors()
         outputs = []
         any_finished = False
         for req, tok, alive in zip(sampled_reqs, tokens, live):
@@ -263,7 +259,7 @@ class EngineCore:
         self.num_steps_ahead += 1
         with torch.cuda.device(self.device), torch.no_grad():
             graph.commit()
-            graph.token_ids.copy_(sampled, non_blocking=True)
+            graph.token_ids[: sampled.numel()].copy_(sampled, non_blocking=True)
             logits = graph.run()
         ahead = self._sample(logits, nreqs, plain_greedy, 1)
         self._inflight = (nsched, nreqs, plain_greedy, ahead, self._read_back(ahead))

@@ -166,11 +166,13 @@ class ModelRunner:
         self.graphs = {}
         self.graph_pool = None
 
-    def _decode_graph(self, entries: Sequence[StepEntry]):
-        from .decode_graph import DecodeGraph, table_width_bucket
+    def _decode_graph(self, entries: Sequence[StepEntry], pad: bool = True):
+        from .decode_graph import DecodeGraph, batch_bucket, table_width_bucket
         page = self.cache.page_size
         blocks = max(-(-(e.start + 1) // page) for e in entries)
-        key = (len(entries), table_width_bucket(blocks))
+        # padding rows use the spare page and state slot 0: only where no run keeps per-request state
+        pad = pad and not self.storage.state
+        key = (batch_bucket(len(entries)) if pad else len(entries), table_width_bucket(blocks))
         g = self.graphs.get(key)
         if g is None:
             if len(self.graphs) >= self.MAX_GRAPHS:
@@ -240,7 +242,7 @@ class ModelRunner:
         with torch.cuda.device(self.device):
             self.storage.zero_slots(self.cache.take_fresh_slots())
             last = [StepEntry(e.req, e.tokens, e.start + num_steps - 1, e.want) for e in entries]
-            g = self._decode_graph(last)            # a table wide enough for the whole run
+            g = self._decode_graph(last, pad=False)            # a table wide enough for the whole run
             if g is None:
                 raise StepError("too many decode graphs")
             g.fill(entries)
@@ -256,6 +258,28 @@ class ModelRunner:
             if timing is not None:
                 timing[2].record()
             return history
+
+    def poll_errors(self) -> None:
+        """The same check without waiting for the GPU: looks at the error words as they were when the
+        last call of this method asked for them (if that copy has arrived), raises if a kernel had
+        flagged a bad index by then, and asks for a fresh copy.  An error is reported a step or two
+        late; steps already queued are not held up."""
+        from ..kernels import ops
+        if not hasattr(self, "_err_host"):
+            self._err_host = torch.zeros(2, dtype=torch.int32, pin_memory=True)
+            self._err_event = None
+        if self._err_event is not None:
+            if not self._err_event.query():
+                return
+            code, gemm = int(self._err_host[0]), int(self._err_host[1])
+            self._err_event = None
+            if code or gemm:
+                self.check_errors()            # the synchronous path words the message and clears the words
+        with torch.cuda.device(self.device):
+            self._err_host[0:1].copy_(self.err, non_blocking=True)
+            self._err_host[1:2].copy_(ops.gemm_error_word(self.device), non_blocking=True)
+            self._err_event = torch.cuda.Event()
+            self._err_event.record()
 
     def check_errors(self) -> None:
         """Raise if a kernel of an earlier step flagged a bad index (synchronises)."""

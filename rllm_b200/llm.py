@@ -78,6 +78,7 @@ class LLM:
                     tokens[out.request_id].extend(out.outputs[0].token_ids)
                     if out.finished:
                         final[out.request_id] = out
+        self.engine.runner.check_errors()          # the steps polled the kernels' error words; this waits for the last
         results = []
         for rid in ids:
             out = final[rid]

@@ -159,6 +159,35 @@ def test_steps_launched_ahead_keep_every_request_right(model_dirs, dtype, temper
     assert llm.engine.cache.num_free_pages() == free and llm.engine.cache.usage()["num_requests"] == 0
 
 
+@pytest.mark.parametrize("name,dtype", [("A", "fp32"), ("C", "bf16")])
+def test_batches_padded_to_captured_sizes(model_dirs, name, dtype):
+    """More than 8 requests decode in graphs of padded batch sizes (12, 16, ...): requests that end one
+    after the other walk the batch down through the sizes; every request's tokens are what it gets alone,
+    and (float32) what the plain implementation generates."""
+    from rllm_b200 import SamplingParams
+    from rllm_b200.engine.decode_graph import batch_bucket
+    assert [batch_bucket(n) for n in (1, 8, 9, 12, 13, 33, 64, 65, 129)] == [1, 8, 12, 12, 16, 40, 64, 80, 160]
+    lengths = [5, 9, 3, 14, 7, 11, 4, 6, 13, 8, 10, 12, 15]
+    prompts = prompts_for(name, lengths, 31)
+    budgets = [6 + 3 * i for i in range(len(prompts))]            # 6 .. 42 tokens: one request ends every third step
+    params = [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True) for n in budgets]
+    llm = make_llm(model_dirs, name, dtype=dtype, max_num_seqs=16, enable_prefix_caching=False)
+    free = llm.engine.cache.num_free_pages()
+    outs = llm.generate(prompts, params)
+    sizes = sorted(k[0] for k in llm.engine.runner.graphs)
+    assert 16 in sizes and 12 in sizes and not any(8 < n and n % 4 for n in sizes), sizes
+    if dtype == "fp32":
+        plain = pl.read_model_dir(model_dirs[name])
+        for p, n, o in zip(prompts, budgets, outs):
+            assert o.outputs[0].token_ids == plain.greedy(p, n)
+    else:
+        alone = make_llm(model_dirs, name, dtype=dtype, max_num_seqs=16, enable_prefix_caching=False)
+        for p, sp, o in list(zip(prompts, params, outs))[::4]:
+            assert alone.generate([p], sp)[0].outputs[0].token_ids == o.outputs[0].token_ids
+    llm.engine.cache.check()
+    assert llm.engine.cache.num_free_pages() == free
+
+
 def test_preemption_does_not_change_outputs(model_dirs):
     from rllm_b200 import SamplingParams
     name = "B"
