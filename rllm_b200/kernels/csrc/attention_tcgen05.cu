@@ -1,33 +1,38 @@
 // Paged causal attention over prompt portions for bfloat16 on the tcgen05
-// tensor cores (head size 64): both products of attention, S = Q K^T and P V,
-// run as tcgen05.mma with accumulators in tensor memory.
+// tensor cores (head sizes 64 and 128): both products of attention, S = Q K^T
+// and P V, run as tcgen05.mma with accumulators in tensor memory.
 //
 // One CTA per (tile of 128 rows, kv head, sequence); a row is a (query token,
-// head of the kv head's group) pair, so 128 / g tokens share every K/V tile.
-//   warp 0     TMA producer: Q once (a 3-D box: 64 dims x g heads x 128/g tokens),
-//              then per 128-key tile the K and V rows of its cache pages (one 2-D
-//              box per page), into a two-stage ring; pages a sequence does not
-//              hold are skipped.
-//   warp 1     allocates TMEM (S: 128 columns, PV: 64) and issues the MMAs:
-//              S = Q K^T (128 x 128 x 64, both operands K-major), then, when the
-//              softmax warps have left P in shared memory, PV = P V (128 x 64 x
-//              128; V is the MN-major operand, straight from its cache layout).
-//   warps 2-5  softmax: thread r owns row r (= TMEM lane r): reads its 128 scores
-//              with tcgen05.ld, masks (causal, window), keeps the running max and
-//              sum in float32, writes P as bfloat16 into the swizzled A-operand
-//              layout, and adds each tile's PV to its float32 output row, rescaled
-//              when the max moved.  No shuffles: a row never leaves its thread.
-// Contract and tile alignment as in attention_mma.cu (keys in tiles of 128 at
-// absolute positions; a row's arithmetic does not depend on the batch).
+// head of the kv head's group) pair, so 128 / g tokens share every K/V tile
+// (if g does not divide 128 the last rows of a tile stay unused).
+// Key tiles hold BN = 8192 / D keys (128 for head size 64, 64 for 128), so that a
+// K or V stage is 16 KB either way, Q and P together 48 KB, and two CTAs share an SM.
+// Every operand lies in shared memory as panels of 64 columns (128 bytes, the
+// span of the 128-byte swizzle): Q and K by head dims, P by keys, V by head dims.
+//   warp 0     TMA producer: Q once (3-D boxes: 64 dims x g heads x 128/g tokens),
+//              then per tile the K and V rows of its cache pages (one 2-D box per
+//              page and panel), into two-stage rings of their own; pages a sequence
+//              does not hold are skipped.
+//   warp 1     allocates TMEM (S: BN columns, output: D, 4 for the softmax warps'
+//              exchange) and issues the MMAs: S = Q K^T (128 x BN x D, both
+//              operands K-major), then, when the softmax warps have left P in
+//              shared memory, output += P V, 64 dims at a time (128 x 64 x BN; V is
+//              the MN-major operand, straight from its cache layout).
+//   warps 2-9  softmax, two threads a row (= TMEM lane): read the row's scores
+//              with tcgen05.ld, mask (causal, window), keep a reference max and the
+//              sum in float32, write P as bfloat16 into the swizzled A-operand
+//              layout; the output stays in TMEM and is rescaled only when a row's
+//              max has grown by more than 2^8.
+// Contract and tile alignment as in attention_mma.cu (key tiles at absolute
+// positions; a row's arithmetic does not depend on the batch).
 // Every mbarrier wait is bounded (bit 16 of the error word, then wind-down).
 // No cluster, no multicast.
 #include "tcgen05.cuh"
 #include <math.h>
 
 #define AT_BM 128
-#define AT_BN 128
-#define AT_D 64
 #define AT_THREADS 320
+#define AT_STAGE 16384          // bytes of a K or V stage: BN keys x D dims
 
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, void* bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -61,25 +66,30 @@ __device__ __forceinline__ bool pair_exchange(unsigned taddr, int half, void* ba
   return true;
 }
 
-#define AT_SMEM_BYTES (16384 + 2 * 16384 + 2 * 16384 + 32768 + 256)
+// Q and P (48 KB together), two stages of K and of V, barriers: two CTAs fit one SM
+#define AT_SMEM_BYTES (49152 + 2 * AT_STAGE + 2 * AT_STAGE + 256)
 
+template <int AT_D>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                          const int* __restrict__ seq_lens, int seq_begin, int seq_end, int nq, int nkv,
                          int page_size, int num_pages, int window, float scale_log2, int* __restrict__ err) {
+  constexpr int AT_BN = 8192 / AT_D;              // keys a tile
+  constexpr int DP = AT_D / 64;                   // panels of head dims (Q, K, V)
+  constexpr int KPANEL = AT_BN * 128;             // bytes of a K or V panel: BN rows of 128 bytes
   extern __shared__ __align__(1024) unsigned char at_raw[];
   unsigned char* base = at_raw;
   if (tg_smem(base) & 1023u) {                    // the swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0) atomicOr(err, 32);
     return;
   }
-  unsigned char* sQ = base;                       // [128 rows][64] bf16, 128B swizzle
-  unsigned char* sK = sQ + 16384;                 // 2 stages x [128 keys][64]
-  unsigned char* sV = sK + 2 * 16384;             // 2 stages x [128 keys][64]
-  unsigned char* sP = sV + 2 * 16384;             // 2 panels x [128 rows][64 keys] bf16
-  unsigned long long* bars = (unsigned long long*)(sP + 32768);
+  unsigned char* sQ = base;                       // DP panels x [128 rows][64 dims] bf16, 128B swizzle
+  unsigned char* sP = sQ + DP * 16384;            // BN / 64 panels x [128 rows][64 keys]
+  unsigned char* sK = base + 49152;               // 2 stages x DP panels x [BN keys][64 dims]
+  unsigned char* sV = sK + 2 * AT_STAGE;          // 2 stages x DP panels x [BN keys][64 dims]
+  unsigned long long* bars = (unsigned long long*)(sV + 2 * AT_STAGE);
   unsigned long long* q_full = bars;              // TMA -> MMA
   unsigned long long* k_full = bars + 1;          // [2] TMA -> MMA
   unsigned long long* k_empty = bars + 3;         // [2] MMA -> TMA: the scores that read the stage are done
@@ -117,7 +127,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int* bt = block_table + (size_t)s * max_blocks;
 
   // stale rows of K and V (pages that are skipped) must hold finite numbers: clear the ring once
-  for (int i = threadIdx.x; i < 4 * 16384 / 16; i += AT_THREADS) ((uint4*)sK)[i] = make_uint4(0u, 0u, 0u, 0u);
+  for (int i = threadIdx.x; i < 4 * AT_STAGE / 16; i += AT_THREADS) ((uint4*)sK)[i] = make_uint4(0u, 0u, 0u, 0u);
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
@@ -143,23 +153,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, 16384u);
-      tma_load_3d(sQ, &map_q, 0, kvh * g, qs + t0, q_full);
+      mbar_expect_tx(q_full, (unsigned)(DP * bq * g * 128));     // bq * g rows of the 128 (all of them if g divides 128)
+      for (int dp = 0; dp < DP; ++dp) tma_load_3d(sQ + dp * 16384, &map_q, dp * 64, kvh * g, qs + t0, q_full);
     }
-    // Lanes 0-7 fetch the boxes of a tile (one page each).  K and V have rings of their own: a K stage is
+    // Lanes 0-7 fetch the boxes of a tile (a page and a panel of 64 dims each).  K and V have rings of their own: a K stage is
     // free once the scores that read it are done, a V stage once its product is, so K runs a tile further
     // ahead.  Lane 0 polls both rings; the pages of the next tile of each are looked up ahead of time.
-    const int boxes = AT_BN / page_size;            // page_size divides 128
+    const int boxes = (AT_BN / page_size) * DP;     // page_size divides BN; at most 8 boxes
+    const int bpage = lane / DP, bpanel = lane % DP; // this lane's box: which page of the tile, which panel
     const int ntiles = tile_hi - tile_lo;
     auto lookup = [&](int it) {
       // the page of this lane's box in tile it, if the sequence holds it and it holds keys below kend
-      const int j = (tile_lo + it) * AT_BN + lane * page_size;
+      const int j = (tile_lo + it) * AT_BN + bpage * page_size;
       int page = -1;
       if (lane < boxes && it < ntiles && j < kend) {
         page = bt[j / page_size];
         if (page < 0 || page >= num_pages) {
           page = -1;
-          if (j + page_size > kmin) atomicOr(err, 4);   // a page with visible keys is missing
+          if (j + page_size > kmin && bpanel == 0) atomicOr(err, 4);   // a page with visible keys is missing
         }
       }
       return page;
@@ -170,7 +181,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (lane == 0) mbar_expect_tx(&full[st], (unsigned)(__popc(have) * page_size * 128));
       __syncwarp();
       if (page >= 0)
-        tma_load_2d(ring + st * 16384 + lane * page_size * 128, map, 0, (page * nkv + kvh) * page_size, &full[st]);
+        tma_load_2d(ring + st * AT_STAGE + bpanel * KPANEL + bpage * page_size * 128, map, bpanel * 64,
+                    (page * nkv + kvh) * page_size, &full[st]);
     };
     int nk = 0, nv = 0;                              // tiles whose K, V have been asked for
     int page_k = lookup(0), page_v = page_k;
@@ -193,18 +205,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
-      // S: float32 accumulate, bf16 x bf16, A and B K-major, M 128, N 128.
-      // PV: the same with N 64 and B (V) MN-major.
+      // S: float32 accumulate, bf16 x bf16, A and B K-major, M 128, N BN.
+      // PV: the same with N 64 (a panel of head dims at a time) and B (V) MN-major.
       const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_BN >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
-      const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(AT_D >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
+      const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(64 >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
       const int ntiles = tile_hi - tile_lo;
       const unsigned long long dq = umma_desc(sQ);
+      // scores of the tile in stage st: D / 16 steps along the head dims, panel by panel
+      auto scores = [&](int st) {
+        const unsigned long long dk = umma_desc(sK + st * AT_STAGE);
+#pragma unroll
+        for (int k = 0; k < AT_D / 16; ++k) {
+          const unsigned long long a = dq + (unsigned long long)((k >> 2) * (16384 >> 4) + 2 * (k & 3));
+          const unsigned long long b = dk + (unsigned long long)((k >> 2) * (KPANEL >> 4) + 2 * (k & 3));
+          umma_bf16(tmem_s, a, b, idesc_s, k != 0);
+        }
+      };
       bool ok = mbar_wait(q_full, 0, err) && mbar_wait(&k_full[0], 0, err);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const unsigned long long dk = umma_desc(sK);
-#pragma unroll
-        for (int k = 0; k < AT_D / 16; ++k) umma_bf16(tmem_s, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);
+        scores(0);
         umma_commit(s_full);
         umma_commit(&k_empty[0]);
       }
@@ -216,20 +236,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           ok = mbar_wait(&k_full[sn], ((it + 1) >> 1) & 1, err) && mbar_wait(s_free, it & 1, err);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const unsigned long long dk = umma_desc(sK + sn * 16384);
-#pragma unroll
-          for (int k = 0; k < AT_D / 16; ++k) umma_bf16(tmem_s, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);
+          scores(sn);
           umma_commit(s_full);
           umma_commit(&k_empty[sn]);
         }
         ok = mbar_wait(&v_full[st], (it >> 1) & 1, err) && mbar_wait(p_full, it & 1, err);   // P is in shared memory, O is rescaled
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const unsigned long long dv = umma_desc(sV + st * 16384);
+        const unsigned long long dv = umma_desc(sV + st * AT_STAGE);
 #pragma unroll
-        for (int kk = 0; kk < AT_BN / 16; ++kk) {     // 16 keys a step: P along K inside a 64-key panel, V two row groups on
-          const unsigned long long dp = umma_desc(sP + (kk >> 2) * 16384) + 2 * (kk & 3);
-          umma_bf16(tmem_o, dp, dv + (unsigned long long)(kk * (2048 >> 4)), idesc_pv, (it != 0) || (kk != 0));
+        for (int np = 0; np < DP; ++np) {               // 64 output dims at a time
+#pragma unroll
+          for (int kk = 0; kk < AT_BN / 16; ++kk) {     // 16 keys a step: P along K inside a 64-key panel, V two row groups on
+            const unsigned long long dp = umma_desc(sP + (kk >> 2) * 16384) + 2 * (kk & 3);
+            umma_bf16(tmem_o + np * 64, dp, dv + (unsigned long long)(np * (KPANEL >> 4) + kk * (2048 >> 4)), idesc_pv,
+                      (it != 0) || (kk != 0));
+          }
         }
         umma_commit(pv_full);
         umma_commit(&v_empty[st]);
@@ -237,10 +259,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     }
     __syncwarp();
   } else {
-    // Two threads a row: warps 2-5 take the tile's keys 0-63 (and output dims 0-31), warps 6-9
-    // keys 64-127 (dims 32-63); warp w and warp w + 4 own the same 32 rows (TMEM lanes) and
-    // exchange the row's max and sum through four spare TMEM columns (shared memory is full:
-    // two CTAs share an SM), under a barrier of their own.
+    // Two threads a row: warps 2-5 take the first half of the tile's keys (and of the output dims),
+    // warps 6-9 the second; warp w and warp w + 4 own the same 32 rows (TMEM lanes) and exchange
+    // the row's max and sum through four spare TMEM columns (shared memory is full: two CTAs share
+    // an SM), under a barrier of their own.
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;               // this thread's row of the tile
     const int tl = r / g, hl = r - tl * g;
@@ -314,29 +336,37 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (__any_sync(0xffffffffu, moves)) {
-          unsigned v[32];
-          tmem_ld32(tmem_o + lane_sel + half * 32, v);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
-          tmem_st32(tmem_o + lane_sel + half * 32, v);
+          for (int c0 = 0; c0 < AT_D / 2; c0 += 32) {
+            unsigned v[32];
+            tmem_ld32(tmem_o + lane_sel + half * (AT_D / 2) + c0, v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * corr);
+            tmem_st32(tmem_o + lane_sel + half * (AT_D / 2) + c0, v);
+          }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      unsigned char* prow = sP + half * 16384 + r * 128;   // this thread's keys are one 64-key panel
+      // this thread's keys half * HC .. + HC - 1 lie in one 64-key panel of P, from chunk (key % 64) / 8 on
+      unsigned char* prow = sP + ((half * HC) >> 6) * 16384 + r * 128;
+      const int chunk0 = ((half * HC) & 63) >> 3;
 #pragma unroll
       for (int c = 0; c < HC / 8; ++c)                 // 8 keys = one 16-byte chunk of the row's 128 bytes
-        *(uint4*)(prow + ((c ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        *(uint4*)(prow + (((chunk0 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
       // rows of V at and behind the last visible key were never written by this sequence: whatever
       // they hold must not reach the product (0 x inf), so they are cleared before P V is issued
       if (it == ntiles - 1) {
         ok = __all_sync(0xffffffffu, mbar_wait(&v_full[it & 1], (it >> 1) & 1, err));   // V has landed: nothing overwrites the zeros
         if (!ok) break;
       }
-      if (it == ntiles - 1 && j0 + r >= kend) {
-        uint4* vrow = (uint4*)(sV + (it & 1) * 16384 + r * 128 + half * 64);
+      if (it == ntiles - 1 && r < AT_BN && j0 + r >= kend) {     // thread r: key row r, half a row of every panel
 #pragma unroll
-        for (int c = 0; c < 4; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+        for (int dp = 0; dp < DP; ++dp) {
+          uint4* vrow = (uint4*)(sV + (it & 1) * AT_STAGE + dp * KPANEL + r * 128 + half * 64);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
       // hand P to the MMA warp: make the shared-memory writes visible to the async proxy first
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -353,19 +383,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
-      bf16* orow = out + ((size_t)(qs + t0 + tl) * nq + kvh * g + hl) * AT_D + half * 32;
-      unsigned v[32];
-      tmem_ld32(tmem_o + lane_sel + half * 32, v);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (live) {
+      bf16* orow = out + ((size_t)(qs + t0 + tl) * nq + kvh * g + hl) * AT_D + half * (AT_D / 2);
 #pragma unroll
-        for (int c = 0; c < 32; c += 8) {
-          uint4 w;
-          __nv_bfloat162* h = (__nv_bfloat162*)&w;
+      for (int c0 = 0; c0 < AT_D / 2; c0 += 32) {
+        unsigned v[32];
+        tmem_ld32(tmem_o + lane_sel + half * (AT_D / 2) + c0, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (live) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            h[q] = __floats2bfloat162_rn(__uint_as_float(v[c + 2 * q]) * inv, __uint_as_float(v[c + 2 * q + 1]) * inv);
-          *(uint4*)(orow + c) = w;
+          for (int c = 0; c < 32; c += 8) {
+            uint4 w;
+            __nv_bfloat162* h = (__nv_bfloat162*)&w;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              h[q] = __floats2bfloat162_rn(__uint_as_float(v[c + 2 * q]) * inv, __uint_as_float(v[c + 2 * q + 1]) * inv);
+            *(uint4*)(orow + c0 + c) = w;
+          }
         }
       }
     }
@@ -389,8 +422,49 @@ static int at_encode(CUtensorMap* map, int rank, const void* ptr, const cuuint64
   return r == CUDA_SUCCESS ? 0 : RLLM_E_BADARG;
 }
 
+template <int D>
+static int at_launch(const void* q, int q_stride, int num_q_rows, void* out, const void* kcache, const void* vcache,
+                     const int* block_table, int max_blocks, const int* q_start, const int* seq_lens, int seq_begin,
+                     int seq_end, int num_tokens, int nq, int nkv, int page_size, int num_pages, int window,
+                     float scale, int* err, cudaStream_t stream) {
+  const int g = nq / nkv;
+  CUtensorMap mq, mk, mv;
+  {
+    // a box is a panel of 64 dims: x selects the panel
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)nq, (cuuint64_t)num_q_rows};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)q_stride * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)g, (cuuint32_t)(AT_BM / g)};
+    int rc = at_encode(&mq, 3, q, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * nkv * page_size};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    int rc = at_encode(&mk, 2, kcache, dims, strides, box);
+    if (rc) return rc;
+    rc = at_encode(&mv, 2, vcache, dims, strides, box);
+    if (rc) return rc;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int bq = AT_BM / g;
+  const long long tiles = (num_tokens + bq - 1) / bq + (seq_end - seq_begin);
+  if (tiles * nkv > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;
+  dim3 grid((unsigned)(tiles * nkv));
+  attention_tcgen05_kernel<D><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(mq, mk, mv, (bf16*)out, block_table, max_blocks,
+      q_start, seq_lens, seq_begin, seq_end, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
 // Sequences seq_begin .. seq_end-1 of the step; q rows q_start[s] .. q_start[s+1]-1 (num_q_rows rows of
-// q exist in all); head size 64; page size 16, 32, 64 or 128; nq / nkv a power of two up to 128.
+// q exist in all); head size 64 (pages of 16, 32, 64 or 128 keys) or 128 (pages of 16, 32 or 64); nq / nkv
+// up to 128 (a tile holds 128 / g tokens, rounded down).
 RLLM_EXPORT int rllm_attention_prefill_tcgen05(const void* q, int q_stride, int num_q_rows, void* out,
                                                const void* kcache, const void* vcache, const int* block_table,
                                                int max_blocks, const int* q_start, const int* seq_lens,
@@ -401,38 +475,13 @@ RLLM_EXPORT int rllm_attention_prefill_tcgen05(const void* q, int q_stride, int 
   if (nq <= 0 || nkv <= 0 || nq % nkv || num_pages <= 0 || max_blocks <= 0 || window < 0 || !(scale > 0.f) || !err)
     return RLLM_E_BADARG;
   const int g = nq / nkv;
-  if (d != AT_D || !(page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128) ||
-      (g & (g - 1)) || g > AT_BM || q_stride % 8 || (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache) & 15))
+  if (!(d == 64 || d == 128) || !(page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128) ||
+      page_size > 8192 / d || g > AT_BM || q_stride % 8 ||
+      (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache) & 15))
     return RLLM_E_UNSUPPORTED;
-  CUtensorMap mq, mk, mv;
-  {
-    cuuint64_t dims[3] = {(cuuint64_t)AT_D, (cuuint64_t)nq, (cuuint64_t)num_q_rows};
-    cuuint64_t strides[2] = {(cuuint64_t)AT_D * 2, (cuuint64_t)q_stride * 2};
-    cuuint32_t box[3] = {AT_D, (cuuint32_t)g, (cuuint32_t)(AT_BM / g)};
-    int rc = at_encode(&mq, 3, q, dims, strides, box);
-    if (rc) return rc;
-  }
-  {
-    cuuint64_t dims[2] = {(cuuint64_t)AT_D, (cuuint64_t)num_pages * nkv * page_size};
-    cuuint64_t strides[1] = {(cuuint64_t)AT_D * 2};
-    cuuint32_t box[2] = {AT_D, (cuuint32_t)page_size};
-    int rc = at_encode(&mk, 2, kcache, dims, strides, box);
-    if (rc) return rc;
-    rc = at_encode(&mv, 2, vcache, dims, strides, box);
-    if (rc) return rc;
-  }
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
-  const int bq = AT_BM / g;
-  const long long tiles = (num_tokens + bq - 1) / bq + (seq_end - seq_begin);
-  if (tiles * nkv > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;
-  dim3 grid((unsigned)(tiles * nkv));
-  attention_tcgen05_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(mq, mk, mv, (bf16*)out, block_table, max_blocks,
-      q_start, seq_lens, seq_begin, seq_end, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
-  RLLM_LAUNCH_CHECK();
-  return 0;
+  if ((long long)num_pages * nkv * page_size > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;   // cache rows are TMA coordinates
+#define AT_LAUNCH(DD) return at_launch<DD>(q, q_stride, num_q_rows, out, kcache, vcache, block_table, max_blocks, q_start, \
+      seq_lens, seq_begin, seq_end, num_tokens, nq, nkv, page_size, num_pages, window, scale, err, stream)
+  if (d == 64) AT_LAUNCH(64);
+  AT_LAUNCH(128);
 }

@@ -431,10 +431,11 @@ def attention_prefill_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, kc
 
 
 def attention_prefill_tcgen05_supported(nq: int, nkv: int, d: int, page_size: int) -> bool:
-    """The sizes the tcgen05 prompt attention takes: head size 64, pages of 16 to
-    128 keys, a power-of-two group of query heads per kv head."""
+    """The sizes the tcgen05 prompt attention takes: head size 64 or 128, pages of 16 keys up to a key
+    tile (128 keys for head size 64, 64 for 128), up to 128 query heads per kv head."""
     g = nq // nkv if nkv else 0
-    return d == 64 and page_size in (16, 32, 64, 128) and g >= 1 and nq % nkv == 0 and g & (g - 1) == 0 and g <= 128
+    return (d in (64, 128) and page_size in (16, 32, 64, 128) and page_size <= 8192 // d
+            and 1 <= g <= 128 and nq % nkv == 0)
 
 
 def attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,

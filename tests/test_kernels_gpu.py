@@ -253,17 +253,19 @@ def test_attention_prefill_mma(ops, err, nq, nkv, d, page, window):
     assert torch.equal(out2[a:b], out[a:b]) and float(out2[:a].abs().max()) == 0 and float(out2[b:].abs().max()) == 0
 
 
-TCGEN05_CASES = [(8, 2, 16, 0), (32, 8, 16, 0), (4, 4, 32, 0), (16, 1, 64, 0), (8, 2, 128, 300), (2, 1, 16, 70),
-                 (64, 1, 16, 0), (6, 3, 32, 129)]
+TCGEN05_CASES = [(8, 2, 64, 16, 0), (32, 8, 64, 16, 0), (4, 4, 64, 32, 0), (16, 1, 64, 64, 0), (8, 2, 64, 128, 300),
+                 (2, 1, 64, 16, 70), (64, 1, 64, 16, 0), (6, 3, 64, 32, 129), (6, 2, 64, 16, 0), (5, 1, 64, 32, 40),
+                 (8, 2, 128, 16, 0), (32, 8, 128, 16, 0), (4, 4, 128, 32, 0), (24, 8, 128, 16, 0), (16, 1, 128, 64, 0),
+                 (8, 2, 128, 32, 300), (3, 1, 128, 16, 65)]
 
 
-@pytest.mark.parametrize("nq,nkv,page,window", TCGEN05_CASES)
-def test_attention_prefill_tcgen05(ops, err, nq, nkv, page, window):
+@pytest.mark.parametrize("nq,nkv,d,page,window", TCGEN05_CASES)
+def test_attention_prefill_tcgen05(ops, err, nq, nkv, d, page, window):
     """The tcgen05 kernel for prompt portions (head size 64): portions after earlier context and whole
     prompts, from 2 tokens to several 128-key tiles, strided q rows as in the engine.  Pages that no
     sequence holds, and the rows of a last page behind a sequence's end, hold NaN: nothing of them
     may reach a result."""
-    dt, d = torch.bfloat16, 64
+    dt = torch.bfloat16
     lens, q_lens = [700, 64, 65, 130, 2, 385], [257, 64, 2, 129, 2, 384]
     ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, lens, q_lens, pages=256)
     held = torch.zeros(256, dtype=torch.bool)
@@ -312,16 +314,16 @@ def test_attention_prefill_tcgen05(ops, err, nq, nkv, page, window):
 
 def test_tcgen05_attention_refuses_other_sizes(ops, err):
     from rllm_b200.kernels.ops import KernelError
-    assert not ops.attention_prefill_tcgen05_supported(8, 2, 128, 16)
-    assert not ops.attention_prefill_tcgen05_supported(6, 2, 64, 16)      # groups of 3
+    assert not ops.attention_prefill_tcgen05_supported(8, 2, 32, 16)      # head size
+    assert not ops.attention_prefill_tcgen05_supported(8, 2, 128, 128)    # a page larger than a key tile
     assert not ops.attention_prefill_tcgen05_supported(8, 2, 64, 8)
-    q = torch.zeros(4, 6 * 64, device=DEV, dtype=torch.bfloat16)
-    kc = torch.zeros(4, 2, 16, 64, device=DEV, dtype=torch.bfloat16)
+    q = torch.zeros(4, 8 * 128, device=DEV, dtype=torch.bfloat16)
+    kc = torch.zeros(4, 2, 128, 128, device=DEV, dtype=torch.bfloat16)
     table = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
     qs = torch.tensor([0, 4], dtype=torch.int32, device=DEV)
     sl = torch.tensor([4], dtype=torch.int32, device=DEV)
     with pytest.raises(KernelError, match="no kernel"):
-        ops.attention_prefill_tcgen05(q, 6 * 64, torch.empty_like(q), kc, kc, table, qs, sl, 0, 1, 4, 6, 2, 64, 0, 1.0, err)
+        ops.attention_prefill_tcgen05(q, 8 * 128, torch.empty_like(q), kc, kc, table, qs, sl, 0, 1, 4, 8, 2, 128, 0, 1.0, err)
 
 
 @pytest.mark.parametrize("nq,nkv,d,page,window", MMA_CASES)
