@@ -1,7 +1,8 @@
 """The pool of cache pages of one group of layers: reference counts, a free
 list, and the table from a content hash to the page that holds it.
 
-Semantics follow the reference's ``BlockPool``
+The pool itself is C++ (``native/csrc/cache_core.cc``); this class is its
+Python face.  Semantics follow the reference's ``BlockPool``
 (crates/rllm-cache/src/block_pool.rs:128-406): a page is handed out with
 reference count 1; ``free`` decrements and at 0 the page joins the free list
 *keeping its hash*, so a later request with the same prefix can revive it
@@ -13,31 +14,83 @@ table.
 """
 from __future__ import annotations
 
-from collections import OrderedDict, deque
-from typing import Deque, Dict, List, Optional
+import ctypes
+from ctypes import c_char_p, c_int, c_void_p
+from typing import List, Optional
+
+from ..native import load_library
 
 
 class PagePoolError(RuntimeError):
     pass
 
 
+RC_NOT_HELD, RC_BUSY, RC_UNKNOWN_REQ, RC_DUPLICATE_REQ, RC_BADARG, RC_CHECK_FAILED = -2, -3, -4, -5, -6, -7
+_lib = None
+
+
+def core():
+    """The C++ library with its argument and result types set."""
+    global _lib
+    if _lib is None:
+        lib = load_library("cache_core")
+        for name in ("rllm_pool_new", "rllm_cache_new", "rllm_cache_pool"):
+            getattr(lib, name).restype = c_void_p
+        for name in ("rllm_page_hashes", "rllm_cache_match_prefix", "rllm_cache_adopt_prefix"):
+            getattr(lib, name).restype = ctypes.c_longlong
+        lib.rllm_pool_delete.restype = None
+        lib.rllm_cache_delete.restype = None
+        _lib = lib
+    return _lib
+
+
+def _hash16(content_hash: bytes) -> bytes:
+    if len(content_hash) > 16:
+        raise ValueError("a content hash has at most 16 bytes")
+    return content_hash.ljust(16, b"\0")
+
+
+class _Refcounts:
+    """``pool.refcount[page]``"""
+
+    def __init__(self, pool: "BlockPool"):
+        self._pool = pool
+
+    def __getitem__(self, page: int) -> int:
+        n = core().rllm_pool_refcount(self._pool._h, c_int(page))
+        if n < 0:
+            raise IndexError(page)
+        return n
+
+    def __len__(self) -> int:
+        return self._pool.num_pages
+
+    def __iter__(self):
+        return (self[p] for p in range(len(self)))
+
+
 class BlockPool:
-    def __init__(self, num_pages: int):
-        if num_pages < 1:
-            raise ValueError("a pool needs at least one page")
-        self.num_pages = num_pages
-        self.refcount: List[int] = [0] * num_pages
-        self.hash_of: List[Optional[bytes]] = [None] * num_pages
-        self.page_of: Dict[bytes, int] = {}
-        # free pages without a hash: last in, first out
-        self._free_plain: Deque[int] = deque(range(num_pages - 1, -1, -1))
-        # free pages that still hold findable content, least recently freed first
-        self._free_cached: "OrderedDict[int, None]" = OrderedDict()
+    def __init__(self, num_pages: int, _handle=None):
+        if _handle is None:
+            if num_pages < 1:
+                raise ValueError("a pool needs at least one page")
+            self._h = c_void_p(core().rllm_pool_new(c_int(num_pages)))
+            self._owned = True
+        else:
+            self._h = c_void_p(_handle)        # a pool inside a cache manager, which owns it
+            self._owned = False
+        self.num_pages = int(core().rllm_pool_num_pages(self._h))
+        self.refcount = _Refcounts(self)
+
+    def __del__(self):
+        if getattr(self, "_owned", False) and _lib is not None:
+            _lib.rllm_pool_delete(self._h)
+            self._owned = False
 
     # -- counts -----------------------------------------------------------
     @property
     def num_free(self) -> int:
-        return len(self._free_plain) + len(self._free_cached)
+        return int(core().rllm_pool_num_free(self._h))
 
     @property
     def num_active(self) -> int:
@@ -45,34 +98,20 @@ class BlockPool:
 
     @property
     def num_cached(self) -> int:
-        return len(self.page_of)
+        return int(core().rllm_pool_num_cached(self._h))
 
     # -- allocation -------------------------------------------------------
     def allocate(self) -> Optional[int]:
-        if self._free_plain:
-            page = self._free_plain.pop()
-        elif self._free_cached:
-            page, _ = self._free_cached.popitem(last=False)
-            self._drop_hash(page)
-        else:
-            return None
-        self.refcount[page] = 1
-        return page
+        page = core().rllm_pool_allocate(self._h)
+        return None if page < 0 else int(page)
 
     def incref(self, page: int) -> None:
-        if self.refcount[page] < 1:
+        if core().rllm_pool_incref(self._h, c_int(page)) < 0:
             raise PagePoolError(f"page {page} is not held")
-        self.refcount[page] += 1
 
     def free(self, page: int) -> None:
-        if not 0 <= page < self.num_pages or self.refcount[page] < 1:
+        if core().rllm_pool_free(self._h, c_int(page)) < 0:
             raise PagePoolError(f"page {page} is freed but not held")
-        self.refcount[page] -= 1
-        if self.refcount[page] == 0:
-            if self.hash_of[page] is not None:
-                self._free_cached[page] = None
-            else:
-                self._free_plain.append(page)
 
     def is_shared(self, page: int) -> bool:
         return self.refcount[page] > 1
@@ -80,55 +119,28 @@ class BlockPool:
     # -- content hashes ---------------------------------------------------
     def register(self, page: int, content_hash: bytes) -> None:
         """Make a held, completely written page findable by its content."""
-        if self.refcount[page] < 1:
+        if core().rllm_pool_register(self._h, c_int(page), c_char_p(_hash16(content_hash))) < 0:
             raise PagePoolError(f"page {page} is not held")
-        if self.hash_of[page] is not None or content_hash in self.page_of:
-            return  # already findable (or the same content lives in another page)
-        self.hash_of[page] = content_hash
-        self.page_of[content_hash] = page
 
     def peek(self, content_hash: bytes) -> Optional[int]:
         """The page with this content, without taking a reference."""
-        return self.page_of.get(content_hash)
+        page = core().rllm_pool_peek(self._h, c_char_p(_hash16(content_hash)))
+        return None if page < 0 else int(page)
 
     def acquire_cached(self, content_hash: bytes) -> Optional[int]:
         """Take a reference to the page with this content, reviving it from the
         free list if need be (block_pool.rs:329-348)."""
-        page = self.page_of.get(content_hash)
-        if page is None:
-            return None
-        if self.refcount[page] == 0:
-            del self._free_cached[page]
-        self.refcount[page] += 1
-        return page
+        page = core().rllm_pool_acquire_cached(self._h, c_char_p(_hash16(content_hash)))
+        return None if page < 0 else int(page)
 
     def reset_prefix_cache(self) -> None:
         """Forget all content hashes; refused while hashed pages are held
         (block_pool.rs:367-385)."""
-        if any(self.refcount[p] > 0 for p in self.page_of.values()):
+        if core().rllm_pool_reset_prefix_cache(self._h) < 0:
             raise PagePoolError("cannot reset the prefix cache while hashed pages are held")
-        for page in list(self._free_cached):
-            self._free_plain.append(page)
-        self._free_cached.clear()
-        for page in self.page_of.values():
-            self.hash_of[page] = None
-        self.page_of.clear()
-
-    def _drop_hash(self, page: int) -> None:
-        h = self.hash_of[page]
-        if h is not None:
-            del self.page_of[h]
-            self.hash_of[page] = None
 
     # -- invariants, for tests -----------------------------------------------
     def check(self) -> None:
-        free = list(self._free_plain) + list(self._free_cached)
-        assert len(free) == len(set(free)), "a page is on the free list twice"
-        for p in range(self.num_pages):
-            assert (self.refcount[p] == 0) == (p in set(free)), f"page {p}: count and free list disagree"
-        for h, p in self.page_of.items():
-            assert self.hash_of[p] == h
-        for p in self._free_plain:
-            assert self.hash_of[p] is None
-        for p in self._free_cached:
-            assert self.hash_of[p] is not None
+        why = ctypes.create_string_buffer(256)
+        if core().rllm_pool_check(self._h, why, c_int(256)) < 0:
+            raise AssertionError(why.value.decode())

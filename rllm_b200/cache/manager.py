@@ -22,48 +22,48 @@ still computes its last page so that there is a logit to sample from
 (the intent of prefix.rs:73-86).  Prefix sharing needs a model whose only
 cache group keeps all keys; with windows or state it is switched off.
 
-This is host-side bookkeeping only; the storage lives in ``CacheStorage``.
+This is host-side bookkeeping only; the storage lives in ``CacheStorage``.  The
+bookkeeping itself is C++ (``native/csrc/cache_core.cc``); this class is its
+Python face: it maps request ids (any hashable) to the integers the C++ side
+knows and turns its return codes into exceptions.
 """
 from __future__ import annotations
 
-import hashlib
-import struct
+import ctypes
+from ctypes import c_char_p, c_int, c_longlong, c_void_p
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import numpy as np
+
 from ..parts.spec import KVPagesNeed, StateNeed
-from .block_pool import BlockPool, PagePoolError
+from .block_pool import RC_DUPLICATE_REQ, RC_NOT_HELD, RC_UNKNOWN_REQ, BlockPool, PagePoolError, core
 
 
 class NoCapacity(RuntimeError):
     """No state slot is free."""
 
 
+def _tokens(tokens: Sequence[int]) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(tokens, dtype=np.int64))
+
+
+def _ptr(a: np.ndarray):
+    return a.ctypes.data_as(c_void_p)
+
+
 def page_hashes(tokens: Sequence[int], page_size: int, salt: bytes = b"",
                 start: int = 0, parent: bytes = b"") -> List[bytes]:
     """Chained hashes of the full pages of ``tokens`` from page ``start`` on:
-    h_k = H(h_{k-1} | tokens of page k | salt), the first parent empty
-    (crates/rllm-cache/src/prefix.rs:43-71)."""
-    out = []
-    for k in range(start, len(tokens) // page_size):
-        chunk = tokens[k * page_size:(k + 1) * page_size]
-        h = hashlib.sha256()
-        h.update(parent)
-        h.update(struct.pack(f"<{page_size}q", *chunk))
-        h.update(salt)
-        parent = h.digest()[:16]
-        out.append(parent)
-    return out
-
-
-class _Request:
-    __slots__ = ("slot", "tables", "released", "hashes", "registered")
-
-    def __init__(self, slot: int, num_groups: int):
-        self.slot = slot
-        self.tables: List[List[int]] = [[] for _ in range(num_groups)]
-        self.released: List[int] = [0] * num_groups   # leading pages given back (windows)
-        self.hashes: List[bytes] = []                 # content hashes of this request's full pages
-        self.registered = 0                           # pages already made findable
+    h_k = SHA-256(h_{k-1} | tokens of page k as little-endian int64 | salt) cut to 16
+    bytes, the first parent empty (crates/rllm-cache/src/prefix.rs:43-71)."""
+    t = _tokens(tokens)
+    n = max(0, len(t) // page_size - start)
+    out = ctypes.create_string_buffer(16 * max(n, 1))
+    got = core().rllm_page_hashes(_ptr(t), c_longlong(len(t)), c_int(page_size), c_char_p(salt), c_int(len(salt)),
+                                  c_int(start), c_char_p(parent) if parent else None, out, c_longlong(n))
+    if got < 0:
+        raise ValueError("page_hashes: bad arguments")
+    return [out.raw[16 * i:16 * i + 16] for i in range(got)]
 
 
 class CacheManager:
@@ -79,121 +79,124 @@ class CacheManager:
         counts = list(num_pages) if isinstance(num_pages, (list, tuple)) else [num_pages] * len(self.paged)
         if len(counts) != len(self.paged):
             raise ValueError("num_pages: one count per paged group")
-        self.pools: Dict[int, BlockPool] = {g: BlockPool(c) for g, c in zip(self.paged, counts)}
-        self.requests: Dict[Hashable, _Request] = {}
-        self._free_slots: List[int] = list(range(max_seqs - 1, -1, -1))
-        self.fresh_slots: List[int] = []   # slots handed out since the last take_fresh_slots()
-        only_full = (len(self.paged) == 1 and not self.stateful
-                     and self.needs[self.paged[0]].window is None)
-        self.prefix_caching = bool(enable_prefix_caching and only_full)
+        G = len(self.needs)
+        kinds = (c_int * max(G, 1))(*[0 if g in self.paged else 1 for g in range(G)])
+        windows = (c_int * max(G, 1))(*[(-1 if getattr(n, "window", None) is None else int(n.window))
+                                        for n in self.needs])
+        per_group = [0] * G
+        for g, c in zip(self.paged, counts):
+            if c < 1:
+                raise ValueError("a pool needs at least one page")
+            per_group[g] = int(c)
+        h = core().rllm_cache_new(c_int(G), kinds, windows, (c_int * max(G, 1))(*per_group), c_int(page_size),
+                                  c_int(max_seqs), c_int(1 if enable_prefix_caching else 0))
+        if not h:
+            raise ValueError("CacheManager: bad sizes")
+        self._h = c_void_p(h)
+        self.pools: Dict[int, BlockPool] = {
+            g: BlockPool(0, _handle=core().rllm_cache_pool(self._h, c_int(g))) for g in self.paged}
+        self.requests: Dict[Hashable, int] = {}       # request id -> the integer the C++ side knows it by
+        self._next_id = 0
+        self.prefix_caching = bool(core().rllm_cache_prefix_caching(self._h))
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h is not None:
+            try:
+                core().rllm_cache_delete(h)
+            except Exception:
+                pass
+            self._h = None
+
+    def _id(self, req: Hashable) -> c_longlong:
+        return c_longlong(self.requests[req])
 
     # -- admission and release -------------------------------------------------
     def has_free_slot(self) -> bool:
-        return bool(self._free_slots)
+        return core().rllm_cache_num_free_slots(self._h) > 0
 
     def admit(self, req: Hashable) -> int:
         if req in self.requests:
             raise KeyError(f"request {req!r} is already admitted")
-        if not self._free_slots:
+        rid = self._next_id
+        slot = core().rllm_cache_admit(self._h, c_longlong(rid))
+        if slot == RC_DUPLICATE_REQ:
+            raise KeyError(f"request {req!r} is already admitted")
+        if slot < 0:
             raise NoCapacity("no free state slot")
-        slot = self._free_slots.pop()
-        self.requests[req] = _Request(slot, len(self.needs))
-        self.fresh_slots.append(slot)
-        return slot
+        self._next_id += 1
+        self.requests[req] = rid
+        return int(slot)
+
+    @property
+    def fresh_slots(self) -> int:
+        """How many slots were handed out since the last ``take_fresh_slots``."""
+        return int(core().rllm_cache_num_fresh_slots(self._h))
 
     def take_fresh_slots(self) -> List[int]:
         """Slots handed out since the last call: their state must be zeroed
         before the next step."""
-        out, self.fresh_slots = self.fresh_slots, []
-        return out
+        n = self.fresh_slots
+        if not n:
+            return []
+        buf = (c_int * n)()
+        got = core().rllm_cache_take_fresh_slots(self._h, buf, c_int(n))
+        return [int(buf[i]) for i in range(got)]
 
     def free(self, req: Hashable) -> None:
-        r = self.requests.pop(req, None)
-        if r is None:
-            return
-        for g in self.paged:
-            for page in r.tables[g]:
-                if page >= 0:
-                    self.pools[g].free(page)
-        self._free_slots.append(r.slot)
-        if r.slot in self.fresh_slots:
-            self.fresh_slots.remove(r.slot)
+        rid = self.requests.pop(req, None)
+        if rid is not None:
+            core().rllm_cache_free(self._h, c_longlong(rid))
 
     def slot(self, req: Hashable) -> int:
-        return self.requests[req].slot
+        return int(core().rllm_cache_slot(self._h, self._id(req)))
+
+    def table_len(self, req: Hashable, group: int) -> int:
+        return int(core().rllm_cache_table_len(self._h, self._id(req), c_int(group)))
 
     def table(self, req: Hashable, group: int) -> List[int]:
-        return self.requests[req].tables[group]
+        """A copy of the request's block table in this group (-1: a page given back)."""
+        n = self.table_len(req, group)
+        if n <= 0:
+            return []
+        buf = (c_int * n)()
+        core().rllm_cache_table(self._h, self._id(req), c_int(group), buf, c_int(n))
+        return list(buf)
+
+    def pack_tables(self, reqs: Sequence[Hashable], group: int, out: np.ndarray) -> None:
+        """Row i of ``out`` (int32 [len(reqs), width], C-contiguous) = the table of reqs[i], -1 behind its end."""
+        assert out.dtype == np.int32 and out.flags.c_contiguous and out.shape[0] >= len(reqs)
+        ids = np.fromiter((self.requests[r] for r in reqs), dtype=np.int64, count=len(reqs))
+        rc = core().rllm_cache_pack_tables(self._h, _ptr(ids), c_int(len(reqs)), c_int(group), _ptr(out),
+                                           c_int(out.shape[1]))
+        if rc < 0:
+            raise KeyError("pack_tables: a request is not admitted")
 
     # -- pages ------------------------------------------------------------------
-    def _first_needed_page(self, group: int, first_query_pos: int) -> int:
-        window = self.needs[group].window
-        if window is None:
-            return 0
-        return max(0, first_query_pos - window + 1) // self.page_size
-
     def release_behind_window(self, req: Hashable, first_query_pos: int) -> int:
         """Give back the pages that no query at or after ``first_query_pos`` can
         see.  Returns how many pages were given back."""
-        r = self.requests[req]
-        n = 0
-        for g in self.paged:
-            upto = min(self._first_needed_page(g, first_query_pos), len(r.tables[g]))
-            for k in range(r.released[g], upto):
-                if r.tables[g][k] >= 0:
-                    self.pools[g].free(r.tables[g][k])
-                    r.tables[g][k] = -1
-                    n += 1
-            r.released[g] = max(r.released[g], upto)
-        return n
+        return int(core().rllm_cache_release_behind_window(self._h, self._id(req), c_longlong(first_query_pos)))
 
     def pages_needed(self, req: Hashable, first_query_pos: int, num_tokens: int) -> Dict[int, int]:
         """New pages per paged group that ``ensure`` would take."""
-        r = self.requests[req]
-        want = -(-num_tokens // self.page_size)
-        out = {}
-        for g in self.paged:
-            have = len(r.tables[g])
-            first = max(self._first_needed_page(g, first_query_pos), have)
-            out[g] = max(0, want - first)
-        return out
+        rid = self._id(req)
+        return {g: int(core().rllm_cache_pages_needed(self._h, rid, c_int(g), c_longlong(first_query_pos),
+                                                      c_longlong(num_tokens))) for g in self.paged}
 
     def ensure(self, req: Hashable, first_query_pos: int, num_tokens: int) -> bool:
         """Make sure the request has pages for positions < ``num_tokens`` that
         queries from ``first_query_pos`` on can see, in every paged group.
         All or nothing: on False no page was taken
         (crates/rllm-cache/src/manager.rs:132-166)."""
-        self.release_behind_window(req, first_query_pos)
-        need = self.pages_needed(req, first_query_pos, num_tokens)
-        if any(self.pools[g].num_free < n for g, n in need.items()):
-            return False
-        r = self.requests[req]
-        want = -(-num_tokens // self.page_size)
-        for g in self.paged:
-            first = self._first_needed_page(g, first_query_pos)
-            while len(r.tables[g]) < want:
-                k = len(r.tables[g])
-                if k < first:           # behind the window from the start: never held
-                    r.tables[g].append(-1)
-                    r.released[g] = k + 1
-                else:
-                    page = self.pools[g].allocate()
-                    assert page is not None
-                    r.tables[g].append(page)
-        return True
+        rc = core().rllm_cache_ensure(self._h, self._id(req), c_longlong(first_query_pos), c_longlong(num_tokens))
+        if rc < 0:
+            raise KeyError(req)
+        return bool(rc)
 
     def fits_at_all(self, num_tokens: int) -> bool:
         """Could one request of ``num_tokens`` tokens ever be held?"""
-        want = -(-num_tokens // self.page_size)
-        for g in self.paged:
-            window = self.needs[g].window
-            if window is not None:
-                want_g = min(want, -(-(window + self.page_size) // self.page_size) + 1)
-            else:
-                want_g = want
-            if want_g > self.pools[g].num_pages:
-                return False
-        return True
+        return bool(core().rllm_cache_fits_at_all(self._h, c_longlong(num_tokens)))
 
     # -- prefix sharing ------------------------------------------------------------
     def match_prefix(self, tokens: Sequence[int]) -> int:
@@ -201,60 +204,36 @@ class CacheManager:
         reference.  A prompt that is cached completely reports one page less."""
         if not self.prefix_caching:
             return 0
-        pool = self.pools[self.paged[0]]
-        n = 0
-        for h in page_hashes(tokens, self.page_size):
-            if pool.peek(h) is None:
-                break
-            n += 1
-        if n and n * self.page_size >= len(tokens):
-            n -= 1
-        return n * self.page_size
+        t = _tokens(tokens)
+        return int(core().rllm_cache_match_prefix(self._h, _ptr(t), c_longlong(len(t))))
 
     def adopt_prefix(self, req: Hashable, tokens: Sequence[int]) -> int:
         """Give a newly admitted request the findable pages of its prefix.
         Returns the number of tokens it need not compute."""
         if not self.prefix_caching:
             return 0
-        r = self.requests[req]
-        g = self.paged[0]
-        if r.tables[g]:
+        t = _tokens(tokens)
+        n = core().rllm_cache_adopt_prefix(self._h, self._id(req), _ptr(t), c_longlong(len(t)))
+        if n == RC_NOT_HELD:
             raise PagePoolError("adopt_prefix on a request that already holds pages")
-        pool = self.pools[g]
-        limit = (len(tokens) - 1) // self.page_size        # keep at least one token to compute
-        hashes = page_hashes(tokens, self.page_size)[:limit]
-        for h in hashes:
-            page = pool.acquire_cached(h)
-            if page is None:
-                break
-            r.tables[g].append(page)
-        n = len(r.tables[g])
-        r.hashes = hashes[:n]
-        r.registered = n
-        return n * self.page_size
+        if n == RC_UNKNOWN_REQ:
+            raise KeyError(req)
+        return int(n)
 
     def register_computed(self, req: Hashable, tokens: Sequence[int], num_computed: int) -> None:
         """Make the pages findable whose keys now exist for all their tokens
         (crates/rllm-cache/src/manager.rs:184-210)."""
         if not self.prefix_caching:
             return
-        r = self.requests[req]
-        g = self.paged[0]
-        full = min(num_computed, len(tokens)) // self.page_size
-        if full > len(r.hashes):
-            parent = r.hashes[-1] if r.hashes else b""
-            r.hashes += page_hashes(tokens[:full * self.page_size], self.page_size,
-                                    start=len(r.hashes), parent=parent)
-        pool = self.pools[g]
-        for k in range(r.registered, full):
-            pool.register(r.tables[g][k], r.hashes[k])
-        r.registered = max(r.registered, full)
+        t = _tokens(tokens)
+        core().rllm_cache_register_computed(self._h, self._id(req), _ptr(t), c_longlong(len(t)),
+                                            c_longlong(num_computed))
 
     # -- statistics and invariants -----------------------------------------------------
     def usage(self) -> dict:
         return {
             "num_requests": len(self.requests),
-            "free_slots": len(self._free_slots),
+            "free_slots": int(core().rllm_cache_num_free_slots(self._h)),
             "groups": {g: {"total": p.num_pages, "free": p.num_free, "active": p.num_active,
                            "cached": p.num_cached} for g, p in self.pools.items()},
         }
@@ -266,16 +245,7 @@ class CacheManager:
 
     def check(self) -> None:
         """No page lost, held twice without a matching count, or freed twice."""
-        for g in self.paged:
-            pool = self.pools[g]
-            pool.check()
-            held: Dict[int, int] = {}
-            for r in self.requests.values():
-                for page in r.tables[g]:
-                    if page >= 0:
-                        held[page] = held.get(page, 0) + 1
-            for page in range(pool.num_pages):
-                assert pool.refcount[page] == held.get(page, 0), \
-                    f"group {g} page {page}: count {pool.refcount[page]}, held by {held.get(page, 0)}"
-        slots = [r.slot for r in self.requests.values()] + self._free_slots
-        assert sorted(slots) == list(range(self.max_seqs)), "a state slot is lost or held twice"
+        why = ctypes.create_string_buffer(256)
+        if core().rllm_cache_check(self._h, why, c_int(256)) < 0:
+            raise AssertionError(why.value.decode())
+        assert core().rllm_cache_num_requests(self._h) == len(self.requests)

@@ -139,17 +139,24 @@ class DecodeGraph:
             h[self.r_seqlens[0] + s] = e.start + 1
             h[self.r_slots[0] + s] = cache.slot(e.req)
         windowed = any(cache.needs[g].window is not None for g in self.paged)
-        for s, e in enumerate(entries):
-            tbs = [cache.table(e.req, g) for g in self.paged]
-            state = (e.req, tuple((id(tb), len(tb)) for tb in tbs))
-            if self.row_state[s] == state and not windowed:
-                continue                      # same request, tables only grow: nothing new to write
-            self.row_state[s] = state
-            for (g, r), tb in zip(zip(self.paged, self.r_tables), tbs):
+        reqs = [e.req for e in entries]
+        for g, r in zip(self.paged, self.r_tables):
+            # rows whose request or table length changed since they were last written (tables only grow,
+            # unless a window gives pages back); the C++ side copies them into the pinned buffer
+            stale = [s for s, e in enumerate(entries)
+                     if windowed or self.row_state[s] != (g, e.req, cache.table_len(e.req, g))]
+            if len(stale) == len(entries):
+                cache.pack_tables(reqs, g, h[r[0]:r[1]].reshape(S, W))
+            else:
                 tab = h[r[0]:r[1]].reshape(S, W)
-                n = min(len(tb), W)
-                tab[s, :n] = tb[:n]
-                tab[s, n:] = -1
+                for s in stale:
+                    cache.pack_tables([reqs[s]], g, tab[s:s + 1])
+            if len(self.paged) == 1:
+                for s in stale:
+                    self.row_state[s] = (g, reqs[s], cache.table_len(reqs[s], g))
+            else:
+                for s in stale:
+                    self.row_state[s] = None      # several groups: rows are written every time
 
     def run(self) -> torch.Tensor:
         """Logits float32 [live rows, vocab]; valid until the next run of this graph."""

@@ -107,17 +107,19 @@ class BatchBuilder:
             seq_lens[s] = e.start + (b - a)
             slots[s] = self.cache.slot(e.req)
         rows = np.asarray([first_of[i] + w for i, e in enumerate(entries) for w in e.want], dtype=np.int32)
+        reqs = [entries[i].req for i in order]
+        need = [-(-int(seq_lens[s]) // self.cache.page_size) for s in range(S)]
+        width = max(1, max(need))
         for g in paged:
-            per_seq = [self.cache.table(entries[i].req, g) for i in order]
-            need = [-(-int(seq_lens[s]) // self.cache.page_size) for s in range(S)]
-            for s, (tb, n) in enumerate(zip(per_seq, need)):
-                if len(tb) < n:
-                    raise StepError(f"request {entries[order[s]].req!r} holds {len(tb)} pages of group {g}, "
+            for s, n in enumerate(need):
+                have = self.cache.table_len(reqs[s], g)
+                if have < n:
+                    raise StepError(f"request {reqs[s]!r} holds {have} pages of group {g}, "
                                     f"its {int(seq_lens[s])} tokens need {n}")
-            width = max(1, max(need))
-            tab = np.full((S, width), -1, dtype=np.int32)
-            for s, (tb, n) in enumerate(zip(per_seq, need)):
-                tab[s, :n] = tb[:n]
+            tab = np.empty((S, width), dtype=np.int32)
+            self.cache.pack_tables(reqs, g, tab)
+            for s, n in enumerate(need):
+                tab[s, n:] = -1                     # pages behind this step's tokens are not this step's business
             tables.append(tab)
         # one pinned staging buffer, one copy to the device
         parts = [token_ids, positions, token_seq, q_start, seq_lens, slots, rows] + [t.ravel() for t in tables]
