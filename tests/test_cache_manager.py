@@ -132,6 +132,26 @@ def test_a_prompt_that_starts_behind_its_window_holds_no_early_pages():
     m.check()
 
 
+def test_page_hashes_are_sha256_chains():
+    """The C++ side's own SHA-256 against hashlib: h_k = SHA-256(h_{k-1} | tokens as little-endian int64 | salt)
+    cut to 16 bytes, for pages of several sizes (message lengths around the padding's edge cases)."""
+    import hashlib
+    import struct
+    for page in (1, 3, 6, 7, 8, 16, 55):
+        toks = [(i * 2654435761) % 100003 - 7 for i in range(page * 5 + 2)]
+        for salt in (b"", b"s", b"a longer salt than one block of the hash function, to cross 64 bytes at once"):
+            parent = b""
+            got = page_hashes(toks, page, salt=salt)
+            assert len(got) == len(toks) // page
+            for k, h in enumerate(got):
+                m = hashlib.sha256()
+                m.update(parent)
+                m.update(struct.pack(f"<{page}q", *toks[k * page:(k + 1) * page]))
+                m.update(salt)
+                parent = m.digest()[:16]
+                assert h == parent, (page, k)
+
+
 def test_page_hashes_chain():
     toks = list(range(40))
     h = page_hashes(toks, 16)
