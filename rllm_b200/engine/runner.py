@@ -162,9 +162,9 @@ class ModelRunner:
         self.device = model.device
         self.builder = BatchBuilder(cache, self.device, model.dtype)
         self.err = self.builder.err
-        # decode steps go through CUDA graphs if every mixer says its forward can be captured
+        # decode steps go through CUDA graphs if every part of every block says its forward can be captured
         self.capture_graphs = bool(enable_cuda_graphs) and all(
-            getattr(b.mixer, "graph_safe", False) for b in model.blocks)
+            getattr(p, "graph_safe", False) for b in model.blocks for p in b.parts())
         self.graphs = {}
         self.graph_pool = None
 

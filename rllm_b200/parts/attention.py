@@ -33,7 +33,10 @@ from .spec import KVPagesNeed, PartSpec, TensorSpec
 
 @register_part("mixer", "attention")
 class PagedAttention(Mixer):
-    graph_safe = True        # forward launches kernels only: a decode step can be captured in a CUDA graph
+    @property
+    def graph_safe(self) -> bool:
+        """forward launches kernels only; so a decode step can be captured if the position part's ``apply`` can."""
+        return bool(self.position.graph_safe)
 
     def __init__(self, spec: PartSpec, prefix: str = ""):
         super().__init__(spec, prefix)

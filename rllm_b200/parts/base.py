@@ -136,6 +136,11 @@ class StateCacheView:
 
 
 class Part:
+    # True only if ``forward``/``apply`` launches kernels without reading anything back to the host and
+    # without host-to-device copies of unpinned memory: decode steps are captured in CUDA graphs only when
+    # every part of every block says so.
+    graph_safe = False
+
     def __init__(self, spec: PartSpec, prefix: str = ""):
         self.spec = spec
         self.prefix = prefix

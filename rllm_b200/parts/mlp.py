@@ -21,6 +21,8 @@ from .spec import PartSpec, TensorSpec
 
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec: PartSpec, prefix: str = ""):
         super().__init__(spec, prefix)
         self.hidden = int(spec["hidden_size"])

@@ -20,6 +20,7 @@ from .spec import PartSpec, TensorSpec
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
     """params: size, eps, name (tensor name below the prefix)."""
+    graph_safe = True
 
     def __init__(self, spec: PartSpec, prefix: str = ""):
         super().__init__(spec, prefix)

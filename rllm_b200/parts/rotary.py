@@ -48,6 +48,7 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict]) -
 @register_part("position_encoding", "rotary")
 class Rotary(PositionEncoding):
     """params: head_dim, rotary_dim (<= head_dim, even), theta, scaling (dict or None)."""
+    graph_safe = True
 
     def __init__(self, spec: PartSpec, prefix: str = ""):
         super().__init__(spec, prefix)
@@ -75,5 +76,7 @@ class Rotary(PositionEncoding):
 
 @register_part("position_encoding", "none")
 class NoPosition(PositionEncoding):
+    graph_safe = True
+
     def fused_rotary(self, device=None):
         return None, 0

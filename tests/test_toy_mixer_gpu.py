@@ -144,3 +144,165 @@ def test_toy_architecture_is_registered_built_and_stepped(tmp_path, dtype):
             have = np.stack([got[(r, p)] for p in range(len(toks))])
             err = np.abs(have - want[r]).max(axis=1) / np.abs(want[r]).max()
             assert err.max() <= tol, (r, int(err.argmax()), float(err.max()))
+
+
+# ---------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, defined here too
+# ---------------------------------------------------------------------------
+E, FF = 3, 48
+AMP = 0.5
+
+
+def register_routed():
+    from rllm_b200.config import register_architecture
+    from rllm_b200.parts import FeedForward, LayerSpec, ModelSpec, PartSpec, Run, TensorSpec, register_part
+    from rllm_b200.parts.base import PositionEncoding
+
+    @register_part("feed_forward", "toy_top1_experts")
+    class Top1Experts(FeedForward):
+        """Router logits in float32, the expert with the largest logit (lowest index on ties) alone computes
+        the token: y = softmax(logits)[e] * W2[e] relu(W1[e] x).  A row depends on nothing but itself."""
+
+        def __init__(self, spec, prefix=""):
+            super().__init__(spec, prefix)
+            self.hidden, self.inner, self.experts = spec["hidden_size"], spec["inner_size"], spec["num_experts"]
+
+        def tensor_specs(self):
+            specs = [TensorSpec(self.prefix + "router.weight", (self.experts, self.hidden), init=("normal", 0.5))]
+            for e in range(self.experts):
+                specs += [TensorSpec(self.prefix + f"experts.{e}.w1", (self.inner, self.hidden), init=("normal", 0.2)),
+                          TensorSpec(self.prefix + f"experts.{e}.w2", (self.hidden, self.inner), init=("normal", 0.2))]
+            return specs
+
+        def load(self, tensors):
+            self.router = tensors[self.prefix + "router.weight"]
+            self.w1 = [tensors[self.prefix + f"experts.{e}.w1"] for e in range(self.experts)]
+            self.w2 = [tensors[self.prefix + f"experts.{e}.w2"] for e in range(self.experts)]
+
+        def forward(self, x):
+            xf = x.float()
+            logits = xf @ self.router.float().t()
+            choice = logits.argmax(dim=1)
+            gate = torch.softmax(logits, dim=1).gather(1, choice[:, None])
+            out = torch.zeros_like(xf)
+            for e in range(self.experts):                       # tokens sorted by expert, one product per expert
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    hid = torch.relu(xf[rows] @ self.w1[e].float().t())
+                    out[rows] = hid @ self.w2[e].float().t()
+            return (out * gate).to(x.dtype)
+
+    @register_part("position_encoding", "toy_additive_waves")
+    class AdditiveWaves(PositionEncoding):
+        """q += amp * sin(p f_i), k += amp * cos(p f_i) on every head dim i: not a rotation, so the mixer
+        calls ``apply`` and fuses nothing."""
+
+        def __init__(self, spec, prefix=""):
+            super().__init__(spec, prefix)
+            self.dim, self.amp = spec["head_dim"], spec["amp"]
+            self.freq = torch.tensor([1.0 / (3.0 + i) for i in range(self.dim)], dtype=torch.float64)
+
+        def tensor_specs(self):
+            return []
+
+        def load(self, tensors):
+            pass
+
+        def apply(self, q, k, positions):
+            ang = positions.double()[:, None, None] * self.freq.to(q.device)[None, None, :]
+            q.add_((self.amp * torch.sin(ang)).to(q.dtype))
+            if k is not None:
+                k.add_((self.amp * torch.cos(ang)).to(k.dtype))
+
+    def build(cfg):
+        norms = lambda: (PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="n0.weight"),
+                         PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="n1.weight"))
+        waves = PartSpec.of("toy_additive_waves", head_dim=16, amp=AMP)
+        rot = PartSpec.of("rotary", head_dim=16, rotary_dim=16, theta=100.0, scaling=None)
+        layers = (
+            LayerSpec("pre_norm", PartSpec.of("attention", hidden_size=H, num_heads=2, num_kv_heads=2, head_dim=16,
+                                              window=24, scale=None, position=waves),
+                      PartSpec.of("gated_mlp", hidden_size=H, intermediate_size=56), norms(), "toy.0."),
+            LayerSpec("pre_norm", PartSpec.of("attention", hidden_size=H, num_heads=2, num_kv_heads=1, head_dim=16,
+                                              window=None, scale=None, position=rot),
+                      PartSpec.of("toy_top1_experts", hidden_size=H, inner_size=FF, num_experts=E, tensor_prefix="moe."),
+                      norms(), "toy.1."),
+        )
+        return ModelSpec(hidden_size=H, vocab_size=V,
+                         embedding=PartSpec.of("token_embedding", vocab_size=V, hidden_size=H, name="toy.embed"),
+                         layers=layers, order=(Run(0, 0), Run(1, 1)),
+                         final_norm=PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="toy.norm"),
+                         head=PartSpec.of("lm_head", vocab_size=V, hidden_size=H, name="toy.head", tied_to=None),
+                         max_positions=512)
+
+    register_architecture("ToyRoutedForCausalLM", lambda raw: dict(raw), build)
+
+
+def plain_routed(w, tokens, eps):
+    """Logits and, per token, the margin between the router's two largest logits."""
+    x = pl.embedding(w["toy.embed"], tokens)
+    t = len(tokens)
+    pos = torch.arange(t)
+    # layer 0: attention over a window of 24 keys with the additive waves, gated mlp
+    xn = pl.rms_norm(x, w["toy.0.n0.weight"], eps)
+    ang = pos.double()[:, None, None] * torch.tensor([1.0 / (3.0 + i) for i in range(16)], dtype=torch.float64)
+    q = (xn @ w["toy.0.self_attn.q_proj.weight"].t()).reshape(t, 2, 16) + AMP * torch.sin(ang)
+    k = (xn @ w["toy.0.self_attn.k_proj.weight"].t()).reshape(t, 2, 16) + AMP * torch.cos(ang)
+    v = (xn @ w["toy.0.self_attn.v_proj.weight"].t()).reshape(t, 2, 16)
+    x = x + pl.attention(q, k, v, pos, window=24) @ w["toy.0.self_attn.o_proj.weight"].t()
+    xn = pl.rms_norm(x, w["toy.0.n1.weight"], eps)
+    x = x + pl.gated_mlp(xn, w["toy.0.mlp.gate_proj.weight"], w["toy.0.mlp.up_proj.weight"], w["toy.0.mlp.down_proj.weight"])
+    # layer 1: attention with rotation, routed experts
+    xn = pl.rms_norm(x, w["toy.1.n0.weight"], eps)
+    inv = pl.rope_inv_freq(16, 100.0, None)
+    q = pl.apply_rope((xn @ w["toy.1.self_attn.q_proj.weight"].t()).reshape(t, 2, 16), pos, inv)
+    k = pl.apply_rope((xn @ w["toy.1.self_attn.k_proj.weight"].t()).reshape(t, 1, 16), pos, inv)
+    v = (xn @ w["toy.1.self_attn.v_proj.weight"].t()).reshape(t, 1, 16)
+    x = x + pl.attention(q, k, v, pos) @ w["toy.1.self_attn.o_proj.weight"].t()
+    xn = pl.rms_norm(x, w["toy.1.n1.weight"], eps)
+    logits = xn @ w["toy.1.moe.router.weight"].t()
+    top = torch.topk(logits, 2, dim=1).values
+    choice = logits.argmax(dim=1)
+    gate = torch.softmax(logits, dim=1).gather(1, choice[:, None])
+    y = torch.zeros_like(xn)
+    for i in range(t):
+        e = int(choice[i])
+        y[i] = torch.relu(xn[i] @ w[f"toy.1.moe.experts.{e}.w1"].t()) @ w[f"toy.1.moe.experts.{e}.w2"].t()
+    x = x + y * gate
+    return pl.rms_norm(x, w["toy.norm"], eps) @ w["toy.head"].t(), (top[:, 0] - top[:, 1])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
+    """A feed-forward that routes every token to one of three experts and a position encoding that is no
+    rotation, both defined in this file, in a model whose first layer keeps a window of 24 keys (its pages
+    are given back as the window passes them): whole, in portions and mixed, against plain formulas.
+    The routed layer is the last one, so a token whose two best router logits are too close to call in
+    bfloat16 changes its own logits only; such tokens are left out of the comparison."""
+    from safetensors import safe_open
+    from rllm_b200.engine.loading import write_random_model
+    register_routed()
+    cfg = {"architectures": ["ToyRoutedForCausalLM"], "eps": 1e-5, "torch_dtype": "float32"}
+    d = str(tmp_path / "routed")
+    write_random_model(d, cfg, seed=11)
+    w = {}
+    with safe_open(os.path.join(d, "model.safetensors"), framework="pt") as f:
+        for n in f.keys():
+            t = f.get_tensor(n)
+            w[n] = (t.to(torch.bfloat16) if dtype == "bfloat16" and t.dim() == 2 else t).double()
+    assert "toy.1.moe.experts.2.w2" in w and "toy.head" in w
+    rng = np.random.default_rng(9)
+    reqs = {f"r{i}": [int(t) for t in rng.integers(0, V, size=n)] for i, n in enumerate([90, 5, 130, 33, 64, 17])}
+    want, clear = {}, {}
+    for r, toks in reqs.items():
+        logits, margin = plain_routed(w, toks, 1e-5)
+        want[r] = logits.numpy()
+        clear[r] = (margin > (1e-6 if dtype == "float32" else 0.15)).numpy()
+    assert sum(int(c.sum()) for c in clear.values()) > 0.7 * sum(len(t) for t in reqs.values())
+    tol = 1e-4 if dtype == "float32" else 3e-2
+    for tb in (ru.trace_whole(reqs), ru.trace_portions(reqs, seed=3), ru.trace_mixed(reqs, seed=4, live=3, tail=6)):
+        got = ru.run_trace(d, dtype, tb, V, page_size=8)
+        for r, toks in reqs.items():
+            have = np.stack([got[(r, p)] for p in range(len(toks))])
+            err = np.abs(have - want[r]).max(axis=1) / np.abs(want[r]).max()
+            assert err[clear[r]].max() <= tol, (r, int(np.argmax(err * clear[r])), float(err[clear[r]].max()))
