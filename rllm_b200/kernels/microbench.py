@@ -50,6 +50,8 @@ def time_graph_us(fn, iters: int) -> float:
             for i in range(iters):
                 fn(i)
     torch.cuda.synchronize()
+    g.replay()                      # the first replay also uploads the graph
+    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     g.replay()
