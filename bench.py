@@ -153,7 +153,7 @@ def main():
     with open(os.path.join(model_dir, "config.json"), "w") as f:
         json.dump(cfg, f)
     max_batch = args.batch if args.no_points else max(args.batch, 64)
-    pages = max_batch * (-(-args.context // BLOCK_SIZE) + 1) + 64
+    pages = max_batch * (-(-args.context // BLOCK_SIZE) + 2) + -(-PREFILL_TOKENS // BLOCK_SIZE) + 64
     t0 = time.time()
     llm = LLM(model_dir, dtype="bf16", max_model_len=args.context, max_num_seqs=max_batch,
               max_num_batched_tokens=8192, long_prefill_token_threshold=8192, block_size=BLOCK_SIZE,
