@@ -20,7 +20,7 @@
 // The residual epilogue also prepares the RMSNorm that reads h next
 // (crates/rllm-model/src/layers.rs:133-140: y = h / sqrt(mean(h^2) + eps) * w,
 // float32), so that no norm kernel stands between this product and the one
-// after the norm (up to 8 rows): it stores scaled[m][n] = bfloat16(h[m][n] *
+// after the norm (up to 16 rows): it stores scaled[m][n] = bfloat16(h[m][n] *
 // w[n]) and, for every row, the sum of squares of the CTA's 16 new values of h.
 // The product that follows takes `scaled` as its operand and, told so (RSTD),
 // adds up a row's partial sums in a fixed order and multiplies row m of its
@@ -61,10 +61,11 @@ struct NormSide {
   bf16* scaled; int lds;                                // out: [M, N] = bfloat16(h * w_next)
 };
 
-// The parts of row m = tid % 8 that fall to this thread's slice tid / 8, added in order; the loads are
-// independent of one another.  Rows past M repeat the last row.
+// The parts of row m = tid % R (R = 8 MT rows) that fall to this thread's slice tid / R, added in order; the
+// loads are independent of one another.  Rows past M repeat the last row.
+template <int R>
 __device__ __forceinline__ float rows_sumsq_slice(const float* __restrict__ parts, int P, int M) {
-  const int m = min((int)(threadIdx.x & 7), M - 1), slice = threadIdx.x >> 3, nslices = blockDim.x >> 3;
+  const int m = min((int)(threadIdx.x % R), M - 1), slice = threadIdx.x / R, nslices = blockDim.x / R;
   float v[4] = {0.f, 0.f, 0.f, 0.f}, acc = 0.f;
   for (int p0 = slice; p0 < P; p0 += 4 * nslices) {
 #pragma unroll
@@ -90,8 +91,8 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
                     void* __restrict__ out, int ldo, int M, int N, int K, int up_offset, int tail_from,
                     NormSide ns) {
   extern __shared__ float red[];                 // [warps][16][8 MT]
-  __shared__ float s_rstd[8];
-  __shared__ float s_part[RSTD ? 64 : 1][8];
+  __shared__ float s_rstd[8 * MT];
+  __shared__ float s_part[RSTD ? 512 : 1];          // [slices][8 MT], one value a thread
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int gq = lane >> 2, t = lane & 3;
   const int rows_per_cta = (EPI == EPI_SILU) ? 8 : 16;
@@ -136,7 +137,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     if (!waited) {
       pdl_wait();
       waited = true;
-      if (RSTD) psum = rows_sumsq_slice(ns.parts, ns.P, M);
+      if (RSTD) psum = rows_sumsq_slice<8 * MT>(ns.parts, ns.P, M);
       if (EPI == EPI_RESID) h_old = resid_old(out, ldo, n0, M, N, MT);
       // no CTA of this grid is still to come once its last wave runs: the stream's next kernel may
       // come in and fetch its own weights while this one works
@@ -175,12 +176,12 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     mine[(gq + 8) * 8 * MT + i * 8 + 2 * t + 1] = c[i][3];
   }
   if (RSTD) {
-    if (!waited) psum = rows_sumsq_slice(ns.parts, ns.P, M);
-    s_part[threadIdx.x >> 3][threadIdx.x & 7] = psum;
+    if (!waited) psum = rows_sumsq_slice<8 * MT>(ns.parts, ns.P, M);
+    s_part[threadIdx.x] = psum;
     __syncthreads();
-    if (threadIdx.x < 8) {
+    if (threadIdx.x < 8 * MT) {
       float ss = 0.f;
-      for (int sl = 0; sl < (int)(blockDim.x >> 3); ++sl) ss += s_part[sl][threadIdx.x];
+      for (int sl = 0; sl < (int)(blockDim.x / (8 * MT)); ++sl) ss += s_part[sl * 8 * MT + threadIdx.x];
       s_rstd[threadIdx.x] = 1.0f / sqrtf(ss / (float)ns.width + ns.eps);     // eps inside the root
     }
   }
@@ -296,7 +297,7 @@ RLLM_EXPORT int rllm_gemm_small_m(const void* x, int ldx, const void* W, int ldw
 // How many partial sums a row gets from rllm_gemm_small_m_residual with N columns.
 RLLM_EXPORT int rllm_gemm_small_m_parts(int N) { return (N + 15) / 16; }
 
-// h[M, N] (float32, in place) += x[M, K] . W[N, K]^T for M <= 8 rows.  parts_out
+// h[M, N] (float32, in place) += x[M, K] . W[N, K]^T for M <= 16 rows.  parts_out
 // [rllm_gemm_small_m_parts(N), M] receives, part by part, the sums of squares of 16 new values of each
 // row; with w_next (weight [N] of the norm that reads h next, float32 or bfloat16), scaled [M, N] receives
 // bfloat16(h * w_next).
@@ -305,14 +306,15 @@ RLLM_EXPORT int rllm_gemm_small_m_residual(const void* x, int ldx, const void* W
                                            int lds, int M, int N, int K, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || ldx < K || ldw < K || ldh < N || !parts_out || (scaled && (!w_next || lds < N))) return RLLM_E_BADARG;
-  if (K % 8 || ldx % 8 || ldw % 8 || M > 8) return RLLM_E_UNSUPPORTED;
+  if (K % 8 || ldx % 8 || ldw % 8 || M > 16) return RLLM_E_UNSUPPORTED;
   if (((uintptr_t)x | (uintptr_t)W) & 15) return RLLM_E_BADARG;
   NormSide ns = {};
   ns.parts_out = parts_out; ns.w_next = w_next; ns.w_is_f32 = w_is_f32; ns.scaled = (bf16*)scaled; ns.lds = lds;
-  return launch_small_m<1, EPI_RESID, false>((const bf16*)x, ldx, (const bf16*)W, ldw, h, ldh, M, N, K, 0, ns, stream);
+  if (M <= 8) return launch_small_m<1, EPI_RESID, false>((const bf16*)x, ldx, (const bf16*)W, ldw, h, ldh, M, N, K, 0, ns, stream);
+  return launch_small_m<2, EPI_RESID, false>((const bf16*)x, ldx, (const bf16*)W, ldw, h, ldh, M, N, K, 0, ns, stream);
 }
 
-// out = (x . W^T) with row m scaled by 1 / sqrt(sum_p parts[p][m] / K + eps), for M <= 8 rows: x is the
+// out = (x . W^T) with row m scaled by 1 / sqrt(sum_p parts[p][m] / K + eps), for M <= 16 rows: x is the
 // `scaled` output of rllm_gemm_small_m_residual and parts [P, M] its partial sums, so that out is the
 // product of the RMS-normalised h with W.  epilogue 0 (bfloat16 out) or 2 (SiLU-gate), as above.
 RLLM_EXPORT int rllm_gemm_small_m_rstd(const void* x, int ldx, const float* parts, int P, float eps, const void* W,
@@ -320,13 +322,18 @@ RLLM_EXPORT int rllm_gemm_small_m_rstd(const void* x, int ldx, const float* part
                                        cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || ldx < K || ldw < K || ldo < N || P <= 0 || !parts || !(eps > 0.f)) return RLLM_E_BADARG;
-  if (K % 8 || ldx % 8 || ldw % 8 || M > 8) return RLLM_E_UNSUPPORTED;
+  if (K % 8 || ldx % 8 || ldw % 8 || M > 16) return RLLM_E_UNSUPPORTED;
   if (((uintptr_t)x | (uintptr_t)W) & 15) return RLLM_E_BADARG;
   NormSide ns = {};
   ns.parts = parts; ns.P = P; ns.eps = eps; ns.width = K;
   const bf16* xp = (const bf16*)x;
   const bf16* wp = (const bf16*)W;
-  if (epilogue == EPI_BF16) return launch_small_m<1, EPI_BF16, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, 0, ns, stream);
-  if (epilogue == EPI_SILU) return launch_small_m<1, EPI_SILU, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, N, ns, stream);
+  if (M <= 8) {
+    if (epilogue == EPI_BF16) return launch_small_m<1, EPI_BF16, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, 0, ns, stream);
+    if (epilogue == EPI_SILU) return launch_small_m<1, EPI_SILU, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, N, ns, stream);
+  } else {
+    if (epilogue == EPI_BF16) return launch_small_m<2, EPI_BF16, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, 0, ns, stream);
+    if (epilogue == EPI_SILU) return launch_small_m<2, EPI_SILU, true>(xp, ldx, wp, ldw, out, ldo, M, N, K, N, ns, stream);
+  }
   return RLLM_E_BADARG;
 }
