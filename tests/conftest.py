@@ -55,7 +55,16 @@ TINY_C = {
     "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "float32",
     "bos_token_id": 1, "eos_token_id": 2,
 }
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16)}   # name -> (config, weight seed, page size)
+# a head size that is a multiple of 16 but no power of two, as many kv heads as heads, partial rotation, one layer
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 1, "hidden_size": 144, "num_attention_heads": 3, "num_key_value_heads": 3,
+    "head_dim": 48, "intermediate_size": 120, "vocab_size": 203, "rope_theta": 20000.0,
+    "rope_scaling": None, "max_position_embeddings": 256, "rms_norm_eps": 2e-5,
+    "tie_word_embeddings": True, "hidden_act": "silu", "torch_dtype": "float32",
+    "bos_token_id": 1, "eos_token_id": 2,
+}
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16), "D": (TINY_D, 9, 4)}   # name -> (config, weight seed, page size)
 
 
 @pytest.fixture(scope="session")

@@ -19,12 +19,12 @@ pytestmark = pytest.mark.gpu
 TOL = {"float32": 1e-4, "bfloat16": 2e-2}
 
 LENGTHS = {"A": [5, 12, 17, 70, 100, 33, 64, 49], "B": [1, 31, 70, 150, 300, 97, 2, 210],
-           "C": [3, 130, 257, 400, 129, 64, 500, 33]}
+           "C": [3, 130, 257, 400, 129, 64, 500, 33], "D": [2, 40, 67, 150, 9, 101]}
 
 
 def make_requests(name: str):
     cfg, _, _ = TINY[name]
-    rng = np.random.default_rng({"A": 1, "B": 3, "C": 8}[name])
+    rng = np.random.default_rng({"A": 1, "B": 3, "C": 8, "D": 4}[name])
     return {f"r{i}": [int(t) for t in rng.integers(0, cfg["vocab_size"], size=n)]
             for i, n in enumerate(LENGTHS[name])}
 
@@ -131,6 +131,17 @@ def test_replay_with_head_size_64(model_dirs, dtype, mode):
     reqs = make_requests("C")
     got = ru.run_trace(model_dirs["C"], dtype, MODES[mode](reqs), cfg["vocab_size"], page_size=page)
     compare(got, plain_logits(model_dirs, "C", dtype), reqs, dtype, f"C/{dtype}/{mode}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", list(MODES))
+def test_replay_with_head_size_48(model_dirs, dtype, mode):
+    """tiny-D: heads of 48 (no tensor-core attention kernel takes them: the general kernel runs in both
+    dtypes), one kv head a head, pages of 4 keys, one layer, tied embeddings."""
+    cfg, _, page = TINY["D"]
+    reqs = make_requests("D")
+    got = ru.run_trace(model_dirs["D"], dtype, MODES[mode](reqs), cfg["vocab_size"], page_size=page)
+    compare(got, plain_logits(model_dirs, "D", dtype), reqs, dtype, f"D/{dtype}/{mode}")
 
 
 def test_attention_kernels_agree_through_replay(model_dirs, monkeypatch):
