@@ -66,11 +66,12 @@ struct NormSide {
 template <int R>
 __device__ __forceinline__ float rows_sumsq_slice(const float* __restrict__ parts, int P, int M) {
   const int m = min((int)(threadIdx.x % R), M - 1), slice = threadIdx.x / R, nslices = blockDim.x / R;
-  float v[4] = {0.f, 0.f, 0.f, 0.f}, acc = 0.f;
-  for (int p0 = slice; p0 < P; p0 += 4 * nslices) {
+  float v[8], acc = 0.f;
+  for (int p0 = slice; p0 < P; p0 += 8 * nslices) {          // eight loads in flight: one latency for up to 8 x nslices parts
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { const int pp = p0 + j * nslices; v[j] = pp < P ? parts[(size_t)pp * M + m] : 0.f; }
-    acc += v[0]; acc += v[1]; acc += v[2]; acc += v[3];
+    for (int j = 0; j < 8; ++j) { const int pp = p0 + j * nslices; v[j] = pp < P ? parts[(size_t)pp * M + m] : 0.f; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += v[j];
   }
   return acc;
 }
@@ -85,8 +86,11 @@ __device__ __forceinline__ float resid_old(const void* h, int ldh, int n0, int M
 
 // 104 registers a thread: a CTA of 512 threads then leaves room for one CTA of the decode attention kernel
 // on its SM (and two CTAs of 256 threads likewise), so that kernels that follow one another overlap
-template <int MT, int EPI, bool RSTD>
-__global__ void __launch_bounds__(512)
+// LIGHT: half as many loads in flight a thread and at most 73 registers, so that seven CTAs of four warps
+// fit on an SM: for grids that then run as one wave where the ordinary form needs two, the second of them
+// three quarters empty.
+template <int MT, int EPI, bool RSTD, bool LIGHT = false>
+__global__ void __launch_bounds__(LIGHT ? 128 : 512, LIGHT ? 7 : 1)
 gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict__ W, int ldw,
                     void* __restrict__ out, int ldo, int M, int N, int K, int up_offset, int tail_from,
                     NormSide ns) {
@@ -113,7 +117,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
   const int nblocks = (K + 31) / 32;
   // U blocks at a time: all their loads are issued before the first multiply, so that a
   // warp has U * (2 + MT) 16-byte loads in flight
-  constexpr int U = MT == 1 ? 8 : (MT == 2 ? 4 : 2);
+  constexpr int U = LIGHT ? 4 : (MT == 1 ? 8 : (MT == 2 ? 4 : 2));
   // a warp takes a contiguous range of k blocks, so that its loads walk along the rows of W
   const int per_warp = (nblocks + nwarps - 1) / nwarps;
   const int b_end = min(nblocks, (warp + 1) * per_warp);
@@ -134,11 +138,10 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
       if (in) { a[u] = ld_stream16(w_lo + k); v[u] = ld_stream16(w_hi + k); }
     }
     // ... then x, which the kernel before this one wrote
-    if (!waited) {
+    const bool first = !waited;
+    if (first) {
       pdl_wait();
       waited = true;
-      if (RSTD) psum = rows_sumsq_slice<8 * MT>(ns.parts, ns.P, M);
-      if (EPI == EPI_RESID) h_old = resid_old(out, ldo, n0, M, N, MT);
       // no CTA of this grid is still to come once its last wave runs: the stream's next kernel may
       // come in and fetch its own weights while this one works
       if ((int)blockIdx.x >= tail_from) pdl_launch();
@@ -152,6 +155,11 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
         xb[u][i] = make_uint4(0u, 0u, 0u, 0u);
         if (in) xb[u][i] = ld_cached16(xr[i] + k);
       }
+    }
+    // what else the kernel before this one wrote: behind the loads of x, so that all of it is on its way at once
+    if (first) {
+      if (RSTD) psum = rows_sumsq_slice<8 * MT>(ns.parts, ns.P, M);
+      if (EPI == EPI_RESID) h_old = resid_old(out, ldo, n0, M, N, MT);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u)
@@ -261,6 +269,20 @@ static int launch_small_m(const bf16* x, int ldx, const bf16* W, int ldw, void* 
   // the step takes 13 % longer than when that product starts at its end; so it lets nothing in early.
   const size_t weight_bytes = (size_t)(EPI == EPI_SILU ? 2 : 1) * N * K * sizeof(bf16);
   if (weight_bytes < ((size_t)12 << 20) && M > 2) tail_from = RLLM_NO_EARLY_LAUNCH;
+  if (MT == 1 && warps == 4 && tiles >= resident[warps]) {
+    static int light = 0;
+    if (!light) {
+      light = rllm_resident_ctas(gemm_small_m_kernel<1, EPI, RSTD, true>, 128, smem) + 1;
+      const char* env = getenv("RLLM_SMALL_M_LIGHT");
+      if (env && env[0] == '0') light = 1;
+    }
+    if (tiles < light) {      // one wave: every CTA is there from the start
+      if (tail_from != RLLM_NO_EARLY_LAUNCH) tail_from = 0;
+      cudaError_t e = rllm_launch_pdl(gemm_small_m_kernel<1, EPI, RSTD, true>, dim3(tiles), dim3(128), smem, stream,
+                                      x, ldx, W, ldw, out, ldo, M, N, K, up_offset, tail_from, ns);
+      return (int)e;
+    }
+  }
   cudaError_t e = rllm_launch_pdl(gemm_small_m_kernel<MT, EPI, RSTD>, dim3(tiles), dim3(32 * warps), smem, stream,
                                   x, ldx, W, ldw, out, ldo, M, N, K, up_offset, tail_from, ns);
   if (e != cudaSuccess) return (int)e;
