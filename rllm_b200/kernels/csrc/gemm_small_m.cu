@@ -124,6 +124,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
   bool waited = false;
   // RSTD: thread (slice, m) = (tid / 8, tid % 8) adds the parts slice, slice + nslices, ... of row m
   float psum = 0.f;
+  bool summed = false;
   // EPI_RESID: the old value of the element of h that this thread will update (threads 0 .. 16 * 8 MT - 1)
   float h_old = 0.f;
   for (int b0 = warp * per_warp; b0 < b_end; b0 += U) {
@@ -156,10 +157,13 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
         if (in) xb[u][i] = ld_cached16(xr[i] + k);
       }
     }
-    // what else the kernel before this one wrote: behind the loads of x, so that all of it is on its way at once
-    if (first) {
-      if (RSTD) psum = rows_sumsq_slice<8 * MT>(ns.parts, ns.P, M);
-      if (EPI == EPI_RESID) h_old = resid_old(out, ldo, n0, M, N, MT);
+    // What else the kernel before this one wrote: behind the loads of x.  The norm's partial sums wait for the
+    // warp's second round of loads where it has one: they are then fetched and added while weights are on
+    // their way, and the first multiplies do not wait for them.
+    if (first && EPI == EPI_RESID) h_old = resid_old(out, ldo, n0, M, N, MT);
+    if (RSTD && !summed && (!first || b0 + U >= b_end)) {
+      psum = rows_sumsq_slice<8 * MT>(ns.parts, ns.P, M);
+      summed = true;
     }
 #pragma unroll
     for (int u = 0; u < U; ++u)
@@ -184,7 +188,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     mine[(gq + 8) * 8 * MT + i * 8 + 2 * t + 1] = c[i][3];
   }
   if (RSTD) {
-    if (!waited) psum = rows_sumsq_slice<8 * MT>(ns.parts, ns.P, M);
+    if (!summed) psum = rows_sumsq_slice<8 * MT>(ns.parts, ns.P, M);
     s_part[threadIdx.x] = psum;
     __syncthreads();
     if (threadIdx.x < 8 * MT) {
