@@ -120,6 +120,8 @@ def gemm_small_m(args) -> None:
     M = args.rows
     for name, N, K in _shapes(args):
         silu = name == "gate_up"
+        if args.only and name != args.only:
+            continue
         if args.variant == "residual" and name not in ("o_proj", "down"):
             continue
         if args.variant == "rstd" and name not in ("qkv", "gate_up"):
@@ -147,6 +149,8 @@ def gemm_small_m(args) -> None:
 def gemm_tcgen05(args) -> None:
     M = args.rows
     for name, N, K in _shapes(args):
+        if args.only and name != args.only:
+            continue
         w = (torch.randn(N, K, device=DEV) * 0.02).bfloat16()
         x = torch.randn(M, K, device=DEV).bfloat16()
         silu = name == "gate_up"
@@ -176,6 +180,8 @@ def main(argv=None) -> int:
     p.add_argument("--page", type=int, default=16)
     p.add_argument("--variant", choices=["plain", "residual", "rstd"], default="plain",
                    help="gemm_small_m: which epilogue / operand form")
+    p.add_argument("--only", choices=["qkv", "o_proj", "gate_up", "down"], default=None,
+                   help="gemm_small_m, gemm_tcgen05: this projection alone")
     p.add_argument("--impl", choices=["mma", "tcgen05"], default="mma",
                    help="attention_prefill: the mma.sync kernel or the tcgen05 kernel")
     args = p.parse_args(argv)
