@@ -83,6 +83,8 @@ def plan_cache_pages(model: DecoderModel, args: EngineArgs, max_model_len: int, 
 
 
 class EngineCore:
+    ERROR_POLL_STEPS = 8           # the kernels' error words are looked at every this many steps
+
     def __init__(self, model: DecoderModel, args: Optional[EngineArgs] = None):
         self.args = args or EngineArgs()
         self.args.validate()
@@ -185,8 +187,10 @@ class EngineCore:
         if nxt is not None and self._launch_ahead(nxt, sampled_reqs, sampled):
             nxt = None
         tokens = self._tokens_of(pending)
-        # the kernels' error words are read without waiting for the GPU; a bad index shows a step or two late
-        self.runner.poll_errors()
+        # the kernels' error words are read without waiting for the GPU, every few steps (two small copies in
+        # the stream each time): a bad index shows a few steps late, and at the latest when generation ends
+        if self.num_steps % self.ERROR_POLL_STEPS == 0:
+            self.runner.poll_errors()
         outputs = []
         any_finished = False
         for req, tok, alive in zip(sampled_reqs, tokens, live):
