@@ -95,7 +95,7 @@ class DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.uses = 0
         self.live = S                  # rows that are requests; the rest pads the batch
-        # what the pinned buffer holds per row: (request, number of table entries written), so that an
+        # what the pinned buffer holds per row: (group, admission, number of table entries written), so that an
         # unchanged block table is not written again
         self.row_state: List[Optional[tuple]] = [None] * S
 
@@ -140,11 +140,14 @@ class DecodeGraph:
             h[self.r_slots[0] + s] = cache.slot(e.req)
         windowed = any(cache.needs[g].window is not None for g in self.paged)
         reqs = [e.req for e in entries]
+        # a request is known by the number of its admission, not by its name: a name may come back (after
+        # its request ended, or was preempted and admitted again) with other pages
+        adm = [cache.requests[r] for r in reqs]
         for g, r in zip(self.paged, self.r_tables):
             # rows whose request or table length changed since they were last written (tables only grow,
             # unless a window gives pages back); the C++ side copies them into the pinned buffer
             stale = [s for s, e in enumerate(entries)
-                     if windowed or self.row_state[s] != (g, e.req, cache.table_len(e.req, g))]
+                     if windowed or self.row_state[s] != (g, adm[s], cache.table_len(e.req, g))]
             if len(stale) == len(entries):
                 cache.pack_tables(reqs, g, h[r[0]:r[1]].reshape(S, W))
             else:
@@ -153,7 +156,7 @@ class DecodeGraph:
                     cache.pack_tables([reqs[s]], g, tab[s:s + 1])
             if len(self.paged) == 1:
                 for s in stale:
-                    self.row_state[s] = (g, reqs[s], cache.table_len(reqs[s], g))
+                    self.row_state[s] = (g, adm[s], cache.table_len(reqs[s], g))
             else:
                 for s in stale:
                     self.row_state[s] = None      # several groups: rows are written every time

@@ -232,3 +232,38 @@ def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
     for k in reqs:
         err = np.abs(batch[(k, 0)] - want[k][0]).max() / np.abs(want[k]).max()
         assert err <= TOL[dtype], (k, err)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_request_id_used_again_after_its_end(model_dirs, dtype):
+    """Request "a" decodes and ends; "b" takes the pages it gave back and stays alive; a new request, again
+    called "a", of the same length but with other tokens, decodes alone in its steps.  Its decode steps
+    have the shape of the first a's (one request, the same number of pages), on other pages: nothing of
+    the first a's block table may be taken for the second's."""
+    cfg, _, page = TINY["A"]
+    rng = np.random.default_rng(21)
+    V = cfg["vocab_size"]
+    first = [int(t) for t in rng.integers(0, V, size=40)]
+    other = [int(t) for t in rng.integers(0, V, size=50)]
+    second = [int(t) for t in rng.integers(0, V, size=40)]
+    tb = ru.TraceBuilder()
+    tb.step([("a", first[:34])])
+    for i in range(34, 40):
+        tb.step([("a", first[i:i + 1])], end=["a"] if i == 39 else [])
+    tb.step([("b", other)])                      # gets the pages that a gave back
+    n_first = len(tb.steps)
+    tb.step([("a", second[:34])])
+    for i in range(34, 40):
+        tb.step([("a", second[i:i + 1])])
+    tb.step([("b", [7])], end=["a", "b"])
+    # the second life of "a" under a name of its own
+    for i in range(n_first, len(tb.rows) - 1):
+        tb.rows[i] = [("a2", pos) for _, pos in tb.rows[i]]
+    got = ru.run_trace(model_dirs["A"], dtype, tb, V, page_size=page, max_tokens=192)
+    model = plain_llama.read_model_dir(model_dirs["A"], round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+    want = {"a": model.logits(first).numpy(), "a2": model.logits(second).numpy(), "b": model.logits(other + [7]).numpy()}
+    tol = 1e-4 if dtype == "float32" else 3e-2
+    for (rid, pos), row in got.items():
+        ref = want[rid][pos]
+        err = float(np.abs(row - ref).max() / np.abs(ref).max())
+        assert err <= tol, (rid, pos, err)
