@@ -181,6 +181,7 @@ def main():
             for _ in range(warm):
                 llm.step()
             torch.cuda.synchronize()
+            h2d0 = sum(g.h2d_bytes for g in runner.graphs.values())
             a = time.time()
             t_a = time.perf_counter()
             n_tok = 0
@@ -189,9 +190,12 @@ def main():
             torch.cuda.synchronize()
             dt = time.perf_counter() - t_a
             windows.append((a, time.time()))
-            g = next(iter(runner.graphs.values()))
-            e2e = {"value": n_tok / dt, "unit": "tok/s", "h2d_bytes_per_step": int(g.static.numel() * 4),
-                   "d2h_bytes_per_step": int(batch * 4 + 4), "ms_per_step": 1e3 * dt / steps}
+            # host -> device: the step's positions, lengths and block tables from pinned memory, on the steps
+            # where a block table changed (the token ids of a decode step are the step before's samples and
+            # stay on the device); device -> host: the sampled tokens, every step, and the error words
+            h2d = sum(g.h2d_bytes for g in runner.graphs.values()) - h2d0
+            e2e = {"value": n_tok / dt, "unit": "tok/s", "h2d_bytes_per_step": int(h2d / steps),
+                   "d2h_bytes_per_step": int(batch * 4 + 1), "ms_per_step": 1e3 * dt / steps}
         # the device-timed run goes on from where the requests are
         entries = []
         for i in ids:

@@ -98,6 +98,12 @@ class DecodeGraph:
         # what the pinned buffer holds per row: (group, admission, number of table entries written), so that an
         # unchanged block table is not written again
         self.row_state: List[Optional[tuple]] = [None] * S
+        # (admission, position) of the live rows as the device buffer holds them (None: not known), as the
+        # pinned buffer holds them, and whether the two differ in anything the graph reads
+        self.h2d_bytes = 0             # bytes copied from the pinned buffer to the device so far
+        self.device_rows: Optional[List[tuple]] = None
+        self.filled_rows: List[tuple] = []
+        self.dirty = True
 
     def fill(self, entries) -> None:
         """Pack the step's inputs into the pinned buffer and copy them over."""
@@ -107,11 +113,32 @@ class DecodeGraph:
     def patch_tokens(self, tokens: Sequence[int]) -> None:
         """Set the input token of every request's row in the pinned buffer (after fill_host, before commit)."""
         self.host[self.r_tokens[0]:self.r_tokens[0] + len(tokens)] = tokens
+        self.dirty = True
 
-    def commit(self) -> None:
-        """Copy the pinned buffer to the device buffer the graph reads."""
+    def commit(self) -> bool:
+        """Copy the pinned buffer to the device buffer the graph reads, unless that buffer already holds
+        this step's inputs (``advance`` moved it there from the step before and no block table has
+        changed).  Returns whether it copied: then the tokens on the device are those of the pinned buffer."""
+        if not self.dirty:
+            return False
         self.static.copy_(self.stage, non_blocking=True)
         self.copied.record()
+        self.h2d_bytes += self.static.numel() * 4
+        self.device_rows = list(self.filled_rows)
+        self.dirty = False
+        return True
+
+    def advance(self, sampled: torch.Tensor, host_row: Optional[torch.Tensor]) -> None:
+        """After the step's tokens were sampled: one kernel makes them the next step's input on the device
+        (positions and lengths grow by one) and writes them to ``host_row`` (pinned memory) for the host.
+        If the next step is these requests again and no block table changes, it needs no copy at all."""
+        from ..kernels import ops
+        n = sampled.numel()
+        ops.decode_advance(self.token_ids, self.ctx.positions, self.ctx.seq_lens, sampled, host_row, n)
+        if self.device_rows is not None and n == len(self.device_rows):
+            self.device_rows = [(a, st + 1) for a, st in self.device_rows]
+        else:
+            self.device_rows = None
 
     def fill_host(self, entries) -> None:
         """Pack the step's inputs into the pinned buffer.  May run while the graph of the step before is
@@ -120,10 +147,12 @@ class DecodeGraph:
         self.copied.synchronize()
         h = self.host
         self.live = len(entries)
+        wrote = False                  # a block table or a padding row changed
         for s in range(len(entries), S):
             # a padding row: one token at position 0 of the spare page
             if self.row_state[s] == "pad":
                 continue
+            wrote = True
             self.row_state[s] = "pad"
             h[self.r_tokens[0] + s] = 0
             h[self.r_pos[0] + s] = 0
@@ -148,6 +177,7 @@ class DecodeGraph:
             # unless a window gives pages back); the C++ side copies them into the pinned buffer
             stale = [s for s, e in enumerate(entries)
                      if windowed or self.row_state[s] != (g, adm[s], cache.table_len(e.req, g))]
+            wrote = wrote or bool(stale)
             if len(stale) == len(entries):
                 cache.pack_tables(reqs, g, h[r[0]:r[1]].reshape(S, W))
             else:
@@ -160,6 +190,8 @@ class DecodeGraph:
             else:
                 for s in stale:
                     self.row_state[s] = None      # several groups: rows are written every time
+        self.filled_rows = [(adm[s], e.start) for s, e in enumerate(entries)]
+        self.dirty = wrote or self.filled_rows != self.device_rows
 
     def run(self) -> torch.Tensor:
         """Logits float32 [live rows, vocab]; valid until the next run of this graph."""

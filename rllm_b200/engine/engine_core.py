@@ -156,7 +156,7 @@ class EngineCore:
             self.last_schedule = sched
             self.num_steps += 1
             sampled = self._sample(self.runner.run_prepared(graph), sampled_reqs, plain_greedy, 0)
-            pending = self._read_back(sampled)
+            pending = self._read_back(sampled, graph)
         else:
             sched = self.scheduler.schedule()
             self.last_schedule = sched
@@ -212,10 +212,11 @@ class EngineCore:
             self._prepared = nxt
         return outputs
 
-    def _read_back(self, sampled):
+    def _read_back(self, sampled, graph=None):
         """Start the copy of a step's sampled tokens to pinned host memory, right behind the sampling
         kernel in the stream; returns what ``_tokens_of`` waits for.  A plain ``tolist`` would wait for
-        everything queued since, a step launched ahead included."""
+        everything queued since, a step launched ahead included.  With the decode graph that ran the
+        step, one kernel writes the tokens to the host and makes them the graph's next input."""
         if sampled is None:
             return None
         n = sampled.numel()
@@ -225,7 +226,10 @@ class EngineCore:
             slot = (torch.empty(max(n, self.args.max_num_seqs), dtype=torch.int32, pin_memory=True), torch.cuda.Event())
             self._readback[self._readback_next ^ 1] = slot
         with torch.cuda.device(self.device):
-            slot[0][:n].copy_(sampled, non_blocking=True)
+            if graph is not None:
+                graph.advance(sampled, slot[0])
+            else:
+                slot[0][:n].copy_(sampled, non_blocking=True)
             slot[1].record()
         return slot[0], slot[1], n
 
@@ -262,11 +266,11 @@ class EngineCore:
         self.num_steps += 1
         self.num_steps_ahead += 1
         with torch.cuda.device(self.device), torch.no_grad():
-            graph.commit()
-            graph.token_ids[: sampled.numel()].copy_(sampled, non_blocking=True)
+            if graph.commit():
+                graph.token_ids[: sampled.numel()].copy_(sampled, non_blocking=True)
             logits = graph.run()
         ahead = self._sample(logits, nreqs, plain_greedy, 1)
-        self._inflight = (nsched, nreqs, plain_greedy, ahead, self._read_back(ahead))
+        self._inflight = (nsched, nreqs, plain_greedy, ahead, self._read_back(ahead, graph))
         return True
 
     def _prepare_next(self, sched: SchedulerOutput, sampled_reqs, plain_greedy):

@@ -259,6 +259,7 @@ class ModelRunner:
                 ops.decode_advance(g.token_ids, g.ctx.positions, g.ctx.seq_lens, sampled, history[i])
             if timing is not None:
                 timing[2].record()
+            g.device_rows = None           # the rows moved on without the graph's own bookkeeping
             return history
 
     def poll_errors(self) -> None:

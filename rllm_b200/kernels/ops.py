@@ -530,8 +530,19 @@ def use_tcgen05_attention(dtype: torch.dtype, nq: int, nkv: int, d: int, page_si
 
 
 def decode_advance(token_ids: torch.Tensor, positions: torch.Tensor, seq_lens: torch.Tensor,
-                   sampled: torch.Tensor, history_row: Optional[torch.Tensor]) -> None:
-    """token_ids = sampled; positions += 1; seq_lens += 1; history_row = sampled."""
+                   sampled: torch.Tensor, history_row: Optional[torch.Tensor], count: Optional[int] = None) -> None:
+    """For the first ``count`` rows (all by default): token_ids = sampled; positions += 1; seq_lens += 1;
+    history_row = sampled.  ``history_row`` may be pinned host memory: the kernel then writes the tokens
+    where the host reads them, and no copy stands in the stream."""
     lib = build.load_library("elementwise")
+    n = token_ids.numel() if count is None else int(count)
+    assert n <= token_ids.numel() and n <= sampled.numel() and (history_row is None or n <= history_row.numel())
+    if history_row is not None and not history_row.is_cuda:
+        # page-locked host memory has the same address on the device
+        if not history_row.is_pinned() or history_row.dtype is not torch.int32:
+            raise KernelError("decode_advance: a host row must be pinned int32 memory")
+        row = c_void_p(history_row.data_ptr())
+    else:
+        row = _ptr(history_row)
     _check(lib.rllm_decode_advance(_ptr(token_ids), _ptr(positions), _ptr(seq_lens), _ptr(sampled),
-                                   _ptr(history_row), c_int(token_ids.numel()), _stream()), "decode_advance")
+                                   row, c_int(n), _stream()), "decode_advance")
