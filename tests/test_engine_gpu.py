@@ -240,3 +240,59 @@ def test_command_line(model_dirs, capsys):
     plain = pl.read_model_dir(model_dirs["A"])
     assert [l["token_ids"] for l in lines] == [plain.greedy([5, 6, 7], 4), plain.greedy([9, 10], 4)]
     assert lines[0]["finish_reason"] == "length" and lines[0]["usage"]["total_tokens"] == 7
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_serving_keeps_every_request_right(model_dirs, seed):
+    """Requests of random lengths, some with a common beginning, arrive while others run; there are few
+    pages (requests get preempted), few sequences at a time, a small token budget, prefix sharing, an
+    abort, and request names that come back after their request has ended.  Every request that ends has
+    the tokens that the plain implementation generates for its prompt alone."""
+    from rllm_b200 import SamplingParams
+    name = "A"
+    cfg, _, page = TINY[name]
+    rng = np.random.default_rng(100 + seed)
+    V = cfg["vocab_size"]
+    plain = pl.read_model_dir(model_dirs[name])
+    llm = make_llm(model_dirs, name, num_gpu_blocks=10, max_num_seqs=4, max_num_batched_tokens=40,
+                   long_prefill_token_threshold=24, enable_prefix_caching=True)
+    bases = [[int(t) for t in rng.integers(8, V, size=48)] for _ in range(2)]
+    todo = []
+    for i in range(22):
+        n = int(rng.integers(1, 70))
+        if rng.random() < 0.4:
+            b = bases[int(rng.integers(0, 2))]
+            k = int(rng.integers(16, 49))
+            prompt = b[:k] + [int(t) for t in rng.integers(8, V, size=max(1, n - k))]
+        else:
+            prompt = [int(t) for t in rng.integers(8, V, size=n)]
+        steps = int(rng.integers(1, 20))
+        prompt = prompt[: 100 - steps]
+        todo.append((f"q{i % 9}", prompt, steps))         # names come back
+    live, done, aborted = {}, [], 0
+    guard = 0
+    while todo or live:
+        guard += 1
+        assert guard < 5000
+        # admit: a name only when its earlier request has ended
+        while todo and todo[0][0] not in live and len(live) < 7 and rng.random() < 0.7:
+            rid, prompt, steps = todo.pop(0)
+            llm.add_request(prompt, SamplingParams(temperature=0.0, max_tokens=steps, ignore_eos=True), request_id=rid)
+            live[rid] = (prompt, steps, [])
+        if live and aborted == 0 and guard == 25:
+            rid = sorted(live)[0]
+            assert llm.abort_request(rid)
+            del live[rid]
+            aborted = 1
+        for out in llm.step():
+            prompt, steps, toks = live[out.request_id]
+            toks += out.outputs[0].token_ids
+            if out.finished:
+                done.append((prompt, steps, toks))
+                del live[out.request_id]
+    assert len(done) >= 20
+    for prompt, steps, toks in done:
+        assert toks == plain.greedy(prompt, steps), (len(prompt), steps)
+    llm.engine.cache.check()
+    assert llm.engine.cache.usage()["num_requests"] == 0
+    print("preemptions", llm.engine.scheduler.num_preemptions, "prefix hits", llm.engine.scheduler.prefix_hit_tokens)
