@@ -306,3 +306,103 @@ def test_routed_feed_forward_and_another_position_encoding(tmp_path, dtype):
             have = np.stack([got[(r, p)] for p in range(len(toks))])
             err = np.abs(have - want[r]).max(axis=1) / np.abs(want[r]).max()
             assert err[clear[r]].max() <= tol, (r, int(np.argmax(err * clear[r])), float(err[clear[r]].max()))
+
+
+# ---------------------------------------------------------------------------
+# The engine's own parts in another arrangement: a layer that sees a window of 20 keys, a layer that sees all
+# ---------------------------------------------------------------------------
+def register_windowed():
+    from rllm_b200.config import register_architecture
+    from rllm_b200.parts import LayerSpec, ModelSpec, PartSpec, Run
+
+    def build(cfg):
+        norms = lambda: (PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="n0.weight"),
+                         PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="n1.weight"))
+        rot = PartSpec.of("rotary", head_dim=16, rotary_dim=16, theta=1000.0, scaling=None)
+        att = lambda window, nkv: PartSpec.of("attention", hidden_size=H, num_heads=2, num_kv_heads=nkv, head_dim=16,
+                                              window=window, scale=None, position=rot)
+        mlp = lambda: PartSpec.of("gated_mlp", hidden_size=H, intermediate_size=56)
+        layers = (LayerSpec("pre_norm", att(20, 2), mlp(), norms(), "toy.0."),
+                  LayerSpec("pre_norm", att(None, 1), mlp(), norms(), "toy.1."))
+        return ModelSpec(hidden_size=H, vocab_size=V,
+                         embedding=PartSpec.of("token_embedding", vocab_size=V, hidden_size=H, name="toy.embed"),
+                         layers=layers, order=(Run(0, 0), Run(1, 1)),
+                         final_norm=PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="toy.norm"),
+                         head=PartSpec.of("lm_head", vocab_size=V, hidden_size=H, name="toy.head", tied_to=None),
+                         max_positions=512)
+
+    register_architecture("ToyWindowedForCausalLM", lambda raw: dict(raw), build)
+
+
+def plain_windowed(w, tokens, eps):
+    x = pl.embedding(w["toy.embed"], tokens)
+    t = len(tokens)
+    pos = torch.arange(t)
+    inv = pl.rope_inv_freq(16, 1000.0, None)
+    for layer, (window, nkv) in enumerate([(20, 2), (None, 1)]):
+        p = f"toy.{layer}."
+        xn = pl.rms_norm(x, w[p + "n0.weight"], eps)
+        q = pl.apply_rope((xn @ w[p + "self_attn.q_proj.weight"].t()).reshape(t, 2, 16), pos, inv)
+        k = pl.apply_rope((xn @ w[p + "self_attn.k_proj.weight"].t()).reshape(t, nkv, 16), pos, inv)
+        v = (xn @ w[p + "self_attn.v_proj.weight"].t()).reshape(t, nkv, 16)
+        x = x + pl.attention(q, k, v, pos, window=window) @ w[p + "self_attn.o_proj.weight"].t()
+        xn = pl.rms_norm(x, w[p + "n1.weight"], eps)
+        x = x + pl.gated_mlp(xn, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return pl.rms_norm(x, w["toy.norm"], eps) @ w["toy.head"].t()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_windowed_layer_beside_a_full_one(tmp_path, dtype):
+    """Two groups of pages with different needs: the windowed layer's pages are given back as the window
+    passes them and are used again, the other layer keeps all.  Every part is the engine's own, so decode
+    steps run as CUDA graphs, over a long decode, in portions and mixed with other requests."""
+    from safetensors import safe_open
+    from rllm_b200.engine.loading import write_random_model
+    register_windowed()
+    cfg = {"architectures": ["ToyWindowedForCausalLM"], "eps": 1e-5, "torch_dtype": "float32"}
+    d = str(tmp_path / "windowed")
+    write_random_model(d, cfg, seed=5)
+    w = {}
+    with safe_open(os.path.join(d, "model.safetensors"), framework="pt") as f:
+        for n in f.keys():
+            t = f.get_tensor(n)
+            w[n] = (t.to(torch.bfloat16) if dtype == "bfloat16" and t.dim() == 2 else t).double()
+    rng = np.random.default_rng(13)
+    reqs = {f"r{i}": [int(t) for t in rng.integers(0, V, size=n)] for i, n in enumerate([120, 7, 64, 33, 150, 21])}
+    want = {r: plain_windowed(w, toks, 1e-5).numpy() for r, toks in reqs.items()}
+    tol = 1e-4 if dtype == "float32" else 3e-2
+    traces = (ru.trace_whole(reqs), ru.trace_tail_decode(reqs, 60), ru.trace_portions(reqs, seed=6),
+              ru.trace_mixed(reqs, seed=8, live=3, tail=40))
+    for tb in traces:
+        got = ru.run_trace(d, dtype, tb, V, page_size=4)
+        for r, toks in reqs.items():
+            have = np.stack([got[(r, p)] for p in range(len(toks))])
+            err = np.abs(have - want[r]).max(axis=1) / np.abs(want[r]).max()
+            assert err.max() <= tol, (r, int(np.argmax(err)), float(err.max()))
+
+
+def test_generation_with_a_windowed_layer(tmp_path):
+    """The same arrangement through the scheduler and the entry point: pages of the windowed layer go back
+    to the pool while requests decode, several requests at a time, and the tokens are the plain ones."""
+    from safetensors import safe_open
+    from rllm_b200 import LLM, SamplingParams
+    from rllm_b200.engine.loading import write_random_model
+    register_windowed()
+    cfg = {"architectures": ["ToyWindowedForCausalLM"], "eps": 1e-5, "torch_dtype": "float32"}
+    d = str(tmp_path / "windowed_gen")
+    write_random_model(d, cfg, seed=6)
+    with safe_open(os.path.join(d, "model.safetensors"), framework="pt") as f:
+        w = {n: f.get_tensor(n).double() for n in f.keys()}
+    rng = np.random.default_rng(2)
+    prompts = [[int(t) for t in rng.integers(0, V, size=n)] for n in (30, 3, 45)]
+    steps = 40
+    llm = LLM(d, dtype="fp32", block_size=4, num_gpu_blocks=80, max_num_seqs=3, max_num_batched_tokens=32,
+              long_prefill_token_threshold=16)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=steps, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        toks = list(p)
+        for _ in range(steps):
+            toks.append(int(torch.argmax(plain_windowed(w, toks, 1e-5)[-1])))
+        assert o.outputs[0].token_ids == toks[len(p):]
+    llm.engine.cache.check()
+    assert llm.engine.cache.usage()["num_requests"] == 0
