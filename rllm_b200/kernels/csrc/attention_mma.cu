@@ -547,22 +547,44 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
   }
   cp_async_wait<0>();
   pdl_launch();                  // the stream's next kernel may start coming in now
-  // this chunk's partial: rows < g, straight from the accumulators
-  if (active) {
+  // The warps' partial results meet in shared memory (each warp's own stages are free by now) and leave the
+  // CTA as one: rows < g, the running max, the sum and the unnormalised output, combined in warp order.
+  {
+    float* part = (float*)mine;                          // [g][D + 4]: output, max, sum, two unused (rows stay 16-byte aligned)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int r = (lane >> 2) + h * 8;
       if (r >= g) continue;
-      const size_t slot = ((size_t)s * nq + kvh * g + r) * max_chunks + chunk;
-      float* dst = ws_o + slot * D + (lane & 3) * 2;
+      float* dst = part + r * (D + 4) + (lane & 3) * 2;
 #pragma unroll
       for (int nt = 0; nt < D / 8; ++nt) *(float2*)(dst + nt * 8) = make_float2(o[nt][h * 2], o[nt][h * 2 + 1]);
-      if ((lane & 3) == 0) *(float2*)(ws_ml + slot * 2) = make_float2(m[h], l[h]);
+      if ((lane & 3) == 0) { part[r * (D + 4) + D] = m[h]; part[r * (D + 4) + D + 1] = l[h]; }
     }
   }
-  // the last CTA of this (sequence, kv head) merges all chunks, in order
+  __syncthreads();
+  for (int item = threadIdx.x; item < g * (D / 4); item += blockDim.x) {
+    const int r = item / (D / 4), q4 = item - r * (D / 4);
+    float mm = -INFINITY;
+    for (int w = 0; w < nwarps; ++w)
+      mm = fmaxf(mm, ((const float*)(smem_raw + (size_t)w * dec_warp_smem<D, STAGES>()))[r * (D + 4) + D]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float ll = 0.f;
+    for (int w = 0; w < nwarps; ++w) {
+      const float* pw = (const float*)(smem_raw + (size_t)w * dec_warp_smem<D, STAGES>()) + r * (D + 4);
+      const float mw = pw[D];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+      const float4 v = *(const float4*)(pw + q4 * 4);
+      acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
+      ll += pw[D + 1] * f;
+    }
+    const size_t slot = ((size_t)s * nq + kvh * g + r) * max_chunks + blockIdx.x;
+    *(float4*)(ws_o + slot * D + q4 * 4) = acc;
+    if (q4 == 0) *(float2*)(ws_ml + slot * 2) = make_float2(mm, ll);
+  }
+  // the last CTA of this (sequence, kv head) merges the CTAs' results, in order
   const int ch_lo = kmin / CHUNK, ch_hi = (len + CHUNK - 1) / CHUNK;
-  const int ncta = (ch_hi - 1) / nwarps - ch_lo / nwarps + 1;
+  const int cta_lo = ch_lo / nwarps, cta_hi = (ch_hi - 1) / nwarps + 1;
+  const int ncta = cta_hi - cta_lo;
   __shared__ int s_last;
   asm volatile("fence.acq_rel.gpu;" ::: "memory");
   __syncthreads();
@@ -575,40 +597,20 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
   if (!s_last) return;
   asm volatile("fence.acq_rel.gpu;" ::: "memory");
   const int tid = threadIdx.x, nthr = blockDim.x;
-  float* sRow = (float*)smem_raw;                       // [16] common max per row (warp 0's tiles are done with)
-  // the rows' common max: a warp takes a row, its lanes the chunks, four loads a lane in flight
-  for (int r = warp; r < g; r += nwarps) {
-    const size_t base = ((size_t)s * nq + kvh * g + r) * max_chunks;
-    float mm = -INFINITY;
-    for (int c0 = ch_lo; c0 < ch_hi; c0 += 128) {
-      float v[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int c = c0 + j * 32 + lane;
-        v[j] = c < ch_hi ? __ldcg(&ws_ml[(base + c) * 2]) : -INFINITY;
-      }
-      mm = fmaxf(fmaxf(mm, fmaxf(v[0], v[1])), fmaxf(v[2], v[3]));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
-    if (lane == 0) sRow[r] = mm;
-  }
-  __syncthreads();
-  // Four outputs of a row and one half of its chunks a thread (neighbouring lanes hold the two halves):
-  // the loads of 8 chunks are issued together (indices are clamped and the factor of a chunk past the
-  // end is 0, so that no load waits for a branch); a half is summed in chunk order, then first half +
-  // second half.  The order depends on the sequence's own length only.
-  const int nch = ch_hi - ch_lo, half_n = (nch + 1) >> 1;
+  // Four outputs of a row and one half of its partial results a thread (neighbouring lanes hold the two
+  // halves).  Eight results are fetched together (indices are clamped and the factor of one past the end is
+  // 0, so that no load waits for a branch) and added under a running max, which is raised batch by batch;
+  // then first half + second half.  The order depends on the sequence's own length only.
+  const int half_n = (ncta + 1) >> 1;
   const int items = g * (D / 4) * 2;
   for (int it0 = 0; it0 < items; it0 += nthr) {
     const int item = it0 + tid;
     const bool valid = item < items;
     const int h = item & 1, q4 = (item >> 1) % (D / 4), r = valid ? (item >> 1) / (D / 4) : 0;
-    const float mm = sRow[r];
     const size_t base = ((size_t)s * nq + kvh * g + r) * max_chunks;
-    const int c_begin = ch_lo + h * half_n, c_end = valid ? min(ch_hi, c_begin + half_n) : c_begin;
+    const int c_begin = cta_lo + h * half_n, c_end = valid ? min(cta_hi, c_begin + half_n) : c_begin;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float ll = 0.f;
+    float ll = 0.f, mm = -INFINITY;
     for (int c0 = c_begin; c0 < c_end; c0 += 8) {
       float4 v[8];
       float2 ml[8];
@@ -618,6 +620,14 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
         v[j] = __ldcg((const float4*)(ws_o + (base + c) * D + q4 * 4));
         ml[j] = __ldcg((const float2*)(ws_ml + (base + c) * 2));
       }
+      float bm = mm;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (c0 + j < c_end) bm = fmaxf(bm, ml[j].x);
+      if (bm == -INFINITY) continue;                       // nothing seen so far
+      const float keep = mm == -INFINITY ? 0.f : exp2f(mm - bm);
+      acc.x *= keep; acc.y *= keep; acc.z *= keep; acc.w *= keep;
+      ll *= keep;
+      mm = bm;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const float f = (c0 + j < c_end && ml[j].x != -INFINITY) ? exp2f(ml[j].x - mm) : 0.f;
@@ -630,12 +640,15 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
     oth.x = __shfl_xor_sync(0xffffffffu, acc.x, 1); oth.y = __shfl_xor_sync(0xffffffffu, acc.y, 1);
     oth.z = __shfl_xor_sync(0xffffffffu, acc.z, 1); oth.w = __shfl_xor_sync(0xffffffffu, acc.w, 1);
     const float llo = __shfl_xor_sync(0xffffffffu, ll, 1);
+    const float mmo = __shfl_xor_sync(0xffffffffu, mm, 1);
     if (valid && h == 0) {
-      const float lt = ll + llo;
+      const float top = fmaxf(mm, mmo);
+      const float fa = mm == -INFINITY ? 0.f : exp2f(mm - top), fb = mmo == -INFINITY ? 0.f : exp2f(mmo - top);
+      const float lt = ll * fa + llo * fb;
       const float inv = lt > 0.f ? 1.0f / lt : 0.f;
       bf16* o = out + ((size_t)s * nq + kvh * g + r) * D + q4 * 4;
-      __nv_bfloat162 lo = __floats2bfloat162_rn((acc.x + oth.x) * inv, (acc.y + oth.y) * inv);
-      __nv_bfloat162 hi = __floats2bfloat162_rn((acc.z + oth.z) * inv, (acc.w + oth.w) * inv);
+      __nv_bfloat162 lo = __floats2bfloat162_rn((acc.x * fa + oth.x * fb) * inv, (acc.y * fa + oth.y * fb) * inv);
+      __nv_bfloat162 hi = __floats2bfloat162_rn((acc.z * fa + oth.z * fb) * inv, (acc.w * fa + oth.w * fb) * inv);
       uint2 w;
       w.x = *(unsigned*)&lo; w.y = *(unsigned*)&hi;
       *(uint2*)o = w;
