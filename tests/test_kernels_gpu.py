@@ -353,6 +353,42 @@ def test_attention_decode_mma(ops, err, nq, nkv, d, page, window):
     assert torch.equal(alone[0], outs[0][4])
 
 
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(8, 2, 64, 16, 0), (8, 2, 64, 16, 5000), (4, 1, 128, 32, 0), (6, 3, 32, 8, 0)])
+def test_attention_decode_long_sequences(ops, err, nq, nkv, d, page, window):
+    """Tens of CTAs a (sequence, kv head): their results are merged in several rounds of eight and two
+    halves; beside them short sequences whose CTAs mostly have nothing to do."""
+    dt = torch.bfloat16
+    lens = [9300, 17, 4097, 20000, 512]
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, lens, [1] * len(lens),
+                                                                 pages=sum(-(-n // page) for n in lens) + 3, seed=6)
+    q = torch.cat(qs).reshape(-1, nq * d).to(DEV)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    out = torch.zeros_like(q)
+    ops.attention_decode_bf16(q, nq * d, out, kc.to(DEV), vc.to(DEV), table.to(DEV), seq_lens, len(lens), 20480,
+                              nq, nkv, d, window, scale, err)
+    assert int(err.item()) == 0
+    for s, n in enumerate(lens):
+        want = pl.attention(qs[s].double(), ks[s].double(), vs[s].double(), torch.tensor([n - 1]),
+                            window=window or None, scale=scale)
+        assert rel_err(out[s:s + 1], want) <= tol(dt), (s, n)
+    # one key far back made to dominate, in a late round of the merge
+    if window == 0:
+        target = 13000
+        kc2, qq = kc.clone(), qs[3].clone()
+        pg = int(table[3, target // page])
+        kc2[pg, :, target % page] = 0
+        kc2[pg, :, target % page, 3] = 30.0
+        qq[:, :, 3] = 30.0
+        q2 = q.clone()
+        q2[3] = qq.reshape(nq * d).to(DEV)
+        out2 = torch.zeros_like(q)
+        ops.attention_decode_bf16(q2, nq * d, out2, kc2.to(DEV), vc.to(DEV), table.to(DEV), seq_lens, len(lens), 20480,
+                                  nq, nkv, d, 0, 1.0, err)
+        want = vs[3][target].repeat_interleave(nq // nkv, dim=0).reshape(1, nq * d)
+        assert rel_err(out2[3:4], want) <= tol(dt)
+
+
 @pytest.mark.parametrize("kind", ["prefill", "decode", "tcgen05"])
 def test_mma_attention_finds_one_far_key(ops, err, kind):
     """One key among a thousand, at a tile's, split's or page's edge, is made to
