@@ -312,6 +312,36 @@ def test_attention_prefill_tcgen05(ops, err, nq, nkv, d, page, window):
     assert rel_err(out3, out[a + cut:a + q_lens[s]].double().cpu()) <= 2e-3    # other tiles of rows: rounding only
 
 
+@pytest.mark.parametrize("kind,nq,nkv,d,page,window", [("tcgen05", 4, 2, 64, 16, 0), ("tcgen05", 4, 1, 128, 16, 0),
+                                                       ("tcgen05", 4, 2, 64, 16, 900), ("mma", 4, 2, 64, 16, 0),
+                                                       ("mma", 6, 2, 32, 8, 0)])
+def test_attention_prefill_long_portion(ops, err, kind, nq, nkv, d, page, window):
+    """A portion of 1,200 tokens behind 1,800 tokens of context: tens of key tiles a row, the rings of the
+    tcgen05 kernel wrapping many times, rows whose max grows late (one far key made to dominate)."""
+    dt = torch.bfloat16
+    n, m = 3000, 1200
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, [n], [m],
+                                                                 pages=-(-n // page) + 5, seed=12)
+    # key 2500 answers the queries from 2600 on with a large score: their running max jumps late
+    qs[0][800:, :, 5] = 12.0
+    pg = int(table[0, 2500 // page])
+    ks[0][2500] = 0
+    ks[0][2500, :, 5] = 12.0
+    kc[pg, :, 2500 % page] = ks[0][2500]
+    q = qs[0].reshape(m, nq * d).to(DEV)
+    out = torch.zeros_like(q)
+    q_start = torch.tensor([0, m], dtype=torch.int32, device=DEV)
+    seq_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(d)
+    fn = ops.attention_prefill_tcgen05 if kind == "tcgen05" else ops.attention_prefill_bf16
+    fn(q, nq * d, out, kc.to(DEV), vc.to(DEV), table.to(DEV), q_start, seq_lens, 0, 1, m, nq, nkv, d, window, scale, err)
+    assert int(err.item()) == 0
+    want = pl.attention(qs[0].double(), ks[0].double(), vs[0].double(), torch.arange(n - m, n),
+                        window=window or None, scale=scale)
+    for a in range(0, m, 300):
+        assert rel_err(out[a:a + 300], want[a:a + 300]) <= tol(dt), a
+
+
 def test_tcgen05_attention_refuses_other_sizes(ops, err):
     from rllm_b200.kernels.ops import KernelError
     assert not ops.attention_prefill_tcgen05_supported(8, 2, 32, 16)      # head size
