@@ -529,7 +529,8 @@ def test_gemm_small_m_silu(ops, M, I, K):
 
 @pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("M,H,K,N2", [(1, 136, 264, 200), (3, 2048, 8192, 3072), (8, 72, 40, 50), (5, 96, 264, 389),
-                                       (9, 136, 264, 200), (13, 2048, 8192, 3072), (16, 72, 40, 50)])
+                                       (9, 136, 264, 200), (13, 2048, 8192, 3072), (16, 72, 40, 50),
+                                       (8, 2048, 264, 16384), (2, 1024, 72, 13000)])   # grids that run as one wave of the lighter form
 def test_gemm_small_m_residual_then_rstd(ops, M, H, K, N2, wdt):
     """The pair of products that stands for 'add into the residual stream, RMSNorm, next product':
     h += x W1^T with the rows' partial sums of squares and h * w_norm on the side, then
