@@ -296,3 +296,58 @@ def test_random_serving_keeps_every_request_right(model_dirs, seed):
     llm.engine.cache.check()
     assert llm.engine.cache.usage()["num_requests"] == 0
     print("preemptions", llm.engine.scheduler.num_preemptions, "prefix hits", llm.engine.scheduler.prefix_hit_tokens)
+
+
+@pytest.mark.parametrize("hidden,heads,kv_heads,head_dim,inter", [(2048, 32, 8, 64, 8192), (3072, 24, 8, 128, 8192)])
+def test_layers_of_real_size_in_bfloat16_follow_float32(tmp_path, hidden, heads, kv_heads, head_dim, inter):
+    """Two layers with the sizes of a Llama-3.2-1B (or 3B: heads of 128) layer and its vocabulary, random weights: the logits of
+    the bfloat16 path (tensor-core products and attention on tcgen05 for the 1,024-token prompt, the
+    weight-streaming products and split-KV attention for the decode steps that follow, as CUDA graphs)
+    agree with those of the float32 path, whose kernels the tiny configurations check against the plain
+    implementation.  Sizes of this kind reach code that the tiny configurations do not (full tiles, the
+    one-wave form of the decode products, several CTAs a sequence in decode attention)."""
+    import json
+    from rllm_b200 import LLM
+    from rllm_b200.engine.runner import StepEntry
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 2, "hidden_size": hidden,
+           "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": head_dim, "intermediate_size": inter,
+           "vocab_size": 128256, "rope_theta": 500000.0,
+           "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                            "original_max_position_embeddings": 8192},
+           "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+           "hidden_act": "silu", "torch_dtype": "bfloat16", "bos_token_id": 128000, "eos_token_id": 128001}
+    d = str(tmp_path / "real_size")
+    import os
+    os.makedirs(d)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    rng = np.random.default_rng(3)
+    prompts = {"long": [int(t) for t in rng.integers(0, 128256, size=1024)],
+               "mid": [int(t) for t in rng.integers(0, 128256, size=700)],
+               "short": [int(t) for t in rng.integers(0, 128256, size=5)]}
+    feed = {k: [int(t) for t in rng.integers(0, 128256, size=6)] for k in prompts}
+    rows = {}
+    for dt in ("fp32", "bf16"):
+        llm = LLM(d, dtype=dt, max_model_len=2048, max_num_seqs=4, max_num_batched_tokens=2048, num_gpu_blocks=160,
+                  enable_prefix_caching=False, random_weights=True, draw_on_device=True, seed=1)
+        eng, runner = llm.engine, llm.engine.runner
+        got = []
+        for k, p in prompts.items():
+            eng.cache.admit(k)
+            assert eng.cache.ensure(k, 0, len(p) + 8)
+        # the prompts as one step, then decode steps of all three
+        logits = runner.step([StepEntry(k, p, 0, [len(p) - 1]) for k, p in prompts.items()])
+        got.append(logits.float().cpu())
+        for i in range(6):
+            logits = runner.step([StepEntry(k, [feed[k][i]], len(prompts[k]) + i, [0]) for k in prompts])
+            got.append(logits.float().cpu())
+        runner.check_errors()
+        rows[dt] = torch.cat(got)
+        del llm, eng, runner
+        torch.cuda.empty_cache()
+    a, b = rows["fp32"].double(), rows["bf16"].double()
+    err = (a - b).abs().amax(dim=1) / a.abs().amax(dim=1)
+    assert float(err.max()) <= 4e-2, err
+    # and the two paths mostly agree on the likeliest token
+    same = (a.argmax(dim=1) == b.argmax(dim=1)).float().mean()
+    assert float(same) >= 0.7, same
