@@ -117,7 +117,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
   const int nblocks = (K + 31) / 32;
   // U blocks at a time: all their loads are issued before the first multiply, so that a
   // warp has U * (2 + MT) 16-byte loads in flight
-  constexpr int U = LIGHT ? 4 : (MT == 1 ? 8 : (MT == 2 ? 4 : 2));
+  constexpr int U = LIGHT ? (MT == 1 ? 4 : 2) : (MT == 1 ? 8 : (MT == 2 ? 4 : 2));
   // a warp takes a contiguous range of k blocks, so that its loads walk along the rows of W
   const int per_warp = (nblocks + nwarps - 1) / nwarps;
   const int b_end = min(nblocks, (warp + 1) * per_warp);
@@ -273,16 +273,16 @@ static int launch_small_m(const bf16* x, int ldx, const bf16* W, int ldw, void* 
   // the step takes 13 % longer than when that product starts at its end; so it lets nothing in early.
   const size_t weight_bytes = (size_t)(EPI == EPI_SILU ? 2 : 1) * N * K * sizeof(bf16);
   if (weight_bytes < ((size_t)12 << 20) && M > 2) tail_from = RLLM_NO_EARLY_LAUNCH;
-  if (MT == 1 && warps == 4 && tiles >= resident[warps]) {
+  if (MT <= 2 && warps == 4 && tiles >= resident[warps]) {
     static int light = 0;
     if (!light) {
-      light = rllm_resident_ctas(gemm_small_m_kernel<1, EPI, RSTD, true>, 128, smem) + 1;
+      light = rllm_resident_ctas(gemm_small_m_kernel<MT, EPI, RSTD, true>, 128, smem) + 1;
       const char* env = getenv("RLLM_SMALL_M_LIGHT");
       if (env && env[0] == '0') light = 1;
     }
     if (tiles < light) {      // one wave: every CTA is there from the start
       if (tail_from != RLLM_NO_EARLY_LAUNCH) tail_from = 0;
-      cudaError_t e = rllm_launch_pdl(gemm_small_m_kernel<1, EPI, RSTD, true>, dim3(tiles), dim3(128), smem, stream,
+      cudaError_t e = rllm_launch_pdl(gemm_small_m_kernel<MT, EPI, RSTD, true>, dim3(tiles), dim3(128), smem, stream,
                                       x, ldx, W, ldw, out, ldo, M, N, K, up_offset, tail_from, ns);
       return (int)e;
     }

@@ -172,9 +172,10 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 
 
 SMALL_M_MAX = 8       # up to here the weight-streaming GEMM beats the library's on a B200 (it takes 16)
-FUSED_M_MAX = 8       # up to here a step goes through the forms of it that carry the residual add and the norm
-                      # (the kernels take 16 rows; measured at batch 16, context 4096: 1.47 ms a step through
-                      # them, 1.40 ms through the library's products and the norm kernels)
+FUSED_M_MAX = 16      # up to here a step goes through the forms of it that carry the residual add and the norm
+                      # (RLLM_FUSED_M_MAX in the environment overrides it, for measurements).  Measured at
+                      # context 4096: batch 12 1.32 -> 1.06 ms a step, batch 16 1.39 -> 1.16 ms, against the
+                      # library's products with norm and SiLU kernels between them
 
 
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: str = "store") -> None:
@@ -249,7 +250,7 @@ def gemm_small_m_rstd(x: torch.Tensor, parts: torch.Tensor, eps: float, w: torch
 def small_m_rows(num_rows: int, dtype: torch.dtype) -> bool:
     """Whether a step of this many rows goes through the weight-streaming kernels."""
     import os
-    return dtype is torch.bfloat16 and 0 < num_rows <= FUSED_M_MAX and os.environ.get("RLLM_GEMM") != "library"
+    return dtype is torch.bfloat16 and 0 < num_rows <= int(os.environ.get("RLLM_FUSED_M_MAX", FUSED_M_MAX)) and os.environ.get("RLLM_GEMM") != "library"
 
 
 def small_m_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
