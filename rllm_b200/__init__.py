@@ -10,6 +10,7 @@ _LAZY = {
     "SamplingParams": ("rllm_b200.sampling.params", "SamplingParams"),
     "RequestOutput": ("rllm_b200.engine.engine_core", "RequestOutput"),
     "CompletionOutput": ("rllm_b200.engine.engine_core", "CompletionOutput"),
+    "Logprob": ("rllm_b200.engine.engine_core", "Logprob"),
     "EngineArgs": ("rllm_b200.config.engine_args", "EngineArgs"),
     "EngineCore": ("rllm_b200.engine.engine_core", "EngineCore"),
 }

@@ -58,6 +58,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--frequency-penalty", type=float, default=0.0)
     g.add_argument("--seed", type=int, default=None, help="sampling seed of the first prompt; prompt i uses seed+i")
     g.add_argument("--ignore-eos", action="store_true")
+    g.add_argument("--logprobs", type=int, default=None, metavar="N",
+                   help="report every generated token's log-probability and the N likeliest tokens of its place (with --json)")
     g.add_argument("--dtype", default="auto", help="auto | bf16 | fp32")
     g.add_argument("--max-model-len", type=int, default=None)
     g.add_argument("--max-num-seqs", type=int, default=256)
@@ -119,7 +121,7 @@ def cmd_generate(args) -> int:
                              min_p=args.min_p, repetition_penalty=args.repetition_penalty,
                              presence_penalty=args.presence_penalty,
                              frequency_penalty=args.frequency_penalty, max_tokens=args.max_tokens,
-                             ignore_eos=args.ignore_eos,
+                             ignore_eos=args.ignore_eos, logprobs=args.logprobs,
                              seed=None if args.seed is None else args.seed + i)
               for i in range(len(prompts))]
     t0 = time.time()
@@ -131,6 +133,9 @@ def cmd_generate(args) -> int:
             print(json.dumps({"request_id": o.request_id, "prompt_token_ids": o.prompt_token_ids,
                               "token_ids": o.outputs[0].token_ids,
                               "finish_reason": o.outputs[0].finish_reason,
+                              "logprobs": None if o.outputs[0].logprobs is None else
+                              [{"token_id": e.token_id, "logprob": e.logprob, "top_logprobs": e.top_logprobs}
+                               for e in o.outputs[0].logprobs],
                               "usage": vars(o.usage)}))
         else:
             print(f"request {o.request_id}: {o.outputs[0].token_ids}  [{o.outputs[0].finish_reason}; "

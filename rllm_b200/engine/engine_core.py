@@ -36,12 +36,23 @@ class Usage:
 
 
 @dataclass
+class Logprob:
+    """crates/rllm-core/src/output.rs:44-49 (no text), with the likeliest tokens of the place beside it
+    (crates/rllm-sampling/src/sampler.rs:27-31)."""
+
+    token_id: int
+    logprob: float
+    top_logprobs: List[tuple] = field(default_factory=list)      # (token id, log-probability), descending
+
+
+@dataclass
 class CompletionOutput:
     """crates/rllm-core/src/output.rs:13-20 (no text: the engine works on ids)."""
 
     index: int
     token_ids: List[int]
     finish_reason: Optional[str] = None      # "stop" | "length" | "aborted"
+    logprobs: Optional[List[Logprob]] = None # one for each token of token_ids, if the request asked for them
 
 
 @dataclass
@@ -149,13 +160,17 @@ class EngineCore:
         if inflight is not None:
             # this step was put on the GPU during the last call, behind the step before it
             sched, sampled_reqs, plain_greedy, sampled, pending = inflight
+            wanted_lp = None               # a request that wants log-probabilities is never launched ahead
             self.last_schedule = sched
         elif prepared is not None:
             # the schedule and the packed inputs of this step were made while the GPU ran the last one
             sched, sampled_reqs, plain_greedy, graph = prepared
             self.last_schedule = sched
             self.num_steps += 1
-            sampled = self._sample(self.runner.run_prepared(graph), sampled_reqs, plain_greedy, 0)
+            logits = self.runner.run_prepared(graph)
+            raw = self._raw_logits(logits, sampled_reqs)
+            sampled = self._sample(logits, sampled_reqs, plain_greedy, 0)
+            wanted_lp = self._logprobs(raw, sampled, sampled_reqs)
             pending = self._read_back(sampled, graph)
         else:
             sched = self.scheduler.schedule()
@@ -173,7 +188,10 @@ class EngineCore:
                     sampled_reqs.append(req)
                     p = req.params
                     plain_greedy = plain_greedy and p.greedy and not p.edits_logits
-            sampled = self._sample(self.runner.step(entries), sampled_reqs, plain_greedy, 0)
+            logits = self.runner.step(entries)
+            raw = self._raw_logits(logits, sampled_reqs)
+            sampled = self._sample(logits, sampled_reqs, plain_greedy, 0)
+            wanted_lp = self._logprobs(raw, sampled, sampled_reqs)
             pending = self._read_back(sampled)
         # requests that ended (or were aborted) after this step went to the GPU: their rows are dropped
         live = [r.status is RequestStatus.RUNNING for r in sampled_reqs]
@@ -193,7 +211,8 @@ class EngineCore:
             self.runner.poll_errors()
         outputs = []
         any_finished = False
-        for req, tok, alive in zip(sampled_reqs, tokens, live):
+        lps = self._logprobs_of(wanted_lp, sampled_reqs, tokens)
+        for row, (req, tok, alive) in enumerate(zip(sampled_reqs, tokens, live)):
             if not alive:
                 continue
             req.output_token_ids.append(int(tok))
@@ -204,7 +223,7 @@ class EngineCore:
                                       else RequestStatus.FINISHED_LENGTH)
             n_prompt, n_out = len(req.prompt_token_ids), len(req.output_token_ids)
             outputs.append(RequestOutput(req.request_id, req.prompt_token_ids,
-                                         [CompletionOutput(0, [int(tok)], reason)], reason is not None,
+                                         [CompletionOutput(0, [int(tok)], reason, lps.get(row))], reason is not None,
                                          Usage(n_prompt, n_out, n_prompt + n_out)))
         if nxt is not None and not any_finished and not self.scheduler.waiting:
             by_req = {r.request_id: t for r, t in zip(sampled_reqs, tokens)}
@@ -253,6 +272,37 @@ class EngineCore:
                 for r in sampled_reqs]
         return self.sampler.sample(logits, rows)
 
+    def _raw_logits(self, logits, sampled_reqs):
+        """A copy of the step's logits before anything edits them, if a request wants log-probabilities
+        (they are taken from the raw logits, crates/rllm-sampling/src/sampler.rs:149-160), else None."""
+        if not any(r.params.logprobs is not None for r in sampled_reqs):
+            return None
+        return logits.clone()
+
+    def _logprobs(self, raw, sampled, sampled_reqs):
+        """Device tensors (lp, top ids, top values) for the rows of the step, or None."""
+        if raw is None or sampled is None:
+            return None
+        from ..kernels import ops
+        top_n = max(r.params.logprobs or 0 for r in sampled_reqs)
+        with torch.cuda.device(self.device):
+            return ops.logprobs(raw, sampled, top_n)
+
+    @staticmethod
+    def _logprobs_of(wanted_lp, sampled_reqs, tokens) -> Dict[int, List[Logprob]]:
+        """row -> [Logprob] for the rows whose request asked for log-probabilities."""
+        if wanted_lp is None:
+            return {}
+        lp, ids, vals = (t.cpu() for t in wanted_lp)
+        out = {}
+        for row, req in enumerate(sampled_reqs):
+            n = req.params.logprobs
+            if n is None:
+                continue
+            top = [(int(i), float(v)) for i, v in zip(ids[row, :n].tolist(), vals[row, :n].tolist()) if i >= 0]
+            out[row] = [Logprob(int(tokens[row]), float(lp[row]), top)]
+        return out
+
     def _launch_ahead(self, nxt, sampled_reqs, sampled) -> bool:
         """Put the prepared next step on the GPU now.  Its rows are the same requests in the same order,
         so the tokens being sampled are copied into its input on the device.  If one of the requests
@@ -261,7 +311,7 @@ class EngineCore:
         nsched, nreqs, plain_greedy, graph = nxt
         if sampled is None or len(nreqs) != len(sampled_reqs) or any(a is not b for a, b in zip(nreqs, sampled_reqs)):
             return False
-        if any(r.params.edits_logits for r in nreqs):
+        if any(r.params.edits_logits or r.params.logprobs is not None for r in nreqs):
             return False
         self.num_steps += 1
         self.num_steps_ahead += 1

@@ -794,3 +794,63 @@ RLLM_EXPORT int rllm_logit_mask(float* logits, int R, int V, int ld, const int* 
   }
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Log-probabilities (natural log) from a row of raw logits, as the reference's sampler reports them
+// (crates/rllm-sampling/src/logprobs.rs:5-28: logit - (max + ln sum exp(logit - max)); :34-70: the N
+// largest, in descending order).  One CTA a row; the sum is taken in a fixed order (a thread's strided
+// elements in index order, then the threads in order), so a row's values do not depend on the batch.
+// Ties in the top N: the lower index first (the reference's order among equals is not defined).
+// A place for which nothing is left (N beyond the vocabulary, or -inf logits only) gets id -1.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+logprobs_kernel(const float* __restrict__ logits, int V, int ld, const int* __restrict__ tokens, int N,
+                float* __restrict__ lp, int* __restrict__ top_ids, float* __restrict__ top_lp) {
+  __shared__ ArgMax sm_arg[32];
+  __shared__ float sm_f[32];
+  pdl_wait();
+  pdl_launch();
+  const int r = blockIdx.x;
+  const float* x = logits + (size_t)r * ld;
+  ArgMax best; best.v = -INFINITY; best.i = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) { ArgMax c; c.v = x[i]; c.i = i; best = argmax_better(best, c); }
+  best = block_argmax(best, sm_arg);
+  const float mx = best.v;
+  float s = 0.f;
+  if (mx != -INFINITY)
+    for (int i = threadIdx.x; i < V; i += blockDim.x) s += expf(x[i] - mx);
+  s = block_sum(s, sm_f);
+  const float log_z = mx + logf(s);
+  if (threadIdx.x == 0) {
+    const int t = tokens[r];
+    lp[r] = (mx == -INFINITY || t < 0 || t >= V) ? -INFINITY : x[t] - log_z;
+  }
+  // the N largest, one pass each: the best element that comes after the last one found
+  ArgMax prev; prev.v = INFINITY; prev.i = -1;
+  for (int n = 0; n < N; ++n) {
+    ArgMax b; b.v = -INFINITY; b.i = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const float v = x[i];
+      if (v == -INFINITY) continue;
+      if (v < prev.v || (v == prev.v && i > prev.i)) { ArgMax c; c.v = v; c.i = i; b = argmax_better(b, c); }
+    }
+    b = block_argmax(b, sm_arg);
+    const bool none = b.i == 0x7fffffff;
+    if (threadIdx.x == 0) {
+      top_ids[(size_t)r * N + n] = none ? -1 : b.i;
+      top_lp[(size_t)r * N + n] = none ? -INFINITY : b.v - log_z;
+    }
+    if (none) { prev.v = -INFINITY; prev.i = 0x7fffffff; } else prev = b;
+    __syncthreads();
+  }
+}
+
+// lp [R]: log-probability of tokens[r] in row r; top_ids, top_lp [R, N]: the N likeliest tokens of every row
+// and their log-probabilities (N may be 0).
+RLLM_EXPORT int rllm_logprobs(const float* logits, int R, int V, int ld, const int* tokens, int N, float* lp,
+                              int* top_ids, float* top_lp, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (V <= 0 || ld < V || N < 0 || !tokens || !lp || (N > 0 && (!top_ids || !top_lp))) return RLLM_E_BADARG;
+  return (int)rllm_launch_pdl(logprobs_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, stream, logits, V, ld, tokens, N, lp,
+                              top_ids, top_lp);
+}

@@ -547,3 +547,19 @@ def decode_advance(token_ids: torch.Tensor, positions: torch.Tensor, seq_lens: t
         row = _ptr(history_row)
     _check(lib.rllm_decode_advance(_ptr(token_ids), _ptr(positions), _ptr(seq_lens), _ptr(sampled),
                                    row, c_int(n), _stream()), "decode_advance")
+
+
+def logprobs(logits: torch.Tensor, tokens: torch.Tensor, top_n: int):
+    """Natural-log probabilities from raw logits float32 [R, V]: (lp [R] of ``tokens`` int32 [R], ids int32
+    [R, top_n] and values float32 [R, top_n] of every row's ``top_n`` likeliest tokens, descending, the lower
+    index first among equals; id -1 where nothing is left)."""
+    lib = build.load_library("sampling")
+    R, V = logits.shape
+    assert logits.dtype is torch.float32 and logits.stride(1) == 1 and tokens.dtype is torch.int32 and tokens.numel() == R
+    lp = torch.empty(R, dtype=torch.float32, device=logits.device)
+    ids = torch.empty((R, top_n), dtype=torch.int32, device=logits.device)
+    vals = torch.empty((R, top_n), dtype=torch.float32, device=logits.device)
+    _check(lib.rllm_logprobs(_ptr(logits), c_int(R), c_int(V), c_int(logits.stride(0)), _ptr(tokens), c_int(top_n),
+                             _ptr(lp), _ptr(ids) if top_n else c_void_p(0), _ptr(vals) if top_n else c_void_p(0),
+                             _stream()), "logprobs")
+    return lp, ids, vals

@@ -71,11 +71,14 @@ class LLM:
                 raise ValueError("one SamplingParams per prompt, or one for all")
         ids = [self.add_request(p, sp) for p, sp in zip(prompt_token_ids, params)]
         tokens = {rid: [] for rid in ids}
+        logprobs = {rid: [] for rid in ids}
         final = {}
         while self.has_work():
             for out in self.step():
                 if out.request_id in tokens:
                     tokens[out.request_id].extend(out.outputs[0].token_ids)
+                    if out.outputs[0].logprobs is not None:
+                        logprobs[out.request_id].extend(out.outputs[0].logprobs)
                     if out.finished:
                         final[out.request_id] = out
         self.engine.runner.check_errors()          # the steps polled the kernels' error words; this waits for the last
@@ -83,6 +86,7 @@ class LLM:
         for rid in ids:
             out = final[rid]
             results.append(RequestOutput(rid, out.prompt_token_ids,
-                                         [CompletionOutput(0, tokens[rid], out.outputs[0].finish_reason)],
+                                         [CompletionOutput(0, tokens[rid], out.outputs[0].finish_reason,
+                                                           logprobs[rid] if out.outputs[0].logprobs is not None else None)],
                                          True, out.usage))
         return results

@@ -5,7 +5,9 @@ Kept: n, presence_penalty, frequency_penalty, repetition_penalty, temperature,
 top_p, top_k, min_p, seed, stop_token_ids, ignore_eos, max_tokens, min_tokens,
 logit_bias, allowed_token_ids.  Text-side options (stop strings, detokenize,
 bad_words, structured outputs) have no meaning for an engine that works on
-token ids; logprobs and n > 1 are refused with a clear error.
+token ids; n > 1 is refused with a clear error.  ``logprobs`` = N asks for the
+log-probability of every generated token and of the N likeliest tokens at its place,
+from the raw logits (crates/rllm-sampling/src/sampler.rs:149-160).
 """
 from __future__ import annotations
 
@@ -57,8 +59,8 @@ class SamplingParams:
             raise InvalidSamplingParams("max_tokens must be >= 1")
         if self.min_tokens < 0:
             raise InvalidSamplingParams("min_tokens must be >= 0")
-        if self.logprobs is not None:
-            raise InvalidSamplingParams("logprobs are not supported")
+        if self.logprobs is not None and not 0 <= self.logprobs <= 32:
+            raise InvalidSamplingParams("logprobs must be in [0, 32]")
 
     @property
     def greedy(self) -> bool:

@@ -347,3 +347,25 @@ def sample_row(processed: np.ndarray, temperature: float, top_k: int, u: float) 
     cum = np.cumsum(p)
     idx = int(np.searchsorted(cum, u, side="right"))
     return min(idx, len(p) - 1)
+
+
+def logprob_of(logits: np.ndarray, token: int) -> float:
+    """Natural-log probability of ``token`` under softmax(logits):
+    logit - (max + ln sum exp(logit - max)) (crates/rllm-sampling/src/logprobs.rs:5-28), in float64."""
+    x = np.asarray(logits, dtype=np.float64)
+    m = x.max()
+    if m == -np.inf or not 0 <= token < len(x):
+        return -np.inf
+    return float(x[token] - (m + math.log(np.exp(x - m).sum())))
+
+
+def top_logprobs(logits: np.ndarray, n: int) -> List[tuple]:
+    """The n likeliest tokens as (id, log-probability), descending (crates/rllm-sampling/src/logprobs.rs:34-70);
+    -inf logits are left out; among equals the lower index comes first (the reference sorts unstably)."""
+    x = np.asarray(logits, dtype=np.float64)
+    m = x.max()
+    if n <= 0 or m == -np.inf:
+        return []
+    log_z = m + math.log(np.exp(x - m).sum())
+    order = sorted((i for i in range(len(x)) if x[i] != -np.inf), key=lambda i: (-x[i], i))[:n]
+    return [(int(i), float(x[i] - log_z)) for i in order]

@@ -351,3 +351,35 @@ def test_layers_of_real_size_in_bfloat16_follow_float32(tmp_path, hidden, heads,
     # and the two paths mostly agree on the likeliest token
     same = (a.argmax(dim=1) == b.argmax(dim=1)).float().mean()
     assert float(same) >= 0.7, same
+
+
+def test_logprobs_come_from_the_raw_logits(model_dirs):
+    """A request that asks for log-probabilities gets, for every generated token, its log-probability and
+    the N likeliest tokens of its place, from the raw logits: also when penalties and a temperature change
+    what is sampled, and beside requests that did not ask."""
+    from rllm_b200 import SamplingParams
+    name = "A"
+    prompts = prompts_for(name, [9, 30, 4], 12)
+    params = [SamplingParams(temperature=0.0, max_tokens=7, ignore_eos=True, logprobs=3),
+              SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True),
+              SamplingParams(temperature=0.8, seed=4, repetition_penalty=1.3, max_tokens=6, ignore_eos=True, logprobs=0)]
+    llm = make_llm(model_dirs, name)
+    outs = llm.generate(prompts, params)
+    plain = pl.read_model_dir(model_dirs[name])
+    assert outs[1].outputs[0].logprobs is None
+    for p, sp, o in zip(prompts, params, outs):
+        if sp.logprobs is None:
+            continue
+        got = o.outputs[0]
+        assert len(got.logprobs) == len(got.token_ids) == sp.max_tokens
+        toks = list(p)
+        for t, entry in zip(got.token_ids, got.logprobs):
+            row = plain.logits(toks)[-1].numpy()
+            assert entry.token_id == t
+            assert abs(entry.logprob - pl.logprob_of(row, t)) <= 1e-3
+            top = pl.top_logprobs(row, sp.logprobs)
+            assert [i for i, _ in entry.top_logprobs] == [i for i, _ in top]
+            np.testing.assert_allclose([v for _, v in entry.top_logprobs], [v for _, v in top], atol=1e-3)
+            toks.append(t)
+    # greedy: the chosen token is the likeliest one
+    assert all(e.top_logprobs[0][0] == e.token_id for e in outs[0].outputs[0].logprobs)

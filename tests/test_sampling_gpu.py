@@ -192,6 +192,32 @@ def test_params_are_validated():
     SamplingParams().validate()
     assert SamplingParams().max_tokens == 16 and SamplingParams().temperature == 1.0
     for bad in (dict(temperature=-1.0), dict(top_p=1.5), dict(n=0), dict(n=2), dict(repetition_penalty=0.0),
-                dict(presence_penalty=3.0), dict(logprobs=5)):
+                dict(presence_penalty=3.0), dict(logprobs=-1), dict(logprobs=33)):
         with pytest.raises(InvalidSamplingParams):
             SamplingParams(**bad).validate()
+
+
+@pytest.mark.parametrize("V", [311, 4097, 128256])
+def test_logprobs_kernel_matches_the_plain_formulas(V):
+    """The log-probability of a chosen token and the N likeliest tokens of a row, from raw logits; equal
+    logits come lower index first; -inf logits are left out; N beyond what is left gives id -1."""
+    from rllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(V)
+    R, N = 5, 6
+    logits = torch.randn(R, V, generator=g) * 3
+    logits[1, 7] = logits[1, 3] = logits[1].max() + 1.0            # a tie at the top
+    logits[2, :] = float("-inf")
+    logits[2, [5, 9, 11]] = torch.tensor([0.5, 0.5, -2.0])          # three tokens left: N runs out
+    logits[3, 100:] = float("-inf")
+    tokens = torch.tensor([0, 7, 9, 50, V - 1], dtype=torch.int32)
+    lp, ids, vals = ops.logprobs(logits.cuda(), tokens.cuda(), N)
+    lp0, ids0, _ = ops.logprobs(logits.cuda(), tokens.cuda(), 0)
+    assert ids0.shape == (R, 0) and torch.equal(lp0, lp)
+    for r in range(R):
+        row = logits[r].numpy()
+        want = pl.logprob_of(row, int(tokens[r]))
+        assert abs(float(lp[r]) - want) <= 1e-4 * max(1.0, abs(want)), (r, float(lp[r]), want)
+        top = pl.top_logprobs(row, N)
+        got_ids = ids[r].tolist()
+        assert got_ids[: len(top)] == [i for i, _ in top] and all(i == -1 for i in got_ids[len(top):])
+        np.testing.assert_allclose(vals[r, : len(top)].cpu().numpy(), [v for _, v in top], rtol=1e-4, atol=1e-4)
