@@ -328,19 +328,30 @@ def test_layers_of_real_size_in_bfloat16_follow_float32(tmp_path, hidden, heads,
     feed = {k: [int(t) for t in rng.integers(0, 128256, size=6)] for k in prompts}
     rows = {}
     for dt in ("fp32", "bf16"):
-        llm = LLM(d, dtype=dt, max_model_len=2048, max_num_seqs=4, max_num_batched_tokens=2048, num_gpu_blocks=160,
+        llm = LLM(d, dtype=dt, max_model_len=2048, max_num_seqs=16, max_num_batched_tokens=2048, num_gpu_blocks=200,
                   enable_prefix_caching=False, random_weights=True, draw_on_device=True, seed=1)
         eng, runner = llm.engine, llm.engine.runner
         got = []
         for k, p in prompts.items():
             eng.cache.admit(k)
-            assert eng.cache.ensure(k, 0, len(p) + 8)
+            assert eng.cache.ensure(k, 0, len(p) + 12)
         # the prompts as one step, then decode steps of all three
         logits = runner.step([StepEntry(k, p, 0, [len(p) - 1]) for k, p in prompts.items()])
         got.append(logits.float().cpu())
         for i in range(6):
             logits = runner.step([StepEntry(k, [feed[k][i]], len(prompts[k]) + i, [0]) for k in prompts])
             got.append(logits.float().cpu())
+        # nine more requests: decode steps of twelve rows go through the decode products in their form for
+        # two batch tiles
+        more = {f"m{i}": [int(t) for t in np.random.default_rng(50 + i).integers(0, 128256, size=4 + i)] for i in range(9)}
+        for k, p in more.items():
+            eng.cache.admit(k)
+            assert eng.cache.ensure(k, 0, len(p) + 4)
+        got.append(runner.step([StepEntry(k, p, 0, [len(p) - 1]) for k, p in more.items()]).float().cpu())
+        for i in range(3):
+            entries = [StepEntry(k, [feed[k][i]], len(prompts[k]) + 6 + i, [0]) for k in prompts]
+            entries += [StepEntry(k, [7 + i], len(p) + i, [0]) for k, p in more.items()]
+            got.append(runner.step(entries).float().cpu())
         runner.check_errors()
         rows[dt] = torch.cat(got)
         del llm, eng, runner
