@@ -259,8 +259,13 @@ static int launch_small_m(const bf16* x, int ldx, const bf16* W, int ldw, void* 
   const int rows_per_cta = (EPI == EPI_SILU) ? 8 : 16;
   const int tiles = (N + rows_per_cta - 1) / rows_per_cta;
   const int nblocks = (K + 31) / 32;
+  // More warps a CTA (K split further) while there are few tiles, but only as long as the whole grid stays
+  // resident at once: 512 threads fit on an SM, and a second wave of a few CTAs costs as much as a full one
+  // (320 tiles of 8 warps: 296 at once and then 24 alone, 12 us where 4 warps take 8).
+  static int sms = 0;
+  if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); if (sms <= 0) sms = 148; }
   int warps = 4;
-  while (warps < 16 && (long long)tiles * warps < 1536) warps *= 2;
+  while (warps < 16 && (long long)tiles * warps < 1536 && tiles <= (16 / (2 * warps)) * sms) warps *= 2;
   while (warps > 1 && warps > nblocks) warps /= 2;
   while (warps > 1 && (size_t)warps * 16 * 8 * MT * sizeof(float) > 40 * 1024) warps /= 2;
   // EPI_RESID keeps the CTA's new values of h behind the warps' partial sums
