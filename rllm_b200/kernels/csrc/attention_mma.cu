@@ -746,10 +746,10 @@ static int launch_decode_cfg(int warps, bf16* qkv, int q_stride, bf16* out, bf16
   return (int)e;
 }
 
-// Head sizes up to 64, 4 warps a CTA: with many chunks in all, one stage a warp, so that 20 warps are
-// resident per SM and hide each other's loads (measured best at batch 8 and 64); with few chunks, two
-// stages a warp (best at batch 1).  Head size 128: a stage is twice as large; few chunks get one warp a
-// CTA and a deep pipeline, many get 2 warps and 3 stages.  The choice changes no result.
+// Four warps a CTA.  With many chunks in all, one stage a warp, so that as many warps as possible are
+// resident per SM and hide each other's loads (measured best at batch 8 and 64, for heads of 64 and of 128:
+// 34.8 and 202 us at head size 128 against 49 and 298 us for two warps with three stages); with few chunks,
+// two stages a warp (best at batch 1).  The choice changes no result.
 template <int D>
 static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc, const int* bt, int max_blocks,
                          const int* seq_lens, int num_seqs, int nq, int nkv, int page_size, int num_pages,
@@ -758,12 +758,8 @@ static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc,
   const long long total = (long long)max_chunks * nkv * num_seqs;
 #define RLLM_DEC_ARGS qkv, q_stride, out, kc, vc, bt, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, \
       window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream
-  if (D < 128) {
-    if (total >= 1024) return launch_decode_cfg<D, 1>(4, RLLM_DEC_ARGS);
-    return launch_decode_cfg<D, 2>(4, RLLM_DEC_ARGS);
-  }
-  if (total <= 148 * 6) return launch_decode_cfg<D, 4>(1, RLLM_DEC_ARGS);
-  return launch_decode_cfg<D, 3>(2, RLLM_DEC_ARGS);
+  if (total >= 1024) return launch_decode_cfg<D, 1>(4, RLLM_DEC_ARGS);
+  return launch_decode_cfg<D, 2>(4, RLLM_DEC_ARGS);
 }
 
 // Decode: sequences 0 .. num_seqs-1 with one query token each.  Row s of qkv
