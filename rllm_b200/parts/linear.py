@@ -20,7 +20,7 @@ from .base import RowSumsq, ScaledRows
 
 def fused_residual_takes(num_rows: int, dtype: torch.dtype, *weights: torch.Tensor) -> bool:
     """Whether ``linear`` takes a ``ScaledRows`` input and a ``residual`` for these weights and rows."""
-    return ops.small_m_rows(num_rows, dtype) and all(
+    return ops.small_m_rows(num_rows, dtype, weights) and all(
         w.dtype is torch.bfloat16 and w.shape[1] % 8 == 0 and w.stride(0) % 8 == 0 and w.stride(1) == 1 for w in weights)
 
 
