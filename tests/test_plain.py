@@ -133,3 +133,20 @@ def test_draws_follow_the_distribution():
     assert np.allclose(counts / 4000, [0.5, 0.25, 0.125, 0.125], atol=0.03)
     masked = np.array([-np.inf, 0.0, 0.0], dtype=np.float32)
     assert pl.sample_row(masked, 1.0, -1, 0.0) == 1         # a masked token is never drawn
+
+
+def test_logprobs_by_hand():
+    """log softmax of [0, ln 2, ln 5] is [-ln 8, ln 2 - ln 8, ln 5 - ln 8]; the largest first, equal logits
+    lower index first, -inf left out (crates/rllm-sampling/src/logprobs.rs:5-28, 34-70)."""
+    import math
+    import numpy as np
+    import plain_llama as pl
+    x = np.array([0.0, math.log(2.0), math.log(5.0)], dtype=np.float32)
+    assert abs(pl.logprob_of(x, 0) + math.log(8.0)) < 1e-6
+    assert abs(pl.logprob_of(x, 2) - (math.log(5.0) - math.log(8.0))) < 1e-6
+    assert pl.logprob_of(x, 3) == -math.inf
+    top = pl.top_logprobs(x, 2)
+    assert [i for i, _ in top] == [2, 1] and abs(top[1][1] - (math.log(2.0) - math.log(8.0))) < 1e-6
+    y = np.array([1.0, -np.inf, 1.0, 0.0], dtype=np.float32)
+    assert [i for i, _ in pl.top_logprobs(y, 5)] == [0, 2, 3]
+    assert pl.top_logprobs(np.array([-np.inf, -np.inf]), 1) == [] and pl.top_logprobs(x, 0) == []
