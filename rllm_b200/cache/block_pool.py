@@ -36,7 +36,7 @@ def core():
         lib = load_library("cache_core")
         for name in ("rllm_pool_new", "rllm_cache_new", "rllm_cache_pool"):
             getattr(lib, name).restype = c_void_p
-        for name in ("rllm_page_hashes", "rllm_cache_match_prefix", "rllm_cache_adopt_prefix"):
+        for name in ("rllm_page_hashes", "rllm_cache_match_prefix", "rllm_cache_adopt_prefix", "rllm_cache_max_tokens"):
             getattr(lib, name).restype = ctypes.c_longlong
         lib.rllm_pool_delete.restype = None
         lib.rllm_cache_delete.restype = None

@@ -194,6 +194,14 @@ class CacheManager:
             raise KeyError(req)
         return bool(rc)
 
+    def max_tokens(self, req: Hashable, first_query_pos: int) -> int:
+        """The largest ``num_tokens`` for which ``ensure(req, first_query_pos, num_tokens)``
+        would succeed now.  Gives back the pages behind the window first, as ``ensure`` does."""
+        n = core().rllm_cache_max_tokens(self._h, self._id(req), c_longlong(first_query_pos))
+        if n < 0:
+            raise KeyError(req)
+        return int(n)
+
     def fits_at_all(self, num_tokens: int) -> bool:
         """Could one request of ``num_tokens`` tokens ever be held?"""
         return bool(core().rllm_cache_fits_at_all(self._h, c_longlong(num_tokens)))

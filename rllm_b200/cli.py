@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 import time
 from typing import List
@@ -73,7 +74,9 @@ def build_parser() -> argparse.ArgumentParser:
                    help="draw weights from --weights-seed; the folder needs config.json only")
     g.add_argument("--weights-seed", type=int, default=0)
     g.add_argument("--json", action="store_true", help="one JSON object per request on stdout")
-    g.add_argument("--log-level", default="info")
+    g.add_argument("--log-level", default=None,
+                   help="error | warn | info | debug (one line of statistics per step) | trace; "
+                        "default: the environment variable RLLM_LOG, else info")
 
     r = sub.add_parser("init-random", help="write a model folder with random weights")
     r.add_argument("model", help="folder to write")
@@ -96,6 +99,8 @@ def _prompts(args) -> List[List[int]]:
 def cmd_generate(args) -> int:
     from . import LLM, SamplingParams
     from .config import read_config_json
+    from . import log
+    log.set_level(args.log_level or os.environ.get("RLLM_LOG") or "info")
     model_dir = args.model or args.model_opt
     if not model_dir:
         print("rllm generate: a model folder is required", file=sys.stderr)
@@ -140,8 +145,8 @@ def cmd_generate(args) -> int:
         else:
             print(f"request {o.request_id}: {o.outputs[0].token_ids}  [{o.outputs[0].finish_reason}; "
                   f"{o.usage.prompt_tokens} prompt + {o.usage.completion_tokens} generated]")
-    print(f"{n_out} tokens in {dt:.3f} s ({n_out / max(dt, 1e-9):.1f} tok/s), "
-          f"{llm.engine.num_steps} steps", file=sys.stderr)
+    log.logger.info(f"{n_out} tokens in {dt:.3f} s ({n_out / max(dt, 1e-9):.1f} tok/s), "
+                    f"{llm.engine.num_steps} steps; {json.dumps(llm.engine.stats())}")
     return 0
 
 

@@ -21,6 +21,7 @@ from ..cache import CacheManager, CacheStorage, page_bytes
 from ..config.engine_args import EngineArgs
 from ..models.decoder import DecoderModel
 from ..parts.spec import KVPagesNeed
+from .. import log
 from ..sampling import Sampler, SamplingParams, SamplingRow
 from .runner import ModelRunner, StepEntry
 from .scheduler import Request, RequestStatus, Scheduler, SchedulerConfig, SchedulerOutput
@@ -153,6 +154,10 @@ class EngineCore:
 
     # ------------------------------------------------------------------
     def step(self) -> List[RequestOutput]:
+        with log.span("engine_step"):
+            return self._step()
+
+    def _step(self) -> List[RequestOutput]:
         inflight, self._inflight = self._inflight, None
         prepared, self._prepared = self._prepared, None
         if inflight is not None and not any(r.status is RequestStatus.RUNNING for r in inflight[1]):
@@ -173,10 +178,16 @@ class EngineCore:
             wanted_lp = self._logprobs(raw, sampled, sampled_reqs)
             pending = self._read_back(sampled, graph)
         else:
-            sched = self.scheduler.schedule()
+            with log.span("schedule"):
+                sched = self.scheduler.schedule()
             self.last_schedule = sched
             self.num_steps += 1
             if not sched.scheduled:
+                if not sched.preempted and not self.scheduler.running and self.scheduler.waiting:
+                    # nothing runs, nothing was preempted and still nobody could be admitted: no later
+                    # call would do better, and a caller that loops on has_work() would never return
+                    raise RuntimeError("the scheduler cannot admit any waiting request although nothing is "
+                                       f"running (cache: {self.cache.usage()})")
                 return []
             entries, sampled_reqs = [], []
             plain_greedy = True            # every sampled row: argmax of untouched logits
@@ -188,9 +199,11 @@ class EngineCore:
                     sampled_reqs.append(req)
                     p = req.params
                     plain_greedy = plain_greedy and p.greedy and not p.edits_logits
-            logits = self.runner.step(entries)
+            with log.span("model_forward"):
+                logits = self.runner.step(entries)
             raw = self._raw_logits(logits, sampled_reqs)
-            sampled = self._sample(logits, sampled_reqs, plain_greedy, 0)
+            with log.span("sampling"):
+                sampled = self._sample(logits, sampled_reqs, plain_greedy, 0)
             wanted_lp = self._logprobs(raw, sampled, sampled_reqs)
             pending = self._read_back(sampled)
         # requests that ended (or were aborted) after this step went to the GPU: their rows are dropped
@@ -225,6 +238,12 @@ class EngineCore:
             outputs.append(RequestOutput(req.request_id, req.prompt_token_ids,
                                          [CompletionOutput(0, [int(tok)], reason, lps.get(row))], reason is not None,
                                          Usage(n_prompt, n_out, n_prompt + n_out)))
+        if log.logger.isEnabledFor(log.logging.DEBUG):
+            log.logger.debug("step %d: %d prompt + %d decode tokens, %d sampled, %d finished, %d preempted; "
+                             "running %d waiting %d free pages %d", self.num_steps, sched.num_prefill_tokens,
+                             sched.num_decode_tokens, len(sampled_reqs), sum(o.finished for o in outputs),
+                             len(sched.preempted), len(self.scheduler.running), len(self.scheduler.waiting),
+                             self.cache.num_free_pages())
         if nxt is not None and not any_finished and not self.scheduler.waiting:
             by_req = {r.request_id: t for r, t in zip(sampled_reqs, tokens)}
             nxt[3].patch_tokens([by_req[s.request.request_id] for s in nxt[0].scheduled])

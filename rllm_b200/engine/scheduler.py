@@ -24,7 +24,10 @@ preempted.  A preempted request keeps its prompt and what it generated and
 computes them again when readmitted; its samples are unchanged because its
 random stream is indexed by the generated token.  A request that could never
 fit (prompt plus ``max_tokens`` beyond ``max_model_len`` or beyond all pages)
-is refused when it is added, so the loop cannot wait for ever.
+is refused when it is added, so the loop cannot wait for ever.  Where a group
+of layers keeps a window only, a request fits as soon as the window does; a
+portion that would need more pages than are free (window plus portion) is cut
+down to what fits instead of preempting the only request that could run.
 """
 from __future__ import annotations
 
@@ -194,6 +197,13 @@ class Scheduler:
                 continue
             while not self.cache.ensure(req.request_id, req.num_computed, req.num_computed + n):
                 victim = max(self.running, key=lambda r: r.arrival)
+                if victim is req and n > 1:
+                    # nobody newer to take pages from: a shorter portion may still fit (a window gives
+                    # pages back on the way, so the rest follows in later steps)
+                    fit = self.cache.max_tokens(req.request_id, req.num_computed) - req.num_computed
+                    if fit >= 1:
+                        n = min(n, fit)
+                        continue
                 self._preempt(victim, out)
                 if victim is req:
                     break
@@ -214,6 +224,12 @@ class Scheduler:
             cached = self.cache.adopt_prefix(req.request_id, tokens)
             req.num_computed = cached
             n = self._portion(req, budget)
+            if not self.running and self.config.enable_chunked_prefill and n > 1:
+                # the pools are empty and the portion still does not fit (a window plus the portion
+                # needs more pages than the window alone): start with what fits
+                fit = self.cache.max_tokens(req.request_id, req.num_computed) - req.num_computed
+                if 1 <= fit < n:
+                    n = fit
             whole = n == req.num_tokens - req.num_computed
             if (not whole and not self.config.enable_chunked_prefill) or \
                     not self.cache.ensure(req.request_id, req.num_computed, req.num_computed + n):

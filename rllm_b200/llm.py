@@ -84,7 +84,16 @@ class LLM:
         self.engine.runner.check_errors()          # the steps polled the kernels' error words; this waits for the last
         results = []
         for rid in ids:
-            out = final[rid]
+            out = final.get(rid)
+            if out is None:
+                # aborted from outside (``abort_request``) while this call was stepping: what it had generated
+                # by then is returned, with the reference's reason for it (crates/rllm-core/src/output.rs:37-42)
+                prompt = [int(t) for t in prompt_token_ids[ids.index(rid)]]
+                n_out = len(tokens[rid])
+                results.append(RequestOutput(rid, prompt, [CompletionOutput(0, tokens[rid], "aborted",
+                                                                            logprobs[rid] or None)],
+                                             True, Usage(len(prompt), n_out, len(prompt) + n_out)))
+                continue
             results.append(RequestOutput(rid, out.prompt_token_ids,
                                          [CompletionOutput(0, tokens[rid], out.outputs[0].finish_reason,
                                                            logprobs[rid] if out.outputs[0].logprobs is not None else None)],

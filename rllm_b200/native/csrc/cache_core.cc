@@ -432,6 +432,22 @@ API int rllm_cache_ensure(void* h, int64_t id, long long first_query_pos, long l
   }
   return 1;
 }
+// The largest num_tokens for which rllm_cache_ensure(id, first_query_pos, num_tokens) would succeed now.
+// Gives back the pages behind the window of first_query_pos first (ensure would do the same).
+API long long rllm_cache_max_tokens(void* h, int64_t id, long long first_query_pos) {
+  Manager* m = M(h);
+  Req* r = m->find(id);
+  if (!r) return RC_UNKNOWN_REQ;
+  m->release_behind_window(r, first_query_pos);
+  long long best = -1;
+  for (int g : m->paged) {
+    long long first = m->first_needed_page(g, first_query_pos);
+    if ((long long)r->tables[g].size() > first) first = (long long)r->tables[g].size();
+    const long long upto = (first + m->pools[g]->num_free()) * m->page_size;
+    if (best < 0 || upto < best) best = upto;
+  }
+  return best < 0 ? (1LL << 62) : best;
+}
 API int rllm_cache_fits_at_all(void* h, long long num_tokens) {
   Manager* m = M(h);
   const long long want = (num_tokens + m->page_size - 1) / m->page_size;

@@ -185,3 +185,37 @@ def test_random_workloads_finish_within_limits(seed):
         assert steps < 5000
     assert all(len(r.output_token_ids) == r.max_tokens for r in done.values())
     assert cache.num_free_pages() == 24 and cache.usage()["free_slots"] == 4
+
+
+def test_a_window_smaller_than_window_plus_portion_still_makes_progress():
+    """A group that keeps a window of 24 keys, portions of 64 tokens and a pool of 4 pages of 16: the
+    window fits (so the request is accepted), window plus portion does not.  The portion is cut to what
+    fits, the window gives pages back on the way, and the request finishes without a preemption."""
+    need = KVPagesNeed(2, 16, 24)
+    cache = CacheManager([need], 16, 4, 4)
+    s = Scheduler(SchedulerConfig(max_num_seqs=4, max_num_batched_tokens=64, long_prefill_token_threshold=64,
+                                  max_model_len=4096), cache)
+    s.add_request(req(0, 200, max_tokens=40))
+    s.add_request(req(1, 90, max_tokens=5))
+    steps, sizes = 0, []
+    while s.has_work():
+        out = run_step(s)
+        assert out.scheduled, "a step without tokens while requests wait: the loop would never end"
+        sizes.append([x.num_tokens for x in out.scheduled])
+        steps += 1
+        assert steps < 400
+    assert s.num_preemptions == 0
+    assert sizes[0] == [64] and sizes[1] == [32]               # 4 pages, then what the window leaves free
+    assert cache.num_free_pages() == 4 and cache.usage()["free_slots"] == 4
+
+
+def test_max_tokens_is_what_ensure_takes():
+    cache = CacheManager([KVPagesNeed(2, 16, None), KVPagesNeed(2, 16, 10)], 8, [6, 3], 2)
+    cache.admit("a")
+    assert cache.max_tokens("a", 0) == 24                        # the windowed pool: 3 pages of 8
+    assert cache.ensure("a", 0, 24) and not cache.ensure("a", 24, 25 + 8)
+    # queries from 24 on see keys 15..: pages 0 of the windowed group can go, one page comes free
+    assert cache.max_tokens("a", 24) == 32
+    assert cache.ensure("a", 24, 32) and cache.max_tokens("a", 32) == 40
+    cache.free("a")
+    cache.check()
