@@ -11,8 +11,9 @@ State group: every owning run gets float32 [max_seqs, *shape], indexed by a
 request's state slot.  All storage is allocated once, here.
 
 Every paged buffer has one page more than the manager hands out: page
-``spare_page(group)`` belongs to no request.  The rows that pad a decode step to
-a captured batch size read and write there.
+``spare_page(group)`` belongs to no request; every state buffer has one slot
+more, ``spare_slot``.  The rows that pad a decode step to a captured batch size
+read and write there.
 """
 from __future__ import annotations
 
@@ -39,6 +40,7 @@ class CacheStorage:
         paged = [g for g, n in enumerate(layout.groups) if isinstance(n, KVPagesNeed)]
         pages_of = dict(zip(paged, num_pages))
         self._pages_of = pages_of
+        self.spare_slot = max_seqs           # the state slot that no request ever holds
         for g, need in enumerate(layout.groups):
             for run in layout.owners[g]:
                 if isinstance(need, KVPagesNeed):
@@ -46,7 +48,7 @@ class CacheStorage:
                     self.kv[run] = (torch.zeros(shape, dtype=dtype, device=device),
                                     torch.zeros(shape, dtype=dtype, device=device))
                 elif isinstance(need, StateNeed):
-                    self.state[run] = torch.zeros((max_seqs,) + tuple(need.shape), dtype=torch.float32,
+                    self.state[run] = torch.zeros((max_seqs + 1,) + tuple(need.shape), dtype=torch.float32,
                                                   device=device)
                 else:
                     raise TypeError(f"unknown cache need {need!r}")

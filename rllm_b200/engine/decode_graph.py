@@ -21,8 +21,9 @@ use, on a private stream; batches of up to 8 get a graph of their own size,
 larger ones are padded to the next size of ``batch_bucket`` (steps of 4, 8, 16,
 ...), so that a batch that shrinks request by request keeps finding captured
 graphs.  A padding row is a request of one token at position 0 whose block
-table names only the storage's spare page: it reads and writes nothing that a
-request holds, and its logits are dropped.
+table names only the storage's spare page and whose state slot is the spare
+one: it reads and writes nothing that a request holds, and its logits are
+dropped.
 """
 from __future__ import annotations
 
@@ -157,7 +158,7 @@ class DecodeGraph:
             h[self.r_tokens[0] + s] = 0
             h[self.r_pos[0] + s] = 0
             h[self.r_seqlens[0] + s] = 1
-            h[self.r_slots[0] + s] = 0
+            h[self.r_slots[0] + s] = self.runner.storage.spare_slot
             for g, r in zip(self.paged, self.r_tables):
                 tab = h[r[0]:r[1]].reshape(S, W)
                 tab[s, :] = -1

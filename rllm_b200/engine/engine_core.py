@@ -67,31 +67,50 @@ class RequestOutput:
     usage: Usage
 
 
-def plan_cache_pages(model: DecoderModel, args: EngineArgs, max_model_len: int, device: torch.device) -> int:
-    """Pages per paged group.  ``num_gpu_blocks`` if given; else what fits into
-    ``gpu_memory_utilization`` of the device's memory beside the weights and a
-    reserve for activations, capped at the reference's sizing rule
-    max_num_seqs * ceil(max_model_len / block_size)
-    (crates/rllm-server/src/server.rs:367-370)."""
-    if args.num_gpu_blocks is not None:
-        return args.num_gpu_blocks
+def plan_cache_pages(model: DecoderModel, args: EngineArgs, max_model_len: int, device: torch.device) -> List[int]:
+    """Pages of every paged group of layers, in the order of the groups.
+
+    A group that keeps all keys can use max_num_seqs * ceil(max_model_len / block_size) pages, the
+    reference's sizing rule (crates/rllm-server/src/server.rs:367-370).  A group that keeps a window
+    holds, per request, the window plus the portion being computed, so it is given
+    ceil((window + portion) / block_size) + 1 pages a request and never more than the rule above.
+    ``num_gpu_blocks``, if given, is the count of the all-keys groups (windowed groups take no more than
+    they can use).  Otherwise the counts come from memory, as the reference's unused formula intends
+    (crates/rllm-cache/src/spec.rs:45-60: available bytes / bytes of a page over all layers): what
+    ``gpu_memory_utilization`` of the device leaves beside the weights and a reserve for activations
+    is shared so that every group gets the same fraction of what it can use."""
+    bs = args.block_size
     elem = 2 if model.dtype is torch.bfloat16 else 4
-    per_page = 0
+    portion = args.max_num_batched_tokens
+    if args.long_prefill_token_threshold > 0:
+        portion = min(portion, args.long_prefill_token_threshold)
+    full = -(-max_model_len // bs)
+    useful, nbytes = [], []
     for g, need in enumerate(model.layout.groups):
-        if isinstance(need, KVPagesNeed):
-            per_page += page_bytes(need, args.block_size, elem) * len(model.layout.owners[g])
-    cap = args.max_num_seqs * -(-max_model_len // args.block_size)
-    if per_page == 0:
-        return 1
+        if not isinstance(need, KVPagesNeed):
+            continue
+        per_request = full if need.window is None else min(full, -(-(need.window + portion) // bs) + 1)
+        useful.append(args.max_num_seqs * per_request)
+        nbytes.append(page_bytes(need, bs, elem) * len(model.layout.owners[g]))
+    if not useful:
+        return []
+    if args.num_gpu_blocks is not None:
+        return [min(args.num_gpu_blocks, u) if need_windowed else args.num_gpu_blocks
+                for u, need_windowed in zip(useful, _windowed(model))]
     free, total = torch.cuda.mem_get_info(device)
     spec = model.spec
     act = args.max_num_batched_tokens * (spec.hidden_size * 16 + 64 * 1024) + \
         min(args.max_num_seqs, args.max_num_batched_tokens) * spec.vocab_size * 8 + (1 << 30)
     budget = int(total * args.gpu_memory_utilization) - (total - free) - act
-    if budget < per_page * 4:
+    if budget < 4 * sum(nbytes):
         raise RuntimeError(f"no room for a KV cache: {free >> 20} MiB free of {total >> 20} MiB with "
                            f"gpu_memory_utilization {args.gpu_memory_utilization}")
-    return max(4, min(cap, budget // per_page))
+    share = min(1.0, budget / sum(u * b for u, b in zip(useful, nbytes)))
+    return [max(4, int(u * share)) for u in useful]
+
+
+def _windowed(model: DecoderModel) -> List[bool]:
+    return [need.window is not None for need in model.layout.groups if isinstance(need, KVPagesNeed)]
 
 
 class EngineCore:
@@ -104,11 +123,11 @@ class EngineCore:
         self.device = model.device
         spec = model.spec
         self.max_model_len = min(self.args.max_model_len or spec.max_positions, spec.max_positions)
-        n_paged = sum(1 for n in model.layout.groups if isinstance(n, KVPagesNeed))
         pages = plan_cache_pages(model, self.args, self.max_model_len, self.device)
-        self.cache = CacheManager(model.layout.groups, self.args.block_size, [pages] * n_paged,
+        self.num_pages = list(pages)
+        self.cache = CacheManager(model.layout.groups, self.args.block_size, pages,
                                   self.args.max_num_seqs, self.args.enable_prefix_caching)
-        self.storage = CacheStorage(model.layout, self.args.block_size, [pages] * n_paged,
+        self.storage = CacheStorage(model.layout, self.args.block_size, pages,
                                     self.args.max_num_seqs, model.dtype, self.device)
         self.runner = ModelRunner(model, self.cache, self.storage, self.args.enable_cuda_graphs)
         self.sampler = Sampler(self.device)

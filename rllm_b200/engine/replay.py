@@ -17,7 +17,9 @@ float32 [wanted, vocab] in the order of the entries and of ``want``.  After
 every step a line ``done <step>`` is printed and flushed.  ``--max-tokens`` is
 the most tokens live requests hold at any time (each request rounded up to a
 multiple of 64); the page pool is made for exactly that many, so pages of
-finished requests are used again.
+finished requests are used again.  ``--max-live`` (8) is the most requests
+that are live at a time; a trace that exceeds either limit ends with exit code
+3 and a message that names the step.
 
 The reference has nothing comparable; the nearest is its hand-stepped sampler
 check (crates/rllm-bench/tests/correctness.rs:120-188).
@@ -31,7 +33,6 @@ import sys
 from typing import Dict, List
 
 PAGE_SIZE = 16
-MAX_LIVE = 8
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -42,6 +43,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-tokens", type=int, required=True,
                    help="most tokens live requests hold at any time")
     p.add_argument("--block-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
+    p.add_argument("--max-live", type=int, default=8,
+                   help="most requests that are live at a time (state slots of the cache manager)")
     p.add_argument("--device", default="cuda:0")
     return p
 
@@ -61,8 +64,9 @@ def main(argv=None) -> int:
     page = args.block_size
     num_pages = max(1, -(-args.max_tokens // page))
     paged = [n for n in model.layout.groups if hasattr(n, "num_kv_heads")]
-    cache = CacheManager(model.layout.groups, page, [num_pages] * len(paged), MAX_LIVE)
-    storage = CacheStorage(model.layout, page, [num_pages] * len(paged), MAX_LIVE, model.dtype, model.device)
+    max_live = max(1, args.max_live)
+    cache = CacheManager(model.layout.groups, page, [num_pages] * len(paged), max_live)
+    storage = CacheStorage(model.layout, page, [num_pages] * len(paged), max_live, model.dtype, model.device)
     runner = ModelRunner(model, cache, storage)
     fed: Dict[str, int] = {}
 
@@ -78,6 +82,10 @@ def main(argv=None) -> int:
             if not tokens:
                 continue
             if rid not in fed:
+                if not cache.has_free_slot():
+                    print(f"trace_run: step {step}: request {rid!r} would be live request number "
+                          f"{len(fed) + 1}; --max-live is {max_live}", file=sys.stderr)
+                    return 3
                 cache.admit(rid)
                 fed[rid] = 0
             start = fed[rid]

@@ -172,8 +172,7 @@ class ModelRunner:
         from .decode_graph import DecodeGraph, batch_bucket, table_width_bucket
         page = self.cache.page_size
         blocks = max(-(-(e.start + 1) // page) for e in entries)
-        # padding rows use the spare page and state slot 0: only where no run keeps per-request state
-        pad = pad and not self.storage.state
+        # padding rows live on the storage's spare page and spare state slot
         key = (batch_bucket(len(entries)) if pad else len(entries), table_width_bucket(blocks))
         g = self.graphs.get(key)
         if g is None:

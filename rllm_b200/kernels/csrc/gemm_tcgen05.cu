@@ -224,6 +224,19 @@ static int tg_make_map(CUtensorMap* map, const void* ptr, int rows, int K, int l
   return r == CUDA_SUCCESS ? 0 : RLLM_E_BADARG;
 }
 
+// SMs of the current device (asked once per device)
+static int tg_num_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (!cached[dev]) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n > 0 ? n : 1;
+  }
+  return cached[dev];
+}
+
 template <int BN, int EPI>
 static int tg_launch(const void* a, int lda, const void* w, int ldw, int w_rows, void* out, int ldo, int M, int N,
                      int K, int up_offset, int* err, cudaStream_t stream) {
@@ -243,13 +256,7 @@ static int tg_launch(const void* a, int lda, const void* w, int ldw, int w_rows,
   const int tiles_m = (M + TG_BM - 1) / TG_BM;
   const long long num_tiles = (long long)tiles_m * ((N + NOUT - 1) / NOUT);
   if (num_tiles > (1ll << 30)) return RLLM_E_UNSUPPORTED;
-  static int num_sms = 0;
-  if (!num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (num_sms <= 0) num_sms = 148;
-  }
+  const int num_sms = tg_num_sms();
   const int grid = (int)(num_tiles < num_sms ? num_tiles : num_sms);
   gemm_tcgen05_kernel<BN, EPI><<<grid, TG_THREADS, tg_smem_bytes<BN>(), stream>>>(ma, mw, out, ldo, M, N, K, up_offset,
                                                                                   tiles_m, (int)num_tiles, err);
@@ -269,7 +276,7 @@ RLLM_EXPORT int rllm_gemm_tcgen05(const void* a, int lda, const void* w, int ldw
   // width x a factor for what a narrower tile costs (A is read again more often, the epilogue overlaps less).
   int bn = N > 192 ? 256 : (N > 128 ? 192 : 128);
   if (N > 128) {
-    const long long tm = (M + TG_BM - 1) / TG_BM, sms = 148;
+    const long long tm = (M + TG_BM - 1) / TG_BM, sms = tg_num_sms();
     double best = 1e30;
     const int widths[3] = {256, 192, 128};
     const double factor[3] = {1.0, 1.05, 1.3};

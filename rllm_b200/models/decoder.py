@@ -45,8 +45,8 @@ class DecoderModel:
         self.embedding = TokenEmbedding(spec.embedding)
         self.blocks = []
         for ls in spec.layers:
-            mixer = part_registry.build_part("mixer", ls.mixer, prefix=ls.prefix + _sub(ls.mixer, "self_attn."))
-            ffn = part_registry.build_part("feed_forward", ls.ffn, prefix=ls.prefix + _sub(ls.ffn, "mlp."))
+            mixer = part_registry.build_part("mixer", ls.mixer, prefix=ls.prefix + _sub(ls.mixer))
+            ffn = part_registry.build_part("feed_forward", ls.ffn, prefix=ls.prefix + _sub(ls.ffn))
             norms = [part_registry.build_part("norm", n, prefix=ls.prefix) for n in ls.norms]
             if ls.block not in part_registry.BLOCKS:
                 raise KeyError(f"no block arrangement {ls.block!r}; known: {sorted(part_registry.BLOCKS)}")
@@ -75,7 +75,8 @@ class DecoderModel:
         return list(seen.values())
 
     def load(self, source: WeightSource, run_dtype: torch.dtype, device: torch.device) -> None:
-        tensors = load_tensors(self.tensor_specs(), source, run_dtype, device)
+        ignored = [n for part in self.parts() for n in part.ignored_tensors()]
+        tensors = load_tensors(self.tensor_specs(), source, run_dtype, device, ignored)
         for part in self.parts():
             part.load(tensors)
         self.dtype, self.device = run_dtype, device
@@ -140,7 +141,8 @@ class DecoderModel:
         return self.head.forward(xn)
 
 
-def _sub(part_spec, default: str) -> str:
-    """Tensor-name segment between the layer prefix and a part's tensors."""
+def _sub(part_spec) -> str:
+    """Tensor-name segment between the layer prefix and a part's tensors: the spec's
+    ``tensor_prefix`` (none: the part's tensors lie directly under the layer prefix)."""
     sub = part_spec.get().get("tensor_prefix")
-    return default if sub is None else str(sub)
+    return "" if sub is None else str(sub)

@@ -17,11 +17,17 @@ from ..parts.spec import LayerSpec, ModelSpec, PartSpec, Run
 def llama_spec(cfg: LlamaConfig) -> ModelSpec:
     scaling = cfg.rope_scaling.to_json() if cfg.rope_scaling else None
     position = PartSpec.of("rotary", head_dim=cfg.head_dim, rotary_dim=cfg.head_dim,
-                           theta=cfg.rope_theta, scaling=scaling)
+                           theta=cfg.rope_theta, scaling=scaling,
+                           ignored_tensors=("rotary_emb.inv_freq",))      # older checkpoints store the table
     mixer = PartSpec.of("attention", hidden_size=cfg.hidden_size, num_heads=cfg.num_attention_heads,
                         num_kv_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, window=None,
-                        scale=None, position=position)
-    ffn = PartSpec.of("gated_mlp", hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size)
+                        scale=None, position=position, tensor_prefix="self_attn.",
+                        tensor_names={"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight",
+                                      "o": "o_proj.weight"})
+    ffn = PartSpec.of("gated_mlp", hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+                      tensor_prefix="mlp.",
+                      tensor_names={"gate": "gate_proj.weight", "up": "up_proj.weight",
+                                    "down": "down_proj.weight"})
     norms = (PartSpec.of("rmsnorm", size=cfg.hidden_size, eps=cfg.rms_norm_eps, name="input_layernorm.weight"),
              PartSpec.of("rmsnorm", size=cfg.hidden_size, eps=cfg.rms_norm_eps,
                          name="post_attention_layernorm.weight"))

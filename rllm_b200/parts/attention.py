@@ -15,7 +15,9 @@ of this step are written to the cache first and every query then reads keys
 
 params: hidden_size, num_heads, num_kv_heads, head_dim, window (None: all
 keys), scale (None: 1/sqrt(head_dim)), position (PartSpec), shares_kv (True:
-the run reads another run's cache, has no k/v projections and writes nothing).
+the run reads another run's cache, has no k/v projections and writes nothing),
+tensor_names (the names of the four projection weights below the part's prefix,
+keys "q", "k", "v", "o": the architecture gives them, the part knows none).
 """
 from __future__ import annotations
 
@@ -52,15 +54,23 @@ class PagedAttention(Mixer):
             raise ValueError(f"num_heads {self.nq} must be a multiple of num_kv_heads {self.nkv}")
         if self.d % 16 or self.d > 256:
             raise ValueError(f"head_dim {self.d}: the attention kernels take multiples of 16 up to 256")
+        names = dict(p.get("tensor_names") or ())
+        if sorted(names) != ["k", "o", "q", "v"]:
+            raise ValueError("an attention spec names its weights: tensor_names with the keys q, k, v, o")
+        self.names = {k: str(v) for k, v in names.items()}
         pos = p.get("position")
-        self.position = build_part("position_encoding", pos if pos is not None else PartSpec.of("none"))
+        self.position = build_part("position_encoding", pos if pos is not None else PartSpec.of("none"),
+                                   prefix=prefix)
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
 
     # -- weights ----------------------------------------------------------
     def _names(self):
         p = self.prefix
-        return (p + "q_proj.weight", p + "k_proj.weight", p + "v_proj.weight", p + "o_proj.weight")
+        return tuple(p + self.names[k] for k in ("q", "k", "v", "o"))
+
+    def ignored_tensors(self) -> List[str]:
+        return self.position.ignored_tensors()
 
     def tensor_specs(self) -> List[TensorSpec]:
         q, k, v, o = self._names()

@@ -151,6 +151,11 @@ class Part:
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Take this part's tensors (by full name) from ``tensors``."""
 
+    def ignored_tensors(self) -> List[str]:
+        """Full names of tensors that a weight file of this part's family may carry and the part
+        does not need (buffers that it computes itself): present, they are no error."""
+        return []
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:

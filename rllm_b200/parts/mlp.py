@@ -3,7 +3,8 @@
 over the stacked weights [Wgate; Wup]; silu(z) = z / (1 + exp(-z)) and the
 product with up are computed in float32.
 
-params: hidden_size, intermediate_size.
+params: hidden_size, intermediate_size, tensor_names (the names of the three
+weights below the part's prefix, keys "gate", "up", "down").
 """
 from __future__ import annotations
 
@@ -27,12 +28,16 @@ class GatedMLP(FeedForward):
         super().__init__(spec, prefix)
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
+        names = dict(spec.get().get("tensor_names") or ())
+        if sorted(names) != ["down", "gate", "up"]:
+            raise ValueError("a gated_mlp spec names its weights: tensor_names with the keys gate, up, down")
+        self.names = {k: str(v) for k, v in names.items()}
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
     def _names(self):
         p = self.prefix
-        return p + "gate_proj.weight", p + "up_proj.weight", p + "down_proj.weight"
+        return tuple(p + self.names[k] for k in ("gate", "up", "down"))
 
     def tensor_specs(self) -> List[TensorSpec]:
         g, u, d = self._names()

@@ -47,7 +47,9 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict]) -
 
 @register_part("position_encoding", "rotary")
 class Rotary(PositionEncoding):
-    """params: head_dim, rotary_dim (<= head_dim, even), theta, scaling (dict or None)."""
+    """params: head_dim, rotary_dim (<= head_dim, even), theta, scaling (dict or None),
+    ignored_tensors (names below the mixer's prefix under which checkpoints of the family store
+    a frequency table; it is computed here, so such a tensor is passed over)."""
     graph_safe = True
 
     def __init__(self, spec: PartSpec, prefix: str = ""):
@@ -61,6 +63,10 @@ class Rotary(PositionEncoding):
         self.scaling = dict(scaling) if scaling else None
         self.freqs = rotary_frequencies(self.rotary_dim, float(p["theta"]), self.scaling)
         self._table: Optional[torch.Tensor] = None
+        self._ignored = [prefix + str(n) for n in (p.get("ignored_tensors") or ())]
+
+    def ignored_tensors(self) -> List[str]:
+        return list(self._ignored)
 
     def load(self, tensors) -> None:
         pass

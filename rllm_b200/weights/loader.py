@@ -28,10 +28,6 @@ import torch
 from ..parts.spec import TensorSpec
 from .safetensors_io import SafetensorsFile, WeightsError, find_weight_files, write_safetensors
 
-# tensors that checkpoints of this family carry and no part needs
-_IGNORED_SUFFIXES = ("rotary_emb.inv_freq",)
-
-
 class WeightsMismatch(WeightsError):
     def __init__(self, missing: Sequence[str], unexpected: Sequence[str],
                  wrong_shape: Sequence[Tuple[str, Tuple[int, ...], Tuple[int, ...]]],
@@ -154,11 +150,13 @@ def _held_dtype(spec: TensorSpec, stored: torch.dtype, run_dtype: torch.dtype) -
     return run_dtype
 
 
-def check_tensors(specs: Sequence[TensorSpec], source: WeightSource) -> None:
+def check_tensors(specs: Sequence[TensorSpec], source: WeightSource, ignored: Iterable[str] = ()) -> None:
+    """``ignored``: full names that the model's parts declared as present-but-unused."""
     have = set(source.names())
     want = {s.name: s for s in specs}
+    skip = set(ignored)
     missing = sorted(n for n, s in want.items() if n not in have and not s.optional)
-    unexpected = sorted(n for n in have if n not in want and not n.endswith(_IGNORED_SUFFIXES))
+    unexpected = sorted(n for n in have if n not in want and n not in skip)
     wrong_shape, wrong_kind = [], []
     for n, s in want.items():
         if n not in have:
@@ -173,9 +171,9 @@ def check_tensors(specs: Sequence[TensorSpec], source: WeightSource) -> None:
 
 
 def load_tensors(specs: Sequence[TensorSpec], source: WeightSource, run_dtype: torch.dtype,
-                 device: torch.device) -> Dict[str, torch.Tensor]:
+                 device: torch.device, ignored: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
     """name -> tensor on ``device`` for every spec the source has."""
-    check_tensors(specs, source)
+    check_tensors(specs, source, ignored)
     have = set(source.names())
     out: Dict[str, torch.Tensor] = {}
     for s in specs:

@@ -30,6 +30,12 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
 
 
+# the checkpoint names of the Llama family, for specs that tests write by hand (a spec names its tensors)
+ATT_NAMES = dict(tensor_prefix="self_attn.", tensor_names={"q": "q_proj.weight", "k": "k_proj.weight",
+                                                            "v": "v_proj.weight", "o": "o_proj.weight"})
+MLP_NAMES = dict(tensor_prefix="mlp.", tensor_names={"gate": "gate_proj.weight", "up": "up_proj.weight",
+                                                      "down": "down_proj.weight"})
+
 TINY_A = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama",
     "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,

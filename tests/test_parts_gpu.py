@@ -9,6 +9,7 @@ import pytest
 import torch
 
 import plain_llama as pl
+from conftest import ATT_NAMES, MLP_NAMES
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
@@ -79,7 +80,7 @@ def test_rotary_part_builds_the_scaled_table():
 @pytest.mark.parametrize("dt", DTYPES)
 def test_feed_forward_part(dt):
     from rllm_b200.parts import PartSpec, build_part
-    mlp = build_part("feed_forward", PartSpec.of("gated_mlp", hidden_size=72, intermediate_size=200), prefix="m.")
+    mlp = build_part("feed_forward", PartSpec.of("gated_mlp", **MLP_NAMES, hidden_size=72, intermediate_size=200), prefix="m.")
     w = load_part(mlp, dt)
     x = (torch.randn(9, 72, device=DEV) * 2).to(dt)
     want = pl.gated_mlp(x.double().cpu(), w["m.gate_proj.weight"], w["m.up_proj.weight"], w["m.down_proj.weight"])
@@ -125,7 +126,7 @@ def test_attention_part_in_portions(dt, nq, nkv, d, rd, window, page):
     from rllm_b200.parts import PartSpec, build_part
     hidden = 56
     pos = PartSpec.of("rotary", head_dim=d, rotary_dim=rd, theta=5000.0, scaling=None)
-    att = build_part("mixer", PartSpec.of("attention", hidden_size=hidden, num_heads=nq, num_kv_heads=nkv,
+    att = build_part("mixer", PartSpec.of("attention", **ATT_NAMES, hidden_size=hidden, num_heads=nq, num_kv_heads=nkv,
                                           head_dim=d, window=window, scale=None, position=pos), prefix="a.")
     w = load_part(att, dt)
     need = att.cache_need()
@@ -168,9 +169,9 @@ def toy_spec(kind):
         pos = PartSpec.of("rotary", head_dim=16, rotary_dim=16, theta=1000.0, scaling=None)
         return LayerSpec(
             block="pre_norm",
-            mixer=PartSpec.of("attention", hidden_size=H, num_heads=4, num_kv_heads=nkv, head_dim=16,
+            mixer=PartSpec.of("attention", **ATT_NAMES, hidden_size=H, num_heads=4, num_kv_heads=nkv, head_dim=16,
                               window=window, scale=None, position=pos, shares_kv=shares_kv),
-            ffn=PartSpec.of("gated_mlp", hidden_size=H, intermediate_size=80 + 8 * i),
+            ffn=PartSpec.of("gated_mlp", **MLP_NAMES, hidden_size=H, intermediate_size=80 + 8 * i),
             norms=(PartSpec.of("rmsnorm", size=H, eps=1e-5, name="input_layernorm.weight"),
                    PartSpec.of("rmsnorm", size=H, eps=1e-5, name="post_attention_layernorm.weight")),
             prefix=f"model.layers.{i}.")

@@ -12,6 +12,7 @@ import pytest
 import torch
 
 import plain_llama as pl
+from conftest import ATT_NAMES, MLP_NAMES
 import replay_util as ru
 
 pytestmark = pytest.mark.gpu
@@ -81,9 +82,9 @@ def register_toy():
             LayerSpec("pre_norm", PartSpec.of("toy_decay_state", hidden_size=H, state_size=STATE, decay=DECAY,
                                               tensor_prefix="state."),
                       PartSpec.of("toy_scale", hidden_size=H, tensor_prefix="ff."), norms(), "toy.0."),
-            LayerSpec("pre_norm", PartSpec.of("attention", hidden_size=H, num_heads=2, num_kv_heads=1, head_dim=16,
+            LayerSpec("pre_norm", PartSpec.of("attention", **ATT_NAMES, hidden_size=H, num_heads=2, num_kv_heads=1, head_dim=16,
                                               window=None, scale=None, position=pos),
-                      PartSpec.of("gated_mlp", hidden_size=H, intermediate_size=56), norms(), "toy.1."),
+                      PartSpec.of("gated_mlp", **MLP_NAMES, hidden_size=H, intermediate_size=56), norms(), "toy.1."),
         )
         return ModelSpec(hidden_size=H, vocab_size=V,
                          embedding=PartSpec.of("token_embedding", vocab_size=V, hidden_size=H, name="toy.embed"),
@@ -220,10 +221,10 @@ def register_routed():
         waves = PartSpec.of("toy_additive_waves", head_dim=16, amp=AMP)
         rot = PartSpec.of("rotary", head_dim=16, rotary_dim=16, theta=100.0, scaling=None)
         layers = (
-            LayerSpec("pre_norm", PartSpec.of("attention", hidden_size=H, num_heads=2, num_kv_heads=2, head_dim=16,
+            LayerSpec("pre_norm", PartSpec.of("attention", **ATT_NAMES, hidden_size=H, num_heads=2, num_kv_heads=2, head_dim=16,
                                               window=24, scale=None, position=waves),
-                      PartSpec.of("gated_mlp", hidden_size=H, intermediate_size=56), norms(), "toy.0."),
-            LayerSpec("pre_norm", PartSpec.of("attention", hidden_size=H, num_heads=2, num_kv_heads=1, head_dim=16,
+                      PartSpec.of("gated_mlp", **MLP_NAMES, hidden_size=H, intermediate_size=56), norms(), "toy.0."),
+            LayerSpec("pre_norm", PartSpec.of("attention", **ATT_NAMES, hidden_size=H, num_heads=2, num_kv_heads=1, head_dim=16,
                                               window=None, scale=None, position=rot),
                       PartSpec.of("toy_top1_experts", hidden_size=H, inner_size=FF, num_experts=E, tensor_prefix="moe."),
                       norms(), "toy.1."),
@@ -319,9 +320,9 @@ def register_windowed():
         norms = lambda: (PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="n0.weight"),
                          PartSpec.of("rmsnorm", size=H, eps=cfg["eps"], name="n1.weight"))
         rot = PartSpec.of("rotary", head_dim=16, rotary_dim=16, theta=1000.0, scaling=None)
-        att = lambda window, nkv: PartSpec.of("attention", hidden_size=H, num_heads=2, num_kv_heads=nkv, head_dim=16,
+        att = lambda window, nkv: PartSpec.of("attention", **ATT_NAMES, hidden_size=H, num_heads=2, num_kv_heads=nkv, head_dim=16,
                                               window=window, scale=None, position=rot)
-        mlp = lambda: PartSpec.of("gated_mlp", hidden_size=H, intermediate_size=56)
+        mlp = lambda: PartSpec.of("gated_mlp", **MLP_NAMES, hidden_size=H, intermediate_size=56)
         layers = (LayerSpec("pre_norm", att(20, 2), mlp(), norms(), "toy.0."),
                   LayerSpec("pre_norm", att(None, 1), mlp(), norms(), "toy.1."))
         return ModelSpec(hidden_size=H, vocab_size=V,

@@ -74,8 +74,12 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path, model_dir
     d.mkdir()
     write_safetensors(str(d / "model.safetensors"), tensors)
     (d / "config.json").write_text(json.dumps(TINY_B))
+    _, spec = load_model_description(str(d))
+    model = DecoderModel(spec)
+    ignored = [n for part in model.parts() for n in part.ignored_tensors()]
+    assert "model.layers.0.self_attn.rotary_emb.inv_freq" in ignored      # declared by the rotary part's spec
     with pytest.raises(WeightsMismatch) as e:
-        check_tensors(specs_of(str(d)), FolderSource(str(d)))
+        check_tensors(model.tensor_specs(), FolderSource(str(d)), ignored)
     err = e.value
     assert err.missing == ["model.layers.1.self_attn.k_proj.weight", "model.norm.weight"]
     assert err.unexpected == ["model.layers.9.extra.weight"]
@@ -137,3 +141,54 @@ def test_corrupt_file(tmp_path):
     p.write_bytes(b"\xff" * 20)
     with pytest.raises(WeightsError, match="header"):
         SafetensorsFile(str(p))
+
+
+def test_an_architecture_with_other_tensor_names_loads_without_a_change_to_the_framework(tmp_path):
+    """Same parts, a checkpoint that calls its tensors otherwise: the names are the spec's, so a new
+    architecture registered from here writes, checks and loads its folder."""
+    from rllm_b200.config.registry import register_architecture
+    from rllm_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, Run
+
+    def parse(cfg):
+        return dict(cfg)
+
+    def build(cfg):
+        H, V = cfg["width"], cfg["vocab"]
+        pos = PartSpec.of("rotary", head_dim=16, rotary_dim=16, theta=100.0, scaling=None,
+                          ignored_tensors=("freq_table",))
+        layer = lambda i: LayerSpec(
+            "pre_norm",
+            PartSpec.of("attention", hidden_size=H, num_heads=2, num_kv_heads=1, head_dim=16, window=None,
+                        scale=None, position=pos, tensor_prefix="att/",
+                        tensor_names={"q": "wq", "k": "wk", "v": "wv", "o": "wo"}),
+            PartSpec.of("gated_mlp", hidden_size=H, intermediate_size=40, tensor_prefix="ff/",
+                        tensor_names={"gate": "w1", "up": "w3", "down": "w2"}),
+            (PartSpec.of("rmsnorm", size=H, eps=1e-5, name="ln1"), PartSpec.of("rmsnorm", size=H, eps=1e-5, name="ln2")),
+            f"blk{i}/")
+        return ModelSpec(hidden_size=H, vocab_size=V,
+                         embedding=PartSpec.of("token_embedding", vocab_size=V, hidden_size=H, name="tok"),
+                         layers=(layer(0), layer(1)), order=(Run(0, 0), Run(1, 1)),
+                         final_norm=PartSpec.of("rmsnorm", size=H, eps=1e-5, name="ln_f"),
+                         head=PartSpec.of("lm_head", vocab_size=V, hidden_size=H, name="out", tied_to="tok"),
+                         max_positions=64)
+
+    register_architecture("ToyRenamedForTest", parse, build)
+    cfg = {"architectures": ["ToyRenamedForTest"], "width": 32, "vocab": 50, "torch_dtype": "float32"}
+    d = str(tmp_path / "renamed")
+    write_random_model(d, cfg, 3, "float32")
+    src = FolderSource(d)
+    assert sorted(src.names()) == sorted(
+        ["tok", "ln_f"] + [f"blk{i}/{n}" for i in (0, 1)
+                           for n in ("att/wq", "att/wk", "att/wv", "att/wo", "ff/w1", "ff/w2", "ff/w3", "ln1", "ln2")])
+    # a stored frequency table under the name the spec declared is passed over; any other extra is not
+    tensors = {n: src.read(n) for n in src.names()}
+    tensors["blk1/att/freq_table"] = torch.zeros(8)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    _, spec = load_model_description(d)
+    model = DecoderModel(spec)
+    model.load(FolderSource(d), torch.float32, torch.device("cpu"))
+    assert model.blocks[1].mixer.w_qkv.shape == (64, 32) and model.blocks[0].ffn.w_gate_up.shape == (80, 32)
+    tensors["blk1/att/other"] = torch.zeros(8)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    with pytest.raises(WeightsMismatch, match="blk1/att/other"):
+        DecoderModel(spec).load(FolderSource(d), torch.float32, torch.device("cpu"))
