@@ -116,6 +116,15 @@ class BlockPool:
     def is_shared(self, page: int) -> bool:
         return self.refcount[page] > 1
 
+    def copy_on_write(self, page: int) -> Optional[int]:
+        """The page to write to in place of ``page``: ``page`` itself if it has one owner;
+        else this owner's reference is dropped and a fresh page is returned, into which
+        the caller copies the data (block_pool.rs:292-302).  None: no page is free."""
+        got = core().rllm_pool_copy_on_write(self._h, c_int(page))
+        if got == RC_NOT_HELD:
+            raise PagePoolError(f"page {page} is not held")
+        return None if got < 0 else int(got)
+
     # -- content hashes ---------------------------------------------------
     def register(self, page: int, content_hash: bytes) -> None:
         """Make a held, completely written page findable by its content."""

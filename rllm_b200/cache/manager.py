@@ -148,6 +148,33 @@ class CacheManager:
         if rid is not None:
             core().rllm_cache_free(self._h, c_longlong(rid))
 
+    def fork(self, parent: Hashable, child: Hashable, num_tokens: int):
+        """Admit ``child`` as a copy of the first ``num_tokens`` tokens of ``parent``
+        (crates/rllm-cache/src/manager.rs:220-245): it shares the parent's full pages by
+        reference count and gets a page of its own for the partly filled last one, and a
+        state slot of its own.  Returns (copies, (parent slot, child slot)) with copies =
+        [(group, parent's page, child's page)]: the caller copies those pages and the
+        state slot on the device (``CacheStorage.copy_for_fork``) before either request
+        runs again.  None if a slot or a page is missing; nothing was taken then."""
+        if child in self.requests:
+            raise KeyError(f"request {child!r} is already admitted")
+        cap = 3 * max(1, len(self.paged))
+        buf = (c_int * cap)()
+        n = c_int(0)
+        rid = self._next_id
+        slot = core().rllm_cache_fork(self._h, self._id(parent), c_longlong(rid), c_longlong(num_tokens), buf,
+                                      c_int(cap), ctypes.byref(n))
+        if slot == -1:
+            return None
+        if slot == RC_NOT_HELD:
+            raise PagePoolError(f"fork: request {parent!r} does not hold pages for {num_tokens} tokens")
+        if slot < 0:
+            raise ValueError(f"fork: bad arguments ({slot})")
+        self._next_id += 1
+        self.requests[child] = rid
+        copies = [(int(buf[3 * i]), int(buf[3 * i + 1]), int(buf[3 * i + 2])) for i in range(n.value)]
+        return copies, (self.slot(parent), int(slot))
+
     def slot(self, req: Hashable) -> int:
         return int(core().rllm_cache_slot(self._h, self._id(req)))
 

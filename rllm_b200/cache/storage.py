@@ -76,6 +76,20 @@ class CacheStorage:
         for t in self.state.values():
             t.index_fill_(0, idx, 0.0)
 
+    def copy_for_fork(self, copies, slots) -> None:
+        """The device side of ``CacheManager.fork``: every owning run of a group copies the
+        page (K and V, one device-to-device copy each, on the current stream) and every
+        state buffer copies the slot.  The reference has the copy kernel
+        (crates/rllm-kernels/src/cuda/cache_ops.cu:252-279) and never calls it."""
+        for g, src, dst in copies:
+            for run in self.layout.owners[g]:
+                k, v = self.kv[run]
+                k[dst].copy_(k[src], non_blocking=True)
+                v[dst].copy_(v[src], non_blocking=True)
+        src, dst = slots
+        for t in self.state.values():
+            t[dst].copy_(t[src], non_blocking=True)
+
     def num_bytes(self) -> int:
         n = sum(k.numel() * k.element_size() * 2 for k, _ in self.kv.values())
         return n + sum(t.numel() * 4 for t in self.state.values())

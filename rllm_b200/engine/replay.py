@@ -17,7 +17,10 @@ float32 [wanted, vocab] in the order of the entries and of ``want``.  After
 every step a line ``done <step>`` is printed and flushed.  ``--max-tokens`` is
 the most tokens live requests hold at any time (each request rounded up to a
 multiple of 64); the page pool is made for exactly that many, so pages of
-finished requests are used again.  ``--max-live`` (8) is the most requests
+finished requests are used again.  An optional key ``"fork": [{"from": "a", "to": "b"}]`` makes request ``b``, before the
+step's entries run, a copy of everything ``a`` has been fed so far (shared full
+pages, a copied last page and state slot); both go on independently.
+``--max-live`` (8) is the most requests
 that are live at a time; a trace that exceeds either limit ends with exit code
 3 and a message that names the step.
 
@@ -77,6 +80,18 @@ def main(argv=None) -> int:
         rec = json.loads(line)
         step = rec["step"]
         entries: List[StepEntry] = []
+        for f in rec.get("fork", []):
+            src, dst = str(f["from"]), str(f["to"])
+            if src not in fed or dst in fed:
+                print(f"trace_run: step {step}: cannot fork {src!r} into {dst!r}", file=sys.stderr)
+                return 3
+            made = cache.fork(src, dst, fed[src])
+            if made is None:
+                print(f"trace_run: step {step}: no page or slot left to fork {src!r}", file=sys.stderr)
+                return 3
+            with torch.cuda.device(model.device):
+                storage.copy_for_fork(*made)
+            fed[dst] = fed[src]
         for e in rec.get("entries", []):
             rid, tokens = str(e["id"]), list(e["tokens"])
             if not tokens:

@@ -176,6 +176,16 @@ struct Pool {
     }
     return 0;
   }
+  // Copy-on-write bookkeeping (block_pool.rs:292-302): a page held by one owner is returned as it is; a shared
+  // page loses this owner's reference and a fresh page is returned, into which the caller copies the data.
+  int copy_on_write(int page) {
+    if (page < 0 || page >= n || ref[page] < 1) return RC_NOT_HELD;
+    if (ref[page] == 1) return page;
+    const int fresh = allocate();
+    if (fresh < 0) return -1;
+    --ref[page];
+    return fresh;
+  }
   int reg(int page, const Hash16& h) {
     if (page < 0 || page >= n || ref[page] < 1) return RC_NOT_HELD;
     if (has_hash[page] || page_of.count(h)) return 0;   // already findable (or the same content lives elsewhere)
@@ -297,6 +307,7 @@ API int rllm_pool_allocate(void* h) { return P(h)->allocate(); }
 API int rllm_pool_incref(void* h, int page) { return P(h)->incref(page); }
 API int rllm_pool_free(void* h, int page) { return P(h)->release(page); }
 API int rllm_pool_refcount(void* h, int page) { return page < 0 || page >= P(h)->n ? RC_BADARG : P(h)->ref[page]; }
+API int rllm_pool_copy_on_write(void* h, int page) { return P(h)->copy_on_write(page); }
 API int rllm_pool_register(void* h, int page, const uint8_t* hash) { return P(h)->reg(page, as_hash(hash)); }
 API int rllm_pool_peek(void* h, const uint8_t* hash) { return P(h)->peek(as_hash(hash)); }
 API int rllm_pool_acquire_cached(void* h, const uint8_t* hash) { return P(h)->acquire_cached(as_hash(hash)); }
@@ -377,6 +388,63 @@ API int rllm_cache_free(void* h, int64_t id) {
     if (m->fresh_slots[i] == r.slot) { m->fresh_slots.erase(m->fresh_slots.begin() + i); break; }
   m->reqs.erase(it);
   return 0;
+}
+// A child request that starts as a copy of the first num_tokens tokens of a parent
+// (crates/rllm-cache/src/manager.rs:220-245 shares every page and leaves the copy to the first write; here the
+// one page that both would write, the partly filled last one, is made the child's own at once).  The child
+// gets a slot of its own, shares the parent's full pages by reference count, and gets a fresh page for the
+// partly filled one in every paged group.  copies: triples (group, page of the parent, page of the child)
+// whose data the caller must copy, and the pair of state slots is (slot of parent, returned slot).
+// Returns the child's slot; -1 if a slot or a page is missing (nothing taken); RC_* on errors.
+API int rllm_cache_fork(void* h, int64_t parent_id, int64_t child_id, long long num_tokens, int* copies, int cap,
+                        int* num_copies) {
+  Manager* m = M(h);
+  if (m->find(child_id)) return RC_DUPLICATE_REQ;
+  Req* p = m->find(parent_id);
+  if (!p) return RC_UNKNOWN_REQ;
+  if (num_tokens < 0 || !num_copies) return RC_BADARG;
+  const long long want = (num_tokens + m->page_size - 1) / m->page_size;
+  const bool partial = num_tokens % m->page_size != 0;
+  int n_copy = 0;
+  for (int g : m->paged) {
+    if ((long long)p->tables[g].size() < want) return RC_NOT_HELD;       // the parent does not hold that much
+    // a window may have passed pages that the child's next query (at position num_tokens) would still see
+    for (long long k = m->first_needed_page(g, num_tokens); k < want; ++k)
+      if (p->tables[g][k] < 0) return RC_NOT_HELD;
+    if (partial && p->tables[g][want - 1] >= 0) {
+      if (m->pools[g]->num_free() < 1) return -1;
+      ++n_copy;
+    }
+  }
+  if (m->free_slots.empty()) return -1;
+  if (3 * n_copy > cap) return RC_BADARG;
+  Req c;
+  c.slot = m->free_slots.back();
+  m->free_slots.pop_back();
+  c.tables.resize(m->num_groups);
+  c.released.assign(m->num_groups, 0);
+  int k = 0;
+  for (int g : m->paged) {
+    c.tables[g].assign(p->tables[g].begin(), p->tables[g].begin() + want);
+    c.released[g] = p->released[g] < (int)want ? p->released[g] : (int)want;
+    for (int page : c.tables[g])
+      if (page >= 0) m->pools[g]->incref(page);
+    if (partial && c.tables[g][want - 1] >= 0) {
+      const int shared = c.tables[g][want - 1];
+      const int own = m->pools[g]->copy_on_write(shared);      // shared by two now: a fresh page comes back
+      c.tables[g][want - 1] = own;
+      copies[3 * k] = g; copies[3 * k + 1] = shared; copies[3 * k + 2] = own;
+      ++k;
+    }
+  }
+  const size_t full = (size_t)(num_tokens / m->page_size);
+  c.hashes.assign(p->hashes.begin(), p->hashes.begin() + (p->hashes.size() < full ? p->hashes.size() : full));
+  c.registered = p->registered < (int)full ? p->registered : (int)full;
+  if (c.registered > (int)c.hashes.size()) c.registered = (int)c.hashes.size();
+  *num_copies = k;
+  const int slot = c.slot;                                       // not a fresh slot: the caller copies the state into it
+  m->reqs.emplace(child_id, std::move(c));
+  return slot;
 }
 API int rllm_cache_slot(void* h, int64_t id) {
   Req* r = M(h)->find(id);

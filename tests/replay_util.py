@@ -30,8 +30,11 @@ class TraceBuilder:
         self.fed: Dict[str, int] = {}
         self.peak = 0
 
-    def step(self, entries: Sequence[Tuple[str, Sequence[int]]], end: Sequence[str] = ()):
+    def step(self, entries: Sequence[Tuple[str, Sequence[int]]], end: Sequence[str] = (),
+             fork: Sequence[Tuple[str, str]] = ()):
         recs, rows = [], []
+        for src, dst in fork:
+            self.fed[dst] = self.fed[src]
         for rid, toks in entries:
             start = self.fed.get(rid, 0)
             recs.append({"id": rid, "tokens": list(toks), "want": list(range(len(toks)))})
@@ -39,6 +42,8 @@ class TraceBuilder:
             self.fed[rid] = start + len(toks)
         self.peak = max(self.peak, sum(round64(n) for n in self.fed.values()))
         self.steps.append({"step": len(self.steps), "entries": recs, "end": list(end)})
+        if fork:
+            self.steps[-1]["fork"] = [{"from": a, "to": b} for a, b in fork]
         self.rows.append(rows)
         for rid in end:
             self.fed.pop(rid, None)

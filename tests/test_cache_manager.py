@@ -97,6 +97,14 @@ def test_random_orders_lose_nothing(seed):
                 tb = m.table(rid, 1)          # the windowed group holds only what queries can still see
                 held = [k for k, p in enumerate(tb) if p >= 0]
                 assert all(k * 8 + 7 >= max(0, live[rid] - 1 - 24 + 1) - 23 for k in held)
+        elif op < 0.88 and live and len(live) < 5:
+            src, dst = rng.choice(list(live)), f"f{step}"
+            upto = rng.randint(0, live[src])
+            try:
+                if m.fork(src, dst, upto) is not None:
+                    live[dst] = upto
+            except PagePoolError:
+                assert upto < live[src]       # refused: the window has passed pages the child would need
         elif live:
             rid = rng.choice(list(live))
             m.free(rid)
@@ -192,3 +200,65 @@ def test_prefix_sharing():
 def test_prefix_sharing_is_off_with_windows_or_state():
     assert not CacheManager([KVPagesNeed(1, 16, 8)], 4, 4, 1, enable_prefix_caching=True).prefix_caching
     assert not CacheManager([FULL, StateNeed((2,))], 4, 4, 1, enable_prefix_caching=True).prefix_caching
+
+
+def test_fork_shares_full_pages_and_copies_the_last():
+    """crates/rllm-cache/src/manager.rs:220-245 (fork) and block_pool.rs:292-302 (copy on write)."""
+    m = CacheManager([FULL, StateNeed((4,))], 8, 6, 3)
+    m.admit("a")
+    m.take_fresh_slots()
+    assert m.ensure("a", 0, 21)                         # pages 0, 1 full, page 2 holds 5 tokens
+    pool = m.pools[0]
+    copies, slots = m.fork("a", "b", 21)
+    ta, tb = m.table("a", 0), m.table("b", 0)
+    assert ta[:2] == tb[:2] and ta[2] != tb[2] and copies == [(0, ta[2], tb[2])]
+    assert [pool.refcount[p] for p in ta] == [2, 2, 1] and pool.refcount[tb[2]] == 1
+    assert slots == (m.slot("a"), m.slot("b")) and slots[0] != slots[1]
+    assert m.take_fresh_slots() == []                   # the child's state is a copy, not zeros
+    # at a page's edge nothing is copied; beyond what the parent holds is an error
+    copies, _ = m.fork("a", "c", 16)
+    assert copies == [] and m.table("c", 0) == ta[:2]
+    with pytest.raises(Exception, match="does not hold"):
+        m.fork("a", "d", 40)
+    # no slot left: nothing taken
+    free_before = pool.num_free
+    assert m.fork("a", "d", 21) is None and pool.num_free == free_before
+    m.check()
+    # each goes on by itself; the shared pages live until the last owner ends
+    assert m.ensure("b", 21, 30) and m.ensure("a", 21, 25)
+    m.free("a")
+    assert [pool.refcount[p] for p in tb[:2]] == [2, 2]
+    m.free("c"); m.free("b")
+    m.check()
+    assert pool.num_free == 6 and m.usage()["free_slots"] == 3
+
+
+def test_fork_without_a_free_page_takes_nothing():
+    m = CacheManager([FULL], 8, 3, 3)
+    m.admit("a")
+    assert m.ensure("a", 0, 21)
+    assert m.fork("a", "b", 21) is None and "b" not in m.requests and m.usage()["free_slots"] == 2
+    assert m.fork("a", "b", 16) is not None             # full pages only: no page needed
+    m.check()
+
+
+def test_fork_behind_a_window_is_refused():
+    m = CacheManager([KVPagesNeed(1, 16, 10)], 4, 8, 2)
+    m.admit("a")
+    assert m.ensure("a", 0, 12) and m.ensure("a", 12, 30) and m.ensure("a", 30, 31)   # keys before 20 are gone
+    with pytest.raises(PagePoolError):
+        m.fork("a", "b", 8)                                    # a query at 8 would see keys from 0 on
+    assert m.fork("a", "b", 31) is not None
+    m.check()
+
+
+def test_pool_copy_on_write():
+    pool = BlockPool(2)
+    a = pool.allocate()
+    assert pool.copy_on_write(a) == a                   # one owner: write in place
+    pool.incref(a)
+    b = pool.copy_on_write(a)
+    assert b is not None and b != a and pool.refcount[a] == 1 and pool.refcount[b] == 1
+    pool.incref(a)
+    assert pool.copy_on_write(a) is None and pool.refcount[a] == 2      # no page free: nothing changes
+    pool.check()

@@ -267,3 +267,41 @@ def test_a_request_id_used_again_after_its_end(model_dirs, dtype):
         ref = want[rid][pos]
         err = float(np.abs(row - ref).max() / np.abs(ref).max())
         assert err <= tol, (rid, pos, err)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,common_len", [("A", 37), ("A", 48), ("B", 21), ("C", 150)])
+def test_fork_parent_and_child_diverge(model_dirs, name, common_len, dtype):
+    """A request is fed ``common_len`` tokens (in two portions), then forked: the child shares its full pages
+    and gets a copy of the partly filled last one (none at a page's edge: 48 = 3 pages of 16).  Parent and
+    child go on with different tokens, portions of one beside decoded tokens of the other, a second child is
+    forked from the first a few tokens later, and every row of all three matches the plain implementation on
+    its own whole sequence: nobody saw a key that another wrote after the fork
+    (crates/rllm-cache/src/manager.rs:220-245, block_pool.rs:292-302)."""
+    cfg, _, page = TINY[name]
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(31)
+    draw = lambda n: [int(t) for t in rng.integers(0, V, size=n)]
+    common, tail_p, tail_c, tail_d = draw(common_len), draw(24), draw(24), draw(9)
+    tb = ru.TraceBuilder()
+    tb.step([("p", common[:common_len - 5])])
+    tb.step([("p", common[common_len - 5:])])
+    tb.step([("p", tail_p[:1]), ("c", tail_c[:7])], fork=[("p", "c")])
+    tb.step([("p", tail_p[1:2]), ("c", tail_c[7:8])])
+    tb.step([("p", tail_p[2:13]), ("c", tail_c[8:9]), ("d", tail_d[:2])], fork=[("c", "d")])
+    for i in range(9, 20):
+        entries = [("p", tail_p[4 + i:5 + i]), ("c", tail_c[i:i + 1])]
+        if i - 7 < len(tail_d):
+            entries.append(("d", tail_d[i - 7:i - 6]))
+        tb.step(entries)
+    tb.step([("c", tail_c[20:])], end=["p", "c", "d"])
+    seqs = {"p": common + tail_p, "c": common + tail_c, "d": common + tail_c[:8] + tail_d}
+    got = ru.run_trace(model_dirs[name], dtype, tb, V, page_size=page)
+    model = plain_llama.read_model_dir(model_dirs[name], round_to=torch.bfloat16 if dtype == "bfloat16" else None)
+    want = {k: model.logits(v).numpy() for k, v in seqs.items()}
+    assert {k for k, _ in got} == {"p", "c", "d"}
+    assert max(pos for k, pos in got if k == "d") == len(seqs["d"]) - 1
+    for (rid, pos), row in got.items():
+        ref = want[rid][pos]
+        err = float(np.abs(row - ref).max() / np.abs(want[rid]).max())
+        assert err <= TOL[dtype], (rid, pos, err)
