@@ -41,8 +41,8 @@ def load_model(model_dir: str, dtype: str = "auto", device: Optional[str] = None
                draw_on_device: bool = False) -> Tuple[Any, DecoderModel]:
     """(typed configuration, model with weights on ``device``).  With
     ``random_weights`` the folder needs config.json only; ``draw_on_device``
-    draws them with the device's generator (fast for large models) instead of
-    the CPU's (the values a written model folder would hold)."""
+    computes them with a kernel on the device (fast for large models) instead of
+    on the CPU: the same values, those a written model folder would hold."""
     config, spec = load_model_description(model_dir)
     run_dtype = torch_dtype_of(EngineArgs(dtype=dtype).run_dtype(getattr(config, "torch_dtype", "bfloat16")))
     dev = require_cuda(device)

@@ -36,7 +36,7 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
 ]
 
-SOURCES = ["elementwise", "attention_simt", "attention_mma", "attention_tcgen05", "gemm_f32", "gemm_small_m", "gemm_tcgen05", "sampling"]
+SOURCES = ["elementwise", "attention_simt", "attention_mma", "attention_tcgen05", "gemm_f32", "gemm_small_m", "gemm_tcgen05", "sampling", "weights_rng"]
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -355,6 +355,27 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> Optio
 
 
 # ---------------------------------------------------------------------------
+def draw_normal(out: torch.Tensor, key: int, std: float, one_plus: bool = False) -> None:
+    """Fills ``out`` (float32 or bfloat16, contiguous) with std * z or 1 + std * z, z the standard normals
+    of the counter-based stream ``key``: element i is the same value wherever it is drawn
+    (``rllm_b200.weights.counter_rng`` is the CPU twin)."""
+    lib = build.load_library("weights_rng")
+    _contig(out, "out")
+    _check(lib.rllm_draw_normal(_ptr(out), c_int(dtype_code(out.dtype)), c_longlong(out.numel()),
+                                ctypes.c_ulonglong(key & 0xFFFFFFFFFFFFFFFF), ctypes.c_double(std),
+                                c_int(1 if one_plus else 0), _stream()), "draw_normal")
+
+
+def draw_randint(out: torch.Tensor, key: int, high: int) -> None:
+    """Fills ``out`` (int32, contiguous) with word i of the stream ``key`` modulo ``high``."""
+    lib = build.load_library("weights_rng")
+    assert out.dtype is torch.int32 and 0 < high < (1 << 32)
+    _contig(out, "out")
+    _check(lib.rllm_draw_randint(_ptr(out), c_longlong(out.numel()), ctypes.c_ulonglong(key & 0xFFFFFFFFFFFFFFFF),
+                                 ctypes.c_uint(high), _stream()), "draw_randint")
+
+
+# ---------------------------------------------------------------------------
 _argmax_scratch = {}
 
 

@@ -12,10 +12,12 @@ Held dtypes: a "matrix" is held in the run's dtype (bfloat16 or float32); a
 "vector" stored in 32-bit stays 32-bit even in a bfloat16 run; an "int" table
 becomes int32.
 
-The random source draws each tensor from its own generator, seeded by the
-model seed and a hash of the tensor's name, so a tensor's values do not depend
-on which other tensors exist.  The reference has only an unseeded test helper
-(crates/rllm-model/src/llama.rs:367-428: N(0, 0.02) matrices, norms of ones).
+The random source draws each tensor from a counter-based generator keyed by
+the model seed and a hash of the tensor's name (``counter_rng``), so a
+tensor's values do not depend on which other tensors exist, nor on where they
+are drawn: the CPU and the GPU give the same bits.  The reference has only an
+unseeded test helper (crates/rllm-model/src/llama.rs:367-428: N(0, 0.02)
+matrices, norms of ones).
 """
 from __future__ import annotations
 
@@ -95,25 +97,44 @@ def _fnv1a64(text: str) -> int:
     return h
 
 
+def tensor_key(name: str, seed: int) -> int:
+    """The 64-bit key of a tensor's random stream: the model seed and a hash of the name."""
+    return ((int(seed) * 0x9E3779B97F4A7C15) ^ _fnv1a64(name)) & 0xFFFFFFFFFFFFFFFF
+
+
 def draw_tensor(spec: TensorSpec, seed: int, device: str = "cpu") -> torch.Tensor:
     """The random tensor for ``spec`` under ``seed``, float32 (int64 for "int").
-    Drawn on the CPU by default, which is what a written model folder holds; a
-    CUDA ``device`` draws with that device's generator (other values, same
-    distribution), which is much faster for large models."""
-    g = torch.Generator(device=device)
-    g.manual_seed(((seed * 0x9E3779B97F4A7C15) ^ _fnv1a64(spec.name)) & 0x7FFFFFFFFFFFFFFF)
+    The values are a function of (seed, tensor name, element index) alone
+    (``counter_rng``): drawn on the CPU they are what a written model folder
+    holds, and a CUDA ``device`` computes the same bits with a kernel, which is
+    much faster for large models."""
     kind = spec.init[0]
-    kw = dict(generator=g, dtype=torch.float32, device=device)
-    if kind == "normal":
-        return torch.randn(spec.shape, **kw) * float(spec.init[1])
-    if kind == "one_plus_normal":
-        return 1.0 + torch.randn(spec.shape, **kw) * float(spec.init[1])
+    n = 1
+    for d in spec.shape:
+        n *= int(d)
+    key = tensor_key(spec.name, seed)
+    on_gpu = str(device).startswith("cuda")
+    if kind in ("normal", "one_plus_normal"):
+        if on_gpu:
+            from ..kernels import ops
+            out = torch.empty(spec.shape, dtype=torch.float32, device=device)
+            ops.draw_normal(out, key, float(spec.init[1]), kind == "one_plus_normal")
+            return out
+        from . import counter_rng
+        v = counter_rng.normal(n, key, float(spec.init[1]), kind == "one_plus_normal")
+        return torch.from_numpy(v).reshape(spec.shape)
     if kind == "zeros":
         return torch.zeros(spec.shape, dtype=torch.float32, device=device)
     if kind == "ones":
         return torch.ones(spec.shape, dtype=torch.float32, device=device)
     if kind == "randint":
-        return torch.randint(0, int(spec.init[1]), spec.shape, generator=g, dtype=torch.int64, device=device)
+        if on_gpu:
+            from ..kernels import ops
+            out = torch.empty(spec.shape, dtype=torch.int32, device=device)
+            ops.draw_randint(out, key, int(spec.init[1]))
+            return out.to(torch.int64)
+        from . import counter_rng
+        return torch.from_numpy(counter_rng.randint(n, key, int(spec.init[1]))).reshape(spec.shape).to(torch.int64)
     raise WeightsError(f"tensor {spec.name!r}: unknown init rule {spec.init!r}")
 
 

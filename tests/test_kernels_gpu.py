@@ -602,3 +602,31 @@ def test_gemm_tcgen05_silu(ops, M, I, K):
     xf, wf = x.float(), w.float()
     want = pl.silu((xf @ wf[:I].t()).double().cpu()) * (xf @ wf[I:].t()).double().cpu()
     assert rel_err(out, want) <= 1e-2
+
+
+@pytest.mark.parametrize("n", [1, 3, 4, 1021, 4096, 300_001])
+def test_random_weights_are_the_same_bits_on_the_gpu_and_on_the_cpu(ops, n):
+    """The kernel of the random-weights mode against its NumPy twin: float32 and bfloat16, both rules,
+    lengths that are no multiple of four; and whole tensors through ``draw_tensor``."""
+    from rllm_b200.weights import counter_rng as cr
+    key = 0x9E3779B97F4A7C15 ^ n
+    for one_plus, std in ((False, 0.02), (True, 0.1)):
+        want = torch.from_numpy(cr.normal(n, key, std, one_plus))
+        got = torch.empty(n, dtype=torch.float32, device=DEV)
+        ops.draw_normal(got, key, std, one_plus)
+        assert torch.equal(got.cpu(), want), (n, one_plus, (got.cpu() != want).sum())
+        got16 = torch.empty(n, dtype=torch.bfloat16, device=DEV)
+        ops.draw_normal(got16, key, std, one_plus)
+        assert torch.equal(got16.cpu(), want.to(torch.bfloat16))
+    ints = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.draw_randint(ints, key, 389)
+    assert torch.equal(ints.cpu(), torch.from_numpy(cr.randint(n, key, 389)))
+
+
+def test_draw_tensor_on_the_device_is_the_written_folder():
+    from rllm_b200.parts.spec import TensorSpec
+    from rllm_b200.weights import draw_tensor
+    for spec in (TensorSpec("model.layers.3.mlp.up_proj.weight", (264, 96)),
+                 TensorSpec("model.norm.weight", (96,), role="vector", init=("one_plus_normal", 0.1)),
+                 TensorSpec("table", (50,), role="int", init=("randint", 11))):
+        assert torch.equal(draw_tensor(spec, 2, str(DEV)).cpu(), draw_tensor(spec, 2))

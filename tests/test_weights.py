@@ -192,3 +192,37 @@ def test_an_architecture_with_other_tensor_names_loads_without_a_change_to_the_f
     write_safetensors(os.path.join(d, "model.safetensors"), tensors)
     with pytest.raises(WeightsMismatch, match="blk1/att/other"):
         DecoderModel(spec).load(FolderSource(d), torch.float32, torch.device("cpu"))
+
+
+def test_counter_generator_known_answers_and_shape_of_the_distribution():
+    """Philox4x32-10: the published known-answer vector for an all-zero counter and key.  The normals: right
+    moments, and element i is a function of (key, i) alone, whatever the tensor's length."""
+    import numpy as np
+    from rllm_b200.weights import counter_rng as cr
+    w = cr.philox4x32_10(np.array([0], dtype=np.uint64), 0)
+    assert [hex(int(x)) for x in w[0]] == ["0x6627e8d5", "0xe169c58d", "0xbc57ac4c", "0x9b00dbd8"]
+    z = cr.standard_normal(400_003, 0x0123456789ABCDEF)
+    assert abs(z.mean()) < 5e-3 and abs(z.std() - 1) < 5e-3 and abs((z ** 4).mean() - 3) < 0.05
+    assert abs(np.corrcoef(z[:-1], z[1:])[0, 1]) < 5e-3
+    assert np.array_equal(cr.standard_normal(1001, 7), cr.standard_normal(5000, 7)[:1001])
+    assert not np.array_equal(cr.standard_normal(64, 7), cr.standard_normal(64, 8))
+    # the pieces that replace the library's logarithm, cosine and sine are accurate to a few ulp
+    words = np.random.default_rng(0).integers(0, 2 ** 32, size=20000, dtype=np.uint64).astype(np.uint32)
+    c, s = cr._cos_sin(words)
+    angle = 2 * np.pi * words.astype(np.float64) / 2 ** 32
+    assert np.abs(c - np.cos(angle)).max() < 2e-15 and np.abs(s - np.sin(angle)).max() < 2e-15
+    u = (words.astype(np.float64) + 0.5) / 2 ** 32
+    assert np.abs(cr._ln(u) / np.log(u) - 1).max() < 2e-15
+    r = cr.randint(1000, 3, 17)
+    assert r.min() >= 0 and r.max() == 16 and r.dtype == np.int32
+
+
+def test_draw_tensor_rules():
+    from rllm_b200.parts.spec import TensorSpec
+    a = draw_tensor(TensorSpec("x.weight", (33, 7), init=("normal", 0.02)), 4)
+    b = draw_tensor(TensorSpec("x.weight", (33, 7), role="vector", init=("one_plus_normal", 0.1)), 4)
+    assert a.dtype is torch.float32 and a.shape == (33, 7) and abs(float(a.std()) - 0.02) < 4e-3
+    # the same stream under both rules: 1 + 0.1 z against 0.02 z
+    assert torch.allclose((b - 1.0) / 0.1, a / 0.02, atol=1e-5)
+    other = draw_tensor(TensorSpec("y.weight", (33, 7), init=("normal", 0.02)), 4)
+    assert not torch.equal(a, other) and not torch.equal(a, draw_tensor(TensorSpec("x.weight", (33, 7)), 5))
