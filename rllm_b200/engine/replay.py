@@ -52,75 +52,98 @@ def build_parser() -> argparse.ArgumentParser:
     return p
 
 
+class TraceError(RuntimeError):
+    """A trace asks for more pages or live requests than the session was given."""
+
+
+class TraceSession:
+    """The state of one replay: a cache manager and storage sized for ``max_tokens``
+    tokens and ``max_live`` requests around a loaded model, and the model runner that
+    generation uses.  ``step`` takes one record of the trace and returns the logits
+    at the wanted places (float32 [wanted, vocab] on the device)."""
+
+    def __init__(self, model, max_tokens: int, block_size: int = PAGE_SIZE, max_live: int = 8):
+        from ..cache import CacheManager, CacheStorage
+        from .runner import ModelRunner
+        self.model = model
+        page = int(block_size)
+        num_pages = max(1, -(-int(max_tokens) // page))
+        paged = [n for n in model.layout.groups if hasattr(n, "num_kv_heads")]
+        self.max_tokens, self.max_live = int(max_tokens), max(1, int(max_live))
+        self.cache = CacheManager(model.layout.groups, page, [num_pages] * len(paged), self.max_live)
+        self.storage = CacheStorage(model.layout, page, [num_pages] * len(paged), self.max_live, model.dtype,
+                                    model.device)
+        self.runner = ModelRunner(model, self.cache, self.storage)
+        self.fed: Dict[str, int] = {}
+
+    def step(self, rec: dict):
+        import torch
+
+        from .runner import StepEntry
+        step = rec.get("step")
+        for f in rec.get("fork", []):
+            src, dst = str(f["from"]), str(f["to"])
+            if src not in self.fed or dst in self.fed:
+                raise TraceError(f"step {step}: cannot fork {src!r} into {dst!r}")
+            made = self.cache.fork(src, dst, self.fed[src])
+            if made is None:
+                raise TraceError(f"step {step}: no page or slot left to fork {src!r}")
+            with torch.cuda.device(self.model.device):
+                self.storage.copy_for_fork(*made)
+            self.fed[dst] = self.fed[src]
+        entries = []
+        for e in rec.get("entries", []):
+            rid, tokens = str(e["id"]), list(e["tokens"])
+            if not tokens:
+                continue
+            if rid not in self.fed:
+                if not self.cache.has_free_slot():
+                    raise TraceError(f"step {step}: request {rid!r} would be live request number "
+                                     f"{len(self.fed) + 1}; --max-live is {self.max_live}")
+                self.cache.admit(rid)
+                self.fed[rid] = 0
+            start = self.fed[rid]
+            if not self.cache.ensure(rid, start, start + len(tokens)):
+                raise TraceError(f"step {step}: request {rid!r} needs more pages than --max-tokens "
+                                 f"{self.max_tokens} leaves free")
+            entries.append(StepEntry(rid, tokens, start, list(e.get("want", []))))
+            self.fed[rid] = start + len(tokens)
+        logits = self.runner.step(entries)
+        self.runner.check_errors()
+        for rid in rec.get("end", []):
+            rid = str(rid)
+            if rid in self.fed:
+                self.cache.free(rid)
+                del self.fed[rid]
+        return logits
+
+
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
     print("[trace_run] loading", args.model, file=sys.stderr, flush=True)
     import numpy as np
     import torch
 
-    from ..cache import CacheManager, CacheStorage
     from .loading import load_model
-    from .runner import ModelRunner, StepEntry
 
     os.makedirs(args.out, exist_ok=True)
     _, model = load_model(args.model, dtype=args.dtype, device=args.device)
-    page = args.block_size
-    num_pages = max(1, -(-args.max_tokens // page))
-    paged = [n for n in model.layout.groups if hasattr(n, "num_kv_heads")]
-    max_live = max(1, args.max_live)
-    cache = CacheManager(model.layout.groups, page, [num_pages] * len(paged), max_live)
-    storage = CacheStorage(model.layout, page, [num_pages] * len(paged), max_live, model.dtype, model.device)
-    runner = ModelRunner(model, cache, storage)
-    fed: Dict[str, int] = {}
-
+    session = TraceSession(model, args.max_tokens, args.block_size, args.max_live)
     for line in sys.stdin:
         line = line.strip()
         if not line:
             continue
         rec = json.loads(line)
         step = rec["step"]
-        entries: List[StepEntry] = []
-        for f in rec.get("fork", []):
-            src, dst = str(f["from"]), str(f["to"])
-            if src not in fed or dst in fed:
-                print(f"trace_run: step {step}: cannot fork {src!r} into {dst!r}", file=sys.stderr)
-                return 3
-            made = cache.fork(src, dst, fed[src])
-            if made is None:
-                print(f"trace_run: step {step}: no page or slot left to fork {src!r}", file=sys.stderr)
-                return 3
-            with torch.cuda.device(model.device):
-                storage.copy_for_fork(*made)
-            fed[dst] = fed[src]
-        for e in rec.get("entries", []):
-            rid, tokens = str(e["id"]), list(e["tokens"])
-            if not tokens:
-                continue
-            if rid not in fed:
-                if not cache.has_free_slot():
-                    print(f"trace_run: step {step}: request {rid!r} would be live request number "
-                          f"{len(fed) + 1}; --max-live is {max_live}", file=sys.stderr)
-                    return 3
-                cache.admit(rid)
-                fed[rid] = 0
-            start = fed[rid]
-            if not cache.ensure(rid, start, start + len(tokens)):
-                print(f"trace_run: step {step}: request {rid!r} needs more pages than --max-tokens "
-                      f"{args.max_tokens} leaves free", file=sys.stderr)
-                return 3
-            entries.append(StepEntry(rid, tokens, start, list(e.get("want", []))))
-            fed[rid] = start + len(tokens)
-        logits = runner.step(entries)
-        runner.check_errors()
+        try:
+            logits = session.step(rec)
+        except TraceError as e:
+            print(f"trace_run: {e}", file=sys.stderr)
+            return 3
         if logits.shape[0]:
             logits.cpu().numpy().astype("<f4").tofile(os.path.join(args.out, f"{step}.f32"))
         else:
             torch.cuda.synchronize()
-        for rid in rec.get("end", []):
-            rid = str(rid)
-            if rid in fed:
-                cache.free(rid)
-                del fed[rid]
         print(f"done {step}", flush=True)
     return 0
 

@@ -228,6 +228,16 @@ class PlainLlama:
         x = rms_norm(x, self.t["model.norm.weight"], self.eps)
         return linear(x, self.head_weight())
 
+    def logits_at(self, token_ids: Sequence[int], rows: Sequence[int]) -> torch.Tensor:
+        """The rows ``rows`` of ``logits(token_ids)``: the output product on those rows only (a large
+        vocabulary makes it the most expensive part of the whole-sequence oracle)."""
+        x = embedding(self.t["model.embed_tokens.weight"], token_ids)
+        positions = torch.arange(len(token_ids))
+        for i in range(self.layers):
+            x = self.decoder_layer(i, x, positions)
+        x = rms_norm(x[list(rows)], self.t["model.norm.weight"], self.eps)
+        return linear(x, self.head_weight())
+
     def greedy(self, prompt: Sequence[int], max_tokens: int) -> List[int]:
         """Greedy continuation by recomputing the whole sequence each step; the
         lowest index wins a tie."""

@@ -24,7 +24,9 @@ def round64(n: int) -> int:
 class TraceBuilder:
     """Collects steps and remembers which (request, position) each written row is."""
 
-    def __init__(self):
+    def __init__(self, want=None):
+        # want(request, position) -> bool: which rows' logits are asked for (default: all)
+        self.want = want or (lambda rid, pos: True)
         self.steps: List[dict] = []
         self.rows: List[List[Tuple[str, int]]] = []     # per step: (request, position) of each row
         self.fed: Dict[str, int] = {}
@@ -37,8 +39,9 @@ class TraceBuilder:
             self.fed[dst] = self.fed[src]
         for rid, toks in entries:
             start = self.fed.get(rid, 0)
-            recs.append({"id": rid, "tokens": list(toks), "want": list(range(len(toks)))})
-            rows += [(rid, start + i) for i in range(len(toks))]
+            wanted = [i for i in range(len(toks)) if self.want(rid, start + i)]
+            recs.append({"id": rid, "tokens": list(toks), "want": wanted})
+            rows += [(rid, start + i) for i in wanted]
             self.fed[rid] = start + len(toks)
         self.peak = max(self.peak, sum(round64(n) for n in self.fed.values()))
         self.steps.append({"step": len(self.steps), "entries": recs, "end": list(end)})
@@ -85,19 +88,37 @@ def run_trace(model_dir: str, dtype: str, tb: TraceBuilder, vocab: int, page_siz
     return got
 
 
+def run_trace_on_model(model, tb: TraceBuilder, page_size: int = 16, max_tokens: int = None,
+                       max_live: int = 8) -> Dict[Tuple[str, int], np.ndarray]:
+    """The same replay on a model that is already loaded (random weights drawn on the device, say):
+    ``TraceSession`` is what ``bin/trace_run`` runs for every line."""
+    from rllm_b200.engine.replay import TraceSession
+    session = TraceSession(model, max_tokens if max_tokens is not None else tb.peak, page_size, max_live)
+    got: Dict[Tuple[str, int], np.ndarray] = {}
+    for rec, rows in zip(tb.steps, tb.rows):
+        arr = session.step(rec).cpu().numpy()
+        assert arr.shape[0] == len(rows)
+        for r, key in enumerate(rows):
+            assert key not in got, f"row {key} written twice"
+            got[key] = arr[r]
+    session.cache.check()
+    assert session.cache.usage()["num_requests"] == 0
+    return got
+
+
 # ---------------------------------------------------------------------------
 # the ways of cutting
 # ---------------------------------------------------------------------------
-def trace_whole(reqs: Dict[str, List[int]]) -> TraceBuilder:
-    tb = TraceBuilder()
+def trace_whole(reqs: Dict[str, List[int]], want=None) -> TraceBuilder:
+    tb = TraceBuilder(want)
     for rid, toks in reqs.items():
         tb.step([(rid, toks)], end=[rid])
     return tb
 
 
-def trace_tail_decode(reqs: Dict[str, List[int]], tail: int = 32) -> TraceBuilder:
+def trace_tail_decode(reqs: Dict[str, List[int]], tail: int = 32, want=None) -> TraceBuilder:
     """Most of a request in one step, the last ``tail`` tokens one by one."""
-    tb = TraceBuilder()
+    tb = TraceBuilder(want)
     for rid, toks in reqs.items():
         head = max(0, len(toks) - tail)
         if head:
@@ -107,10 +128,10 @@ def trace_tail_decode(reqs: Dict[str, List[int]], tail: int = 32) -> TraceBuilde
     return tb
 
 
-def trace_portions(reqs: Dict[str, List[int]], seed: int = 0) -> TraceBuilder:
+def trace_portions(reqs: Dict[str, List[int]], seed: int = 0, want=None) -> TraceBuilder:
     """Portions of changing size, down to two tokens."""
     rng = random.Random(seed)
-    tb = TraceBuilder()
+    tb = TraceBuilder(want)
     sizes = [7, 2, 13, 2, 5, 16, 3, 2, 33, 8, 17, 2]
     for rid, toks in reqs.items():
         pos, k = 0, rng.randrange(len(sizes))
@@ -122,13 +143,14 @@ def trace_portions(reqs: Dict[str, List[int]], seed: int = 0) -> TraceBuilder:
     return tb
 
 
-def trace_mixed(reqs: Dict[str, List[int]], seed: int = 0, live: int = 4, tail: int = 32) -> TraceBuilder:
+def trace_mixed(reqs: Dict[str, List[int]], seed: int = 0, live: int = 4, tail: int = 32,
+                want=None) -> TraceBuilder:
     """Up to ``live`` requests at a time; each feeds portions of changing size
     (2..23 tokens), its last ``tail`` tokens one by one, and sometimes sits a
     step out; a finished request is ended and the next one starts, so its pages
     are used again."""
     rng = random.Random(seed)
-    tb = TraceBuilder()
+    tb = TraceBuilder(want)
     waiting = list(reqs.items())
     active: List[List] = []        # [rid, tokens, pos]
     while waiting or active:

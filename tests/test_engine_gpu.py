@@ -358,9 +358,11 @@ def test_layers_of_real_size_in_bfloat16_follow_float32(tmp_path, hidden, heads,
         torch.cuda.empty_cache()
     a, b = rows["fp32"].double(), rows["bf16"].double()
     err = (a - b).abs().amax(dim=1) / a.abs().amax(dim=1)
+    same = (a.argmax(dim=1) == b.argmax(dim=1)).float().mean()
+    print(f"layers of real size (hidden {hidden}): bfloat16 against float32 worst {float(err.max()):.3e}, "
+          f"mean {float(err.mean()):.3e}, same argmax {float(same):.3f}")
     assert float(err.max()) <= 4e-2, err
     # and the two paths mostly agree on the likeliest token
-    same = (a.argmax(dim=1) == b.argmax(dim=1)).float().mean()
     assert float(same) >= 0.7, same
 
 
