@@ -8,6 +8,8 @@ tiny-B: 3 layers, hidden 96, 3 heads / 1 kv head, head_dim 32, intermediate
 (no power of two, odd), theta 5e5 with llama3 scaling (factor 4, low 1, high 4,
 original 32: its 16 frequencies hit all three branches), eps 1e-6, untied
 head, pages of 8.
+tiny-B0: tiny-B with intermediate 256, vocab 384 and 256 positions (powers of
+two and multiples of 128, which take other tile paths than 264 and 389).
 tiny-C: head_dim 64 (the size the tcgen05 attention kernel takes), 2 layers,
 hidden 256, 4 heads / 2 kv heads, intermediate 200,
 vocab 311, theta 1e6, eps 1e-5, untied head, pages of 16, contexts of several
@@ -53,6 +55,9 @@ TINY_B = {
     "max_position_embeddings": 512, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
     "hidden_act": "silu", "torch_dtype": "float32", "bos_token_id": 0, "eos_token_id": [3, 7],
 }
+# tiny-B with the sizes that are powers of two or multiples of 128 (intermediate 256, vocabulary 384,
+# 256 positions): other tile paths of the kernels than tiny-B's odd sizes reach
+TINY_B0 = dict(TINY_B, intermediate_size=256, vocab_size=384, max_position_embeddings=256)
 TINY_C = {
     "architectures": ["LlamaForCausalLM"], "model_type": "llama",
     "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4, "num_key_value_heads": 2,
@@ -70,7 +75,8 @@ TINY_D = {
     "tie_word_embeddings": True, "hidden_act": "silu", "torch_dtype": "float32",
     "bos_token_id": 1, "eos_token_id": 2,
 }
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16), "D": (TINY_D, 9, 4)}   # name -> (config, weight seed, page size)
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16), "D": (TINY_D, 9, 4),
+        "B0": (TINY_B0, 2, 8)}   # name -> (config, weight seed, page size)
 
 
 @pytest.fixture(scope="session")

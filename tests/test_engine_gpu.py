@@ -58,9 +58,11 @@ def test_greedy_generation_in_bfloat16(model_dirs):
             toks.append(t)
 
 
-def test_temperature_sampling_matches_plain_and_ignores_batching(model_dirs):
+@pytest.mark.parametrize("name", ["B", "B0"])
+def test_temperature_sampling_matches_plain_and_ignores_batching(model_dirs, name):
+    """Four requests with prompts of 1, 31, 70 and 150 tokens, portions of 16 tokens beside decoded tokens of
+    the others, 10 tokens each at temperature 0.7 with a Philox stream per request."""
     from rllm_b200 import SamplingParams
-    name = "B"
     prompts = prompts_for(name, [1, 31, 70, 150], 3)
     params = [SamplingParams(temperature=0.7, max_tokens=10, seed=100 + i, ignore_eos=True) for i in range(4)]
     together = make_llm(model_dirs, name, max_num_batched_tokens=40, long_prefill_token_threshold=16)
@@ -361,9 +363,12 @@ def test_layers_of_real_size_in_bfloat16_follow_float32(tmp_path, hidden, heads,
     same = (a.argmax(dim=1) == b.argmax(dim=1)).float().mean()
     print(f"layers of real size (hidden {hidden}): bfloat16 against float32 worst {float(err.max()):.3e}, "
           f"mean {float(err.mean()):.3e}, same argmax {float(same):.3f}")
-    assert float(err.max()) <= 4e-2, err
-    # and the two paths mostly agree on the likeliest token
-    assert float(same) >= 0.7, same
+    assert float(err.max()) <= 2.5e-2, err
+    # and the two paths agree on the likeliest token except at near-ties (a vocabulary of 128,256 has some)
+    assert float(same) >= 0.9, same
+    top = torch.topk(a, 2, dim=1).values
+    clear = (top[:, 0] - top[:, 1]) > 2 * 2.5e-2 * a.abs().amax(dim=1)
+    assert bool((a.argmax(dim=1) == b.argmax(dim=1))[clear].all())
 
 
 def test_logprobs_come_from_the_raw_logits(model_dirs):

@@ -19,12 +19,13 @@ pytestmark = pytest.mark.gpu
 TOL = {"float32": 1e-4, "bfloat16": 2e-2}
 
 LENGTHS = {"A": [5, 12, 17, 70, 100, 33, 64, 49], "B": [1, 31, 70, 150, 300, 97, 2, 210],
-           "C": [3, 130, 257, 400, 129, 64, 500, 33], "D": [2, 40, 67, 150, 9, 101]}
+           "C": [3, 130, 257, 400, 129, 64, 500, 33], "D": [2, 40, 67, 150, 9, 101],
+           "B0": [1, 31, 70, 150, 97, 2, 210, 256]}
 
 
 def make_requests(name: str):
     cfg, _, _ = TINY[name]
-    rng = np.random.default_rng({"A": 1, "B": 3, "C": 8, "D": 4}[name])
+    rng = np.random.default_rng({"A": 1, "B": 3, "C": 8, "D": 4, "B0": 3}[name])
     return {f"r{i}": [int(t) for t in rng.integers(0, cfg["vocab_size"], size=n)]
             for i, n in enumerate(LENGTHS[name])}
 
@@ -65,7 +66,7 @@ MODES = {
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "B0"])
 @pytest.mark.parametrize("mode", list(MODES))
 def test_replay_matches_plain(model_dirs, name, dtype, mode):
     cfg, _, page = TINY[name]
