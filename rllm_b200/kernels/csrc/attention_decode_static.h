@@ -20,15 +20,23 @@
 //    RLLM_DECODE_STATIC_COUNTERS; otherwise the call returns
 //    RLLM_E_STATIC_TOO_LARGE (-3) and launches nothing.
 //  * The first call on a device looks up the array's device address (once per
-//    device, with that device current).  Make that first call before any stream
-//    capture begins on that device.
+//    device, with that device current).  With CUDA's lazy module loading that
+//    first call is also the moment at which the driver loads this library's
+//    device code and reserves the array, so it may take longer and may
+//    synchronise; later calls do neither.  Make that first call before any
+//    stream capture begins on that device.  Two host threads may make their
+//    first call at the same time.
 //  * All calls share the one array, and it keeps what the last call left in it.
 //    The counters are cleared on the caller's stream at the start of every call;
 //    the partial results need no clearing (every slot is written before it is
 //    read).  Two calls that overlap on the GPU (different streams without an
 //    ordering between them) race on the array: order them.
 //  * Inputs, outputs and their meaning are exactly those of
-//    rllm_attention_decode_bf16.
+//    rllm_attention_decode_bf16, and so is its ordering rule: with write_kv the
+//    kernel reads seq_lens, the block table and older cache rows before it
+//    waits for the kernel ahead of it in the stream, so those must be complete
+//    by the time that kernel starts (here the memset of the counters stands
+//    between, which is enough); every seq_lens[s] is at least 1.
 #pragma once
 #include <cuda_runtime.h>
 

@@ -431,7 +431,13 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
   const int nwarps = blockDim.x >> 5;
   {  // a CTA none of whose chunks holds a visible key has nothing to do
     const int first = blockIdx.x * nwarps * CHUNK;
-    if (first >= len || first + nwarps * CHUNK <= kmin) return;
+    if (first >= len || first + nwarps * CHUNK <= kmin) {
+      // It still waits for the kernel ahead (it has not yet, with write_kv): a CTA that exits counts as
+      // having let the next kernel in, and that kernel may then assume that everything but this kernel is
+      // complete.  These CTAs do no work, so the wait costs nothing.
+      if (write_kv) pdl_wait();
+      return;
+    }
   }
   const bool active = w0 < len && w0 + CHUNK > kmin;
   const int* bt = block_table + (size_t)s * max_blocks;
@@ -769,6 +775,11 @@ static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc,
 // the cache.  max_seq_len bounds every seq_lens[s]; workspace holds
 // rllm_attention_decode_workspace(...) floats; counters holds num_seqs * nkv
 // ints that are zero before the call (the kernel leaves them zero).
+// The kernel is launched with programmatic dependent launch.  With write_kv it reads seq_lens, the block
+// table and the cache rows of earlier positions BEFORE it waits for the kernel ahead of it in the stream:
+// these must be complete when that kernel starts, i.e. written by a kernel at least two launches ahead
+// (or by a copy); only qkv may come from the kernel directly ahead.  Without write_kv it waits first.
+// Every seq_lens[s] must be at least 1.
 RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, void* kcache, void* vcache,
                                            const int* block_table, int max_blocks, const int* seq_lens,
                                            int num_seqs, int max_seq_len, int nq, int nkv, int d, int page_size,
@@ -801,6 +812,7 @@ RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, v
 // needs this and for the rules; nothing like it exists in the reference.
 // ---------------------------------------------------------------------------
 #include "attention_decode_static.h"
+#include <atomic>
 
 // partial results first, then the counters; fixed size, one per GPU that loads the library
 static __device__ __align__(256) float rllm_decode_static_scratch[RLLM_DECODE_STATIC_FLOATS + RLLM_DECODE_STATIC_COUNTERS];
@@ -809,18 +821,22 @@ static __device__ __align__(256) float rllm_decode_static_scratch[RLLM_DECODE_ST
 // array's name is only a stand-in; a kernel must be given the address that
 // cudaGetSymbolAddress reports.  Looked up once per device.
 static int decode_static_address(float** ptr) {
-  static float* cached[64] = {nullptr};
+  // Atomic so that two host threads may make their first call together: both look the address up (the
+  // same value) and store it.
+  static std::atomic<float*> cached[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= 64) return RLLM_E_UNSUPPORTED;
-  if (!cached[dev]) {
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, rllm_decode_static_scratch);
+  float* p = cached[dev].load(std::memory_order_acquire);
+  if (!p) {
+    void* q = nullptr;
+    e = cudaGetSymbolAddress(&q, rllm_decode_static_scratch);
     if (e != cudaSuccess) return (int)e;
-    cached[dev] = (float*)p;
+    p = (float*)q;
+    cached[dev].store(p, std::memory_order_release);
   }
-  *ptr = cached[dev];
+  *ptr = p;
   return 0;
 }
 

@@ -500,13 +500,21 @@ def attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor,
 
 
 _decode_counters = {}
+_retired_counters = []          # buffers that grew out of use: captured graphs may still hold their address
 
 
 def _counters_for(device: torch.device, n: int) -> torch.Tensor:
     """Zeroed per-device counters of the decode kernel's split merge; the kernel
-    leaves them zero, so one buffer serves every call (also under CUDA graphs)."""
+    leaves them zero, so one buffer serves every call (also under CUDA graphs).
+    A buffer that is outgrown is never freed (a captured graph replays with its
+    address), and none is made while a stream is being captured."""
     buf = _decode_counters.get(device)
     if buf is None or buf.numel() < n:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError(f"attention_decode: {n} merge counters are needed and the buffer cannot grow during "
+                              "a stream capture; run this size once outside a capture first")
+        if buf is not None:
+            _retired_counters.append(buf)
         buf = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=device)
         _decode_counters[device] = buf
     return buf

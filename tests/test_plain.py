@@ -55,6 +55,38 @@ def test_llama3_scaling_hits_all_three_branches():
     assert kinds == {"kept", "divided", "blended"}
 
 
+def test_llama3_scaling_is_continuous_and_monotone_in_the_frequency():
+    """What a misreading of the rule would break.  The ratio f'/f as a function of f: 1 for short
+    wavelengths, 1/factor for long ones, and between the two bounds a blend that meets both ends without a
+    jump, rises with f, and is halfway at the middle of the band in orig / wavelength.  A blend in the
+    wrong direction, swapped bounds or a blend in the wavelength instead of its inverse jumps at a bound
+    or misses the middle.  Checked for the oracle and for the engine's table."""
+    from rllm_b200.parts.rotary import rotary_frequencies
+    sc = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 8192}
+    orig, low, high, factor = 8192.0, 1.0, 4.0, 8.0
+    f_keep, f_divide = 2 * math.pi * high / orig, 2 * math.pi * low / orig     # wavelength orig/high, orig/low
+
+    def ratio_plain(f):
+        return float(pl.rope_inv_freq(4, 1.0 / (f * f), sc)[1]) / f          # the second of the two frequencies is f
+
+    def ratio_engine(f):
+        return rotary_frequencies(4, 1.0 / (f * f), sc)[1] / f
+    for ratio in (ratio_plain, ratio_engine):
+        assert math.isclose(ratio(f_keep * 1.5), 1.0, rel_tol=1e-12) and math.isclose(ratio(f_divide / 1.5), 1 / factor, rel_tol=1e-12)
+        for eps in (1e-6, 1e-9):
+            assert math.isclose(ratio(f_keep * (1 - eps)), 1.0, rel_tol=0, abs_tol=10 * eps)
+            assert math.isclose(ratio(f_keep * (1 + eps)), 1.0, rel_tol=0, abs_tol=10 * eps)
+            assert math.isclose(ratio(f_divide * (1 - eps)), 1 / factor, rel_tol=0, abs_tol=10 * eps)
+            assert math.isclose(ratio(f_divide * (1 + eps)), 1 / factor, rel_tol=0, abs_tol=10 * eps)
+        grid = [f_divide * (f_keep / f_divide) ** (i / 200) for i in range(1, 200)]
+        vals = [ratio(f) for f in grid]
+        assert all(a < b for a, b in zip(vals, vals[1:])) and 1 / factor < vals[0] and vals[-1] < 1.0
+        # orig / wavelength = orig f / (2 pi) runs from low to high; at its middle the blend is half and half
+        f_mid = 2 * math.pi * (low + high) / 2 / orig
+        assert math.isclose(ratio(f_mid), 0.5 * (1 + 1 / factor), rel_tol=1e-9)
+
+
 def test_attention_matches_a_per_query_loop_and_respects_window_and_groups():
     torch.manual_seed(0)
     T, nq, nkv, d = 9, 4, 2, 8

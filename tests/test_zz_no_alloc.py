@@ -47,14 +47,14 @@ def _case(seed, lens, nq=8, nkv=2, d=64, page=16):
                 inv=inv, seq_lens=seq_lens, max_len=max(lens))
 
 
-def _call(lib, fn_name, c, kc, vc, out, err, extra):
+def _call(lib, fn_name, c, kc, vc, out, err, extra, window=0, write_kv=1):
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
     p = lambda t: c_void_p(t.data_ptr())
     fn = getattr(lib, fn_name)
     args = [p(c["qkv"]), c_int(c["qkv"].shape[1]), p(out), p(kc), p(vc), p(c["table"]), c_int(c["table"].shape[1]),
             p(c["seq_lens"]), c_int(c["S"]), c_int(c["max_len"]), c_int(c["nq"]), c_int(c["nkv"]), c_int(c["d"]),
-            c_int(c["page"]), c_int(c["pages"]), c_int(0), c_float(1.0 / math.sqrt(c["d"])), p(c["inv"]),
-            c_int(c["d"]), c_int(1)] + extra + [p(err), stream]
+            c_int(c["page"]), c_int(c["pages"]), c_int(window), c_float(1.0 / math.sqrt(c["d"])), p(c["inv"]),
+            c_int(c["d"]), c_int(write_kv)] + extra + [p(err), stream]
     return fn(*args)
 
 
@@ -85,12 +85,66 @@ def test_allocation_free_decode_attention_matches_the_ordinary_one_twice():
         diff = (out_a.float() - out_b.float()).abs().max() / out_a.float().abs().max()
         assert float(diff) <= 1.6e-2 and torch.equal(out_a, out_b)
         assert torch.equal(kc_a, kc_b) and torch.equal(vc_a, vc_b)      # the token's k and v were stored alike
-        # and again at once: the scratch now holds what the call before left in it
+        # and again at once: the scratch now holds what the call before left in it.  The device's free
+        # memory, as the driver counts it, is the same after the call as before: nothing was allocated
+        # behind PyTorch's back either (the first call above has loaded the module and its array).
         kc_c, vc_c = c["kc"].clone(), c["vc"].clone()
         out_c = torch.zeros_like(out_a)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = _call(lib, "rllm_attention_decode_bf16_static", c, kc_c, vc_c, out_c, err, [])
         torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
         assert rc == 0 and int(err.item()) == 0 and torch.equal(out_a, out_c)
+
+
+def _plain_decode(c, window, write_kv):
+    """The formula in float64 on the CPU: sequence s has one query at position len - 1 that sees keys
+    max(0, len - window) .. len - 1 through its block table; q (and, with write_kv, the token's own key,
+    which then comes from qkv and not from the cache) is rotated by the rotate-half rule."""
+    nq, nkv, d, page = c["nq"], c["nkv"], c["d"], c["page"]
+    qkv, kc, vc = c["qkv"].double().cpu(), c["kc"].double().cpu(), c["vc"].double().cpu()
+    inv, table = c["inv"].cpu(), c["table"].cpu()
+    out = torch.zeros(c["S"], nq * d, dtype=torch.float64)
+
+    def rot(x, pos):
+        a = pos * inv
+        x1, x2 = x[..., : d // 2], x[..., d // 2:]
+        return torch.cat([x1 * torch.cos(a) - x2 * torch.sin(a), x2 * torch.cos(a) + x1 * torch.sin(a)], dim=-1)
+    for s, n in enumerate(c["seq_lens"].tolist()):
+        pos = n - 1
+        q = rot(qkv[s, : nq * d].view(nq, d), pos)
+        lo = max(0, n - window) if window else 0
+        rows = [(int(table[s, j // page]), j % page) for j in range(lo, n)]
+        k = torch.stack([kc[pg, :, r] for pg, r in rows])            # [keys, nkv, d]
+        v = torch.stack([vc[pg, :, r] for pg, r in rows])
+        if write_kv:
+            k[-1] = rot(qkv[s, nq * d:(nq + nkv) * d].view(nkv, d), pos).bfloat16().double()
+            v[-1] = qkv[s, (nq + nkv) * d:].view(nkv, d)
+        for h in range(nq):
+            kv = h // (nq // nkv)
+            p = torch.softmax((k[:, kv] @ q[h]) / math.sqrt(d), dim=0)
+            out[s, h * d:(h + 1) * d] = p @ v[:, kv]
+    return out
+
+
+@pytest.mark.parametrize("window,write_kv", [(100, 1), (0, 0), (37, 0)])
+def test_allocation_free_decode_attention_with_a_window_and_without_the_cache_write(window, write_kv):
+    """The same entry point with a sliding window, and reading the token's own key from the cache instead of
+    storing it, against the formula in float64."""
+    lib = _lib()
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    c = _case(5 + window, [1, 36, 37, 38, 130, 600])
+    kc, vc = c["kc"].clone(), c["vc"].clone()
+    out = torch.zeros(c["S"], c["nq"] * c["d"], dtype=torch.bfloat16, device=DEV)
+    rc = _call(lib, "rllm_attention_decode_bf16_static", c, kc, vc, out, err, [], window=window, write_kv=write_kv)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(err.item()) == 0
+    want = _plain_decode(c, window, write_kv)
+    diff = (out.double().cpu() - want).abs().max() / want.abs().max()
+    assert float(diff) <= 1.6e-2, float(diff)
+    if not write_kv:
+        assert torch.equal(kc, c["kc"]) and torch.equal(vc, c["vc"])      # nothing was stored
 
 
 def test_sizes_beyond_the_fixed_scratch_are_refused():
