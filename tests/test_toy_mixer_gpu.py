@@ -28,7 +28,11 @@ def register_toy():
 
     @register_part("mixer", "toy_decay_state")
     class DecayState(Mixer):
-        """s_t = decay * s_{t-1} + W_in x_t ;  y_t = W_out s_t, state float32 [STATE] per request."""
+        """s_t = decay * s_{t-1} + W_in x_t ;  y_t = W_out s_t, state float32 [STATE] per request.
+        A step in which every sequence brings one token is computed for all rows at once from the device's
+        slot indices, without a look at the host's lists: such steps may be captured in a CUDA graph, so
+        the class says ``graph_safe``."""
+        graph_safe = True
 
         def __init__(self, spec, prefix=""):
             super().__init__(spec, prefix)
@@ -46,6 +50,11 @@ def register_toy():
 
         def forward(self, x, ctx, cache):
             u = x.float() @ self.w_in.float().t()                      # [T, STATE]
+            if ctx.num_decode == ctx.num_seqs:                         # one token a sequence: all rows at once
+                slots = ctx.state_slots.long()
+                state = cache.state.index_select(0, slots) * self.decay + u
+                cache.state.index_copy_(0, slots, state)
+                return (state @ self.w_out.float().t()).to(x.dtype)
             out = torch.empty_like(u)
             off = 0
             for s, n in enumerate(ctx.q_lens_host):                    # a sequence's tokens in order
@@ -58,6 +67,8 @@ def register_toy():
 
     @register_part("feed_forward", "toy_scale")
     class Scale(FeedForward):
+        graph_safe = True
+
         def __init__(self, spec, prefix=""):
             super().__init__(spec, prefix)
             self.hidden = spec["hidden_size"]
@@ -145,6 +156,64 @@ def test_toy_architecture_is_registered_built_and_stepped(tmp_path, dtype):
             have = np.stack([got[(r, p)] for p in range(len(toks))])
             err = np.abs(have - want[r]).max(axis=1) / np.abs(want[r]).max()
             assert err.max() <= tol, (r, int(err.argmax()), float(err.max()))
+
+
+def _toy_folder(tmp_path, name="toy"):
+    from safetensors import safe_open
+    from rllm_b200.engine.loading import write_random_model
+    register_toy()
+    cfg = {"architectures": ["ToyStateForCausalLM"], "eps": 1e-4, "torch_dtype": "float32"}
+    d = str(tmp_path / name)
+    write_random_model(d, cfg, seed=3)
+    with safe_open(os.path.join(d, "model.safetensors"), framework="pt") as f:
+        w = {n: f.get_tensor(n).double() for n in f.keys()}
+    return d, w
+
+
+def test_a_forked_request_takes_a_copy_of_the_state(tmp_path):
+    """Fork with a mixer that keeps state of fixed size: the child's slot starts as a copy of the parent's
+    (not zeroed, not shared), both go on with different tokens and match the plain formulas."""
+    d, w = _toy_folder(tmp_path)
+    rng = np.random.default_rng(8)
+    common, tail_p, tail_c = ([int(t) for t in rng.integers(0, V, size=n)] for n in (21, 12, 12))
+    tb = ru.TraceBuilder()
+    tb.step([("p", common)])
+    tb.step([("p", tail_p[:1]), ("c", tail_c[:5])], fork=[("p", "c")])
+    for i in range(1, 8):
+        tb.step([("p", tail_p[i:i + 1]), ("c", tail_c[4 + i:5 + i])])
+    tb.step([("p", tail_p[8:])], end=["p", "c"])
+    got = ru.run_trace(d, "float32", tb, V, page_size=16)
+    want = {"p": plain_toy(w, common + tail_p, 1e-4).numpy(), "c": plain_toy(w, common + tail_c, 1e-4).numpy()}
+    assert max(pos for r, pos in got if r == "c") == len(common) + len(tail_c) - 1
+    for (r, pos), row in got.items():
+        err = np.abs(row - want[r][pos]).max() / np.abs(want[r]).max()
+        assert err <= 1e-4, (r, pos, float(err))
+
+
+def test_a_stateful_mixer_decodes_in_captured_graphs_and_padded_batches(tmp_path):
+    """Eleven requests generate through the entry point with the toy model: decode steps of 9 to 11 rows are
+    padded to captured sizes (12), whose spare rows use the storage's spare state slot; the next step is
+    prepared and launched ahead like the Llama's.  Tokens are those of the plain formulas, and a request's
+    state is untouched by the padding rows beside it."""
+    from rllm_b200 import LLM, SamplingParams
+    d, w = _toy_folder(tmp_path, "toy_gen")
+    rng = np.random.default_rng(4)
+    prompts = [[int(t) for t in rng.integers(0, V, size=int(n))] for n in rng.integers(2, 30, size=11)]
+    budgets = [8 + 2 * i for i in range(11)]
+    params = [SamplingParams(temperature=0.0, max_tokens=n, ignore_eos=True) for n in budgets]
+    llm = LLM(d, dtype="fp32", num_gpu_blocks=64, max_num_seqs=12, enable_prefix_caching=False)
+    assert llm.engine.runner.capture_graphs
+    outs = llm.generate(prompts, params)
+    captured = [k for k, g in llm.engine.runner.graphs.items() if g.graph is not None]
+    assert any(k[0] == 12 for k in captured), captured
+    assert llm.engine.stats()["num_steps_ahead"] > 5
+    for p, n, o in zip(prompts, budgets, outs):
+        toks = list(p)
+        for _ in range(n):
+            toks.append(int(torch.argmax(plain_toy(w, toks, 1e-4)[-1])))
+        assert o.outputs[0].token_ids == toks[len(p):]
+    llm.engine.cache.check()
+    assert llm.engine.cache.usage()["num_requests"] == 0
 
 
 # ---------------------------------------------------------------------------
