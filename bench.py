@@ -1,19 +1,32 @@
 #!/usr/bin/env python3
-"""Decode and prefill throughput of rllm_b200 on one B200, Llama-3.2-1B shape.
+"""Decode and prefill throughput of rllm_b200 on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--no-workloads]
 
-Prints ONE JSON line.  A "step" is one decode step of a batch of 8 sequences
-at the benchmark context (each sequence ends the run holding ``context_len``
-tokens).  ``value`` is decoded tokens per second timed on the device with CUDA
-events around exactly K steps that stay on the device (graph replay, argmax,
-next-token feed-back); ``e2e`` is the same metric through the Python entry
-point (``LLM.step``): host token ids in, pinned-memory copy of the step's
-inputs to the device, sampled tokens read back to the host, every step.
-Weights are random (N(0, 0.02), seed 0), token ids uniform random: synthetic
-data, as in the reference's own workloads.  No flush of L2 is needed between
-steps: every step reads all weights (2.5 GB) and the live KV cache, far more
-than the 126 MB of L2.
+Prints ONE JSON line.
+
+Headline (Llama-3.2-1B shape, bfloat16, random weights): a batch of 8 sequences, each holding a 2,048-token
+prompt, decodes greedily; a "step" is one decode step.  After W warm-up steps exactly K steps are timed
+(K = 256 by default: the sequences then go from 2,048 to 2,304 tokens).  ``value`` is decoded tokens per
+second timed on the device with CUDA events around K steps that stay on the device (graph replay, argmax,
+next-token feed-back).  ``e2e`` is the same metric through the Python entry point (``LLM.step``): host token
+ids in, pinned-memory copy of the step's inputs to the device, sampled tokens read back to the host, every
+step, timed by the host's clock between two device synchronisations.  ``points`` holds the same two figures
+at batch 1 and 64, and device-timed decoding at the full context of 4,096 tokens.  ``prefill`` is one
+2,048-token prompt as one step.  ``roofline`` is the decode step against the measured copy bandwidth: the
+bytes it has to read (every weight once, the keys and values of the live requests) over its time.
+
+``workloads`` holds two serving runs through ``LLM.add_request`` / ``LLM.step`` with continuous batching:
+the Llama-3.2-3B shape (32 requests, prompts of 128 to 4,096 tokens, at most 4,096 tokens a step, 128 tokens
+each at temperature 0.8) and the Llama-3.1-8B shape (16 requests that share a 1,024-token prefix, 512-token
+portions beside decoded tokens, 256 greedy tokens, prefix caching on), after the reference's synthetic
+workload generator (crates/rllm-bench/src/workload.rs:74-90).  Each gives wall time, generated and prompt
+tokens per second, preemptions, prefix-hit tokens, steps launched ahead, and the fraction of the roofline:
+the sum over the steps that ran of max(flops / peak flops, bytes / peak bandwidth), over the wall time.
+
+Weights are random (N(0, 0.02), seed 0), token ids uniform random: synthetic data, as in the reference's own
+workloads.  No flush of L2 is needed between steps: every step reads all weights (2.5 GB and more) and the
+live KV cache, far more than the 126 MB of L2.
 """
 from __future__ import annotations
 
@@ -29,16 +42,25 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-LLAMA_1B = {
-    "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 16,
-    "hidden_size": 2048, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64,
-    "intermediate_size": 8192, "vocab_size": 128256, "rope_theta": 500000.0,
-    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
-                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
-    "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
-    "hidden_act": "silu", "torch_dtype": "bfloat16", "bos_token_id": 128000, "eos_token_id": 128001,
-}
+
+def llama(layers, hidden, heads, kv_heads, head_dim, inter, factor, tied):
+    return {
+        "architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": layers,
+        "hidden_size": hidden, "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": head_dim,
+        "intermediate_size": inter, "vocab_size": 128256, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": factor, "low_freq_factor": 1.0,
+                         "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+        "max_position_embeddings": 131072, "rms_norm_eps": 1e-5, "tie_word_embeddings": tied,
+        "hidden_act": "silu", "torch_dtype": "bfloat16", "bos_token_id": 128000, "eos_token_id": 128001,
+    }
+
+
+LLAMA_1B = llama(16, 2048, 32, 8, 64, 8192, 32.0, True)
+LLAMA_3B = llama(28, 3072, 24, 8, 128, 8192, 32.0, True)
+LLAMA_8B = llama(32, 4096, 32, 8, 128, 14336, 8.0, False)
 CONTEXT_LEN = 4096
+PROMPT_LEN = 2048
+DECODE_TOKENS = 256
 BLOCK_SIZE = 16
 PREFILL_TOKENS = 2048
 
@@ -98,11 +120,16 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# -- what a step has to read and to compute ---------------------------------------------------------------
 def layer_param_count(c, layers):
     h, i, d = c["hidden_size"], c["intermediate_size"], c["head_dim"]
     nq, nkv = c["num_attention_heads"], c["num_key_value_heads"]
     per_layer = h * (nq + 2 * nkv) * d + nq * d * h + 3 * h * i
     return per_layer * layers
+
+
+def kv_bytes_per_token(c, layers):
+    return layers * 2 * c["num_key_value_heads"] * c["head_dim"] * 2
 
 
 def prefill_flops(c, layers, T):
@@ -113,20 +140,142 @@ def prefill_flops(c, layers, T):
 
 def decode_bytes(c, layers, batch, ctx_mid):
     weights = 2 * (layer_param_count(c, layers) + c["hidden_size"] * c["vocab_size"])
-    kv = batch * ctx_mid * layers * 2 * c["num_key_value_heads"] * c["head_dim"] * 2
-    return weights + kv
+    return weights + batch * ctx_mid * kv_bytes_per_token(c, layers)
+
+
+def step_floor_seconds(c, layers, scheduled, pk):
+    """The least time a step of these (start, tokens, wants logits) entries can take: the larger of its
+    flops over the tensor peak and the bytes it must read over the copy bandwidth."""
+    tokens = sum(n for _, n, _ in scheduled)
+    rows = sum(1 for _, _, w in scheduled if w)
+    flops = 2 * tokens * layer_param_count(c, layers) + 2 * rows * c["hidden_size"] * c["vocab_size"]
+    nbytes = 2 * (layer_param_count(c, layers) + c["hidden_size"] * c["vocab_size"])
+    for start, n, _ in scheduled:
+        # token i of the portion sees start + i + 1 keys; the keys are read once per portion
+        flops += layers * 4 * c["head_dim"] * c["num_attention_heads"] * (n * start + n * (n + 1) // 2)
+        nbytes += (start + n) * kv_bytes_per_token(c, layers)
+    return max(flops / (pk["bf16_tflops"] * 1e12), nbytes / (pk["hbm_gbs"] * 1e9))
+
+
+def write_config(cfg):
+    d = tempfile.mkdtemp(prefix="rllm_bench_")
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    return d
+
+
+# -- a serving workload through the entry point -------------------------------------------------------------
+def run_workload(cfg, prompts, params, pk, windows, warm_prompts, **llm_kw):
+    """All requests are added at once and stepped until none is left.  A workload of the same shape with
+    other tokens (``warm_prompts``) runs once untimed first (graphs are captured, libraries warmed, and
+    nothing of the timed prompts is in the prefix cache), then the workload itself, timed by the host's
+    clock."""
+    import torch
+
+    from rllm_b200 import LLM
+    layers = cfg["num_hidden_layers"]
+    t0 = time.time()
+    llm = LLM(write_config(cfg), dtype="bf16", random_weights=True, seed=0, draw_on_device=True,
+              block_size=BLOCK_SIZE, **llm_kw)
+    load_s = time.time() - t0
+    eng = llm.engine
+    result = None
+    for timed in (False, True):
+        before = dict(eng.stats())
+        floor = 0.0
+        n_out = n_prompt_steps = 0
+        prompt_tokens = prompt_time = 0.0
+        torch.cuda.synchronize()
+        a_wall = time.time()
+        a = time.perf_counter()
+        for p, sp in zip(prompts if timed else warm_prompts, params):
+            llm.add_request(p, sp)
+        while llm.has_work():
+            t_step = time.perf_counter()
+            outs = llm.step()
+            sched = eng.last_schedule
+            n_out += len(outs)
+            if sched is not None and sched.scheduled:
+                floor += step_floor_seconds(cfg, layers, [(s.start, s.num_tokens, s.want_logits)
+                                                          for s in sched.scheduled], pk)
+                if sched.num_prefill_tokens:
+                    # a step with prompt tokens is never launched ahead: its host time is its own
+                    torch.cuda.synchronize()
+                    prompt_time += time.perf_counter() - t_step
+                    prompt_tokens += sched.num_prefill_tokens
+                    n_prompt_steps += 1
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - a
+        eng.runner.check_errors()
+        if timed:
+            windows.append((a_wall, time.time()))
+            st = eng.stats()
+            result = {
+                "wall_s": round(wall, 4), "requests": len(prompts), "generated_tokens": n_out,
+                "prompt_tokens": sum(len(p) for p in prompts),
+                "output_tok_s": round(n_out / wall, 1),
+                "total_tok_s": round((n_out + prompt_tokens) / wall, 1),
+                "prefill_tok_s": round(prompt_tokens / prompt_time, 1) if prompt_time else None,
+                "prompt_tokens_computed": int(prompt_tokens), "steps": st["num_steps"] - before["num_steps"],
+                "steps_with_prompt_tokens": n_prompt_steps,
+                "preemptions": st["num_preemptions"] - before["num_preemptions"],
+                "prefix_hit_tokens": st["prefix_hit_tokens"] - before["prefix_hit_tokens"],
+                "steps_launched_ahead": st["num_steps_ahead"] - before["num_steps_ahead"],
+                "roofline_frac": round(floor / wall, 4), "cache_pages": eng.num_pages[0],
+                "layers": layers, "load_s": round(load_s, 1),
+            }
+    del llm, eng
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return result
+
+
+def workload_3b(pk, windows):
+    """BASELINE.json configs[3]: 32 requests, prompts uniform in [128, 4096], at most 4,096 tokens a step with
+    chunked prefill, 128 tokens each at temperature 0.8, context 8,192."""
+    import numpy as np
+
+    from rllm_b200 import SamplingParams
+    rng = np.random.default_rng(3)
+    lengths = rng.integers(128, 4097, size=32)
+    prompts = [[int(t) for t in rng.integers(0, 128256, size=int(n))] for n in lengths]
+    warm = [[int(t) for t in rng.integers(0, 128256, size=int(n))] for n in lengths]
+    params = [SamplingParams(temperature=0.8, seed=1000 + i, max_tokens=128, ignore_eos=True) for i in range(32)]
+    return run_workload(LLAMA_3B, prompts, params, pk, windows, warm, max_model_len=8192, max_num_seqs=32,
+                        max_num_batched_tokens=4096, long_prefill_token_threshold=4096,
+                        enable_prefix_caching=False)
+
+
+def workload_8b(pk, windows):
+    """BASELINE.json configs[4]: 16 requests that share a 1,024-token prefix, followed by suffixes of 256 to
+    2,048 tokens of their own; 512-token portions beside decoded tokens; 256 greedy tokens each; context 8,192;
+    prefix caching on."""
+    import numpy as np
+
+    from rllm_b200 import SamplingParams
+    rng = np.random.default_rng(4)
+    lengths = rng.integers(256, 2049, size=16)
+    shared, shared_warm = ([int(t) for t in rng.integers(0, 128256, size=1024)] for _ in range(2))
+    prompts = [shared + [int(t) for t in rng.integers(0, 128256, size=int(n))] for n in lengths]
+    warm = [shared_warm + [int(t) for t in rng.integers(0, 128256, size=int(n))] for n in lengths]
+    params = [SamplingParams(temperature=0.0, max_tokens=256, ignore_eos=True) for _ in range(16)]
+    return run_workload(LLAMA_8B, prompts, params, pk, windows, warm, max_model_len=8192, max_num_seqs=16,
+                        max_num_batched_tokens=4096, long_prefill_token_threshold=512,
+                        enable_prefix_caching=True)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=DECODE_TOKENS)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (stated in config)")
-    ap.add_argument("--context", type=int, default=CONTEXT_LEN)
-    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    ap.add_argument("--no-points", action="store_true", help="skip the other batch sizes and contexts")
+    ap.add_argument("--no-workloads", action="store_true", help="skip the 3B and 8B serving workloads")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -138,6 +287,9 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not measured")
         return 2
     K, W = args.steps, max(3, args.warmup)
+    if args.prompt_len + K + W + 4 > CONTEXT_LEN:
+        print(f"bench.py: a prompt of {args.prompt_len} tokens and {K} + {W} steps do not fit the context of {CONTEXT_LEN}")
+        return 2
 
     import numpy as np
     import torch
@@ -149,13 +301,11 @@ def main():
     cfg = dict(LLAMA_1B)
     layers = args.layers or cfg["num_hidden_layers"]
     cfg["num_hidden_layers"] = layers
-    model_dir = tempfile.mkdtemp(prefix="rllm_bench_")
-    with open(os.path.join(model_dir, "config.json"), "w") as f:
-        json.dump(cfg, f)
+    model_dir = write_config(cfg)
     max_batch = args.batch if args.no_points else max(args.batch, 64)
-    pages = max_batch * (-(-args.context // BLOCK_SIZE) + 2) + -(-PREFILL_TOKENS // BLOCK_SIZE) + 64
+    pages = max_batch * (-(-CONTEXT_LEN // BLOCK_SIZE) + 2) + -(-PREFILL_TOKENS // BLOCK_SIZE) + 64
     t0 = time.time()
-    llm = LLM(model_dir, dtype="bf16", max_model_len=args.context, max_num_seqs=max_batch,
+    llm = LLM(model_dir, dtype="bf16", max_model_len=CONTEXT_LEN, max_num_seqs=max_batch,
               max_num_batched_tokens=8192, long_prefill_token_threshold=8192, block_size=BLOCK_SIZE,
               num_gpu_blocks=pages, enable_prefix_caching=False, random_weights=True, seed=0,
               draw_on_device=True)
@@ -167,41 +317,49 @@ def main():
     clocks.start()
     windows = []
 
-    def decode_point(batch, steps, warm, with_e2e):
-        """(device tok/s, ms per step, e2e dict or None) at this batch."""
-        total_new = 2 * (steps + warm) + 2
-        prompt_len = args.context - total_new
+    def e2e_point(batch, prompt_len, steps, warm):
+        """Through ``LLM.step``: tokens a second, ms a step, bytes to and from the device a step."""
         prompts = [[int(t) for t in rng.integers(0, cfg["vocab_size"], size=prompt_len)] for _ in range(batch)]
-        sp = SamplingParams(temperature=0.0, max_tokens=total_new, ignore_eos=True)
+        # no request may end inside the timed steps (those whose prompts are computed first decode a few
+        # tokens while the others' prompts are still being computed)
+        sp = SamplingParams(temperature=0.0, max_tokens=CONTEXT_LEN - prompt_len, ignore_eos=True)
         ids = [llm.add_request(p, sp) for p in prompts]
         while any(eng.scheduler.requests[i].num_computed < prompt_len for i in ids):
-            llm.step()                                         # prefill
-        e2e = None
-        if with_e2e:
-            for _ in range(warm):
-                llm.step()
-            torch.cuda.synchronize()
-            h2d0 = sum(g.h2d_bytes for g in runner.graphs.values())
-            a = time.time()
-            t_a = time.perf_counter()
-            n_tok = 0
-            for _ in range(steps):
-                n_tok += len(llm.step())
-            torch.cuda.synchronize()
-            dt = time.perf_counter() - t_a
-            windows.append((a, time.time()))
-            # host -> device: the step's positions, lengths and block tables from pinned memory, on the steps
-            # where a block table changed (the token ids of a decode step are the step before's samples and
-            # stay on the device); device -> host: the sampled tokens, every step, and the error words
-            h2d = sum(g.h2d_bytes for g in runner.graphs.values()) - h2d0
-            e2e = {"value": n_tok / dt, "unit": "tok/s", "h2d_bytes_per_step": int(h2d / steps),
-                   "d2h_bytes_per_step": int(batch * 4 + 1), "ms_per_step": 1e3 * dt / steps}
-        # the device-timed run goes on from where the requests are
-        entries = []
+            llm.step()                                         # the prompts
+        for _ in range(warm):
+            llm.step()
+        torch.cuda.synchronize()
+        h2d0 = sum(g.h2d_bytes for g in runner.graphs.values())
+        a = time.time()
+        t_a = time.perf_counter()
+        n_tok = 0
+        for _ in range(steps):
+            n_tok += len(llm.step())
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t_a
+        windows.append((a, time.time()))
+        assert n_tok == batch * steps, (n_tok, batch, steps)
+        # host -> device: the step's positions, lengths and block tables from pinned memory, on the steps
+        # where a block table changed (the token ids of a decode step are the step before's samples and
+        # stay on the device); device -> host: the sampled tokens, every step, and the error words
+        h2d = sum(g.h2d_bytes for g in runner.graphs.values()) - h2d0
         for i in ids:
-            r = eng.scheduler.requests[i]
-            assert eng.cache.ensure(i, r.num_computed, r.num_computed + steps + warm)
-            entries.append(StepEntry(i, [r.all_token_ids[r.num_computed]], r.num_computed, [0]))
+            llm.abort_request(i)
+        return {"value": n_tok / dt, "unit": "tok/s", "h2d_bytes_per_step": int(h2d / steps),
+                "d2h_bytes_per_step": int(batch * 4 + 1), "ms_per_step": 1e3 * dt / steps}
+
+    def device_point(batch, prompt_len, steps, warm):
+        """(tokens a second, ms a step) timed on the device around ``steps`` steps that stay there, every
+        sequence holding ``prompt_len`` tokens when they begin.  The step function is driven directly."""
+        ids = [f"dev{i}" for i in range(batch)]
+        for i in ids:
+            eng.cache.admit(i)
+            assert eng.cache.ensure(i, 0, prompt_len + steps + warm + 1)
+        per_step = max(1, 8192 // prompt_len)
+        for a in range(0, batch, per_step):                    # the prompts, some at a time
+            runner.step([StepEntry(i, [int(t) for t in rng.integers(0, cfg["vocab_size"], size=prompt_len)], 0, [])
+                         for i in ids[a:a + per_step]])
+        entries = [StepEntry(i, [int(rng.integers(0, cfg["vocab_size"]))], prompt_len, [0]) for i in ids]
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         a = time.time()
@@ -211,16 +369,30 @@ def main():
         ms = ev0.elapsed_time(ev1)
         runner.check_errors()
         for i in ids:
-            llm.abort_request(i)
-        return batch * steps / (ms / 1e3), ms / steps, e2e
+            eng.cache.free(i)
+        return batch * steps / (ms / 1e3), ms / steps
 
-    # launches of this engine's own kernels in one decode step (counted on an eager step)
-    value, ms_step, e2e = decode_point(args.batch, K, W, True)
+    def frac(batch, ms, ctx_mid):
+        return decode_bytes(cfg, layers, batch, ctx_mid) / (ms / 1e3) / 1e9 / pk["hbm_gbs"]
+
+    P = args.prompt_len
+    ctx_mid = P + W + K // 2
+    e2e = e2e_point(args.batch, P, K, W)
+    value, ms_step = device_point(args.batch, P, K, W)
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            pv, _, _ = decode_point(b, min(K, 64), W, False)
+            pv, pms = device_point(b, P, K, W)
+            pe = e2e_point(b, P, K, W)
             points[f"decode_b{b}"] = round(pv, 1)
+            points[f"decode_b{b}_e2e"] = round(pe["value"], 1)
+            points[f"decode_b{b}_hbm_frac"] = round(frac(b, pms, ctx_mid), 4)
+        # the whole context of the configuration: sequences that end the run with 4,096 tokens
+        k4 = min(K, 64)
+        for b in (1, 8, 64):
+            pv, pms = device_point(b, CONTEXT_LEN - (k4 + W) - 4, k4, W)      # ends with 4,092 tokens
+            points[f"decode_b{b}_ctx4096"] = round(pv, 1)
+            points[f"decode_b{b}_ctx4096_hbm_frac"] = round(frac(b, pms, CONTEXT_LEN - 4 - k4 // 2), 4)
 
     # prefill of one 2,048-token prompt, device-timed
     eng.cache.admit("prefill")
@@ -258,13 +430,22 @@ def main():
     runner.capture_graphs = was
     eng.cache.free("count")
     torch.cuda.synchronize()
+
+    workloads = {}
+    if not args.no_workloads and args.layers is None:
+        del llm, eng, runner
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        workloads["llama3b_continuous_batching"] = workload_3b(pk, windows)
+        workloads["llama8b_shared_prefix"] = workload_8b(pk, windows)
     clocks.stop()
 
-    ctx_mid = args.context - K // 2
     nbytes = decode_bytes(cfg, layers, args.batch, ctx_mid)
     achieved = nbytes / (ms_step / 1e3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8 (Llama-3.2-1B shape, bf16)", "value": round(value, 1),
+        "metric": f"decode tok/s at batch {args.batch}, 2,048-token prompts + 256 tokens (Llama-3.2-1B shape, bf16)",
+        "value": round(value, 1),
         "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(ms_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (random weights N(0,0.02) seed 0, uniform random token ids)", "impl": "ours",
@@ -272,16 +453,17 @@ def main():
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "global_batch": args.batch, "seq_len": args.context, "block_size": BLOCK_SIZE,
-                   "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU", "cuda_graphs": True,
-                   "l2": "inputs larger than L2 (2.5 GB of weights per step)", "peaks": pk["source"],
-                   "load_s": round(load_s, 1)},
+                   "global_batch": args.batch, "seq_len": P + W + K, "prompt_len": P, "context_cap": CONTEXT_LEN,
+                   "block_size": BLOCK_SIZE, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
+                   "cuda_graphs": True, "l2": "inputs larger than L2 (2.5 GB of weights per step)",
+                   "peaks": pk["source"], "load_s": round(load_s, 1)},
         "e2e": {k: (round(v, 3) if isinstance(v, float) else v) for k, v in e2e.items()},
         "gpu_launches": int(per_step * K),
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "workloads": workloads,
         "clocks": clocks.summary(windows),
         "launches_per_decode_step": int(per_step), "launches_per_prefill": int(prefill_launches),
     }
