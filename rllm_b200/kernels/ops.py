@@ -281,7 +281,7 @@ _gemm_err = {}
 
 
 def gemm_error_word(device: torch.device) -> torch.Tensor:
-    """The per-device error word of the tcgen05 GEMM (bit 16: a bounded wait ran out)."""
+    """The per-device error word of the tcgen05 GEMM (bit 4: a bounded wait ran out)."""
     t = _gemm_err.get(device)
     if t is None:
         t = _gemm_err[device] = torch.zeros(1, dtype=torch.int32, device=device)
@@ -290,9 +290,13 @@ def gemm_error_word(device: torch.device) -> torch.Tensor:
 
 def check_gemm_errors(device: torch.device) -> None:
     t = _gemm_err.get(device)
-    if t is not None and int(t.item()):
+    code = int(t.item()) if t is not None else 0
+    if code:
         t.zero_()
-        raise KernelError("gemm_tcgen05: a wait on an mbarrier ran out; the result of that product is undefined")
+        what = []
+        if code & 16:
+            what.append("gemm_tcgen05: a wait on an mbarrier ran out")
+        raise KernelError("; ".join(what or [f"error word {code}"]) + "; the result of that product is undefined")
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: str = "store") -> None:

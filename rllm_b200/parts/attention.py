@@ -98,9 +98,15 @@ class PagedAttention(Mixer):
         return fused_residual_takes(num_rows, dtype, self.w_qkv, self.w_o)
 
     def forward(self, x, ctx: StepContext, cache: KVCacheView, residual=None):
-        T = x.shape[0]
+        out = self.attend(linear(x, self.w_qkv), ctx, cache)          # qkv [T, (nq + 2 nkv) d]
+        return linear(out, self.w_o, residual=residual)
+
+    def attend(self, qkv: torch.Tensor, ctx: StepContext, cache: KVCacheView) -> torch.Tensor:
+        """From the tokens' projections (q, k and v heads side by side) to the attention's output
+        [T, nq * d], before the output projection: position encoding, cache write, attention."""
+        x = qkv
+        T = qkv.shape[0]
         nkv_here = 0 if self.shares_kv else self.nkv
-        qkv = linear(x, self.w_qkv)                                   # [T, (nq + 2 nkv) d]
         table = ctx.block_tables[cache.group]
         fused = self.position.fused_rotary(x.device)
         writes = cache.writes and not self.shares_kv
@@ -135,4 +141,4 @@ class PagedAttention(Mixer):
             else:
                 ops.attention_simt(qkv, stride, out, cache.k, cache.v, table, ctx.positions, ctx.token_seq,
                                    self.nq, self.nkv, self.d, window, self.scale, ctx.err)
-        return linear(out, self.w_o, residual=residual)
+        return out
