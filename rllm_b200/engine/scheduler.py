@@ -14,6 +14,12 @@ never scheduled as portions (:355-382) and a token is sampled after every
 portion; here logits are asked for only when a portion ends at the last known
 token.
 
+With prefix sharing a waiting request whose prompt shares pages with a running
+request that is still computing them is held back until they exist (the
+reference picks the waiting request with the longest cached prefix,
+:540-603, but registers pages after the compute like this engine, so requests
+that arrive together would all compute their common prefix).
+
 When pages run out: a waiting request is simply not admitted yet (:497-505).
 A running request that needs a page and cannot get one makes room by
 preemption (:357-375, :606-625): the newest running request (latest arrival)
@@ -35,7 +41,7 @@ import enum
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, page_hashes
 from ..sampling.params import SamplingParams
 
 
@@ -68,6 +74,7 @@ class Request:
     num_cached_prefix: int = 0       # tokens taken over from shared pages at admission
     num_preemptions: int = 0
     status: RequestStatus = RequestStatus.WAITING
+    prompt_page_hashes: Optional[List[bytes]] = None     # chained hashes of the prompt's full pages, made on demand
 
     @property
     def all_token_ids(self) -> List[int]:
@@ -164,6 +171,33 @@ class Scheduler:
             n = min(n, self.config.long_prefill_token_threshold)
         return n
 
+    def _prompt_hashes(self, req: Request) -> List[bytes]:
+        if req.prompt_page_hashes is None:
+            req.prompt_page_hashes = page_hashes(req.prompt_token_ids, self.cache.page_size)
+        return req.prompt_page_hashes
+
+    def _prefix_is_on_its_way(self, req: Request) -> bool:
+        """With prefix sharing: whether a running request is still computing pages of its prompt that
+        this waiting request's prompt shares and cannot find yet.  Admitting it now would compute the
+        same pages twice (pages become findable only after their keys exist); a step or two later it
+        finds them.  The running request makes progress whatever happens to this one, and if it is
+        preempted or ends the test fails and the request is admitted as usual."""
+        mine = self._prompt_hashes(req)
+        if not mine:
+            return False
+        page = self.cache.page_size
+        have = self.cache.match_prefix(req.all_token_ids) // page
+        for r in self.running:
+            if r.num_computed >= len(r.prompt_token_ids):
+                continue                              # its prompt's pages are all findable (or evicted: nothing to wait for)
+            theirs = self._prompt_hashes(r)
+            common = 0
+            while common < len(mine) and common < len(theirs) and mine[common] == theirs[common]:
+                common += 1
+            if common > have and common > r.num_computed // page:
+                return True
+        return False
+
     def _preempt(self, req: Request, out: SchedulerOutput) -> None:
         self.cache.free(req.request_id)
         req.num_computed = 0
@@ -219,6 +253,8 @@ class Scheduler:
             req = self.waiting[0]
             if req.request_id in out.preempted:
                 break                         # just preempted: not in the same step
+            if self.cache.prefix_caching and self._prefix_is_on_its_way(req):
+                break                         # first come, first served: those behind it wait too
             tokens = req.all_token_ids
             self.cache.admit(req.request_id)
             cached = self.cache.adopt_prefix(req.request_id, tokens)

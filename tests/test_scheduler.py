@@ -219,3 +219,39 @@ def test_max_tokens_is_what_ensure_takes():
     assert cache.ensure("a", 24, 32) and cache.max_tokens("a", 32) == 40
     cache.free("a")
     cache.check()
+
+
+def test_requests_that_arrive_together_share_a_prefix_that_only_one_computes():
+    """Four requests with the same 48-token prefix arrive at once.  Pages become findable only after their
+    keys exist, so the first is admitted alone; the others wait while it computes the common pages and are
+    then admitted with hits: the prefix is computed once."""
+    s, cache = make(prefix=True, page=16, pages=64, max_num_batched_tokens=32, long_prefill_token_threshold=0)
+    shared = list(range(100, 148))
+    for i in range(4):
+        s.add_request(Request(f"r{i}", shared + [900 + 7 * i + j for j in range(10 + i)],
+                              SamplingParams(max_tokens=3), i, i, 3))
+    out = run_step(s)
+    assert [(x.request.request_id, x.start, x.num_tokens) for x in out.scheduled] == [("r0", 0, 32)]
+    out = run_step(s)                                  # r0's second portion: the third common page is still to come
+    assert [x.request.request_id for x in out.scheduled] == ["r0"]
+    out = run_step(s)                                  # the common pages exist: the others come in behind them
+    got = {x.request.request_id: (x.start, x.num_tokens) for x in out.scheduled}
+    assert got["r1"][0] == 48 and got["r2"][0] == 48 and s.prefix_hit_tokens >= 96
+    while s.has_work():
+        run_step(s)
+    assert s.prefix_hit_tokens == 3 * 48 and cache.num_free_pages() == 64
+
+
+def test_a_held_back_request_is_admitted_when_the_one_it_waits_for_goes_away():
+    s, cache = make(prefix=True, page=16, pages=64, max_num_batched_tokens=16, long_prefill_token_threshold=0)
+    shared = list(range(100, 148))
+    s.add_request(Request("a", shared + [1, 2], SamplingParams(max_tokens=2), 0, 0, 2))
+    s.add_request(Request("b", shared + [3, 4, 5], SamplingParams(max_tokens=2), 1, 1, 2))
+    out = run_step(s)
+    assert [x.request.request_id for x in out.scheduled] == ["a"]
+    assert s.abort_request("a")
+    out = run_step(s)                                  # nobody computes the prefix any more
+    assert [(x.request.request_id, x.start) for x in out.scheduled] == [("b", 16)]     # a's first page had been registered
+    while s.has_work():
+        run_step(s)
+    cache.check()
