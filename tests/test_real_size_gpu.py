@@ -190,7 +190,8 @@ def test_generation_at_real_widths_with_a_shared_prefix_and_preemption(folder, d
     alone = [roomy.generate([p], [sp])[0].outputs[0].token_ids for p, sp in zip(prompts, params)]
     del roomy
     torch.cuda.empty_cache()
-    need = sum(-(-(len(p) + 24) // 16) for p in prompts)
+    # pages the twelve need when the six pages of the prefix are held once; half of that is the pool
+    need = sum(-(-(len(p) + 24) // 16) for p in prompts) - 11 * (96 // 16)
     tight = _llm(folder, dtype, max_num_seqs=12, num_gpu_blocks=need // 2, max_num_batched_tokens=128,
                  long_prefill_token_threshold=48, enable_prefix_caching=True)
     outs = tight.generate(prompts, params)
