@@ -168,8 +168,9 @@ def write_config(cfg):
 def run_workload(cfg, prompts, params, pk, windows, warm_prompts, **llm_kw):
     """All requests are added at once and stepped until none is left.  A workload of the same shape with
     other tokens (``warm_prompts``) runs once untimed first (graphs are captured, libraries warmed, and
-    nothing of the timed prompts is in the prefix cache), then the workload itself, timed by the host's
-    clock."""
+    nothing of the timed prompts is in the prefix cache), then the workload itself three times, each timed
+    by the host's clock with the prefix cache emptied in between; the pass with the median wall time is
+    reported."""
     import torch
 
     from rllm_b200 import LLM
@@ -179,8 +180,8 @@ def run_workload(cfg, prompts, params, pk, windows, warm_prompts, **llm_kw):
               block_size=BLOCK_SIZE, **llm_kw)
     load_s = time.time() - t0
     eng = llm.engine
-    result = None
-    for timed in (False, True):
+    results = []
+    for timed in (False, True, True, True):
         before = dict(eng.stats())
         floor = 0.0
         n_out = n_prompt_steps = 0
@@ -210,7 +211,7 @@ def run_workload(cfg, prompts, params, pk, windows, warm_prompts, **llm_kw):
         if timed:
             windows.append((a_wall, time.time()))
             st = eng.stats()
-            result = {
+            results.append({
                 "wall_s": round(wall, 4), "requests": len(prompts), "generated_tokens": n_out,
                 "prompt_tokens": sum(len(p) for p in prompts),
                 "output_tok_s": round(n_out / wall, 1),
@@ -223,7 +224,13 @@ def run_workload(cfg, prompts, params, pk, windows, warm_prompts, **llm_kw):
                 "steps_launched_ahead": st["num_steps_ahead"] - before["num_steps_ahead"],
                 "roofline_frac": round(floor / wall, 4), "cache_pages": eng.num_pages[0],
                 "layers": layers, "load_s": round(load_s, 1),
-            }
+            })
+            # the prompts of this pass must not be found in the prefix cache by the next one
+            if eng.cache.prefix_caching:
+                eng.cache.pools[eng.cache.paged[0]].reset_prefix_cache()
+    results.sort(key=lambda r: r["wall_s"])
+    result = dict(results[len(results) // 2], timed_passes=len(results),
+                  wall_s_all=[r["wall_s"] for r in results])
     del llm, eng
     import gc
     gc.collect()

@@ -97,6 +97,7 @@ def plan_cache_pages(model: DecoderModel, args: EngineArgs, max_model_len: int, 
     if args.num_gpu_blocks is not None:
         return [min(args.num_gpu_blocks, u) if need_windowed else args.num_gpu_blocks
                 for u, need_windowed in zip(useful, _windowed(model))]
+    torch.cuda.empty_cache()          # blocks that PyTorch's allocator holds but nobody uses (the loader's temporaries) are free
     free, total = torch.cuda.mem_get_info(device)
     spec = model.spec
     act = args.max_num_batched_tokens * (spec.hidden_size * 16 + 64 * 1024) + \

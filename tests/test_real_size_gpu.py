@@ -240,11 +240,11 @@ def test_cache_sized_from_free_memory(folder):
     torch.cuda.empty_cache()
     free, total = torch.cuda.mem_get_info()
     used_frac = (total - free) / total
-    tiny_share = min(0.99, used_frac + (3 << 30) / total)          # about 3 GiB beyond what is in use now
+    tiny_share = min(0.99, used_frac + (6 << 30) / total)          # about 6 GiB beyond what is in use now
     small = _llm(folder, "bf16", max_model_len=65536, max_num_seqs=256, gpu_memory_utilization=tiny_share)
     n = small.engine.num_pages[0]
     assert 4 <= n < 256 * 4096
-    assert small.engine.storage.num_bytes() <= 3 << 30
+    assert small.engine.storage.num_bytes() <= 6 << 30
     outs = small.generate(prompts[:1], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
     assert len(outs[0].outputs[0].token_ids) == 4
 
