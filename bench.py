@@ -24,6 +24,10 @@ workload generator (crates/rllm-bench/src/workload.rs:74-90).  Each gives wall t
 tokens per second, preemptions, prefix-hit tokens, steps launched ahead, and the fraction of the roofline:
 the sum over the steps that ran of max(flops / peak flops, bytes / peak bandwidth), over the wall time.
 
+``library_standin`` is not the reference (which cannot be built here): it is the same model shape written
+with PyTorch's library operators only, timed the same way, so that the figures above have something
+beside the roofline to stand against.
+
 Weights are random (N(0, 0.02), seed 0), token ids uniform random: synthetic data, as in the reference's own
 workloads.  No flush of L2 is needed between steps: every step reads all weights (2.5 GB and more) and the
 live KV cache, far more than the 126 MB of L2.
@@ -230,12 +234,124 @@ def run_workload(cfg, prompts, params, pk, windows, warm_prompts, **llm_kw):
                 eng.cache.pools[eng.cache.paged[0]].reset_prefix_cache()
     results.sort(key=lambda r: r["wall_s"])
     result = dict(results[len(results) // 2], timed_passes=len(results),
-                  wall_s_all=[r["wall_s"] for r in results])
+                  wall_s_all=" ".join(str(r["wall_s"]) for r in results))
     del llm, eng
     import gc
     gc.collect()
     torch.cuda.empty_cache()
     return result
+
+
+# -- a stand-in for the missing reference arm: the same model through library operators only --------------
+def library_standin(cfg, batches, prompt_len, steps, warm, windows):
+    """The reference cannot be built here (no Rust toolchain), so nothing of this engine can be compared with
+    it.  This is NOT the reference: it is the same Llama shape written with PyTorch's library operators
+    alone (torch.mm -> cuBLAS, scaled_dot_product_attention, rms_norm, silu), random weights, a contiguous
+    key/value cache of exactly the context (no paging, no scheduler), greedy decoding captured in one CUDA
+    graph a batch size, timed with CUDA events like ``value``.  It says what stock library kernels reach on
+    this GPU for the same arithmetic; none of this engine's code runs in it."""
+    import torch
+    import torch.nn.functional as F
+    dev = torch.device("cuda:0")
+    L, H, I = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"]
+    nq, nkv, d, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["vocab_size"]
+    eps = cfg["rms_norm_eps"]
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *shape: (torch.randn(*shape, generator=g, device=dev) * 0.02).bfloat16()
+    emb = rnd(V, H)
+    layers = [dict(qkv=rnd((nq + 2 * nkv) * d, H), o=rnd(H, nq * d), gu=rnd(2 * I, H), down=rnd(H, I),
+                   n1=torch.ones(H, device=dev, dtype=torch.bfloat16), n2=torch.ones(H, device=dev, dtype=torch.bfloat16))
+              for _ in range(L)]
+    nf = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, d, 2, device=dev, dtype=torch.float32) / d))
+
+    def rope(x, pos):                                  # x [B, T, heads, d], pos [B, T]
+        ang = pos[..., None].float() * inv
+        cos, sin = ang.cos()[:, :, None, :], ang.sin()[:, :, None, :]
+        a, b = x[..., : d // 2].float(), x[..., d // 2:].float()
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1).to(x.dtype)
+
+    def forward(ids, pos, kc, vc, causal):
+        """ids, pos [B, T]; kc, vc: per layer [B, nkv, C, d]; the T tokens sit at positions pos."""
+        B, T = ids.shape
+        x = emb[ids]
+        for w, k_l, v_l in zip(layers, kc, vc):
+            h = F.rms_norm(x, (H,), w["n1"], eps)
+            qkv = (h.view(B * T, H) @ w["qkv"].t()).view(B, T, nq + 2 * nkv, d)
+            q, k, v = rope(qkv[:, :, :nq], pos), rope(qkv[:, :, nq:nq + nkv], pos), qkv[:, :, nq + nkv:]
+            idx = pos[:, None, :, None].expand(B, nkv, T, d)
+            k_l.scatter_(2, idx, k.transpose(1, 2))
+            v_l.scatter_(2, idx, v.transpose(1, 2))
+            if causal:
+                att = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                     is_causal=True, enable_gqa=True)
+            else:
+                att = F.scaled_dot_product_attention(q.transpose(1, 2), k_l, v_l, enable_gqa=True)
+            x = x + (att.transpose(1, 2).reshape(B * T, nq * d) @ w["o"].t()).view(B, T, H)
+            h = F.rms_norm(x, (H,), w["n2"], eps)
+            gu = h.view(B * T, H) @ w["gu"].t()
+            x = x + ((F.silu(gu[:, :I]) * gu[:, I:]) @ w["down"].t()).view(B, T, H)
+        last = F.rms_norm(x[:, -1], (H,), nf, eps)
+        return (last @ emb.t()).float().argmax(dim=-1)
+
+    out = {"what": "PyTorch library operators only (cuBLAS, SDPA), contiguous cache, CUDA graph; not the reference"}
+    with torch.no_grad():
+        for B in batches:
+            C = prompt_len + warm + steps                 # the cache holds exactly what the run needs
+            kc = [torch.randn(B, nkv, C, d, device=dev).bfloat16() for _ in range(L)]
+            vc = [torch.randn(B, nkv, C, d, device=dev).bfloat16() for _ in range(L)]
+            ids = torch.randint(0, V, (B, 1), device=dev)
+            pos = torch.full((B, 1), prompt_len, device=dev, dtype=torch.long)
+
+            def step():
+                nxt = forward(ids, pos, kc, vc, causal=False)
+                ids.copy_(nxt[:, None])
+            # every step attends over the whole cache (a few more keys than the engine's sequences hold on
+            # average: C against prompt_len + warm + steps / 2)
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    step()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            for _ in range(warm):
+                graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a = time.time()
+            e0.record()
+            for _ in range(steps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            windows.append((a, time.time()))
+            out[f"decode_b{B}"] = round(B * steps / (e0.elapsed_time(e1) / 1e3), 1)
+            del kc, vc, graph
+            torch.cuda.empty_cache()
+        T = PREFILL_TOKENS
+        kc = [torch.zeros(1, nkv, T, d, device=dev, dtype=torch.bfloat16) for _ in range(L)]
+        vc = [torch.zeros(1, nkv, T, d, device=dev, dtype=torch.bfloat16) for _ in range(L)]
+        ids = torch.randint(0, V, (1, T), device=dev)
+        pos = torch.arange(T, device=dev)[None]
+        for _ in range(3):
+            forward(ids, pos, kc, vc, causal=True)
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+        torch.cuda.synchronize()
+        a = time.time()
+        for i in range(5):
+            evs[i].record()
+            forward(ids, pos, kc, vc, causal=True)
+        evs[5].record()
+        torch.cuda.synchronize()
+        windows.append((a, time.time()))
+        ms = min(evs[i].elapsed_time(evs[i + 1]) for i in range(5))
+        out["prefill_tok_s"] = round(T / (ms / 1e3), 1)
+        out["prefill_ms"] = round(ms, 3)
+    del emb, layers, kc, vc
+    torch.cuda.empty_cache()
+    return out
 
 
 def workload_3b(pk, windows):
@@ -283,6 +399,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--no-points", action="store_true", help="skip the other batch sizes and contexts")
     ap.add_argument("--no-workloads", action="store_true", help="skip the 3B and 8B serving workloads")
+    ap.add_argument("--no-standin", action="store_true", help="skip the library-operator stand-in")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -439,11 +556,20 @@ def main():
     torch.cuda.synchronize()
 
     workloads = {}
-    if not args.no_workloads and args.layers is None:
-        del llm, eng, runner
-        import gc
+    standin = None
+    del llm, eng, runner
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    if not args.no_standin:
+        try:
+            standin = library_standin(cfg, (args.batch,) if args.no_points else (1, args.batch, 64), P, min(K, 64), W,
+                                      windows)
+        except Exception as e:                             # a stand-in must never take the measurement down with it
+            standin = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
         gc.collect()
         torch.cuda.empty_cache()
+    if not args.no_workloads and args.layers is None:
         workloads["llama3b_continuous_batching"] = workload_3b(pk, windows)
         workloads["llama8b_shared_prefix"] = workload_8b(pk, windows)
     clocks.stop()
@@ -471,6 +597,7 @@ def main():
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
         "workloads": workloads,
+        "library_standin": standin,
         "clocks": clocks.summary(windows),
         "launches_per_decode_step": int(per_step), "launches_per_prefill": int(prefill_launches),
     }
