@@ -346,8 +346,9 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> Optio
     takes the shape (the caller then uses the library's matrix product).  Few rows:
     the weight-streaming kernel; more: the tcgen05 kernel."""
     if small_m_takes(x, w):
-        if w.shape[0] > 65536:          # very tall weights (the vocabulary): the library's kernel is ahead
-            return None
+        import os
+        if w.shape[0] > 65536 and (x.shape[0] > 8 or os.environ.get("RLLM_HEAD") == "library"):
+            return None                 # very tall weights (the vocabulary) at 9 to 16 rows: the library's kernel is ahead
         out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
         gemm_small_m(x, w, out)
         return out
