@@ -51,6 +51,7 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--random-prompts", metavar="N:LEN", help="N random prompts of LEN tokens")
     g.add_argument("--max-tokens", type=int, default=64)
     g.add_argument("--temperature", type=float, default=1.0, help="0 = greedy")
+    g.add_argument("-n", "--n", type=int, default=1, help="samples per prompt (the prompt is computed once)")
     g.add_argument("--top-k", type=int, default=-1)
     g.add_argument("--top-p", type=float, default=1.0)
     g.add_argument("--min-p", type=float, default=0.0)
@@ -126,25 +127,30 @@ def cmd_generate(args) -> int:
                              min_p=args.min_p, repetition_penalty=args.repetition_penalty,
                              presence_penalty=args.presence_penalty,
                              frequency_penalty=args.frequency_penalty, max_tokens=args.max_tokens,
-                             ignore_eos=args.ignore_eos, logprobs=args.logprobs,
+                             ignore_eos=args.ignore_eos, logprobs=args.logprobs, n=args.n,
                              seed=None if args.seed is None else args.seed + i)
               for i in range(len(prompts))]
     t0 = time.time()
     outs = llm.generate(prompts, params)
     dt = time.time() - t0
     n_out = sum(o.usage.completion_tokens for o in outs)
+    def sample(c):
+        return {"index": c.index, "token_ids": c.token_ids, "finish_reason": c.finish_reason,
+                "logprobs": None if c.logprobs is None else
+                [{"token_id": e.token_id, "logprob": e.logprob, "top_logprobs": e.top_logprobs} for e in c.logprobs]}
+
     for o in outs:
         if args.json:
+            first = sample(o.outputs[0])
             print(json.dumps({"request_id": o.request_id, "prompt_token_ids": o.prompt_token_ids,
-                              "token_ids": o.outputs[0].token_ids,
-                              "finish_reason": o.outputs[0].finish_reason,
-                              "logprobs": None if o.outputs[0].logprobs is None else
-                              [{"token_id": e.token_id, "logprob": e.logprob, "top_logprobs": e.top_logprobs}
-                               for e in o.outputs[0].logprobs],
+                              "token_ids": first["token_ids"], "finish_reason": first["finish_reason"],
+                              "logprobs": first["logprobs"], "outputs": [sample(c) for c in o.outputs],
                               "usage": vars(o.usage)}))
         else:
-            print(f"request {o.request_id}: {o.outputs[0].token_ids}  [{o.outputs[0].finish_reason}; "
-                  f"{o.usage.prompt_tokens} prompt + {o.usage.completion_tokens} generated]")
+            for c in o.outputs:
+                name = f"request {o.request_id}" + (f" sample {c.index}" if len(o.outputs) > 1 else "")
+                print(f"{name}: {c.token_ids}  [{c.finish_reason}; "
+                      f"{o.usage.prompt_tokens} prompt + {len(c.token_ids)} generated]")
     log.logger.info(f"{n_out} tokens in {dt:.3f} s ({n_out / max(dt, 1e-9):.1f} tok/s), "
                     f"{llm.engine.num_steps} steps; {json.dumps(llm.engine.stats())}")
     return 0

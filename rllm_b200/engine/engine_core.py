@@ -24,7 +24,7 @@ from ..parts.spec import KVPagesNeed
 from .. import log
 from ..sampling import Sampler, SamplingParams, SamplingRow
 from .runner import ModelRunner, StepEntry
-from .scheduler import Request, RequestStatus, Scheduler, SchedulerConfig, SchedulerOutput
+from .scheduler import Request, RequestRefused, RequestStatus, Scheduler, SchedulerConfig, SchedulerOutput
 
 
 @dataclass
@@ -114,6 +114,24 @@ def _windowed(model: DecoderModel) -> List[bool]:
     return [need.window is not None for need in model.layout.groups if isinstance(need, KVPagesNeed)]
 
 
+@dataclass(frozen=True)
+class SampleId:
+    """The scheduler's and the cache's name of sample ``index`` > 0 of request ``request``."""
+
+    request: Hashable
+    index: int
+
+
+@dataclass
+class _Family:
+    """The samples of a request with ``n`` > 1: ``members`` as far as they exist yet."""
+
+    n: int
+    members: List[Request]
+    unfinished: int
+    spread: bool = False           # the samples beyond the first have been made
+
+
 class EngineCore:
     ERROR_POLL_STEPS = 8           # the kernels' error words are looked at every this many steps
 
@@ -146,6 +164,7 @@ class EngineCore:
         self._readback_next = 0
         self.num_steps_ahead = 0       # steps that were put on the GPU before the tokens of the step before were read
         self.last_schedule: Optional[SchedulerOutput] = None
+        self._families: Dict[Hashable, _Family] = {}      # requests with n > 1, by their id
 
     # ------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
@@ -161,13 +180,50 @@ class EngineCore:
             raise ValueError(f"request {rid!r}: a prompt token lies outside the vocabulary of {vocab}")
         max_tokens = params.max_tokens if params.max_tokens is not None else self.max_model_len - len(prompt)
         seed = params.seed if params.seed is not None else (self.args.seed * 1000003 + arrival)
-        self.scheduler.add_request(Request(rid, prompt, params, arrival, seed, max_tokens))
+        if rid in self._families:
+            raise RequestRefused(f"request id {rid!r} is in use")
+        req = Request(rid, prompt, params, arrival, seed, max_tokens, family=rid)
+        self.scheduler.add_request(req)
         self._prepared = None          # a step prepared ahead did not know of this request
+        if params.n > 1:
+            fam = self._families[rid] = _Family(params.n, [req], params.n)
+            if len(prompt) > 1 and self.args.enable_chunked_prefill:
+                req.pause_at = len(prompt) - 1       # the other samples branch off before the prompt's last token
+            else:
+                self._spread(fam)
         return rid
+
+    def _spread(self, fam: _Family) -> None:
+        """Make samples 1 .. n-1 of a request.  The first sample has computed all of the prompt but its
+        last token: the others take that over (shared pages, a copy of the last, partly filled page and
+        of the state slot) and every sample computes the last token itself, so that a mixer's state
+        branches at the right place and no row of logits has to serve twice.  Each sample has a random
+        stream of its own: its seed is the request's seed moved on by the sample's index.  Where nothing
+        can be taken over (a prompt of one token, prompts that run whole, no slot or page free right
+        now) the samples wait like new requests with the same prompt."""
+        first = fam.members[0]
+        fam.spread = True
+        # (a prompt whose pages were all found in the cache starts at the branching point and has passed it)
+        share = first.pause_at is not None and first.num_computed == first.pause_at
+        first.pause_at = None
+        for i in range(1, fam.n):
+            seed = (first.seed + i * 0x9E3779B97F4A7C15) & 0x7FFFFFFFFFFFFFFF
+            child = Request(SampleId(first.request_id, i), first.prompt_token_ids, first.params,
+                            next(self._arrivals), seed, first.max_tokens, family=first.request_id, index=i)
+            took = self.scheduler.add_copy(first, child, share)
+            if took is not None:
+                with torch.cuda.device(self.device):
+                    self.storage.copy_for_fork(*took)
+            fam.members.append(child)
+        self._prepared = None
 
     def abort_request(self, request_id: Hashable) -> bool:
         self._prepared = None
-        return self.scheduler.abort_request(request_id)
+        fam = self._families.pop(request_id, None)
+        if fam is None:
+            return self.scheduler.abort_request(request_id)
+        found = [self.scheduler.abort_request(r.request_id) for r in fam.members]
+        return any(found)
 
     def has_work(self) -> bool:
         return self.scheduler.has_work()
@@ -234,6 +290,11 @@ class EngineCore:
         # one, with this step's tokens as its input on the device, unless a request wants its logits
         # edited by what it has generated.
         self.scheduler.after_step(sched)
+        if self._families:
+            for s in sched.scheduled:
+                r = s.request
+                if r.pause_at is not None and r.num_computed >= r.pause_at and r.status is RequestStatus.RUNNING:
+                    self._spread(self._families[r.family])
         nxt = self._prepare_next(sched, sampled_reqs, plain_greedy) if all(live) else None
         if nxt is not None and self._launch_ahead(nxt, sampled_reqs, sampled):
             nxt = None
@@ -255,8 +316,18 @@ class EngineCore:
                 self.scheduler.finish(req, RequestStatus.FINISHED_STOPPED if reason == "stop"
                                       else RequestStatus.FINISHED_LENGTH)
             n_prompt, n_out = len(req.prompt_token_ids), len(req.output_token_ids)
-            outputs.append(RequestOutput(req.request_id, req.prompt_token_ids,
-                                         [CompletionOutput(0, [int(tok)], reason, lps.get(row))], reason is not None,
+            done = reason is not None
+            fam = self._families.get(req.family)
+            if fam is not None:
+                # several samples of one prompt: reported under the request's id, finished with the last of them
+                n_out = sum(len(r.output_token_ids) for r in fam.members)
+                if done:
+                    fam.unfinished -= 1
+                    done = fam.unfinished == 0
+                    if done:
+                        del self._families[req.family]
+            outputs.append(RequestOutput(req.family, req.prompt_token_ids,
+                                         [CompletionOutput(req.index, [int(tok)], reason, lps.get(row))], done,
                                          Usage(n_prompt, n_out, n_prompt + n_out)))
         if log.logger.isEnabledFor(log.logging.DEBUG):
             log.logger.debug("step %d: %d prompt + %d decode tokens, %d sampled, %d finished, %d preempted; "

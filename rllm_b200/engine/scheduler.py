@@ -75,6 +75,9 @@ class Request:
     num_preemptions: int = 0
     status: RequestStatus = RequestStatus.WAITING
     prompt_page_hashes: Optional[List[bytes]] = None     # chained hashes of the prompt's full pages, made on demand
+    family: Optional[Hashable] = None    # the id under which results are reported (several samples of one prompt share it)
+    index: int = 0                       # which of the family's samples this is
+    pause_at: Optional[int] = None       # a portion must end at this token, if it lies ahead: copies are taken there
 
     @property
     def all_token_ids(self) -> List[int]:
@@ -134,6 +137,7 @@ class Scheduler:
         self.requests: Dict[Hashable, Request] = {}
         self.num_preemptions = 0
         self.prefix_hit_tokens = 0
+        self.num_copied_tokens = 0          # tokens that requests took over from another by ``add_copy``
         self._windowed = any(getattr(cache.needs[g], "window", None) is not None for g in cache.paged)
 
     # ------------------------------------------------------------------
@@ -160,6 +164,31 @@ class Scheduler:
             i += 1
         self.waiting.insert(i, req)
 
+    def add_copy(self, parent: Request, child: Request, share: bool = True):
+        """``child`` goes on from where ``parent`` stands: it shares the pages that hold the parent's
+        first ``num_computed`` tokens (a copy of a partly filled last page, a copy of the state slot) and
+        runs from the next step on, without computing them again
+        (crates/rllm-cache/src/manager.rs:220-245, which the reference's scheduler never calls).
+        Returns what ``CacheStorage.copy_for_fork`` has to copy on the device before the next step.
+        Where that cannot be (``share`` is off, the parent is not running or holds nothing yet, or a slot
+        or a page is missing), the child waits like a new request and None is returned."""
+        if child.request_id in self.requests:
+            raise RequestRefused(f"request id {child.request_id!r} is in use")
+        self.requests[child.request_id] = child
+        took = None
+        if (share and parent.status is RequestStatus.RUNNING and parent.num_computed > 0
+                and len(self.running) < self.config.max_num_seqs):
+            took = self.cache.fork(parent.request_id, child.request_id, parent.num_computed)
+        if took is None:
+            self._enqueue(child)
+            return None
+        child.num_computed = parent.num_computed
+        self.num_copied_tokens += parent.num_computed
+        child.status = RequestStatus.RUNNING
+        self.running.append(child)
+        self.running.sort(key=lambda r: r.arrival)
+        return took
+
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 
@@ -169,6 +198,8 @@ class Scheduler:
         n = min(left, budget)
         if left > 1 and self.config.long_prefill_token_threshold > 0:
             n = min(n, self.config.long_prefill_token_threshold)
+        if req.pause_at is not None and req.num_computed < req.pause_at:
+            n = min(n, req.pause_at - req.num_computed)
         return n
 
     def _prompt_hashes(self, req: Request) -> List[bytes]:
@@ -322,4 +353,5 @@ class Scheduler:
         """Fields of crates/rllm-scheduler/src/output.rs:51-64, plus prefix hits."""
         return {"num_running": len(self.running), "num_waiting": len(self.waiting),
                 "num_preemptions": self.num_preemptions, "prefix_hit_tokens": self.prefix_hit_tokens,
+                "num_copied_tokens": self.num_copied_tokens,
                 "cache": self.cache.usage()}

@@ -60,8 +60,8 @@ class LLM:
     def generate(self, prompt_token_ids: Sequence[Sequence[int]],
                  sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None
                  ) -> List[RequestOutput]:
-        """One RequestOutput per prompt, in the order of the prompts, each with
-        all generated tokens."""
+        """One RequestOutput per prompt, in the order of the prompts, each with all generated
+        tokens: ``outputs[i]`` is sample i of the prompt (one sample unless ``n`` > 1)."""
         n = len(prompt_token_ids)
         if sampling_params is None or isinstance(sampling_params, SamplingParams):
             params = [sampling_params or SamplingParams()] * n
@@ -70,32 +70,29 @@ class LLM:
             if len(params) != n:
                 raise ValueError("one SamplingParams per prompt, or one for all")
         ids = [self.add_request(p, sp) for p, sp in zip(prompt_token_ids, params)]
-        tokens = {rid: [] for rid in ids}
-        logprobs = {rid: [] for rid in ids}
-        final = {}
+        # per request: sample index -> [tokens, log-probabilities, finish reason]
+        samples = {rid: {i: [[], [], None] for i in range(sp.n)} for rid, sp in zip(ids, params)}
         while self.has_work():
             for out in self.step():
-                if out.request_id in tokens:
-                    tokens[out.request_id].extend(out.outputs[0].token_ids)
-                    if out.outputs[0].logprobs is not None:
-                        logprobs[out.request_id].extend(out.outputs[0].logprobs)
-                    if out.finished:
-                        final[out.request_id] = out
+                mine = samples.get(out.request_id)
+                if mine is None:
+                    continue
+                for c in out.outputs:
+                    got = mine[c.index]
+                    got[0].extend(c.token_ids)
+                    if c.logprobs is not None:
+                        got[1].extend(c.logprobs)
+                    if c.finish_reason is not None:
+                        got[2] = c.finish_reason
         self.engine.runner.check_errors()          # the steps polled the kernels' error words; this waits for the last
         results = []
-        for rid in ids:
-            out = final.get(rid)
-            if out is None:
-                # aborted from outside (``abort_request``) while this call was stepping: what it had generated
-                # by then is returned, with the reference's reason for it (crates/rllm-core/src/output.rs:37-42)
-                prompt = [int(t) for t in prompt_token_ids[ids.index(rid)]]
-                n_out = len(tokens[rid])
-                results.append(RequestOutput(rid, prompt, [CompletionOutput(0, tokens[rid], "aborted",
-                                                                            logprobs[rid] or None)],
-                                             True, Usage(len(prompt), n_out, len(prompt) + n_out)))
-                continue
-            results.append(RequestOutput(rid, out.prompt_token_ids,
-                                         [CompletionOutput(0, tokens[rid], out.outputs[0].finish_reason,
-                                                           logprobs[rid] if out.outputs[0].logprobs is not None else None)],
-                                         True, out.usage))
+        for rid, prompt, sp in zip(ids, prompt_token_ids, params):
+            # a sample without a reason was aborted from outside (``abort_request``) while this call was
+            # stepping: what it had generated by then is returned, with the reference's reason for it
+            # (crates/rllm-core/src/output.rs:37-42)
+            outs = [CompletionOutput(i, toks, reason or "aborted", lps if sp.logprobs is not None else None)
+                    for i, (toks, lps, reason) in sorted(samples[rid].items())]
+            prompt = [int(t) for t in prompt]
+            n_out = sum(len(o.token_ids) for o in outs)
+            results.append(RequestOutput(rid, prompt, outs, True, Usage(len(prompt), n_out, len(prompt) + n_out)))
         return results

@@ -5,7 +5,10 @@ Kept: n, presence_penalty, frequency_penalty, repetition_penalty, temperature,
 top_p, top_k, min_p, seed, stop_token_ids, ignore_eos, max_tokens, min_tokens,
 logit_bias, allowed_token_ids.  Text-side options (stop strings, detokenize,
 bad_words, structured outputs) have no meaning for an engine that works on
-token ids; n > 1 is refused with a clear error.  ``logprobs`` = N asks for the
+token ids.  ``n`` > 1 asks for n samples of one prompt (the reference checks the
+field, :91 and :113, and then generates one): the prompt is computed once and
+the samples branch off before its last token, each with a random stream of its
+own.  ``logprobs`` = N asks for the
 log-probability of every generated token and of the N likeliest tokens at its place,
 from the raw logits (crates/rllm-sampling/src/sampler.rs:149-160).
 """
@@ -41,8 +44,8 @@ class SamplingParams:
     def validate(self) -> None:
         if self.n < 1:
             raise InvalidSamplingParams("n must be >= 1")
-        if self.n > 1:
-            raise InvalidSamplingParams("n > 1 is not supported: submit the prompt n times with different seeds")
+        if self.n > 1 and self.greedy:
+            raise InvalidSamplingParams("n must be 1 when sampling is greedy (temperature 0 or top_k 1)")
         if self.temperature < 0.0:
             raise InvalidSamplingParams("temperature must be >= 0")
         if not 0.0 <= self.presence_penalty <= 2.0:

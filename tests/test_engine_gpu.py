@@ -219,6 +219,71 @@ def test_prefix_sharing_does_not_change_outputs(model_dirs):
     on.engine.cache.check()
 
 
+def sample_seed(seed, index):
+    """The seed of sample ``index`` of a request: the request's seed moved on by the index."""
+    return (seed + index * 0x9E3779B97F4A7C15) & 0x7FFFFFFFFFFFFFFF
+
+
+@pytest.mark.parametrize("name,prefix,pages", [("B", False, 256), ("B", True, 256), ("B0", False, 20), ("A", True, 256)])
+def test_several_samples_of_one_prompt(model_dirs, name, prefix, pages):
+    """n = 3 samples of prompts of 1, 33, 70 and 16 k + 1 tokens beside a request with one sample: the
+    prompt is computed once up to its last token, the samples take its pages over and go on by
+    themselves; every sample is what the plain model draws with the sample's own random stream.  With
+    20 pages the samples do not all fit: some wait like new requests, some are preempted and computed
+    again."""
+    from rllm_b200 import SamplingParams
+    _, _, page = TINY[name]
+    lengths = [1, 33, 70, 4 * page + 1, 21]
+    prompts = prompts_for(name, lengths, 12)
+    params = [SamplingParams(temperature=0.9, max_tokens=9, seed=300 + i, ignore_eos=True, n=3) for i in range(4)]
+    params.append(SamplingParams(temperature=0.9, max_tokens=9, seed=304, ignore_eos=True))
+    llm = make_llm(model_dirs, name, num_gpu_blocks=pages, max_num_seqs=16, max_num_batched_tokens=48,
+                   long_prefill_token_threshold=16, enable_prefix_caching=prefix)
+    outs = llm.generate(prompts, params)
+    plain = pl.read_model_dir(model_dirs[name])
+    for i, (p, sp, o) in enumerate(zip(prompts, params, outs)):
+        assert [c.index for c in o.outputs] == list(range(sp.n)) and all(c.finish_reason == "length" for c in o.outputs)
+        assert o.usage.completion_tokens == 9 * sp.n and o.usage.prompt_tokens == len(p)
+        for c in o.outputs:
+            toks = list(p)
+            for j, t in enumerate(c.token_ids):
+                x = pl.process_logits(plain.logits(toks)[-1].numpy(), temperature=0.9)
+                assert t == pl.sample_row(x, 0.9, -1, pl.uniform_for(sample_seed(300 + i, c.index), j)), (i, c.index, j)
+                toks.append(t)
+        if sp.n > 1:
+            assert len({tuple(c.token_ids) for c in o.outputs}) > 1         # streams of their own
+    stats = llm.engine.stats()
+    if pages == 256:
+        # prompts of 33, 70 and 4 pages + 1: two samples each took over all but the last token
+        assert stats["num_copied_tokens"] == 2 * (32 + 69 + 4 * page)
+    else:
+        assert stats["num_preemptions"] > 0 and 0 < stats["num_copied_tokens"] < 2 * (32 + 69 + 4 * page)
+    llm.engine.cache.check()
+    assert llm.engine.cache.num_free_pages() == pages and not llm.engine._families
+
+
+def test_samples_of_one_prompt_can_be_aborted_and_greedy_refuses_them(model_dirs):
+    from rllm_b200 import SamplingParams
+    from rllm_b200.sampling.params import InvalidSamplingParams
+    llm = make_llm(model_dirs, "A")
+    with pytest.raises(InvalidSamplingParams):
+        llm.add_request([9, 10, 11], SamplingParams(temperature=0.0, n=2))
+    p = prompts_for("A", [40], 3)[0]
+    rid = llm.add_request(p, SamplingParams(temperature=1.0, max_tokens=30, n=4, seed=5, ignore_eos=True))
+    seen = set()
+    for _ in range(6):
+        for o in llm.step():
+            assert o.request_id == rid and not o.finished
+            seen.update(c.index for c in o.outputs)
+    assert seen == {0, 1, 2, 3}
+    assert llm.abort_request(rid) and not llm.has_work() and not llm.abort_request(rid)
+    llm.engine.cache.check()
+    assert llm.engine.cache.num_free_pages() == 256
+    # the engine goes on as before
+    out = llm.generate([p], SamplingParams(temperature=1.0, max_tokens=5, n=2, seed=5, ignore_eos=True))[0]
+    assert [len(c.token_ids) for c in out.outputs] == [5, 5]
+
+
 def test_requests_beyond_the_limits_are_refused(model_dirs):
     from rllm_b200 import SamplingParams
     from rllm_b200.engine.scheduler import RequestRefused

@@ -383,7 +383,8 @@ def test_attention_decode_mma(ops, err, nq, nkv, d, page, window):
     assert torch.equal(alone[0], outs[0][4])
 
 
-@pytest.mark.parametrize("nq,nkv,d,page,window", [(8, 2, 64, 16, 0), (8, 2, 64, 16, 5000), (4, 1, 128, 32, 0), (6, 3, 32, 8, 0)])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(8, 2, 64, 16, 0), (8, 2, 64, 16, 5000), (4, 1, 128, 32, 0), (6, 3, 32, 8, 0),
+                                                  (8, 2, 128, 16, 0), (6, 2, 128, 64, 3000)])
 def test_attention_decode_long_sequences(ops, err, nq, nkv, d, page, window):
     """Tens of CTAs a (sequence, kv head): their results are merged in several rounds of eight and two
     halves; beside them short sequences whose CTAs mostly have nothing to do."""
@@ -419,18 +420,22 @@ def test_attention_decode_long_sequences(ops, err, nq, nkv, d, page, window):
         assert rel_err(out2[3:4], want) <= tol(dt)
 
 
-@pytest.mark.parametrize("kind", ["prefill", "decode", "tcgen05"])
+@pytest.mark.parametrize("kind", ["prefill", "decode", "tcgen05", "decode_many_64", "decode_many_128"])
 def test_mma_attention_finds_one_far_key(ops, err, kind):
     """One key among a thousand, at a tile's, split's or page's edge, is made to
-    dominate: the output must be its value."""
+    dominate: the output must be its value.  The "many" kinds give the decode kernel
+    a bound on the length so large that it takes the tiling it uses for large batches
+    (tiles of 16 keys for heads of 128)."""
     dt = torch.bfloat16
-    nq, nkv, d, page = 8, 2, 64, 16
+    nq, nkv, d, page = (4, 2, 128, 16) if kind == "decode_many_128" else (8, 2, 64, 16)
     n = 1100
-    m = {"decode": 1, "prefill": 5, "tcgen05": 40}[kind]
+    bound = 65536 if kind.startswith("decode_many") else n
+    m = {"prefill": 5, "tcgen05": 40}.get(kind, 1)
     ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, [n], [m], pages=128, seed=9)
     seq_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
     q_start = torch.tensor([0, m], dtype=torch.int32, device=DEV)
-    for target in (0, 63, 64, 127, 128, 255, 256, 511, 512, 1023, 1024, n - m - 1, n - m):
+    for target in (0, 15, 16, 31, 32, 47, 48, 63, 64, 127, 128, 143, 144, 255, 256, 511, 512, 1023, 1024, 1039, 1040,
+                   n - m - 1, n - m):
         kc2, qq = kc.clone(), qs[0].clone()
         pg = int(table[0, target // page])
         kc2[pg, :, target % page] = 0
@@ -438,8 +443,8 @@ def test_mma_attention_finds_one_far_key(ops, err, kind):
         qq[:, :, 3] = 30.0
         q = qq.reshape(m, nq * d).to(DEV)
         out = torch.zeros_like(q)
-        if kind == "decode":
-            ops.attention_decode_bf16(q, nq * d, out, kc2.to(DEV), vc.to(DEV), table.to(DEV), seq_lens, 1, n,
+        if kind.startswith("decode"):
+            ops.attention_decode_bf16(q, nq * d, out, kc2.to(DEV), vc.to(DEV), table.to(DEV), seq_lens, 1, bound,
                                       nq, nkv, d, 0, 1.0, err)
         else:
             fn = ops.attention_prefill_tcgen05 if kind == "tcgen05" else ops.attention_prefill_bf16

@@ -255,3 +255,59 @@ def test_a_held_back_request_is_admitted_when_the_one_it_waits_for_goes_away():
     while s.has_work():
         run_step(s)
     cache.check()
+
+
+def test_a_portion_ends_at_the_pause_point_and_copies_go_on_from_there():
+    """Several samples of one prompt: the first request stops before the prompt's last token, the others
+    take its pages over (full pages shared, the partly filled one copied) and all compute the last
+    token themselves."""
+    s, cache = make(pages=16, max_num_batched_tokens=64)
+    first = req(0, 41)
+    first.pause_at = 40
+    s.add_request(first)
+    out = run_step(s)
+    assert [(x.start, x.num_tokens, x.want_logits) for x in out.scheduled] == [(0, 40, False)]
+    free_before = cache.num_free_pages()
+    kids = []
+    for i in (1, 2):
+        kid = Request(("r0", i), first.prompt_token_ids, first.params, arrival=10 + i, seed=i, max_tokens=8)
+        took = s.add_copy(first, kid)
+        assert took is not None
+        copies, (pslot, cslot) = took
+        assert len(copies) == 1 and copies[0][0] == 0 and copies[0][1] == cache.table("r0", 0)[2]   # tokens 32..39 sit in page 2
+        assert cslot != pslot and kid.status is RequestStatus.RUNNING and kid.num_computed == 40
+        assert cache.table(kid.request_id, 0)[:2] == cache.table("r0", 0)[:2]
+        assert cache.table(kid.request_id, 0)[2] == copies[0][2] != cache.table("r0", 0)[2]
+        kids.append(kid)
+    assert cache.num_free_pages() == free_before - 2 and s.num_copied_tokens == 80
+    first.pause_at = None
+    cache.check()
+    out = run_step(s)
+    assert [(x.request.request_id, x.start, x.num_tokens, x.want_logits) for x in out.scheduled] == \
+        [("r0", 40, 1, True), (("r0", 1), 40, 1, True), (("r0", 2), 40, 1, True)]
+    while s.has_work():
+        run_step(s)
+    assert cache.num_free_pages() == 16
+    assert all(len(r.output_token_ids) == 8 for r in [first] + kids)
+
+
+def test_a_copy_waits_like_a_new_request_when_nothing_can_be_taken_over():
+    s, cache = make(pages=3, max_num_batched_tokens=64)
+    first = req(0, 41, max_tokens=4)
+    first.pause_at = 40
+    s.add_request(first)
+    run_step(s)                                   # 40 tokens: 3 pages, none left for a copy of the third
+    kid = Request(("r0", 1), first.prompt_token_ids, first.params, arrival=11, seed=1, max_tokens=4)
+    assert s.add_copy(first, kid) is None and kid.status is RequestStatus.WAITING and kid in s.waiting
+    cache.check()
+    other = Request(("r0", 2), first.prompt_token_ids, first.params, arrival=12, seed=2, max_tokens=4)
+    assert s.add_copy(first, other, share=False) is None and other in s.waiting
+    with pytest.raises(RequestRefused):
+        s.add_copy(first, Request(("r0", 2), first.prompt_token_ids, first.params, arrival=13, seed=3, max_tokens=4))
+    first.pause_at = None
+    steps = 0
+    while s.has_work():
+        run_step(s)
+        steps += 1
+        assert steps < 200
+    assert len(kid.output_token_ids) == 4 and len(other.output_token_ids) == 4 and cache.num_free_pages() == 3

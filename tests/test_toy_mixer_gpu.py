@@ -216,6 +216,32 @@ def test_a_stateful_mixer_decodes_in_captured_graphs_and_padded_batches(tmp_path
     assert llm.engine.cache.usage()["num_requests"] == 0
 
 
+def test_several_samples_of_one_prompt_branch_with_the_state(tmp_path):
+    """n = 3 samples with the toy model: the samples branch off before the prompt's last token, each with a
+    copy of the first sample's state slot as it was there, so every sample's tokens are those that the plain
+    formulas draw with the sample's random stream."""
+    from rllm_b200 import LLM, SamplingParams
+    d, w = _toy_folder(tmp_path, "toy_samples")
+    rng = np.random.default_rng(6)
+    prompts = [[int(t) for t in rng.integers(0, V, size=n)] for n in (19, 2, 33)]
+    llm = LLM(d, dtype="fp32", num_gpu_blocks=64, max_num_seqs=12, max_num_batched_tokens=24,
+              long_prefill_token_threshold=8, enable_prefix_caching=False)
+    outs = llm.generate(prompts, [SamplingParams(temperature=0.8, max_tokens=7, seed=50 + i, ignore_eos=True, n=3)
+                                  for i in range(3)])
+    assert llm.engine.stats()["num_copied_tokens"] == 2 * (18 + 1 + 32)
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        assert len(o.outputs) == 3
+        for c in o.outputs:
+            seed = (50 + i + c.index * 0x9E3779B97F4A7C15) & 0x7FFFFFFFFFFFFFFF
+            toks = list(p)
+            for j, t in enumerate(c.token_ids):
+                x = pl.process_logits(plain_toy(w, toks, 1e-4)[-1].numpy(), temperature=0.8)
+                assert t == pl.sample_row(x, 0.8, -1, pl.uniform_for(seed, j)), (i, c.index, j)
+                toks.append(t)
+    llm.engine.cache.check()
+    assert llm.engine.cache.usage()["num_requests"] == 0
+
+
 # ---------------------------------------------------------------------------
 # A feed-forward with routing and another position encoding, defined here too
 # ---------------------------------------------------------------------------
