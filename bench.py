@@ -231,7 +231,7 @@ def run_workload(cfg, prompts, params, pk, windows, warm_prompts, **llm_kw):
             })
             # the prompts of this pass must not be found in the prefix cache by the next one
             if eng.cache.prefix_caching:
-                eng.cache.pools[eng.cache.paged[0]].reset_prefix_cache()
+                eng.cache.reset_prefix_cache()
     results.sort(key=lambda r: r["wall_s"])
     result = dict(results[len(results) // 2], timed_passes=len(results),
                   wall_s_all=" ".join(str(r["wall_s"]) for r in results))

@@ -19,8 +19,13 @@ manager.rs:80-121, registration after the compute :184-210).  Unlike it, a
 prefix lookup takes no references until the request is admitted, pages are
 hashed only after their keys exist, and a prompt that is cached completely
 still computes its last page so that there is a logit to sample from
-(the intent of prefix.rs:73-86).  Prefix sharing needs a model whose only
-cache group keeps all keys; with windows or state it is switched off.
+(the intent of prefix.rs:73-86).  With several paged groups every group keeps
+the hashes of its own pages, and a request takes over the longest prefix for
+which every group still has what the request's next query can see: all pages
+where every key is kept, those that reach into the window where a window is
+kept (the pages before them are left out of its table, as if the window had
+passed them).  State of fixed size cannot be taken over from pages: with a
+group of that kind prefix sharing is switched off.
 
 This is host-side bookkeeping only; the storage lives in ``CacheStorage``.  The
 bookkeeping itself is C++ (``native/csrc/cache_core.cc``); this class is its
@@ -263,6 +268,14 @@ class CacheManager:
         t = _tokens(tokens)
         core().rllm_cache_register_computed(self._h, self._id(req), _ptr(t), c_longlong(len(t)),
                                             c_longlong(num_computed))
+
+    def reset_prefix_cache(self) -> None:
+        """Forget the hashes of all pages (crates/rllm-cache/src/block_pool.rs:367-385); refused while
+        a request holds a hashed page."""
+        if any(p.num_active for p in self.pools.values()):
+            raise PagePoolError("reset_prefix_cache while requests hold pages")
+        for p in self.pools.values():
+            p.reset_prefix_cache()
 
     # -- statistics and invariants -----------------------------------------------------
     def usage(self) -> dict:

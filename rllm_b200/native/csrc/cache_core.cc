@@ -268,6 +268,28 @@ struct Manager {
     }
     return n;
   }
+  // How many leading pages with these hashes a new request can take over: the largest k such that every
+  // group has, findable, all pages below k that a query at position k * page_size can still see (all of
+  // them where every key is kept; those that reach into the window elsewhere).
+  long long shareable_pages(const std::vector<Hash16>& hs) const {
+    long long k = (long long)hs.size();
+    for (int g : paged) {
+      if (window[g] >= 0) continue;
+      long long have = 0;
+      while (have < k && pools[g]->peek(hs[have]) >= 0) ++have;
+      k = have;
+    }
+    for (; k > 0; --k) {
+      bool ok = true;
+      for (int g : paged) {
+        if (window[g] < 0) continue;
+        for (long long j = first_needed_page(g, k * page_size); j < k && ok; ++j) ok = pools[g]->peek(hs[j]) >= 0;
+        if (!ok) break;
+      }
+      if (ok) break;
+    }
+    return k;
+  }
   int pages_needed(const Req* r, int g, long long first_query_pos, long long num_tokens) const {
     const long long want = (num_tokens + page_size - 1) / page_size;
     long long first = first_needed_page(g, first_query_pos);
@@ -340,8 +362,8 @@ API void* rllm_cache_new(int num_groups, const int* kinds, const int* windows, c
     }
   }
   for (int s = max_seqs - 1; s >= 0; --s) m->free_slots.push_back(s);
-  const bool only_full = m->paged.size() == 1 && !stateful && m->window[m->paged[0]] < 0;
-  m->prefix_caching = enable_prefix_caching && only_full;
+  // State of fixed size cannot be taken over from pages: with such a group every request computes its own.
+  m->prefix_caching = enable_prefix_caching && !stateful && !m->paged.empty();
   return m;
 }
 API void rllm_cache_delete(void* h) { delete M(h); }
@@ -533,39 +555,35 @@ API int rllm_cache_fits_at_all(void* h, long long num_tokens) {
 API long long rllm_cache_match_prefix(void* h, const int64_t* tokens, long long n) {
   Manager* m = M(h);
   if (!m->prefix_caching) return 0;
-  Pool* pool = m->pools[m->paged[0]];
   std::vector<Hash16> hs;
   chain_hashes(tokens, n, m->page_size, nullptr, 0, 0, false, Hash16(), &hs);
-  long long k = 0;
-  for (const Hash16& x : hs) {
-    if (pool->peek(x) < 0) break;
-    ++k;
-  }
-  if (k && k * m->page_size >= n) --k;
-  return k * m->page_size;
+  if (!hs.empty() && (long long)hs.size() * m->page_size >= n) hs.pop_back();
+  return m->shareable_pages(hs) * m->page_size;
 }
-// gives a newly admitted request the findable pages of its prefix; returns the tokens it need not compute
+// gives a newly admitted request the findable pages of its prefix; returns the tokens it need not compute.
+// In a group that keeps a window the pages that the request's first query can no longer see are not taken
+// (their table entries are -1, as if the window had passed them).
 API long long rllm_cache_adopt_prefix(void* h, int64_t id, const int64_t* tokens, long long n) {
   Manager* m = M(h);
   if (!m->prefix_caching) return 0;
   Req* r = m->find(id);
   if (!r) return RC_UNKNOWN_REQ;
-  const int g = m->paged[0];
-  if (!r->tables[g].empty()) return RC_NOT_HELD;
-  Pool* pool = m->pools[g];
+  for (int g : m->paged)
+    if (!r->tables[g].empty()) return RC_NOT_HELD;
   const long long limit = n > 0 ? (n - 1) / m->page_size : 0;    // keep at least one token to compute
   std::vector<Hash16> hs;
   chain_hashes(tokens, limit * m->page_size, m->page_size, nullptr, 0, 0, false, Hash16(), &hs);
-  for (const Hash16& x : hs) {
-    const int page = pool->acquire_cached(x);
-    if (page < 0) break;
-    r->tables[g].push_back(page);
+  const long long got = m->shareable_pages(hs);
+  for (int g : m->paged) {
+    const long long first = m->first_needed_page(g, got * m->page_size);
+    for (long long k = 0; k < got; ++k)
+      r->tables[g].push_back(k < first ? -1 : m->pools[g]->acquire_cached(hs[k]));
+    r->released[g] = (int)(first < got ? first : got);
   }
-  const size_t got = r->tables[g].size();
-  hs.resize(got);
+  hs.resize((size_t)got);
   r->hashes = hs;
   r->registered = (int)got;
-  return (long long)got * m->page_size;
+  return got * m->page_size;
 }
 // makes the pages findable whose keys now exist for all their tokens
 API int rllm_cache_register_computed(void* h, int64_t id, const int64_t* tokens, long long n, long long num_computed) {
@@ -573,7 +591,6 @@ API int rllm_cache_register_computed(void* h, int64_t id, const int64_t* tokens,
   if (!m->prefix_caching) return 0;
   Req* r = m->find(id);
   if (!r) return RC_UNKNOWN_REQ;
-  const int g = m->paged[0];
   const long long upto = num_computed < n ? num_computed : n;
   const long long full = upto / m->page_size;
   if (full > (long long)r->hashes.size()) {
@@ -581,7 +598,9 @@ API int rllm_cache_register_computed(void* h, int64_t id, const int64_t* tokens,
     chain_hashes(tokens, full * m->page_size, m->page_size, nullptr, 0, (int)r->hashes.size(), has_parent,
                  has_parent ? r->hashes.back() : Hash16(), &r->hashes);
   }
-  for (long long k = r->registered; k < full; ++k) m->pools[g]->reg(r->tables[g][k], r->hashes[k]);
+  for (int g : m->paged)
+    for (long long k = r->registered; k < full; ++k)
+      if (r->tables[g][k] >= 0) m->pools[g]->reg(r->tables[g][k], r->hashes[k]);   // (-1: the window has passed it)
   if (full > r->registered) r->registered = (int)full;
   return 0;
 }

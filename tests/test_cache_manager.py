@@ -197,9 +197,104 @@ def test_prefix_sharing():
     m.check()
 
 
-def test_prefix_sharing_is_off_with_windows_or_state():
-    assert not CacheManager([KVPagesNeed(1, 16, 8)], 4, 4, 1, enable_prefix_caching=True).prefix_caching
+def test_prefix_sharing_is_off_with_state():
     assert not CacheManager([FULL, StateNeed((2,))], 4, 4, 1, enable_prefix_caching=True).prefix_caching
+    assert CacheManager([KVPagesNeed(1, 16, 8)], 4, 4, 1, enable_prefix_caching=True).prefix_caching
+
+
+def test_prefix_sharing_with_a_window_takes_what_the_next_query_sees():
+    """Two groups, one keeps all keys, one a window of 6 (pages of 4).  A request that finds its prefix takes all
+    pages of the first group and, of the second, only those that reach into the window of its first query."""
+    win = KVPagesNeed(1, 16, 6)
+    m = CacheManager([FULL, win], 4, [16, 8], 3, enable_prefix_caching=True)
+    toks = list(range(100, 130))                       # 7 full pages + 2 tokens
+    m.admit("a")
+    pos = 0
+    for n in (9, 9, 12):                               # portions; the window gives pages back on the way
+        assert m.ensure("a", pos, pos + n)
+        pos += n
+        m.register_computed("a", toks, pos)
+    assert m.table("a", 1)[:3] == [-1, -1, -1]
+    m.check()
+    # 28 tokens in full pages, the prompt has 30: 7 pages can be taken; the query at 28 sees keys 23..: pages 5, 6
+    assert m.match_prefix(toks) == 28
+    m.admit("b")
+    assert m.adopt_prefix("b", toks) == 28
+    assert m.table("b", 0) == m.table("a", 0)[:7]
+    assert m.table("b", 1) == [-1] * 5 + m.table("a", 1)[5:7]
+    m.check()
+    assert m.ensure("b", 28, 30) and m.ensure("b", 30, 31)
+    m.free("a")
+    m.check()
+    # pages that the window gave back stay findable until they are used again: a shorter prompt finds them
+    assert m.match_prefix(toks[:14]) == 12             # 3 pages; the query at 12 sees 7..: pages 1, 2
+    m.admit("c")
+    assert m.adopt_prefix("c", toks[:14]) == 12
+    assert m.table("c", 1)[0] == -1 and all(p >= 0 for p in m.table("c", 1)[1:3])
+    m.check()
+    m.free("b"); m.free("c")
+    m.check()
+    assert m.num_free_pages(0) == 16 and m.num_free_pages(1) == 8
+    # once the window group's pages have been used again, only a shorter prefix (or none) can be taken
+    m.admit("d")
+    assert m.ensure("d", 0, 30)                        # one portion: every page of the windowed group at once
+    assert m.match_prefix(toks) < 28
+    k = m.match_prefix(toks) // 4
+    m.admit("e")
+    assert m.adopt_prefix("e", toks) == 4 * k
+    assert all(p >= 0 for p in m.table("e", 0)) and len(m.table("e", 0)) == k
+    m.check()
+    m.free("d"); m.free("e")
+    m.reset_prefix_cache()
+    assert m.match_prefix(toks) == 0
+    m.check()
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_random_orders_with_prefix_sharing_over_two_groups(seed):
+    """Requests with prompts drawn from a few families run in random portions, end in random order, and take
+    over what they find: nothing is lost or held twice, and a request never lacks a page its query sees."""
+    rng = random.Random(seed)
+    window = 10
+    m = CacheManager([FULL, KVPagesNeed(1, 16, window)], 4, [48, 14], 4, enable_prefix_caching=True)
+    families = [[rng.randrange(1000) for _ in range(60)] for _ in range(3)]
+    live = {}
+    hits = 0
+    for step in range(800):
+        op = rng.random()
+        if op < 0.2 and len(live) < 4:
+            rid = f"r{step}"
+            fam = rng.choice(families)
+            toks = fam[:rng.randint(1, 60)] + [rng.randrange(1000) for _ in range(rng.randint(0, 6))]
+            expect = m.match_prefix(toks)
+            m.admit(rid)
+            got = m.adopt_prefix(rid, toks)
+            assert got == expect and got % 4 == 0 and got < len(toks)
+            hits += got
+            live[rid] = [toks, got]
+        elif op < 0.85 and live:
+            rid = rng.choice(list(live))
+            toks, pos = live[rid]
+            if pos == len(toks):
+                toks.append(rng.randrange(1000))       # a generated token
+            n = min(len(toks), pos + rng.choice([1, 1, 2, 5, 9]))
+            if m.ensure(rid, pos, n):
+                for g, w in ((0, None), (1, window)):
+                    tb = m.table(rid, g)
+                    lo = 0 if w is None else max(0, pos - w + 1) // 4
+                    assert all(p >= 0 for p in tb[lo:-(-n // 4)]), (rid, g, pos, n, tb)
+                live[rid][1] = n
+                m.register_computed(rid, toks, n)
+        elif live:
+            rid = rng.choice(list(live))
+            m.free(rid)
+            del live[rid]
+        m.check()
+    for rid in list(live):
+        m.free(rid)
+    m.check()
+    assert hits > 0
+    assert m.num_free_pages(0) == 48 and m.num_free_pages(1) == 14
 
 
 def test_fork_shares_full_pages_and_copies_the_last():

@@ -502,3 +502,39 @@ def test_generation_with_a_windowed_layer(tmp_path):
         assert o.outputs[0].token_ids == toks[len(p):]
     llm.engine.cache.check()
     assert llm.engine.cache.usage()["num_requests"] == 0
+
+
+def test_prefix_sharing_with_a_windowed_layer(tmp_path):
+    """Requests with a common prefix of 50 tokens on a model whose first layer sees 20 keys: later requests take
+    the prefix's pages over (all of the layer that sees every key; of the windowed layer those that reach into
+    their first query's window, found again although the window gave them back long ago) and generate the
+    plain tokens."""
+    from safetensors import safe_open
+    from rllm_b200 import LLM, SamplingParams
+    from rllm_b200.engine.loading import write_random_model
+    register_windowed()
+    cfg = {"architectures": ["ToyWindowedForCausalLM"], "eps": 1e-5, "torch_dtype": "float32"}
+    d = str(tmp_path / "windowed_prefix")
+    write_random_model(d, cfg, seed=6)
+    with safe_open(os.path.join(d, "model.safetensors"), framework="pt") as f:
+        w = {n: f.get_tensor(n).double() for n in f.keys()}
+    rng = np.random.default_rng(9)
+    common = [int(t) for t in rng.integers(0, V, size=50)]
+    prompts = [common + [int(t) for t in rng.integers(0, V, size=n)] for n in (3, 11, 1)] + [common[:48], common[:21]]
+    steps = 12
+    llm = LLM(d, dtype="fp32", block_size=4, num_gpu_blocks=80, max_num_seqs=2, max_num_batched_tokens=32,
+              long_prefill_token_threshold=16, enable_prefix_caching=True)
+    assert llm.engine.cache.prefix_caching
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=steps, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        toks = list(p)
+        for _ in range(steps):
+            toks.append(int(torch.argmax(plain_windowed(w, toks, 1e-5)[-1])))
+        assert o.outputs[0].token_ids == toks[len(p):]
+    # 48 tokens of the prefix lie in full pages: the second and third prompt take them, the fourth (48 tokens, cached
+    # whole) computes its last page again; the fifth needs the windowed layer's first pages, which may have been
+    # used again by then (that layer has 20 pages in all)
+    hits = llm.engine.stats()["prefix_hit_tokens"]
+    assert 48 + 48 + 44 <= hits <= 48 + 48 + 44 + 20, hits
+    llm.engine.cache.check()
+    assert llm.engine.cache.usage()["num_requests"] == 0
