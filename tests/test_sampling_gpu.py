@@ -190,8 +190,10 @@ def test_processors_match_the_plain_ones(sampler):
 def test_params_are_validated():
     from rllm_b200.sampling import InvalidSamplingParams, SamplingParams
     SamplingParams().validate()
+    SamplingParams(n=3).validate()
     assert SamplingParams().max_tokens == 16 and SamplingParams().temperature == 1.0
-    for bad in (dict(temperature=-1.0), dict(top_p=1.5), dict(n=0), dict(n=2), dict(repetition_penalty=0.0),
+    for bad in (dict(temperature=-1.0), dict(top_p=1.5), dict(n=0), dict(n=2, temperature=0.0), dict(n=2, top_k=1),
+                dict(repetition_penalty=0.0),
                 dict(presence_penalty=3.0), dict(logprobs=-1), dict(logprobs=33)):
         with pytest.raises(InvalidSamplingParams):
             SamplingParams(**bad).validate()
