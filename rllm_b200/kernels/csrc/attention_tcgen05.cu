@@ -43,6 +43,33 @@ __device__ __forceinline__ float at_ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// The softmax warps' arithmetic uses the instructions of sm_100 that do two float32 operations
+// (fma.rn.f32x2, add.rn.f32x2 on register pairs) or take three inputs (max.f32): a quarter fewer
+// instructions a tile (measured: 2 to 3 % less time at 8,192 tokens; the exponentials and the
+// hand-overs between warps weigh more).
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long at_pack2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void at_unpack2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long at_fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long at_add2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 
 // Q, two stages of K and of V, P, barriers: two CTAs fit one SM, so that one CTA's
 // softmax runs beside the other's products.
@@ -297,10 +324,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         for (int j = 0; j < HC; ++j)
           if (!((unsigned)j - lo_rel < span)) sc[j] = -INFINITY;
       }
-      float mx0 = sc[0], mx1 = sc[1], mx2 = sc[2], mx3 = sc[3];
+      float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]), mx2 = fmaxf(sc[4], sc[5]), mx3 = fmaxf(sc[6], sc[7]);
 #pragma unroll
-      for (int j = 4; j < HC; j += 4) {
-        mx0 = fmaxf(mx0, sc[j]); mx1 = fmaxf(mx1, sc[j + 1]); mx2 = fmaxf(mx2, sc[j + 2]); mx3 = fmaxf(mx3, sc[j + 3]);
+      for (int j = 8; j < HC; j += 8) {
+        mx0 = at_max3(mx0, sc[j], sc[j + 1]); mx1 = at_max3(mx1, sc[j + 2], sc[j + 3]);
+        mx2 = at_max3(mx2, sc[j + 4], sc[j + 5]); mx3 = at_max3(mx3, sc[j + 6], sc[j + 7]);
       }
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       float mx_other;
@@ -319,17 +347,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
       const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
       unsigned pk[HC / 2];
-      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+      const unsigned long long scale2 = at_pack2(scale_log2, scale_log2), shift2 = at_pack2(-m_safe, -m_safe);
+      unsigned long long sum01 = at_pack2(0.f, 0.f), sum23 = sum01;
 #pragma unroll
       for (int j = 0; j < HC; j += 4) {
-        const float p0 = at_ex2(fmaf(sc[j], scale_log2, -m_safe)), p1 = at_ex2(fmaf(sc[j + 1], scale_log2, -m_safe));
-        const float p2 = at_ex2(fmaf(sc[j + 2], scale_log2, -m_safe)), p3 = at_ex2(fmaf(sc[j + 3], scale_log2, -m_safe));
-        sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+        float x0, x1, x2, x3;
+        at_unpack2(at_fma2(at_pack2(sc[j], sc[j + 1]), scale2, shift2), x0, x1);
+        at_unpack2(at_fma2(at_pack2(sc[j + 2], sc[j + 3]), scale2, shift2), x2, x3);
+        const float p0 = at_ex2(x0), p1 = at_ex2(x1), p2 = at_ex2(x2), p3 = at_ex2(x3);
+        sum01 = at_add2(sum01, at_pack2(p0, p1));
+        sum23 = at_add2(sum23, at_pack2(p2, p3));
         __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
         pk[j / 2] = *(unsigned*)&h0;
         pk[j / 2 + 1] = *(unsigned*)&h1;
       }
-      l += (sum0 + sum1) + (sum2 + sum3);
+      {
+        float sum0, sum1, sum2, sum3;
+        at_unpack2(sum01, sum0, sum1);
+        at_unpack2(sum23, sum2, sum3);
+        l += (sum0 + sum1) + (sum2 + sum3);
+      }
       // the product of the tile before has to be through: it read P, and it wrote the output that is rescaled here
       if (it > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(pv_full, (it - 1) & 1, err));
