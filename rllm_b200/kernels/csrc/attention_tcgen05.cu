@@ -6,23 +6,28 @@
 // head of the kv head's group) pair, so 128 / g tokens share every K/V tile
 // (if g does not divide 128 the last rows of a tile stay unused).
 // Key tiles hold BN = 8192 / D keys (128 for head size 64, 64 for 128), so that a
-// K or V stage is 16 KB either way, Q and P together 48 KB, and two CTAs share an SM.
-// Every operand lies in shared memory as panels of 64 columns (128 bytes, the
-// span of the 128-byte swizzle): Q and K by head dims, P by keys, V by head dims.
+// K or V stage is 16 KB either way, and two CTAs share an SM (their tensor memory too:
+// 256 columns each).
+// Q, K and V lie in shared memory as panels of 64 columns (128 bytes, the span of the
+// 128-byte swizzle) by head dims; the probabilities P go from the softmax warps'
+// registers into tensor memory (two bfloat16 a column) and are the A operand of
+// P V from there: no shared memory, no fence between the proxies.
 //   warp 0     TMA producer: Q once (3-D boxes: 64 dims x g heads x 128/g tokens),
 //              then per tile the K and V rows of its cache pages (one 2-D box per
 //              page and panel), into two-stage rings of their own; pages a sequence
 //              does not hold are skipped.
-//   warp 1     allocates TMEM (S: BN columns, output: D, 4 for the softmax warps'
-//              exchange) and issues the MMAs: S = Q K^T (128 x BN x D, both
-//              operands K-major), then, when the softmax warps have left P in
-//              shared memory, output += P V, 64 dims at a time (128 x 64 x BN; V is
-//              the MN-major operand, straight from its cache layout).
+//   warp 1     allocates TMEM (S: BN columns, output: D, P: BN / 2) and issues the
+//              MMAs: S = Q K^T (128 x BN x D, both operands K-major), then, when
+//              the softmax warps have left P in tensor memory, output += P V
+//              (128 x D x BN; V is the MN-major operand, straight from its cache
+//              layout).
 //   warps 2-9  softmax, two threads a row (= TMEM lane): read the row's scores
 //              with tcgen05.ld, mask (causal, window), keep a reference max and the
-//              sum in float32, write P as bfloat16 into the swizzled A-operand
-//              layout; the output stays in TMEM and is rescaled only when a row's
-//              max has grown by more than 2^8.
+//              sum in float32, write P as bfloat16 pairs with tcgen05.st; the
+//              output stays in TMEM and is rescaled only when a row's max has grown
+//              by more than 2^8.  The two threads of a row swap their maxima
+//              through spare columns behind P (heads of 128) or through columns
+//              of S that each has already read (heads of 64: no column is spare).
 // Contract and tile alignment as in attention_mma.cu (key tiles at absolute
 // positions; a row's arithmetic does not depend on the batch).
 // Every mbarrier wait is bounded (bit 16 of the error word, then wind-down).
@@ -71,15 +76,17 @@ __device__ __forceinline__ unsigned long long at_add2(unsigned long long a, unsi
   return d;
 }
 
-// Q, two stages of K and of V, P, barriers: two CTAs fit one SM, so that one CTA's
-// softmax runs beside the other's products.
+// Two CTAs fit one SM, so that one CTA's softmax runs beside the other's products.
 // The two threads of a row (one in warp w, one in warp w + 4, same TMEM lane) swap one value:
-// each stores its own into column `half` of a pair of columns and reads the other's after the
-// pair's mbarrier (two arrivals, one a warp; exchange n completes phase n).  A pair of columns is
-// used again two exchanges later at the earliest, when the partner, having passed the barrier
-// between, has read it.  False if the wait ran out.
-__device__ __forceinline__ bool pair_exchange(unsigned taddr, int half, void* bar, int n, float mine, float* theirs, int* err) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr + half), "r"(__float_as_uint(mine)) : "memory");
+// each stores its own into a column of its own (`t_mine`, among the score columns it has read) and
+// reads the other's (`t_theirs`) after the pair's mbarrier (two arrivals, one a warp; exchange n
+// completes phase n).  Exchanges take two columns in turn: a column is used again two exchanges
+// later at the earliest, when the partner, having passed the barrier between, has read it.  The
+// columns may be score columns that the thread has read: the next tile's scores are written over
+// them only after both have told the MMA warp that they are through with the tile.  False if the
+// wait ran out.
+__device__ __forceinline__ bool pair_exchange(unsigned t_mine, unsigned t_theirs, void* bar, int n, float mine, float* theirs, int* err) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(t_mine), "r"(__float_as_uint(mine)) : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncwarp();
@@ -87,14 +94,14 @@ __device__ __forceinline__ bool pair_exchange(unsigned taddr, int half, void* ba
   if (!__all_sync(0xffffffffu, mbar_wait(bar, n & 1, err))) return false;
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   unsigned other;
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(other) : "r"(taddr + (half ^ 1)) : "memory");
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(other) : "r"(t_theirs) : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
   *theirs = __uint_as_float(other);
   return true;
 }
 
-// Q and P (48 KB together), two stages of K and of V, barriers: two CTAs fit one SM
-#define AT_SMEM_BYTES (49152 + 2 * AT_STAGE + 2 * AT_STAGE + 256)
+// Q, two stages of K and of V, barriers: two CTAs fit one SM
+template <int AT_D> constexpr int at_smem_bytes() { return (AT_D / 64) * 16384 + 2 * AT_STAGE + 2 * AT_STAGE + 512; }
 
 template <int AT_D>
 __global__ void __launch_bounds__(AT_THREADS, 2)
@@ -113,8 +120,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     return;
   }
   unsigned char* sQ = base;                       // DP panels x [128 rows][64 dims] bf16, 128B swizzle
-  unsigned char* sP = sQ + DP * 16384;            // BN / 64 panels x [128 rows][64 keys]
-  unsigned char* sK = base + 49152;               // 2 stages x DP panels x [BN keys][64 dims]
+  unsigned char* sK = sQ + DP * 16384;            // 2 stages x DP panels x [BN keys][64 dims]
   unsigned char* sV = sK + 2 * AT_STAGE;          // 2 stages x DP panels x [BN keys][64 dims]
   unsigned long long* bars = (unsigned long long*)(sV + 2 * AT_STAGE);
   unsigned long long* q_full = bars;              // TMA -> MMA
@@ -128,6 +134,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   unsigned long long* s_free = bars + 12;         // softmax (8 warps) -> MMA
   unsigned long long* xbar = bars + 13;           // [4] the two warps of a row quarter, one another
   unsigned* tmem_slot = (unsigned*)(bars + 17);
+  int* s_pages = (int*)(bars + 18);               // [4 tiles][8 boxes]: the producer's page numbers, from K's request to V's
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = nq / nkv;
   const int bq = AT_BM / g;                        // query tokens per tile
@@ -176,7 +183,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + AT_BN, tmem_x = tmem_o + AT_D;
+  const unsigned tmem_s = *tmem_slot, tmem_o = tmem_s + AT_BN, tmem_p = tmem_o + AT_D;   // BN + D + BN / 2 <= 256 columns
 
   if (warp == 0) {
     if (lane == 0) {
@@ -185,22 +192,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     }
     // Lanes 0-7 fetch the boxes of a tile (a page and a panel of 64 dims each).  K and V have rings of their own: a K stage is
     // free once the scores that read it are done, a V stage once its product is, so K runs a tile further
-    // ahead.  Lane 0 polls both rings; the pages of the next tile of each are looked up ahead of time.
+    // ahead.  Lane 0 polls both rings.  (A request costs the warp about 140 cycles, eight boxes 1,100: with
+    // pages of 16 keys the requests, not the bytes, bound how fast tiles come in.)
     const int boxes = (AT_BN / page_size) * DP;     // page_size divides BN; at most 8 boxes
     const int bpage = lane / DP, bpanel = lane % DP; // this lane's box: which page of the tile, which panel
     const int ntiles = tile_hi - tile_lo;
-    auto lookup = [&](int it) {
-      // the page of this lane's box in tile it, if the sequence holds it and it holds keys below kend
+    // The page of this lane's box in tile `it`: read from the block table a tile ahead of its use (the load
+    // is on its way while the warp polls), checked when the tile's keys are asked for, and kept in shared
+    // memory until the tile's values are asked for (K runs at most three tiles ahead of V).
+    auto fetch = [&](int it) {
       const int j = (tile_lo + it) * AT_BN + bpage * page_size;
-      int page = -1;
-      if (lane < boxes && it < ntiles && j < kend) {
-        page = bt[j / page_size];
-        if (page < 0 || page >= num_pages) {
-          page = -1;
-          if (j + page_size > kmin && bpanel == 0) atomicOr(err, 4);   // a page with visible keys is missing
-        }
+      return (lane < boxes && it < ntiles && j < kend) ? bt[j / page_size] : -2;      // -2: no box
+    };
+    auto checked = [&](int it, int raw) {
+      if (raw == -2) return -1;
+      if (raw < 0 || raw >= num_pages) {
+        const int j = (tile_lo + it) * AT_BN + bpage * page_size;
+        if (j + page_size > kmin && bpanel == 0) atomicOr(err, 4);   // a page with visible keys is missing
+        return -1;
       }
-      return page;
+      return raw;
     };
     auto issue = [&](unsigned char* ring, const CUtensorMap* map, unsigned long long* full, int it, int page) {
       const int st = it & 1;
@@ -212,13 +223,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     (page * nkv + kvh) * page_size, &full[st]);
     };
     int nk = 0, nv = 0;                              // tiles whose K, V have been asked for
-    int page_k = lookup(0), page_v = page_k;
+    int raw_next = fetch(0);
     unsigned spin = 0;
     while (nk < ntiles || nv < ntiles) {
       unsigned ready = 0;
       if (lane == 0) {
-        if (nk < ntiles && mbar_test(&k_empty[nk & 1], ((nk >> 1) & 1) ^ 1)) ready |= 1u;
-        if (nv < ntiles && mbar_test(&v_empty[nv & 1], ((nv >> 1) & 1) ^ 1)) ready |= 2u;
+        if (nk < ntiles && nk - nv < 4 && mbar_test(&k_empty[nk & 1], ((nk >> 1) & 1) ^ 1)) ready |= 1u;
+        if (nv < nk && mbar_test(&v_empty[nv & 1], ((nv >> 1) & 1) ^ 1)) ready |= 2u;
       }
       ready = __shfl_sync(0xffffffffu, ready, 0);
       if (!ready) {
@@ -226,16 +237,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         continue;
       }
       spin = 0;
-      if (ready & 1u) { issue(sK, &map_k, k_full, nk, page_k); ++nk; page_k = lookup(nk); }
-      if (ready & 2u) { issue(sV, &map_v, v_full, nv, page_v); ++nv; page_v = lookup(nv); }
+      if (ready & 1u) {
+        const int page = checked(nk, raw_next);
+        if (lane < 8) s_pages[(nk & 3) * 8 + lane] = page;
+        raw_next = fetch(nk + 1);
+        issue(sK, &map_k, k_full, nk, page);
+        ++nk;
+      }
+      if (ready & 2u) {
+        issue(sV, &map_v, v_full, nv, lane < 8 ? s_pages[(nv & 3) * 8 + lane] : -1);
+        ++nv;
+      }
     }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
       // S: float32 accumulate, bf16 x bf16, A and B K-major, M 128, N BN.
-      // PV: the same with N 64 (a panel of head dims at a time) and B (V) MN-major.
+      // PV: the same with N = D, A (P) in tensor memory and B (V) MN-major.
       const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_BN >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
-      const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(64 >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
+      // (all D dims in one instruction: for D = 128 the two panels of V are a leading-dimension step apart)
+      const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(AT_D >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
       const int ntiles = tile_hi - tile_lo;
       const unsigned long long dq = umma_desc(sQ);
       // scores of the tile in stage st: D / 16 steps along the head dims, panel by panel
@@ -267,19 +288,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           umma_commit(s_full);
           umma_commit(&k_empty[sn]);
         }
-        ok = mbar_wait(&v_full[st], (it >> 1) & 1, err) && mbar_wait(p_full, it & 1, err);   // P is in shared memory, O is rescaled
+        ok = mbar_wait(&v_full[st], (it >> 1) & 1, err) && mbar_wait(p_full, it & 1, err);   // P is in tensor memory, O is rescaled
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const unsigned long long dv = umma_desc(sV + st * AT_STAGE);
+        // V is the MN-major operand: 64 dims x 8 keys a swizzle atom, 8 keys on 1024 bytes further (stride
+        // field), 64 dims on a panel further (leading-dimension field)
+        const unsigned long long dv = (umma_desc(sV + st * AT_STAGE) & ~(0x3FFFull << 16)) | ((unsigned long long)(KPANEL >> 4) << 16);
 #pragma unroll
-        for (int np = 0; np < DP; ++np) {               // 64 output dims at a time
-#pragma unroll
-          for (int kk = 0; kk < AT_BN / 16; ++kk) {     // 16 keys a step: P along K inside a 64-key panel, V two row groups on
-            const unsigned long long dp = umma_desc(sP + (kk >> 2) * 16384) + 2 * (kk & 3);
-            umma_bf16(tmem_o + np * 64, dp, dv + (unsigned long long)(np * (KPANEL >> 4) + kk * (2048 >> 4)), idesc_pv,
-                      (it != 0) || (kk != 0));
-          }
-        }
+        for (int kk = 0; kk < AT_BN / 16; ++kk)         // 16 keys a step: 8 columns of P on, V two row groups on
+          umma_bf16_tmem_a(tmem_o, tmem_p + kk * 8, dv + (unsigned long long)(kk * (2048 >> 4)), idesc_pv,
+                           (it != 0) || (kk != 0));
         umma_commit(pv_full);
         umma_commit(&v_empty[st]);
       }
@@ -288,8 +306,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   } else {
     // Two threads a row: warps 2-5 take the first half of the tile's keys (and of the output dims),
     // warps 6-9 the second; warp w and warp w + 4 own the same 32 rows (TMEM lanes) and exchange
-    // the row's max and sum through four spare TMEM columns (shared memory is full: two CTAs share
-    // an SM), under a barrier of their own.
+    // the row's max and sum through score columns that they have read, under a barrier of their own.
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;               // this thread's row of the tile
     const int tl = r / g, hl = r - tl * g;
@@ -305,6 +322,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const unsigned lane_sel = (unsigned)(quarter * 32) << 16;
     const int ntiles = tile_hi - tile_lo;
     constexpr int HC = AT_BN / 2;                    // keys a thread
+    // Where the two threads of a row swap values: in spare columns behind P if the CTA's 256 columns leave
+    // four (heads of 128); else in the score columns that each thread has read itself (its first two), and
+    // then the MMA warp may write the next tile's scores only when the exchange is over.
+    constexpr bool X_SPARE = AT_BN + AT_D + AT_BN / 2 + 4 <= 256;
+    const unsigned x_mine = X_SPARE ? tmem_p + AT_BN / 2 + lane_sel + half * 2 : tmem_s + lane_sel + half * HC;
+    const unsigned x_theirs = X_SPARE ? tmem_p + AT_BN / 2 + lane_sel + (half ^ 1) * 2 : tmem_s + lane_sel + (half ^ 1) * HC;
     bool ok = true;
     for (int it = 0; it < ntiles; ++it) {
       const int j0 = (tile_lo + it) * AT_BN;
@@ -315,9 +338,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
       for (int c0 = 0; c0 < HC; c0 += 32) tmem_ld32(tmem_s + lane_sel + half * HC + c0, (unsigned*)(sc + c0));
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_free);
+      if (X_SPARE) {                                   // the scores are in registers: the next tile's may come
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
+      }
       if (!(j0 >= clear_lo && j0 + AT_BN <= clear_hi)) {
         const unsigned lo_rel = (unsigned)(row_lo - j0 - half * HC), span = (unsigned)(row_hi - row_lo);
 #pragma unroll
@@ -332,8 +357,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
       float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       float mx_other;
-      ok = pair_exchange(tmem_x + lane_sel + (it & 1) * 2, half, &xbar[quarter], it, mx, &mx_other, err);
+      ok = pair_exchange(x_mine + (it & 1), x_theirs + (it & 1), &xbar[quarter], it, mx, &mx_other, err);
       if (!ok) break;
+      if (!X_SPARE) {                                  // through with the tile's score columns, the exchange's too
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
+      }
       mx = fmaxf(mx, mx_other) * scale_log2;
       // The reference point of the exponentials moves only when the max has grown by more than 2^8: until
       // then the old one serves (probabilities up to 256, the sum and the output scale alike), and the
@@ -385,28 +415,28 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-      // this thread's keys half * HC .. + HC - 1 lie in one 64-key panel of P, from chunk (key % 64) / 8 on
-      unsigned char* prow = sP + ((half * HC) >> 6) * 16384 + r * 128;
-      const int chunk0 = ((half * HC) & 63) >> 3;
-#pragma unroll
-      for (int c = 0; c < HC / 8; ++c)                 // 8 keys = one 16-byte chunk of the row's 128 bytes
-        *(uint4*)(prow + (((chunk0 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      // this thread's keys half * HC .. + HC - 1: columns half * HC / 2 .. of P, two keys a column
+      if constexpr (HC == 64) tmem_st32(tmem_p + lane_sel + half * (HC / 2), pk);
+      else tmem_st16(tmem_p + lane_sel + half * (HC / 2), pk);
       // rows of V at and behind the last visible key were never written by this sequence: whatever
       // they hold must not reach the product (0 x inf), so they are cleared before P V is issued
       if (it == ntiles - 1) {
         ok = __all_sync(0xffffffffu, mbar_wait(&v_full[it & 1], (it >> 1) & 1, err));   // V has landed: nothing overwrites the zeros
         if (!ok) break;
       }
-      if (it == ntiles - 1 && r < AT_BN && j0 + r >= kend) {     // thread r: key row r, half a row of every panel
+      if (it == ntiles - 1) {
+        if (r < AT_BN && j0 + r >= kend) {            // thread r: key row r, half a row of every panel
 #pragma unroll
-        for (int dp = 0; dp < DP; ++dp) {
-          uint4* vrow = (uint4*)(sV + (it & 1) * AT_STAGE + dp * KPANEL + r * 128 + half * 64);
+          for (int dp = 0; dp < DP; ++dp) {
+            uint4* vrow = (uint4*)(sV + (it & 1) * AT_STAGE + dp * KPANEL + r * 128 + half * 64);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+            for (int c = 0; c < 4; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+          }
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeros, before the MMA reads V
       }
-      // hand P to the MMA warp: make the shared-memory writes visible to the async proxy first
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      // hand P to the MMA warp
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
@@ -415,7 +445,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // the row's sum is the two halves' sums (an exchange slot no tile is using: the pair's last
     // exchange was for tile ntiles-1, this one takes the other parity)
     float lother = 0.f;
-    if (ok) ok = pair_exchange(tmem_x + lane_sel + (ntiles & 1) * 2, half, &xbar[quarter], ntiles, l, &lother, err);
+    if (ok) ok = pair_exchange(x_mine + (ntiles & 1), x_theirs + (ntiles & 1), &xbar[quarter], ntiles, l, &lother, err);
     const float lsum = half == 0 ? l + lother : lother + l;
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -485,7 +515,7 @@ static int at_launch(const void* q, int q_stride, int num_q_rows, void* out, con
   }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_smem_bytes<D>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -493,7 +523,7 @@ static int at_launch(const void* q, int q_stride, int num_q_rows, void* out, con
   const long long tiles = (num_tokens + bq - 1) / bq + (seq_end - seq_begin);
   if (tiles * nkv > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;
   dim3 grid((unsigned)(tiles * nkv));
-  attention_tcgen05_kernel<D><<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(mq, mk, mv, (bf16*)out, block_table, max_blocks,
+  attention_tcgen05_kernel<D><<<grid, AT_THREADS, at_smem_bytes<D>(), stream>>>(mq, mk, mv, (bf16*)out, block_table, max_blocks,
       q_start, seq_lens, seq_begin, seq_end, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
   RLLM_LAUNCH_CHECK();
   return 0;
