@@ -402,9 +402,13 @@ API int rllm_cache_free(void* h, int64_t id) {
   auto it = m->reqs.find(id);
   if (it == m->reqs.end()) return 0;
   Req& r = it->second;
+  // Last page first (the reference frees in table order, crates/rllm-cache/src/manager.rs:169-177): of a
+  // request's findable pages the last are then evicted first, and a prefix stays findable as long as its
+  // first pages are; and pages without a hash come back in rising order, so that the next request's
+  // pages follow one another in the cache.
   for (int g : m->paged)
-    for (int page : r.tables[g])
-      if (page >= 0) m->pools[g]->release(page);
+    for (auto it = r.tables[g].rbegin(); it != r.tables[g].rend(); ++it)
+      if (*it >= 0) m->pools[g]->release(*it);
   m->free_slots.push_back(r.slot);
   for (size_t i = 0; i < m->fresh_slots.size(); ++i)
     if (m->fresh_slots[i] == r.slot) { m->fresh_slots.erase(m->fresh_slots.begin() + i); break; }

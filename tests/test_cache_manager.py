@@ -357,3 +357,33 @@ def test_pool_copy_on_write():
     pool.incref(a)
     assert pool.copy_on_write(a) is None and pool.refcount[a] == 2      # no page free: nothing changes
     pool.check()
+
+
+def test_pages_are_given_back_last_page_first():
+    """Without hashes the pages of a finished request come back in rising order, so the next request's pages
+    follow one another; with hashes the last pages of a finished request are the first to be used again, and
+    what stays findable is a prefix."""
+    m = CacheManager([FULL], 4, 12, 2)
+    m.admit("a")
+    assert m.ensure("a", 0, 40)
+    first = m.table("a", 0)
+    assert first == sorted(first)
+    m.free("a")
+    m.admit("b")
+    assert m.ensure("b", 0, 24)
+    assert m.table("b", 0) == first[:6]
+    m.free("b")
+    m.check()
+    c = CacheManager([FULL], 4, 8, 2, enable_prefix_caching=True)
+    toks = list(range(200, 232))                       # 8 full pages
+    c.admit("a")
+    assert c.ensure("a", 0, 32)
+    c.register_computed("a", toks, 32)
+    pages = c.table("a", 0)
+    c.free("a")
+    c.admit("b")
+    assert c.ensure("b", 0, 12)                         # three pages: taken from the end of a's
+    assert sorted(c.table("b", 0)) == sorted(pages[5:])
+    assert c.match_prefix(toks) == 20                   # pages 0..4 of the prefix are still findable
+    c.free("b")
+    c.check()

@@ -128,8 +128,10 @@ def test_rope_and_cache_write(ops, err, dt, nq, nkv, d, rd, page):
     assert int(err.item()) == 2
 
 
-def paged_case(dt, nq, nkv, d, page, lens, q_lens, pages=64, seed=4):
-    """Sequences with contexts ``lens`` whose last ``q_lens`` tokens are queries."""
+def paged_case(dt, nq, nkv, d, page, lens, q_lens, pages=64, seed=4, order="random"):
+    """Sequences with contexts ``lens`` whose last ``q_lens`` tokens are queries.  ``order``: the pages of a
+    sequence in random order, "sequential" (one after the other in the cache, as from a fresh pool) or "runs"
+    (one after the other with a stray page now and then)."""
     g = torch.Generator().manual_seed(seed)
     S = len(lens)
     ks = [torch.randn(n, nkv, d, generator=g).to(dt) for n in lens]
@@ -137,12 +139,13 @@ def paged_case(dt, nq, nkv, d, page, lens, q_lens, pages=64, seed=4):
     qs = [torch.randn(m, nq, d, generator=g).to(dt) for m in q_lens]
     maxb = max(-(-n // page) for n in lens)
     table = torch.full((S, maxb), -1, dtype=torch.int32)
-    perm = torch.randperm(pages, generator=g).tolist()
+    perm = torch.randperm(pages, generator=g).tolist() if order == "random" else list(range(pages - 1, -1, -1))
     kc = torch.zeros(pages, nkv, page, d, dtype=dt)
     vc = torch.zeros_like(kc)
     for s, n in enumerate(lens):
         for b in range(-(-n // page)):
-            pg = perm.pop()
+            stray = order == "runs" and int(torch.randint(0, 7, (1,), generator=g)) == 0
+            pg = perm.pop(int(torch.randint(0, len(perm), (1,), generator=g))) if stray else perm.pop()
             table[s, b] = pg
             m = min(page, n - b * page)
             kc[pg, :, :m] = ks[s][b * page:b * page + m].transpose(0, 1)
@@ -257,6 +260,33 @@ TCGEN05_CASES = [(8, 2, 64, 16, 0), (32, 8, 64, 16, 0), (4, 4, 64, 32, 0), (16, 
                  (2, 1, 64, 16, 70), (64, 1, 64, 16, 0), (6, 3, 64, 32, 129), (6, 2, 64, 16, 0), (5, 1, 64, 32, 40),
                  (8, 2, 128, 16, 0), (32, 8, 128, 16, 0), (4, 4, 128, 32, 0), (24, 8, 128, 16, 0), (16, 1, 128, 64, 0),
                  (8, 2, 128, 32, 300), (3, 1, 128, 16, 65)]
+
+
+@pytest.mark.parametrize("order", ["sequential", "runs"])
+@pytest.mark.parametrize("nq,nkv,d,page,window", [(32, 8, 64, 16, 0), (6, 3, 64, 32, 129), (16, 1, 64, 64, 0), (8, 2, 64, 128, 0),
+                                                  (24, 8, 128, 16, 0), (8, 2, 128, 32, 300), (16, 1, 128, 64, 0)])
+def test_attention_prefill_tcgen05_pages_that_follow_one_another(ops, err, nq, nkv, d, page, window, order):
+    """Sequences whose pages follow one another in the cache (what a fresh pool hands out), with or without a
+    stray page now and then, up to the last page of the pool."""
+    dt = torch.bfloat16
+    lens, q_lens = [700, 64, 65, 130, 2, 385, 1000], [257, 64, 2, 129, 2, 384, 1000]
+    need = sum(-(-n // page) for n in lens)
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, lens, q_lens, pages=need, order=order)
+    T = sum(q_lens)
+    q = torch.cat(qs).reshape(T, nq * d).to(DEV)
+    out = torch.zeros(T, nq * d, dtype=dt, device=DEV)
+    q_start = torch.tensor([0] + list(np.cumsum(q_lens)), dtype=torch.int32, device=DEV)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    scale = 1.1 / math.sqrt(d)
+    ops.attention_prefill_tcgen05(q, nq * d, out, kc.to(DEV), vc.to(DEV), table.to(DEV), q_start, seq_lens,
+                                  0, len(lens), T, nq, nkv, d, window, scale, err)
+    assert int(err.item()) == 0
+    off = 0
+    for s, (n, m) in enumerate(zip(lens, q_lens)):
+        want = pl.attention(qs[s].double(), ks[s].double(), vs[s].double(), torch.arange(n - m, n),
+                            window=window or None, scale=scale)
+        assert rel_err(out[off:off + m], want) <= tol(dt), (s, n, m)
+        off += m
 
 
 @pytest.mark.parametrize("nq,nkv,d,page,window", TCGEN05_CASES)
