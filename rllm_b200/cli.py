@@ -79,6 +79,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="error | warn | info | debug (one line of statistics per step) | trace; "
                         "default: the environment variable RLLM_LOG, else info")
 
+    sub.add_parser("replay", add_help=False,
+                   help="feed token ids through the model step by step and write logits (options of bin/trace_run)")
     r = sub.add_parser("init-random", help="write a model folder with random weights")
     r.add_argument("model", help="folder to write")
     r.add_argument("--config", required=True, help="config.json to build the model from")
@@ -166,6 +168,11 @@ def cmd_init_random(args) -> int:
 
 
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "replay":
+        # trace replay (the program behind bin/trace_run) takes its own options: --model --dtype --out --max-tokens
+        from .engine.replay import main as replay_main
+        return replay_main(argv[1:])
     args = build_parser().parse_args(argv)
     if args.command == "generate":
         return cmd_generate(args)

@@ -307,6 +307,20 @@ def test_command_line(model_dirs, capsys):
     plain = pl.read_model_dir(model_dirs["A"])
     assert [l["token_ids"] for l in lines] == [plain.greedy([5, 6, 7], 4), plain.greedy([9, 10], 4)]
     assert lines[0]["finish_reason"] == "length" and lines[0]["usage"]["total_tokens"] == 7
+    # two samples of a prompt, each from a stream of its own
+    code = main(["generate", model_dirs["A"], "--prompt-ids", "5,6,7,8,9", "--max-tokens", "6", "--temperature", "1.0",
+                 "-n", "2", "--seed", "11", "--dtype", "fp32", "--num-gpu-blocks", "32", "--max-num-seqs", "4",
+                 "--ignore-eos", "--json"])
+    assert code == 0
+    line = json.loads(capsys.readouterr().out.strip())
+    assert [o["index"] for o in line["outputs"]] == [0, 1] and all(len(o["token_ids"]) == 6 for o in line["outputs"])
+    assert line["token_ids"] == line["outputs"][0]["token_ids"] and line["usage"]["completion_tokens"] == 12
+    for o in line["outputs"]:
+        toks = [5, 6, 7, 8, 9]
+        for j, t in enumerate(o["token_ids"]):
+            x = pl.process_logits(plain.logits(toks)[-1].numpy(), temperature=1.0)
+            assert t == pl.sample_row(x, 1.0, -1, pl.uniform_for(sample_seed(11, o["index"]), j))
+            toks.append(t)
 
 
 @pytest.mark.parametrize("seed", [0, 1, 2])
