@@ -327,8 +327,9 @@ def test_command_line(model_dirs, capsys):
 def test_random_serving_keeps_every_request_right(model_dirs, seed):
     """Requests of random lengths, some with a common beginning, arrive while others run; there are few
     pages (requests get preempted), few sequences at a time, a small token budget, prefix sharing, an
-    abort, and request names that come back after their request has ended.  Every request that ends has
-    the tokens that the plain implementation generates for its prompt alone."""
+    abort, request names that come back after their request has ended, and requests that want two or three
+    samples at a temperature.  Every request that ends has the tokens that the plain implementation
+    generates (or draws, with the sample's own random stream) for its prompt alone."""
     from rllm_b200 import SamplingParams
     name = "A"
     cfg, _, page = TINY[name]
@@ -355,27 +356,39 @@ def test_random_serving_keeps_every_request_right(model_dirs, seed):
     while todo or live:
         guard += 1
         assert guard < 5000
-        # admit: a name only when its earlier request has ended
+        # admit: a name only when its earlier request has ended; every fourth request wants several samples
         while todo and todo[0][0] not in live and len(live) < 7 and rng.random() < 0.7:
             rid, prompt, steps = todo.pop(0)
-            llm.add_request(prompt, SamplingParams(temperature=0.0, max_tokens=steps, ignore_eos=True), request_id=rid)
-            live[rid] = (prompt, steps, [])
+            n = int(rng.integers(2, 4)) if len(todo) % 4 == 0 else 1
+            sp = SamplingParams(temperature=0.8 if n > 1 else 0.0, max_tokens=steps, ignore_eos=True, n=n, seed=1000 + len(todo))
+            llm.add_request(prompt, sp, request_id=rid)
+            live[rid] = (prompt, steps, {i: [] for i in range(n)}, sp)
         if live and aborted == 0 and guard == 25:
             rid = sorted(live)[0]
             assert llm.abort_request(rid)
             del live[rid]
             aborted = 1
         for out in llm.step():
-            prompt, steps, toks = live[out.request_id]
-            toks += out.outputs[0].token_ids
+            prompt, steps, toks, sp = live[out.request_id]
+            for c in out.outputs:
+                toks[c.index] += c.token_ids
             if out.finished:
-                done.append((prompt, steps, toks))
+                done.append((prompt, steps, toks, sp))
                 del live[out.request_id]
-    assert len(done) >= 20
-    for prompt, steps, toks in done:
-        assert toks == plain.greedy(prompt, steps), (len(prompt), steps)
+    assert len(done) >= 20 and any(sp.n > 1 for _, _, _, sp in done)
+    for prompt, steps, toks, sp in done:
+        if sp.n == 1:
+            assert toks[0] == plain.greedy(prompt, steps), (len(prompt), steps)
+            continue
+        for i, got in toks.items():
+            assert len(got) == steps
+            seq = list(prompt)
+            for j, t in enumerate(got):
+                x = pl.process_logits(plain.logits(seq)[-1].numpy(), temperature=0.8)
+                assert t == pl.sample_row(x, 0.8, -1, pl.uniform_for(sample_seed(sp.seed, i), j)), (len(prompt), i, j)
+                seq.append(t)
     llm.engine.cache.check()
-    assert llm.engine.cache.usage()["num_requests"] == 0
+    assert llm.engine.cache.usage()["num_requests"] == 0 and not llm.engine._families
     print("preemptions", llm.engine.scheduler.num_preemptions, "prefix hits", llm.engine.scheduler.prefix_hit_tokens)
 
 
