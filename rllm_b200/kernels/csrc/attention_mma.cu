@@ -427,7 +427,7 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
                         const int* __restrict__ seq_lens, int nq, int nkv, int page_size, int num_pages,
                         int window, float scale_log2, int max_chunks, const double* __restrict__ inv_freq,
                         int rotary_dim, int write_kv, float* __restrict__ ws_o, float* __restrict__ ws_ml,
-                        int* __restrict__ counters, int* __restrict__ err, int tail_from) {
+                        int* __restrict__ counters, int* __restrict__ err, int tail_from, int first_wave) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned char* mine = smem_raw + (size_t)warp * dec_warp_smem<D, STAGES, TBN>();
@@ -500,21 +500,42 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
     }
     cp_async_commit();
   };
+  // Q rows = heads of the group, rows >= g zero: 16-byte loads into registers.  The loads take as long as a
+  // tile's, so they go out before the first tiles are asked for wherever the kernel ahead in the stream is
+  // through anyway: without write_kv (waited for above), and in CTAs behind the grid's first wave, which
+  // start when CTAs of this grid have finished (if that kernel should still run, they wait here, no more).
+  // A CTA of the first wave starts while that kernel runs: it asks for its tiles first and waits then.
+  constexpr int QN = 16 * (D / 8) / 32;
+  uint4 qreg[QN];
+  auto load_q = [&]() {
+#pragma unroll
+    for (int i = 0; i < QN; ++i) {
+      const int idx = lane + 32 * i, r = idx / (D / 8), c = idx % (D / 8);
+      qreg[i] = r < g ? *(const uint4*)(qrow + (size_t)(kvh * g + r) * D + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  const int cta_id = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+  const bool q_first = !write_kv || cta_id >= first_wave;
+  if (q_first) {
+    if (write_kv) pdl_wait();
+    load_q();
+  }
 #pragma unroll
   for (int i = 0; i < STAGES; ++i) issue(t_lo + i);
   // the rotation's angles depend on the position alone
   for (int i = lane; i < half; i += 32) rope_cos_sin(pos, inv_freq[i], &sCS[i], &sCS[half + i]);
-  if (write_kv) pdl_wait();
+  if (!q_first) {
+    pdl_wait();
+    load_q();
+  }
   // no CTA of this grid is still to come once its last wave runs: the stream's next kernel may come in
-  if ((int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) >= tail_from) pdl_launch();
+  if (cta_id >= tail_from) pdl_launch();
 
-  // Q rows = heads of the group, rows >= g zero: 16-byte loads first, then the rotation in
-  // shared memory (a lane rotates the pairs (i, i + half) it owns)
-  for (int idx = lane; idx < 16 * (D / 8); idx += 32) {
-    const int r = idx / (D / 8), c = idx % (D / 8);
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (r < g) v = *(const uint4*)(qrow + (size_t)(kvh * g + r) * D + c * 8);
-    *(uint4*)tile_ptr<D>(sQ, r, c) = v;
+  // the Q tile in shared memory, then the rotation there (a lane rotates the pairs (i, i + half) it owns)
+#pragma unroll
+  for (int i = 0; i < QN; ++i) {
+    const int idx = lane + 32 * i, r = idx / (D / 8), c = idx % (D / 8);
+    *(uint4*)tile_ptr<D>(sQ, r, c) = qreg[i];
   }
   __syncwarp();
   for (int idx = lane; idx < g * half; idx += 32) {
@@ -776,7 +797,8 @@ static int launch_decode_cfg(int warps, bf16* qkv, int q_stride, bf16* out, bf16
   const int tail_from = (int)(ctas > resident[warps] - 1 ? ctas - (resident[warps] - 1) : 0);
   cudaError_t e = rllm_launch_pdl(attention_decode_kernel<D, STAGES, TBN>, grid, dim3(32 * warps), smem, stream, qkv,
       q_stride, out, kc, vc, bt, max_blocks, seq_lens, nq, nkv, page_size, num_pages, window,
-      scale * 1.4426950408889634f, max_chunks, inv_freq, rotary_dim, write_kv, ws_o, ws_ml, counters, err, tail_from);
+      scale * 1.4426950408889634f, max_chunks, inv_freq, rotary_dim, write_kv, ws_o, ws_ml, counters, err, tail_from,
+      resident[warps] - 1);
   return (int)e;
 }
 
