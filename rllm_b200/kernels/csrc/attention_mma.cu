@@ -505,13 +505,17 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
   // through anyway: without write_kv (waited for above), and in CTAs behind the grid's first wave, which
   // start when CTAs of this grid have finished (if that kernel should still run, they wait here, no more).
   // A CTA of the first wave starts while that kernel runs: it asks for its tiles first and waits then.
+  // (The row is the output of the kernel ahead: it is read through a pointer made behind the wait, so that no
+  // load of it can be merged with another or moved above the wait; see pdl_fresh.)
   constexpr int QN = 16 * (D / 8) / 32;
   uint4 qreg[QN];
+  const bf16* qrow_now = nullptr;
   auto load_q = [&]() {
+    qrow_now = pdl_fresh((const bf16*)qrow);
 #pragma unroll
     for (int i = 0; i < QN; ++i) {
       const int idx = lane + 32 * i, r = idx / (D / 8), c = idx % (D / 8);
-      qreg[i] = r < g ? *(const uint4*)(qrow + (size_t)(kvh * g + r) * D + c * 8) : make_uint4(0u, 0u, 0u, 0u);
+      qreg[i] = r < g ? *(const uint4*)(qrow_now + (size_t)(kvh * g + r) * D + c * 8) : make_uint4(0u, 0u, 0u, 0u);
     }
   };
   const int cta_id = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
@@ -578,8 +582,8 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
         const bool okp = page >= 0 && page < num_pages;
         if (!okp && lane == 0) atomicOr(err, 2);
         const long long off = (((long long)(okp ? page : 0) * nkv + kvh) * page_size + (pos - pi * page_size)) * D;
-        const bf16* kx = qrow + (size_t)(nq + kvh) * D;
-        const bf16* vx = qrow + (size_t)(nq + nkv + kvh) * D;
+        const bf16* kx = qrow_now + (size_t)(nq + kvh) * D;
+        const bf16* vx = qrow_now + (size_t)(nq + nkv + kvh) * D;
         const int r = pos - j0;
         for (int i = lane; i < D; i += 32) {
           float kv = to_f32(kx[i]);

@@ -79,6 +79,27 @@ __device__ __forceinline__ void rope_cos_sin(int pos, double inv_freq, float* c,
 // what it reads before its own pdl_wait may include what those earlier kernels wrote.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// A pointer to what the kernel ahead wrote must be taken through pdl_fresh (or pdl_wait_on) after the wait.
+// The "memory" clobber of the wait does not hold back loads that the compiler has proved to read memory no
+// one writes during the kernel (const __restrict__ parameters: ld.global.nc, free to move): merged or
+// hoisted above the wait they return what was there before the kernel ahead wrote.  (Seen once: the Q tile
+// of decode attention, loaded in two branches of which one lay before the wait, came out of a graph replay
+// as the step before's.)  A pointer that comes out of an asm statement behind the wait carries no such
+// proof, and its loads stay behind it.
+template <typename T>
+__device__ __forceinline__ T* pdl_fresh(T* p) {
+  asm volatile("" : "+l"(p) : : "memory");
+  return p;
+}
+template <typename P>
+__device__ __forceinline__ void pdl_fresh_in_place(P& p) {      // P: any pointer type, qualifiers and all
+  asm volatile("" : "+l"(p) : : "memory");
+}
+template <typename... P>
+__device__ __forceinline__ void pdl_wait_on(P&... ptrs) {
+  pdl_wait();
+  (pdl_fresh_in_place(ptrs), ...);
+}
 
 // Launch `kernel` so that it may start before the kernel ahead of it in the stream has
 // finished (the kernel must call pdl_wait before it reads that kernel's output).

@@ -15,7 +15,7 @@
 template <typename TW>
 __global__ void embedding_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                  float* __restrict__ out, int H, int V, int* __restrict__ err) {
-  pdl_wait();
+  pdl_wait_on(ids);              // (in a decode graph the token ids come from the kernel directly ahead)
   pdl_launch();
   const int t = blockIdx.x;
   const int id = ids[t];
@@ -75,7 +75,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TD* __restrict__ del
                                const int* __restrict__ rows, const TW* __restrict__ w,
                                TO* __restrict__ out, int H, float eps, int writeback, int early_launch) {
   __shared__ float red[32];
-  pdl_wait();
+  pdl_wait_on(x, delta, rows);
   if (early_launch) pdl_launch();      // a small grid: the next kernel's CTAs find room beside it
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
@@ -437,7 +437,7 @@ RLLM_EXPORT int rllm_silu_mul(const void* gu, void* out, int dtype, int T, int I
 __global__ void decode_advance_kernel(int* __restrict__ token_ids, int* __restrict__ positions,
                                       int* __restrict__ seq_lens, const int* __restrict__ sampled,
                                       int* __restrict__ history_row, int S) {
-  pdl_wait();
+  pdl_wait_on(sampled);
   pdl_launch();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= S) return;

@@ -62,7 +62,8 @@ struct NormSide {
 };
 
 // The parts of row m = tid % R (R = 8 MT rows) that fall to this thread's slice tid / R, added in order; the
-// loads are independent of one another.  Rows past M repeat the last row.
+// loads are independent of one another.  Rows past M repeat the last row.  (The kernel ahead wrote them: the
+// caller passes a pointer made behind the wait, see pdl_fresh.)
 template <int R>
 __device__ __forceinline__ float rows_sumsq_slice(const float* __restrict__ parts, int P, int M) {
   const int m = min((int)(threadIdx.x % R), M - 1), slice = threadIdx.x / R, nslices = blockDim.x / R;
@@ -162,7 +163,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     // their way, and the first multiplies do not wait for them.
     if (first && EPI == EPI_RESID) h_old = resid_old(out, ldo, n0, M, N, MT);
     if (RSTD && !summed && (!first || b0 + U >= b_end)) {
-      psum = rows_sumsq_slice<8 * MT>(ns.parts, ns.P, M);
+      psum = rows_sumsq_slice<8 * MT>(pdl_fresh(ns.parts), ns.P, M);
       summed = true;
     }
 #pragma unroll
@@ -188,7 +189,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, int ldx, const bf16* __restrict_
     mine[(gq + 8) * 8 * MT + i * 8 + 2 * t + 1] = c[i][3];
   }
   if (RSTD) {
-    if (!summed) psum = rows_sumsq_slice<8 * MT>(ns.parts, ns.P, M);
+    if (!summed) psum = rows_sumsq_slice<8 * MT>(pdl_fresh(ns.parts), ns.P, M);
     s_part[threadIdx.x] = psum;
     __syncthreads();
     if (threadIdx.x < 8 * MT) {

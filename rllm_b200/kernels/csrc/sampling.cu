@@ -266,7 +266,7 @@ argmax_kernel(const float* __restrict__ logits, int V, int ld, int* __restrict__
               ArgMax* __restrict__ partials, int* __restrict__ counters, int split) {
   __shared__ ArgMax sm_arg[32];
   __shared__ int s_last;
-  pdl_wait();
+  pdl_wait_on(logits);
   pdl_launch();
   const int r = blockIdx.y, part = blockIdx.x;
   const float* x = logits + (size_t)r * ld;
@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(256)
 sample_split_max_kernel(const float* __restrict__ logits, int V, int ld, const float* __restrict__ temperature,
                         const int* __restrict__ top_k, ArgMax* __restrict__ partials, int split) {
   __shared__ ArgMax sm_arg[32];
-  pdl_wait();
+  pdl_wait_on(logits);
   pdl_launch();
   const int r = blockIdx.y, part = blockIdx.x;
   const float* x = logits + (size_t)r * ld;
@@ -393,7 +393,7 @@ sample_split_mass_kernel(const float* __restrict__ logits, int V, int ld, const 
                          int* __restrict__ out_tokens, const SelectState* __restrict__ states) {
   __shared__ ArgMax sm_arg[32];
   __shared__ unsigned long long sm_sum[8];
-  pdl_wait();
+  pdl_wait_on(logits, partials, states);
   pdl_launch();
   const int r = blockIdx.y, part = blockIdx.x;
   const float* x = logits + (size_t)r * ld;
@@ -435,7 +435,7 @@ sample_split_draw_kernel(const float* __restrict__ logits, int V, int ld, const 
   __shared__ unsigned long long seg_sum[256];
   __shared__ int sh_pick;
   __shared__ unsigned long long sh_rest;
-  pdl_wait();
+  pdl_wait_on(logits, partials, psum, states);
   pdl_launch();
   const int r = blockIdx.x;
   const float* x = logits + (size_t)r * ld;
@@ -543,7 +543,7 @@ select_pass_kernel(const float* __restrict__ logits, int V, int ld, const float*
   __shared__ ArgMax sm_arg[32];
   __shared__ unsigned long long sh[256];
   __shared__ int s_last;
-  pdl_wait();
+  pdl_wait_on(logits, partials);
   pdl_launch();
   const int r = blockIdx.y, part = blockIdx.x;
   SelectState* st = states + r;
@@ -621,7 +621,7 @@ select_total_kernel(const float* __restrict__ logits, int V, int ld, const float
                     const ArgMax* __restrict__ partials, int split, SelectState* __restrict__ states) {
   __shared__ ArgMax sm_arg[32];
   __shared__ unsigned long long sm_sum[8];
-  pdl_wait();
+  pdl_wait_on(logits, partials);
   pdl_launch();
   const int r = blockIdx.y, part = blockIdx.x;
   SelectState* st = states + r;
@@ -808,7 +808,7 @@ logprobs_kernel(const float* __restrict__ logits, int V, int ld, const int* __re
                 float* __restrict__ lp, int* __restrict__ top_ids, float* __restrict__ top_lp) {
   __shared__ ArgMax sm_arg[32];
   __shared__ float sm_f[32];
-  pdl_wait();
+  pdl_wait_on(logits, tokens);
   pdl_launch();
   const int r = blockIdx.x;
   const float* x = logits + (size_t)r * ld;

@@ -485,7 +485,7 @@ def test_mma_attention_finds_one_far_key(ops, err, kind):
 
 
 @pytest.mark.parametrize("nq,nkv,d,rd,page,window", [(8, 2, 64, 64, 16, 0), (3, 1, 32, 16, 8, 0), (4, 4, 128, 128, 16, 40),
-                                                     (12, 2, 16, 16, 4, 0)])
+                                                     (12, 2, 16, 16, 4, 0), (24, 8, 128, 128, 16, 0), (6, 2, 128, 64, 32, 0)])
 def test_decode_with_fused_rotation_and_cache_write(ops, err, nq, nkv, d, rd, page, window):
     """The decode kernel that also rotates the token's q and k and stores k and v
     gives what the separate rotation-and-write kernel followed by attention gives."""
