@@ -60,6 +60,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--frequency-penalty", type=float, default=0.0)
     g.add_argument("--seed", type=int, default=None, help="sampling seed of the first prompt; prompt i uses seed+i")
     g.add_argument("--ignore-eos", action="store_true")
+    g.add_argument("--stop-token-ids", default="", metavar="ID,ID", help="token ids that end a request (beside the model's EOS)")
+    g.add_argument("--min-tokens", type=int, default=0, help="the model's EOS cannot be drawn before this many tokens have been generated")
     g.add_argument("--logprobs", type=int, default=None, metavar="N",
                    help="report every generated token's log-probability and the N likeliest tokens of its place (with --json)")
     g.add_argument("--dtype", default="auto", help="auto | bf16 | fp32")
@@ -81,6 +83,9 @@ def build_parser() -> argparse.ArgumentParser:
 
     sub.add_parser("replay", add_help=False,
                    help="feed token ids through the model step by step and write logits (options of bin/trace_run)")
+    sub.add_parser("bench", add_help=False,
+                   help="time one kernel alone: attention_decode | attention_prefill | gemm_small_m | gemm_tcgen05 "
+                        "(options of python -m rllm_b200.kernels.microbench)")
     r = sub.add_parser("init-random", help="write a model folder with random weights")
     r.add_argument("model", help="folder to write")
     r.add_argument("--config", required=True, help="config.json to build the model from")
@@ -130,6 +135,8 @@ def cmd_generate(args) -> int:
                              presence_penalty=args.presence_penalty,
                              frequency_penalty=args.frequency_penalty, max_tokens=args.max_tokens,
                              ignore_eos=args.ignore_eos, logprobs=args.logprobs, n=args.n,
+                             stop_token_ids=[int(x) for x in args.stop_token_ids.replace(" ", "").split(",") if x],
+                             min_tokens=args.min_tokens,
                              seed=None if args.seed is None else args.seed + i)
               for i in range(len(prompts))]
     t0 = time.time()
@@ -173,6 +180,9 @@ def main(argv=None) -> int:
         # trace replay (the program behind bin/trace_run) takes its own options: --model --dtype --out --max-tokens
         from .engine.replay import main as replay_main
         return replay_main(argv[1:])
+    if argv and argv[0] == "bench":
+        from .kernels.microbench import main as bench_main
+        return bench_main(argv[1:])
     args = build_parser().parse_args(argv)
     if args.command == "generate":
         return cmd_generate(args)

@@ -307,6 +307,16 @@ def test_command_line(model_dirs, capsys):
     plain = pl.read_model_dir(model_dirs["A"])
     assert [l["token_ids"] for l in lines] == [plain.greedy([5, 6, 7], 4), plain.greedy([9, 10], 4)]
     assert lines[0]["finish_reason"] == "length" and lines[0]["usage"]["total_tokens"] == 7
+    # a stop token ends the request at its first appearance
+    want = plain.greedy([5, 6, 7], 8)
+    stop = want[2]
+    first = want.index(stop)
+    code = main(["generate", model_dirs["A"], "--prompt-ids", "5,6,7", "--max-tokens", "8", "--temperature", "0",
+                 "--dtype", "fp32", "--num-gpu-blocks", "32", "--max-num-seqs", "4", "--ignore-eos",
+                 "--stop-token-ids", f"{stop}", "--json"])
+    assert code == 0
+    line = json.loads(capsys.readouterr().out.strip())
+    assert line["token_ids"] == want[:first + 1] and line["finish_reason"] == "stop"
     # two samples of a prompt, each from a stream of its own
     code = main(["generate", model_dirs["A"], "--prompt-ids", "5,6,7,8,9", "--max-tokens", "6", "--temperature", "1.0",
                  "-n", "2", "--seed", "11", "--dtype", "fp32", "--num-gpu-blocks", "32", "--max-num-seqs", "4",
