@@ -484,6 +484,38 @@ def test_mma_attention_finds_one_far_key(ops, err, kind):
         assert rel_err(out, want) <= tol(dt), target
 
 
+@pytest.mark.parametrize("kind,d", [("decode", 64), ("decode", 128), ("tcgen05", 64), ("tcgen05", 128), ("prefill", 64)])
+def test_attention_finds_one_key_among_forty_thousand(ops, err, kind, d):
+    """A context of 40,003 keys in 2,501 pages scattered over the cache (313 tiles of 128 keys, 1,251 chunks of
+    a decode warp): one key at a time is made to dominate, at the very start, around 2^15, at tile and page
+    edges in the middle and at the end; the output must be its value for every query row."""
+    dt = torch.bfloat16
+    nq, nkv, page = (4, 2, 16) if d == 128 else (8, 2, 16)
+    n = 40_003
+    m = 1 if kind == "decode" else 37
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, [n], [m], pages=2600, seed=12)
+    seq_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
+    q_start = torch.tensor([0, m], dtype=torch.int32, device=DEV)
+    kc_d, vc_d, table_d = kc.to(DEV), vc.to(DEV), table.to(DEV)
+    qq = qs[0].clone()
+    qq[:, :, 3] = 30.0
+    q = qq.reshape(m, nq * d).to(DEV)
+    for target in (0, 1, 127, 128, 4095, 4096, 20_000, 32_767, 32_768, 32_769, 39_935, 39_936, n - m - 1, n - m):
+        kc2 = kc_d.clone()
+        pg = int(table[0, target // page])
+        kc2[pg, :, target % page] = 0
+        kc2[pg, :, target % page, 3] = 30.0
+        out = torch.zeros_like(q)
+        if kind == "decode":
+            ops.attention_decode_bf16(q, nq * d, out, kc2, vc_d, table_d, seq_lens, 1, n, nq, nkv, d, 0, 1.0, err)
+        else:
+            fn = ops.attention_prefill_tcgen05 if kind == "tcgen05" else ops.attention_prefill_bf16
+            fn(q, nq * d, out, kc2, vc_d, table_d, q_start, seq_lens, 0, 1, m, nq, nkv, d, 0, 1.0, err)
+        want = vs[0][target].repeat_interleave(nq // nkv, dim=0).reshape(1, nq * d).expand(m, -1)
+        assert rel_err(out, want) <= tol(dt), target
+    assert int(err.item()) == 0
+
+
 @pytest.mark.parametrize("nq,nkv,d,rd,page,window", [(8, 2, 64, 64, 16, 0), (3, 1, 32, 16, 8, 0), (4, 4, 128, 128, 16, 40),
                                                      (12, 2, 16, 16, 4, 0), (24, 8, 128, 128, 16, 0), (6, 2, 128, 64, 32, 0)])
 def test_decode_with_fused_rotation_and_cache_write(ops, err, nq, nkv, d, rd, page, window):

@@ -173,42 +173,44 @@ def test_decode_steps_of_32_and_64_rows_in_bfloat16_follow_float32(folder):
     assert bool((a.argmax(dim=1) == b.argmax(dim=1))[clear].all())
 
 
-def test_a_long_prompt_in_portions_and_decoding_behind_it_in_bfloat16_follow_float32(folder):
-    """One request of 6,100 tokens in portions of 2,048 (prompt attention over up to 48 key tiles a row, the
-    later portions with thousands of keys of context before them), a second, short request beside it, then
-    decode steps of both (decode attention with 48 chunks in 12 CTAs a kv head for the long one).  Rows of the
-    bfloat16 path against the float32 path."""
+@pytest.mark.parametrize("n_long,portion", [(6100, 2048), (33_000, 4096)])
+def test_a_long_prompt_in_portions_and_decoding_behind_it_in_bfloat16_follow_float32(folder, n_long, portion):
+    """One request of 6,100 (33,000) tokens in portions of 2,048 (4,096): prompt attention over up to 48 (258)
+    key tiles a row, the later portions with thousands of keys of context before them; a second, short
+    request beside it; then decode steps of both (decode attention with 48 (258) chunks a kv head for the
+    long one).  Rows of the bfloat16 path against the float32 path."""
     from rllm_b200.engine.runner import StepEntry
     rng = np.random.default_rng(21)
-    long_p = [int(t) for t in rng.integers(0, V, size=6100)]
+    long_p = [int(t) for t in rng.integers(0, V, size=n_long)]
     short_p = [int(t) for t in rng.integers(0, V, size=37)]
     feed = rng.integers(0, V, size=(6, 2))
     rows = {}
     for dt in ("fp32", "bf16"):
-        llm = _llm(folder, dt, max_num_seqs=4, max_num_batched_tokens=4096, num_gpu_blocks=420, max_model_len=8192)
+        llm = _llm(folder, dt, max_num_seqs=4, max_num_batched_tokens=portion + 64, num_gpu_blocks=(n_long + 8) // 16 + 8,
+                   max_model_len=n_long + 64)
         eng, runner = llm.engine, llm.engine.runner
-        for k, n in (("long", 6100 + 8), ("short", 37 + 8)):
+        for k, n in (("long", n_long + 8), ("short", 37 + 8)):
             eng.cache.admit(k)
             assert eng.cache.ensure(k, 0, n)
         got = []
-        for a in range(0, 6100, 2048):
-            part = long_p[a:a + 2048]
+        for a in range(0, n_long, portion):
+            part = long_p[a:a + portion]
             entries = [StepEntry("long", part, a, [0, len(part) // 2, len(part) - 1])]
-            if a == 2048:
+            if a == portion:
                 entries.append(StepEntry("short", short_p, 0, [len(short_p) - 1]))
             got.append(runner.step(entries).float().cpu())
         for i in range(6):
-            entries = [StepEntry("long", [int(feed[i][0])], 6100 + i, [0]), StepEntry("short", [int(feed[i][1])], 37 + i, [0])]
+            entries = [StepEntry("long", [int(feed[i][0])], n_long + i, [0]), StepEntry("short", [int(feed[i][1])], 37 + i, [0])]
             got.append(runner.step(entries).float().cpu())
         runner.check_errors()
         rows[dt] = torch.cat(got)
         del llm, eng, runner
         torch.cuda.empty_cache()
     a, b = rows["fp32"].double(), rows["bf16"].double()
-    assert a.shape == (3 * 3 + 1 + 12, V)
+    assert a.shape == (3 * -(-n_long // portion) + 1 + 12, V)
     err = (a - b).abs().amax(dim=1) / a.abs().amax(dim=1)
     same = float((a.argmax(dim=1) == b.argmax(dim=1)).float().mean())
-    print(f"real widths, 6,100 tokens: bfloat16 against float32 worst {float(err.max()):.3e}, mean {float(err.mean()):.3e}, "
+    print(f"real widths, {n_long} tokens: bfloat16 against float32 worst {float(err.max()):.3e}, mean {float(err.mean()):.3e}, "
           f"same argmax {same:.3f}")
     assert float(err.max()) <= 2.5e-2, err
     top = torch.topk(a, 2, dim=1).values
