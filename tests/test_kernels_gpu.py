@@ -484,6 +484,67 @@ def test_mma_attention_finds_one_far_key(ops, err, kind):
         assert rel_err(out, want) <= tol(dt), target
 
 
+@pytest.mark.parametrize("kind,d,dt", [("simt", 48, torch.float32), ("simt", 64, torch.bfloat16), ("prefill", 64, torch.bfloat16),
+                                       ("tcgen05", 64, torch.bfloat16), ("tcgen05", 128, torch.bfloat16),
+                                       ("decode", 64, torch.bfloat16), ("decode", 128, torch.bfloat16)])
+def test_a_dominant_key_at_the_windows_edge(ops, err, kind, d, dt):
+    """A window of 129 keys over a context of 700: the key that is made to dominate lies just outside or just
+    inside the window of the first and of the last query row, and at the tile and page edges between; a row
+    that sees it returns its value, a row that does not must show no trace of it.  The pages that lie
+    wholly ahead of every row's window are given back (-1 in the block table) and hold NaN."""
+    nq, nkv, page, window, n = (4, 2, 16, 129, 700) if d == 128 else (6, 2, 16, 129, 700)
+    m = 1 if kind == "decode" else 40
+    ks, vs, qs, table, kc, vc, positions, token_seq = paged_case(dt, nq, nkv, d, page, [n], [m], pages=64, seed=17)
+    first_seen = (n - m) - window + 1                       # the first key that the first row sees
+    for b in range(first_seen // page):                     # pages wholly ahead of it
+        pg = int(table[0, b])
+        kc[pg] = float("nan")
+        vc[pg] = float("nan")
+        table[0, b] = -1
+    seq_lens = torch.tensor([n], dtype=torch.int32, device=DEV)
+    q_start = torch.tensor([0, m], dtype=torch.int32, device=DEV)
+    kc_d, vc_d, table_d = kc.to(DEV), vc.to(DEV), table.to(DEV)
+    qq = qs[0].clone()
+    qq[:, :, 3] = 30.0
+    q = qq.reshape(m, nq * d).to(DEV)
+    pos = torch.arange(n - m, n)
+    targets = sorted({t for p in (n - m, n - 1) for t in (p - window, p - window + 1, p - window + 2, p)}
+                     | {first_seen + 16 - first_seen % 16, 639, 640, n - m - 1, n - 20})
+    for target in targets:
+        if target < first_seen - first_seen % page:         # its page has been given back
+            continue
+        kc2, k2 = kc_d.clone(), ks[0].clone()
+        pg = int(table[0, target // page])
+        assert pg >= 0
+        kc2[pg, :, target % page] = 0
+        kc2[pg, :, target % page, 3] = 30.0
+        k2[target] = 0
+        k2[target, :, 3] = 30.0
+        out = torch.zeros_like(q)
+        if kind == "decode":
+            ops.attention_decode_bf16(q, nq * d, out, kc2, vc_d, table_d, seq_lens, 1, n, nq, nkv, d, window, 1.0, err)
+        elif kind == "simt":
+            ops.attention_simt(q, nq * d, out, kc2, vc_d, table_d, positions.to(DEV), token_seq.to(DEV),
+                               nq, nkv, d, window, 1.0, err)
+        else:
+            fn = ops.attention_prefill_tcgen05 if kind == "tcgen05" else ops.attention_prefill_bf16
+            fn(q, nq * d, out, kc2, vc_d, table_d, q_start, seq_lens, 0, 1, m, nq, nkv, d, window, 1.0, err)
+        k_ref, v_ref = k2.double(), vs[0].double()
+        k_ref[:first_seen - first_seen % page] = 0           # never seen by any row: any finite value will do
+        v_ref[:first_seen - first_seen % page] = 0
+        want = pl.attention(qq.double(), k_ref, v_ref, pos, window=window, scale=1.0)
+        sees = (pos - window + 1 <= target) & (target <= pos)
+        # float32: a score s is rounded to 2^-24 |s| before its exponential is taken, and the scores here are
+        # large by construction (the rows that do not see the key still multiply by q's 30)
+        smax = float(torch.einsum("mhd,nhd->mhn", qq.double(), k_ref.repeat_interleave(nq // nkv, dim=1)).abs().max())
+        bound = max(tol(dt), 4 * smax * 2.0 ** -23)
+        assert rel_err(out, want) <= bound, (target, int(sees.sum()), smax)
+        if sees.any():                                        # and the rows that see it return its value
+            val = vs[0][target].repeat_interleave(nq // nkv, dim=0).reshape(1, nq * d).double()
+            assert rel_err(out[sees.to(out.device)], val.expand(int(sees.sum()), -1)) <= tol(dt), target
+    assert int(err.item()) == 0
+
+
 @pytest.mark.parametrize("kind,d", [("decode", 64), ("decode", 128), ("tcgen05", 64), ("tcgen05", 128), ("prefill", 64)])
 def test_attention_finds_one_key_among_forty_thousand(ops, err, kind, d):
     """A context of 40,003 keys in 2,501 pages scattered over the cache (313 tiles of 128 keys, 1,251 chunks of
