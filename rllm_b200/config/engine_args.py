@@ -31,6 +31,7 @@ class EngineArgs:
     long_prefill_token_threshold: int = 2048
     enable_chunked_prefill: bool = True
     enable_cuda_graphs: bool = True
+    step_row_multiple: int = 128         # this engine's own: see Scheduler._trim_to_row_multiple; 0 = off
     seed: int = 0
 
     def validate(self) -> None:
@@ -49,6 +50,8 @@ class EngineArgs:
             raise ConfigError("max_model_len must be >= 1")
         if self.long_prefill_token_threshold < 0:
             raise ConfigError("long_prefill_token_threshold must be >= 0")
+        if self.step_row_multiple < 0:
+            raise ConfigError("step_row_multiple must be >= 0")
         normalize_dtype_name(self.dtype)
 
     def run_dtype(self, model_dtype: str) -> str:

@@ -153,7 +153,8 @@ class EngineCore:
         self.scheduler = Scheduler(SchedulerConfig(
             max_num_seqs=self.args.max_num_seqs, max_num_batched_tokens=self.args.max_num_batched_tokens,
             long_prefill_token_threshold=self.args.long_prefill_token_threshold,
-            enable_chunked_prefill=self.args.enable_chunked_prefill, max_model_len=self.max_model_len),
+            enable_chunked_prefill=self.args.enable_chunked_prefill, max_model_len=self.max_model_len,
+            step_row_multiple=self.args.step_row_multiple),
             self.cache)
         self.eos_token_ids = tuple(spec.eos_token_ids)
         self._arrivals = itertools.count()

@@ -7,7 +7,8 @@ token budget lasts, fewer than ``max_num_seqs`` run and a state slot is free.
 A prompt is cut into portions under the step's token budget
 (``max_num_batched_tokens``) and the portion cap
 (``long_prefill_token_threshold``), anywhere, and continues over as many steps
-as it needs.  This is the reference's order
+as it needs.  A step that ends a few rows over a multiple of the products' row
+tile gives those rows back (``step_row_multiple``, this engine's own).  This is the reference's order
 (crates/rllm-scheduler/src/scheduler.rs:175-233; running :328-397, waiting
 :402-532, budgets :480-495), except that there a prompt's later portions are
 never scheduled as portions (:355-382) and a token is sampled after every
@@ -126,6 +127,7 @@ class SchedulerConfig:
     long_prefill_token_threshold: int = 2048
     enable_chunked_prefill: bool = True
     max_model_len: int = 4096
+    step_row_multiple: int = 0          # > 0: a step of many rows is cut down to a multiple of this many (see schedule)
 
 
 class Scheduler:
@@ -311,12 +313,33 @@ class Scheduler:
             self.running.sort(key=lambda r: r.arrival)
             out.scheduled.append(Scheduled(req, req.num_computed, n, whole))
             budget -= n
+        self._trim_to_row_multiple(out)
         for s in out.scheduled:
             if s.num_tokens == 1 and s.start >= len(s.request.prompt_token_ids):
                 out.num_decode_tokens += 1
             else:
                 out.num_prefill_tokens += s.num_tokens
         return out
+
+    def _trim_to_row_multiple(self, out: SchedulerOutput) -> None:
+        """The matrix products of a step work on tiles of ``step_row_multiple`` rows (128 for the tensor-core
+        kernels), so a 512-token portion beside 15 decoding requests costs five row tiles where 512 rows cost
+        four (measured on the products of a layer: 7 to 21 % more time for 3 % more tokens).  Where a step of
+        at least two tiles ends up to a quarter tile over a multiple, the overhang is taken off a prompt
+        portion that is not its prompt's last (its request samples nothing in this step either way, and the
+        tokens come with its next portion).  The pages that were set aside for them stay with the request."""
+        m = self.config.step_row_multiple
+        total = out.total_tokens
+        if m <= 0 or total < 2 * m:
+            return
+        over = total % m
+        if over == 0 or over > m // 4:
+            return
+        for i in range(len(out.scheduled) - 1, -1, -1):
+            s = out.scheduled[i]
+            if not s.want_logits and s.num_tokens > over and s.start + s.num_tokens < s.request.num_tokens:
+                out.scheduled[i] = Scheduled(s.request, s.start, s.num_tokens - over, False)
+                return
 
     # ------------------------------------------------------------------
     def after_step(self, out: SchedulerOutput) -> None:

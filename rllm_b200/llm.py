@@ -27,7 +27,7 @@ class LLM:
                  block_size: int = 16, num_gpu_blocks: Optional[int] = None,
                  long_prefill_token_threshold: int = 2048, enable_chunked_prefill: bool = True,
                  enable_cuda_graphs: bool = True, random_weights: bool = False, seed: int = 0,
-                 device: Optional[str] = None, draw_on_device: bool = False):
+                 device: Optional[str] = None, draw_on_device: bool = False, step_row_multiple: int = 128):
         self.args = EngineArgs(dtype=dtype, max_model_len=max_model_len, max_num_seqs=max_num_seqs,
                                max_num_batched_tokens=max_num_batched_tokens,
                                gpu_memory_utilization=gpu_memory_utilization,
@@ -35,7 +35,8 @@ class LLM:
                                num_gpu_blocks=num_gpu_blocks,
                                long_prefill_token_threshold=long_prefill_token_threshold,
                                enable_chunked_prefill=enable_chunked_prefill,
-                               enable_cuda_graphs=enable_cuda_graphs, seed=seed)
+                               enable_cuda_graphs=enable_cuda_graphs, seed=seed,
+                               step_row_multiple=step_row_multiple)
         self.args.validate()
         self.config, self.model = load_model(model, dtype=dtype, device=device,
                                              random_weights=random_weights, seed=seed,

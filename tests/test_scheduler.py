@@ -66,6 +66,64 @@ def test_portion_cap_and_logits_only_at_the_end():
     assert seen == [[(0, 16, False)], [(16, 16, False)], [(32, 8, True)]]
 
 
+def test_a_step_a_few_rows_over_a_row_tile_gives_them_back():
+    """Five decoding requests beside a 64-token portion are 69 rows, five over two tiles of 32: the portion
+    shrinks to 59.  Nothing is cut where the step is under two tiles, lands on a multiple, is more than a
+    quarter tile over, or where the only portion is its prompt's last."""
+    s, cache = make(pages=256, max_num_batched_tokens=256, long_prefill_token_threshold=64, step_row_multiple=32)
+    for i in range(5):
+        s.add_request(req(i, 3, max_tokens=40))
+    run_step(s)                                               # five prompts of 3 tokens: 15 rows, under two tiles
+    s.add_request(req(9, 300, max_tokens=4))
+    out = run_step(s)
+    assert [(x.request.request_id, x.start, x.num_tokens, x.want_logits) for x in out.scheduled][-1] == ("r9", 0, 59, False)
+    assert out.total_tokens == 64 and out.num_decode_tokens == 5 and out.num_prefill_tokens == 59
+    out = run_step(s)                                         # the rows come with the next portion
+    assert [(x.start, x.num_tokens) for x in out.scheduled][-1] == (59, 59) and out.total_tokens == 64
+    # on a multiple already: 5 + 27 = 32 rows is under two tiles; 64 rows exactly stay
+    s2, _ = make(pages=256, max_num_batched_tokens=256, long_prefill_token_threshold=64, step_row_multiple=32)
+    s2.add_request(req(0, 200, max_tokens=4))
+    assert [(x.start, x.num_tokens) for x in run_step(s2).scheduled] == [(0, 64)]
+    # more than a quarter tile over: 64 + 9 decoding requests = 73 = 2 * 32 + 9 > 8
+    s3, _ = make(pages=256, seqs=16, max_num_batched_tokens=256, long_prefill_token_threshold=64, step_row_multiple=32)
+    for i in range(9):
+        s3.add_request(req(i, 2, max_tokens=40))
+    run_step(s3)
+    s3.add_request(req(20, 300, max_tokens=4))
+    out = run_step(s3)
+    assert out.total_tokens == 73 and out.scheduled[-1].num_tokens == 64
+    # the portion is the prompt's last: its request samples in this step and keeps its rows
+    s4, _ = make(pages=256, max_num_batched_tokens=256, long_prefill_token_threshold=64, step_row_multiple=32)
+    for i in range(5):
+        s4.add_request(req(i, 3, max_tokens=40))
+    run_step(s4)
+    s4.add_request(req(9, 64, max_tokens=4))
+    out = run_step(s4)
+    assert out.total_tokens == 69 and out.scheduled[-1].want_logits
+
+
+@pytest.mark.parametrize("seed", range(3))
+def test_random_workloads_with_a_row_multiple_finish_too(seed):
+    rng = random.Random(40 + seed)
+    s, cache = make(pages=80, page=8, seqs=6, max_num_batched_tokens=96, long_prefill_token_threshold=40,
+                    step_row_multiple=16, prefix=bool(seed % 2))
+    todo = [req(i, rng.randint(1, 150), max_tokens=rng.randint(1, 30), first=1000 * (i % 3)) for i in range(16)]
+    done, steps, cut = {}, 0, 0
+    while todo or s.has_work():
+        for _ in range(rng.randint(0, 2)):
+            if todo:
+                r = todo.pop(0)
+                s.add_request(r)
+                done[r.request_id] = r
+        out = run_step(s)
+        assert out.total_tokens <= 96 and len(s.running) <= 6
+        cut += out.total_tokens >= 32 and out.total_tokens % 16 == 0
+        steps += 1
+        assert steps < 5000
+    assert all(len(r.output_token_ids) == r.max_tokens for r in done.values()) and cut > 0
+    assert cache.num_free_pages() == 80 and cache.usage()["free_slots"] == 6
+
+
 def test_max_num_seqs():
     s, _ = make(seqs=2)
     for i in range(4):
