@@ -61,6 +61,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--seed", type=int, default=None, help="sampling seed of the first prompt; prompt i uses seed+i")
     g.add_argument("--ignore-eos", action="store_true")
     g.add_argument("--stop-token-ids", default="", metavar="ID,ID", help="token ids that end a request (beside the model's EOS)")
+    g.add_argument("--bad-words-token-ids", default="", metavar="ID,ID;ID",
+                   help="token sequences, separated by ';': a sequence's last token cannot follow its first ones")
+    g.add_argument("--skip-reading-prefix-cache", action="store_true",
+                   help="compute the whole prompt even where shared pages hold a part of it")
     g.add_argument("--min-tokens", type=int, default=0, help="the model's EOS cannot be drawn before this many tokens have been generated")
     g.add_argument("--logprobs", type=int, default=None, metavar="N",
                    help="report every generated token's log-probability and the N likeliest tokens of its place (with --json)")
@@ -140,6 +144,9 @@ def cmd_generate(args) -> int:
                              ignore_eos=args.ignore_eos, logprobs=args.logprobs, n=args.n,
                              stop_token_ids=[int(x) for x in args.stop_token_ids.replace(" ", "").split(",") if x],
                              min_tokens=args.min_tokens,
+                             bad_words_token_ids=[[int(x) for x in w.split(",") if x]
+                                                  for w in args.bad_words_token_ids.replace(" ", "").split(";") if w],
+                             skip_reading_prefix_cache=args.skip_reading_prefix_cache,
                              seed=None if args.seed is None else args.seed + i)
               for i in range(len(prompts))]
     t0 = time.time()

@@ -216,7 +216,7 @@ class Scheduler:
         finds them.  The running request makes progress whatever happens to this one, and if it is
         preempted or ends the test fails and the request is admitted as usual."""
         mine = self._prompt_hashes(req)
-        if not mine:
+        if not mine or req.params.skip_reading_prefix_cache:
             return False
         page = self.cache.page_size
         have = self.cache.match_prefix(req.all_token_ids) // page
@@ -290,7 +290,7 @@ class Scheduler:
                 break                         # first come, first served: those behind it wait too
             tokens = req.all_token_ids
             self.cache.admit(req.request_id)
-            cached = self.cache.adopt_prefix(req.request_id, tokens)
+            cached = 0 if req.params.skip_reading_prefix_cache else self.cache.adopt_prefix(req.request_id, tokens)
             req.num_computed = cached
             n = self._portion(req, budget)
             if not self.running and self.config.enable_chunked_prefill and n > 1:

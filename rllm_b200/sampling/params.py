@@ -3,9 +3,14 @@
 
 Kept: n, presence_penalty, frequency_penalty, repetition_penalty, temperature,
 top_p, top_k, min_p, seed, stop_token_ids, ignore_eos, max_tokens, min_tokens,
-logit_bias, allowed_token_ids.  Text-side options (stop strings, detokenize,
-bad_words, structured outputs) have no meaning for an engine that works on
-token ids.  ``n`` > 1 asks for n samples of one prompt (the reference checks the
+logit_bias, allowed_token_ids, skip_reading_prefix_cache.  Text-side options
+(stop strings, detokenize, structured outputs) have no meaning for an engine
+that works on token ids; ``bad_words`` is taken as token sequences
+(``bad_words_token_ids``, the form the reference's sampler receives,
+crates/rllm-sampling/src/sampler.rs:20): the last token of a sequence cannot
+be drawn while the tokens before it are the context's last ones (the
+reference masks the last token whatever the context, :95-98, so a two-token
+word would ban its second token everywhere).  ``n`` > 1 asks for n samples of one prompt (the reference checks the
 field, :91 and :113, and then generates one): the prompt is computed once and
 the samples branch off before its last token, each with a random stream of its
 own.  ``logprobs`` = N asks for the
@@ -40,6 +45,8 @@ class SamplingParams:
     logit_bias: Dict[int, float] = field(default_factory=dict)
     allowed_token_ids: Optional[Sequence[int]] = None
     logprobs: Optional[int] = None
+    bad_words_token_ids: Sequence[Sequence[int]] = ()
+    skip_reading_prefix_cache: bool = False        # compute the whole prompt even where shared pages hold a part of it
 
     def validate(self) -> None:
         if self.n < 1:
@@ -64,6 +71,8 @@ class SamplingParams:
             raise InvalidSamplingParams("min_tokens must be >= 0")
         if self.logprobs is not None and not 0 <= self.logprobs <= 32:
             raise InvalidSamplingParams("logprobs must be in [0, 32]")
+        if any(len(w) == 0 for w in self.bad_words_token_ids):
+            raise InvalidSamplingParams("a bad word needs at least one token")
 
     @property
     def greedy(self) -> bool:
@@ -73,4 +82,4 @@ class SamplingParams:
     @property
     def edits_logits(self) -> bool:
         return bool(self.logit_bias) or self.repetition_penalty != 1.0 or self.frequency_penalty != 0.0 \
-            or self.presence_penalty != 0.0 or bool(self.allowed_token_ids) or self.min_tokens > 0
+            or self.presence_penalty != 0.0 or bool(self.allowed_token_ids) or self.min_tokens > 0 or bool(self.bad_words_token_ids)

@@ -2,8 +2,9 @@
 
 The order of the reference's pipeline is kept
 (crates/rllm-sampling/src/sampler.rs:62-169): logit bias, repetition,
-frequency and presence penalties, allowed-token mask, EOS suppression below
-``min_tokens``; then greedy, or temperature, top-k, top-p, min-p and a draw.
+frequency and presence penalties, bad words, allowed-token mask, EOS
+suppression below ``min_tokens`` (the three masks set logits to -inf, so their
+order among themselves changes nothing); then greedy, or temperature, top-k, top-p, min-p and a draw.
 The kernels are in ``kernels/csrc/sampling.cu``, which also lists the
 deliberate differences (per-request Philox stream, exact fixed-point mass,
 ties).  The host's part is to turn the requests' histories and options into
@@ -86,6 +87,12 @@ class Sampler:
                 for t in row.eos_token_ids:
                     sup_rows.append(r)
                     sup_tok.append(int(t))
+            for word in p.bad_words_token_ids:
+                # the word's last token, where the context ends with the tokens before it
+                k = len(word) - 1
+                if k == 0 or (len(row.context) >= k and list(row.context[len(row.context) - k:]) == [int(t) for t in word[:k]]):
+                    sup_rows.append(r)
+                    sup_tok.append(int(word[-1]))
         if e_rows:
             ops.logit_edits(logits, self._dev(np.asarray(e_rows, np.int32)), self._dev(np.asarray(e_tok, np.int32)),
                             self._dev(np.asarray(e_cnt, np.int32)), self._dev(np.asarray(e_bias, np.float32)),

@@ -296,6 +296,40 @@ def test_requests_beyond_the_limits_are_refused(model_dirs):
         llm.add_request([1, 2, 256])
 
 
+def test_bad_words_keep_their_last_token_out_behind_their_first_ones(model_dirs):
+    """Greedy generation with a one-token word (never drawn) and a two-token word (its second token is not
+    drawn behind its first, but elsewhere it is), against the plain implementation with the same rule."""
+    from rllm_b200 import SamplingParams
+    plain = pl.read_model_dir(model_dirs["A"])
+    prompt = [5, 6, 7, 8]
+    free = plain.greedy(prompt, 10)
+    one = [free[1]]                               # the token that greedy decoding would draw second
+    two = [free[3], free[4]]                      # and the pair that it would draw fourth and fifth
+    words = [one, two]
+
+    def plain_with_rule(n):
+        toks, out = list(prompt), []
+        for _ in range(n):
+            row = plain.logits(toks)[-1].clone()
+            for w in words:
+                k = len(w) - 1
+                if k == 0 or toks[-k:] == w[:k]:
+                    row[w[-1]] = float("-inf")
+            t = int(torch.argmax(row))
+            out.append(t)
+            toks.append(t)
+        return out
+
+    want = plain_with_rule(10)
+    assert one[0] not in want and want != free
+    llm = make_llm(model_dirs, "A")
+    got = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True,
+                                                bad_words_token_ids=words))[0].outputs[0].token_ids
+    assert got == want
+    for a, b in zip([prompt[-1]] + got, got):
+        assert not (a == two[0] and b == two[1])
+
+
 def test_command_line(model_dirs, capsys):
     from rllm_b200.cli import main
     import json

@@ -22,8 +22,21 @@ def rows_for(params_list, seeds, gen_index, contexts=None, eos=()):
             for i, (p, s, g) in enumerate(zip(params_list, seeds, gen_index))]
 
 
+def banned(p, context):
+    """Tokens that the bad words rule out behind ``context``: a word's last token, if the tokens before it are
+    the context's last ones (the plain restatement; the reference masks it whatever the context,
+    crates/rllm-sampling/src/sampler.rs:95-98)."""
+    out = []
+    for w in p.bad_words_token_ids:
+        k = len(w) - 1
+        if k == 0 or list(context[-k:]) == list(w[:k]) and len(context) >= k:
+            out.append(int(w[-1]))
+    return out
+
+
 def plain_pick(logits_row, p, seed, gen_index, context=(), eos=()):
-    suppress = eos if (p.min_tokens > 0 and gen_index < p.min_tokens) else ()
+    suppress = list(eos) if (p.min_tokens > 0 and gen_index < p.min_tokens) else []
+    suppress += banned(p, context)
     x = pl.process_logits(logits_row, context=context, logit_bias=p.logit_bias,
                           repetition_penalty=p.repetition_penalty, frequency_penalty=p.frequency_penalty,
                           presence_penalty=p.presence_penalty, allowed_token_ids=p.allowed_token_ids,
@@ -168,6 +181,9 @@ def test_processors_match_the_plain_ones(sampler):
             frequency_penalty=[0.0, 0.4][(r // 2) % 2], presence_penalty=[0.0, 1.5][(r // 3) % 2],
             logit_bias={3: 5.0, 700: -2.0} if r % 4 == 0 else {},
             allowed_token_ids=list(range(0, V, 3)) if r % 5 == 0 else None,
+            # a one-token word, a word whose first tokens are the context's last ones, and one that does not fit
+            bad_words_token_ids=[[int(np.argmax(logits[r]))], contexts[r][-2:] + [int(np.argsort(logits[r])[-2])],
+                                 [contexts[r][-1] + 1, int(np.argsort(logits[r])[-3])]] if r % 3 == 1 else (),
             min_tokens=4 if r % 2 else 0))
     seeds, gen = list(range(R)), [r % 6 for r in range(R)]
     dev = torch.from_numpy(logits).to(DEV)
@@ -178,7 +194,12 @@ def test_processors_match_the_plain_ones(sampler):
     dev = torch.from_numpy(logits).to(DEV)
     sampler.apply_processors(dev, rows_for(ps, seeds, gen, contexts, eos))
     for r in range(R):
-        suppress = eos if (ps[r].min_tokens > 0 and gen[r] < ps[r].min_tokens) else ()
+        suppress = list(eos) if (ps[r].min_tokens > 0 and gen[r] < ps[r].min_tokens) else []
+        suppress += banned(ps[r], contexts[r])
+        if ps[r].bad_words_token_ids:
+            top3 = [int(t) for t in np.argsort(logits[r])[-3:]]
+            assert top3[2] in suppress and top3[0] not in banned(ps[r], contexts[r])
+            assert (top3[1] in suppress) == (len(contexts[r]) >= 2)
         x = pl.process_logits(logits[r], context=contexts[r], logit_bias=ps[r].logit_bias,
                               repetition_penalty=ps[r].repetition_penalty,
                               frequency_penalty=ps[r].frequency_penalty,
@@ -194,7 +215,7 @@ def test_params_are_validated():
     assert SamplingParams().max_tokens == 16 and SamplingParams().temperature == 1.0
     for bad in (dict(temperature=-1.0), dict(top_p=1.5), dict(n=0), dict(n=2, temperature=0.0), dict(n=2, top_k=1),
                 dict(repetition_penalty=0.0),
-                dict(presence_penalty=3.0), dict(logprobs=-1), dict(logprobs=33)):
+                dict(presence_penalty=3.0), dict(logprobs=-1), dict(logprobs=33), dict(bad_words_token_ids=[[1], []])):
         with pytest.raises(InvalidSamplingParams):
             SamplingParams(**bad).validate()
 

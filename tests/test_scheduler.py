@@ -220,6 +220,18 @@ def test_prefix_hits_skip_computed_pages():
     assert [(x.start, x.num_tokens) for x in out.scheduled] == [(16, 3)] and s.prefix_hit_tokens == 16
 
 
+def test_a_request_may_refuse_the_shared_pages():
+    """crates/rllm-scheduler/src/scheduler.rs:565-580: ``skip_reading_prefix_cache`` computes the whole prompt."""
+    s, cache = make(prefix=True)
+    s.add_request(Request("a", list(range(50, 90)), SamplingParams(max_tokens=1), 0, 0, 1))
+    run_step(s)
+    s.add_request(Request("b", list(range(50, 90)) + [1], SamplingParams(max_tokens=1, skip_reading_prefix_cache=True), 1, 1, 1))
+    s.add_request(Request("c", list(range(50, 90)) + [2], SamplingParams(max_tokens=1), 2, 2, 1))
+    out = run_step(s)
+    assert [(x.request.request_id, x.start, x.num_tokens) for x in out.scheduled] == [("b", 0, 41), ("c", 32, 9)]
+    assert s.prefix_hit_tokens == 32
+
+
 @pytest.mark.parametrize("seed", range(5))
 def test_random_workloads_finish_within_limits(seed):
     """Never more than max_num_seqs running or max_num_batched_tokens in a step;
