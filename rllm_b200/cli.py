@@ -75,6 +75,8 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--long-prefill-token-threshold", type=int, default=2048)
     g.add_argument("--gpu-memory-utilization", type=_gpu_util, default=0.9)
     g.add_argument("--enable-prefix-caching", type=_bool, nargs="?", const=True, default=True)
+    g.add_argument("--scheduling-policy", choices=["fcfs", "priority"], default="fcfs")
+    g.add_argument("--priorities", default="", metavar="P,P", help="a priority for each prompt (priority policy: larger first)")
     g.add_argument("--step-row-multiple", type=int, default=128,
                    help="a step that ends up to a quarter of this many rows over a multiple of it gives them back (0: off)")
     g.add_argument("--block-size", type=int, default=16)
@@ -135,7 +137,7 @@ def cmd_generate(args) -> int:
               enable_prefix_caching=args.enable_prefix_caching, block_size=args.block_size,
               num_gpu_blocks=args.num_gpu_blocks,
               long_prefill_token_threshold=args.long_prefill_token_threshold,
-              step_row_multiple=args.step_row_multiple,
+              step_row_multiple=args.step_row_multiple, scheduling_policy=args.scheduling_policy,
               random_weights=args.random_weights, seed=args.weights_seed)
     params = [SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
                              min_p=args.min_p, repetition_penalty=args.repetition_penalty,
@@ -150,7 +152,8 @@ def cmd_generate(args) -> int:
                              seed=None if args.seed is None else args.seed + i)
               for i in range(len(prompts))]
     t0 = time.time()
-    outs = llm.generate(prompts, params)
+    prios = [int(x) for x in args.priorities.replace(" ", "").split(",") if x] or None
+    outs = llm.generate(prompts, params, priorities=prios)
     dt = time.time() - t0
     n_out = sum(o.usage.completion_tokens for o in outs)
     def sample(c):

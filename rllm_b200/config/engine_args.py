@@ -32,6 +32,7 @@ class EngineArgs:
     enable_chunked_prefill: bool = True
     enable_cuda_graphs: bool = True
     step_row_multiple: int = 128         # this engine's own: see Scheduler._trim_to_row_multiple; 0 = off
+    scheduling_policy: str = "fcfs"      # or "priority" (crates/rllm-core/src/config.rs:86-98)
     seed: int = 0
 
     def validate(self) -> None:
@@ -52,6 +53,8 @@ class EngineArgs:
             raise ConfigError("long_prefill_token_threshold must be >= 0")
         if self.step_row_multiple < 0:
             raise ConfigError("step_row_multiple must be >= 0")
+        if self.scheduling_policy not in ("fcfs", "priority"):
+            raise ConfigError(f"scheduling_policy must be fcfs or priority, got {self.scheduling_policy!r}")
         normalize_dtype_name(self.dtype)
 
     def run_dtype(self, model_dtype: str) -> str:

@@ -154,7 +154,7 @@ class EngineCore:
             max_num_seqs=self.args.max_num_seqs, max_num_batched_tokens=self.args.max_num_batched_tokens,
             long_prefill_token_threshold=self.args.long_prefill_token_threshold,
             enable_chunked_prefill=self.args.enable_chunked_prefill, max_model_len=self.max_model_len,
-            step_row_multiple=self.args.step_row_multiple),
+            step_row_multiple=self.args.step_row_multiple, scheduling_policy=self.args.scheduling_policy),
             self.cache)
         self.eos_token_ids = tuple(spec.eos_token_ids)
         self._arrivals = itertools.count()
@@ -169,8 +169,9 @@ class EngineCore:
 
     # ------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None,
-                    request_id: Optional[Hashable] = None) -> Hashable:
-        """crates/rllm-engine/src/engine_core.rs:55-80."""
+                    request_id: Optional[Hashable] = None, priority: int = 0) -> Hashable:
+        """crates/rllm-engine/src/engine_core.rs:55-80.  ``priority`` counts under the priority policy only
+        (crates/rllm-core/src/request.rs:136)."""
         params = params or SamplingParams()
         params.validate()
         arrival = next(self._arrivals)
@@ -183,7 +184,7 @@ class EngineCore:
         seed = params.seed if params.seed is not None else (self.args.seed * 1000003 + arrival)
         if rid in self._families:
             raise RequestRefused(f"request id {rid!r} is in use")
-        req = Request(rid, prompt, params, arrival, seed, max_tokens, family=rid)
+        req = Request(rid, prompt, params, arrival, seed, max_tokens, family=rid, priority=int(priority))
         self.scheduler.add_request(req)
         self._prepared = None          # a step prepared ahead did not know of this request
         if params.n > 1:
@@ -210,7 +211,8 @@ class EngineCore:
         for i in range(1, fam.n):
             seed = (first.seed + i * 0x9E3779B97F4A7C15) & 0x7FFFFFFFFFFFFFFF
             child = Request(SampleId(first.request_id, i), first.prompt_token_ids, first.params,
-                            next(self._arrivals), seed, first.max_tokens, family=first.request_id, index=i)
+                            next(self._arrivals), seed, first.max_tokens, family=first.request_id, index=i,
+                            priority=first.priority)
             took = self.scheduler.add_copy(first, child, share)
             if took is not None:
                 with torch.cuda.device(self.device):

@@ -2,7 +2,9 @@
 
 Each call of ``schedule`` (1) lets every running request go on, in order of
 arrival: one token if it is decoding, the next portion of its prompt
-otherwise; (2) admits waiting requests, first come first served, while the
+otherwise; (2) admits waiting requests, first come first served (or, under the
+``priority`` policy, larger ``Request.priority`` first and arrival among equals,
+crates/rllm-scheduler/src/policy.rs:16-95), while the
 token budget lasts, fewer than ``max_num_seqs`` run and a state slot is free.
 A prompt is cut into portions under the step's token budget
 (``max_num_batched_tokens``) and the portion cap
@@ -23,9 +25,9 @@ that arrive together would all compute their common prefix).
 
 When pages run out: a waiting request is simply not admitted yet (:497-505).
 A running request that needs a page and cannot get one makes room by
-preemption (:357-375, :606-625): the newest running request (latest arrival)
-loses all its pages and its slot and goes back to the front of the waiting
-queue by arrival order; that is repeated until the page is there or the
+preemption (:357-375, :606-625): the newest running request (latest arrival; under
+the priority policy the newest of the lowest priority) loses all its pages and
+its slot and goes back into the waiting queue at its place in the queue's order; that is repeated until the page is there or the
 request that asked is itself the newest, in which case it is the one
 preempted.  A preempted request keeps its prompt and what it generated and
 computes them again when readmitted; its samples are unchanged because its
@@ -79,6 +81,7 @@ class Request:
     family: Optional[Hashable] = None    # the id under which results are reported (several samples of one prompt share it)
     index: int = 0                       # which of the family's samples this is
     pause_at: Optional[int] = None       # a portion must end at this token, if it lies ahead: copies are taken there
+    priority: int = 0                    # under the priority policy: larger values are admitted first
 
     @property
     def all_token_ids(self) -> List[int]:
@@ -128,10 +131,13 @@ class SchedulerConfig:
     enable_chunked_prefill: bool = True
     max_model_len: int = 4096
     step_row_multiple: int = 0          # > 0: a step of many rows is cut down to a multiple of this many (see schedule)
+    scheduling_policy: str = "fcfs"     # or "priority" (crates/rllm-core/src/config.rs:86-98)
 
 
 class Scheduler:
     def __init__(self, config: SchedulerConfig, cache: CacheManager):
+        if config.scheduling_policy not in ("fcfs", "priority"):
+            raise ValueError(f"scheduling_policy must be fcfs or priority, not {config.scheduling_policy!r}")
         self.config = config
         self.cache = cache
         self.waiting: List[Request] = []
@@ -159,10 +165,15 @@ class Scheduler:
         self.requests[req.request_id] = req
         self._enqueue(req)
 
+    def _queue_key(self, req: Request):
+        """The waiting queue's order: arrival, or priority (larger first) and then arrival
+        (crates/rllm-scheduler/src/policy.rs:28-40, 88-95)."""
+        return (-req.priority, req.arrival) if self.config.scheduling_policy == "priority" else (0, req.arrival)
+
     def _enqueue(self, req: Request) -> None:
         req.status = RequestStatus.WAITING
         i = 0
-        while i < len(self.waiting) and self.waiting[i].arrival < req.arrival:
+        while i < len(self.waiting) and self._queue_key(self.waiting[i]) < self._queue_key(req):
             i += 1
         self.waiting.insert(i, req)
 
@@ -263,7 +274,7 @@ class Scheduler:
                 budget -= 1
                 continue
             while not self.cache.ensure(req.request_id, req.num_computed, req.num_computed + n):
-                victim = max(self.running, key=lambda r: r.arrival)
+                victim = max(self.running, key=self._queue_key)      # the newest (of the lowest priority)
                 if victim is req and n > 1:
                     # nobody newer to take pages from: a shorter portion may still fit (a window gives
                     # pages back on the way, so the rest follows in later steps)

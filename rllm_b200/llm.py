@@ -27,7 +27,8 @@ class LLM:
                  block_size: int = 16, num_gpu_blocks: Optional[int] = None,
                  long_prefill_token_threshold: int = 2048, enable_chunked_prefill: bool = True,
                  enable_cuda_graphs: bool = True, random_weights: bool = False, seed: int = 0,
-                 device: Optional[str] = None, draw_on_device: bool = False, step_row_multiple: int = 128):
+                 device: Optional[str] = None, draw_on_device: bool = False, step_row_multiple: int = 128,
+                 scheduling_policy: str = "fcfs"):
         self.args = EngineArgs(dtype=dtype, max_model_len=max_model_len, max_num_seqs=max_num_seqs,
                                max_num_batched_tokens=max_num_batched_tokens,
                                gpu_memory_utilization=gpu_memory_utilization,
@@ -36,7 +37,7 @@ class LLM:
                                long_prefill_token_threshold=long_prefill_token_threshold,
                                enable_chunked_prefill=enable_chunked_prefill,
                                enable_cuda_graphs=enable_cuda_graphs, seed=seed,
-                               step_row_multiple=step_row_multiple)
+                               step_row_multiple=step_row_multiple, scheduling_policy=scheduling_policy)
         self.args.validate()
         self.config, self.model = load_model(model, dtype=dtype, device=device,
                                              random_weights=random_weights, seed=seed,
@@ -45,8 +46,8 @@ class LLM:
 
     # -- the reference's three calls ------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], sampling_params: Optional[SamplingParams] = None,
-                    request_id: Optional[Hashable] = None) -> Hashable:
-        return self.engine.add_request(prompt_token_ids, sampling_params, request_id)
+                    request_id: Optional[Hashable] = None, priority: int = 0) -> Hashable:
+        return self.engine.add_request(prompt_token_ids, sampling_params, request_id, priority)
 
     def step(self) -> List[RequestOutput]:
         return self.engine.step()
@@ -59,10 +60,11 @@ class LLM:
 
     # -- blocking generation ---------------------------------------------------
     def generate(self, prompt_token_ids: Sequence[Sequence[int]],
-                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None
-                 ) -> List[RequestOutput]:
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None,
+                 priorities: Optional[Sequence[int]] = None) -> List[RequestOutput]:
         """One RequestOutput per prompt, in the order of the prompts, each with all generated
-        tokens: ``outputs[i]`` is sample i of the prompt (one sample unless ``n`` > 1)."""
+        tokens: ``outputs[i]`` is sample i of the prompt (one sample unless ``n`` > 1).
+        ``priorities``: one per prompt, for the priority policy."""
         n = len(prompt_token_ids)
         if sampling_params is None or isinstance(sampling_params, SamplingParams):
             params = [sampling_params or SamplingParams()] * n
@@ -70,7 +72,10 @@ class LLM:
             params = list(sampling_params)
             if len(params) != n:
                 raise ValueError("one SamplingParams per prompt, or one for all")
-        ids = [self.add_request(p, sp) for p, sp in zip(prompt_token_ids, params)]
+        if priorities is not None and len(priorities) != n:
+            raise ValueError("one priority per prompt")
+        ids = [self.add_request(p, sp, priority=0 if priorities is None else int(priorities[i]))
+               for i, (p, sp) in enumerate(zip(prompt_token_ids, params))]
         # per request: sample index -> [tokens, log-probabilities, finish reason]
         samples = {rid: {i: [[], [], None] for i in range(sp.n)} for rid, sp in zip(ids, params)}
         while self.has_work():

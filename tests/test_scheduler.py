@@ -220,6 +220,40 @@ def test_prefix_hits_skip_computed_pages():
     assert [(x.start, x.num_tokens) for x in out.scheduled] == [(16, 3)] and s.prefix_hit_tokens == 16
 
 
+def test_priority_policy_orders_the_waiting_queue_and_picks_the_victim():
+    """crates/rllm-scheduler/src/policy.rs:16-95: larger priority first, arrival among equals; first come first
+    served ignores the field.  A preempted request goes back to its place in that order, and the request that
+    gives up its pages is the newest of the lowest priority."""
+    def admitted(policy):
+        s, _ = make(seqs=1, scheduling_policy=policy)
+        for i, pr in enumerate([0, 5, 5, 9, -1]):
+            r = req(i, 4, max_tokens=1)
+            r.priority = pr
+            s.add_request(r)
+        order = []
+        while s.has_work():
+            out = run_step(s)
+            order += [x.request.request_id for x in out.scheduled if x.start == 0]
+        return order
+    assert admitted("fcfs") == ["r0", "r1", "r2", "r3", "r4"]
+    assert admitted("priority") == ["r3", "r1", "r2", "r0", "r4"]
+    with pytest.raises(ValueError):
+        make(scheduling_policy="lifo")
+    # three requests of 16 tokens in a pool of four pages of 16: the first token that opens a page takes one from
+    # the lowest priority, not from the newest
+    s, cache = make(pages=4, page=16, seqs=4, scheduling_policy="priority")
+    for i, pr in enumerate([1, 0, 2]):
+        r = req(i, 16, max_tokens=20)
+        r.priority = pr
+        s.add_request(r)
+    out = run_step(s)
+    assert [x.request.request_id for x in out.scheduled] == ["r2", "r0", "r1"]        # admitted by priority
+    out = run_step(s)                                       # each needs a second page: only one is free
+    assert out.preempted == ["r1"] and [r.request_id for r in s.waiting] == ["r1"]
+    s.add_request(req(7, 3, max_tokens=1))                  # priority 0, arrived later: behind r1 in the queue
+    assert [r.request_id for r in s.waiting] == ["r1", "r7"]
+
+
 def test_a_request_may_refuse_the_shared_pages():
     """crates/rllm-scheduler/src/scheduler.rs:565-580: ``skip_reading_prefix_cache`` computes the whole prompt."""
     s, cache = make(prefix=True)
