@@ -296,6 +296,25 @@ def test_requests_beyond_the_limits_are_refused(model_dirs):
         llm.add_request([1, 2, 256])
 
 
+def test_priorities_decide_who_runs_first_and_change_no_token(model_dirs):
+    from rllm_b200 import SamplingParams
+    plain = pl.read_model_dir(model_dirs["A"])
+    prompts = prompts_for("A", [9, 4, 13], 5)
+    llm = make_llm(model_dirs, "A", max_num_seqs=1, scheduling_policy="priority")
+    sp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+    ids = [llm.add_request(p, sp, priority=pr) for p, pr in zip(prompts, [0, 7, 3])]
+    finished, got = [], {i: [] for i in ids}
+    while llm.has_work():
+        for out in llm.step():
+            got[out.request_id] += out.outputs[0].token_ids
+            if out.finished:
+                finished.append(out.request_id)
+    assert finished == [ids[1], ids[2], ids[0]]
+    assert [got[i] for i in ids] == [plain.greedy(p, 3) for p in prompts]
+    outs = llm.generate(prompts, sp, priorities=[1, 2, 3])
+    assert [o.outputs[0].token_ids for o in outs] == [plain.greedy(p, 3) for p in prompts]
+
+
 def test_bad_words_keep_their_last_token_out_behind_their_first_ones(model_dirs):
     """Greedy generation with a one-token word (never drawn) and a two-token word (its second token is not
     drawn behind its first, but elsewhere it is), against the plain implementation with the same rule."""
