@@ -391,6 +391,7 @@ def workload_8b(pk, windows):
 
 
 def main():
+    global SETTLE_STEPS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=DECODE_TOKENS)
@@ -402,7 +403,10 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip the other batch sizes and contexts")
     ap.add_argument("--no-workloads", action="store_true", help="skip the 3B and 8B serving workloads")
     ap.add_argument("--no-standin", action="store_true", help="skip the library-operator stand-in")
+    ap.add_argument("--settle-steps", type=int, default=SETTLE_STEPS,
+                    help="untimed decode steps of a device-timed point before its warm-up steps (0 for a short capture under a profiler)")
     args = ap.parse_args()
+    SETTLE_STEPS = max(0, args.settle_steps)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
