@@ -415,3 +415,63 @@ def test_a_copy_waits_like_a_new_request_when_nothing_can_be_taken_over():
         steps += 1
         assert steps < 200
     assert len(kid.output_token_ids) == 4 and len(other.output_token_ids) == 4 and cache.num_free_pages() == 3
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_everything_at_once_in_random_order(seed):
+    """Priorities or first come first served, a row multiple, prefix sharing, a group with a window beside one
+    that keeps every key, requests that pause before their last prompt token and hand copies on, aborts, few
+    pages: every request that is not aborted finishes with its tokens, no step is empty while work waits,
+    budgets hold, and nothing is held at the end."""
+    rng = random.Random(900 + seed)
+    windowed = seed % 2 == 1
+    needs = [KVPagesNeed(2, 16, None)] + ([KVPagesNeed(1, 16, 24)] if windowed else [])
+    pages = [40, 12] if windowed else [40]
+    cache = CacheManager(needs, 8, pages, 6, enable_prefix_caching=seed % 4 < 2)
+    budget = rng.choice([48, 96])
+    s = Scheduler(SchedulerConfig(max_num_seqs=6, max_num_batched_tokens=budget, long_prefill_token_threshold=rng.choice([0, 24, 40]),
+                                  max_model_len=4096, step_row_multiple=rng.choice([0, 16]),
+                                  scheduling_policy=rng.choice(["fcfs", "priority"])), cache)
+    todo = []
+    for i in range(18):
+        r = req(i, rng.randint(1, 120), max_tokens=rng.randint(1, 25), first=1000 * (i % 3))
+        r.priority = rng.randint(-2, 2)
+        if rng.random() < 0.3 and len(r.prompt_token_ids) > 1:
+            r.pause_at = len(r.prompt_token_ids) - 1
+        todo.append(r)
+    live, aborted, copies, steps, arrivals = {}, set(), 0, 0, 100
+    while todo or s.has_work():
+        for _ in range(rng.randint(0, 2)):
+            if todo:
+                r = todo.pop(0)
+                s.add_request(r)
+                live[r.request_id] = r
+        if live and rng.random() < 0.04:
+            victim = rng.choice(sorted(live))
+            if s.abort_request(victim):
+                aborted.add(victim)
+            live.pop(victim)
+        had_work = s.has_work()
+        out = run_step(s)
+        assert out.total_tokens <= budget and len(s.running) <= 6
+        assert len({x.request.request_id for x in out.scheduled}) == len(out.scheduled)
+        if had_work and not out.scheduled:
+            assert out.preempted or todo or not s.has_work() or s.running, "an empty step with nothing to wait for"
+        for sc in out.scheduled:                                  # the engine's part: copies at the pause point
+            r = sc.request
+            if r.pause_at is not None and r.num_computed >= r.pause_at and r.status is RequestStatus.RUNNING:
+                share = r.num_computed == r.pause_at
+                r.pause_at = None
+                arrivals += 1
+                child = Request(f"{r.request_id}+", r.prompt_token_ids, r.params, arrivals, 7, r.max_tokens, priority=r.priority)
+                s.add_copy(r, child, share)
+                live[child.request_id] = child
+                copies += 1
+        for rid in [rid for rid, r in live.items() if r.status.finished]:
+            live.pop(rid)
+        steps += 1
+        assert steps < 6000
+    assert not live or all(r.status.finished for r in live.values())
+    for g, n_all in enumerate(pages):
+        assert cache.num_free_pages(g) == n_all
+    assert cache.usage()["free_slots"] == 6
