@@ -82,6 +82,11 @@ def test_engine_args():
     assert EngineArgs().gpu_memory_utilization == 0.9
     with pytest.raises(ConfigError, match="0.01"):
         EngineArgs(gpu_memory_utilization=1.5).validate()
+    assert EngineArgs().scheduling_policy == "fcfs" and EngineArgs().step_row_multiple == 128
+    EngineArgs(scheduling_policy="priority", step_row_multiple=0).validate()
+    for bad in (dict(scheduling_policy="lifo"), dict(step_row_multiple=-1), dict(block_size=0), dict(max_num_seqs=0)):
+        with pytest.raises(ConfigError):
+            EngineArgs(**bad).validate()
     assert EngineArgs(dtype="auto").run_dtype("float32") == "float32"
     assert EngineArgs(dtype="auto").run_dtype("float16") == "bfloat16"
     assert EngineArgs(dtype="bf16").run_dtype("float32") == "bfloat16"
