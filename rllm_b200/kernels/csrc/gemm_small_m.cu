@@ -85,8 +85,9 @@ __device__ __forceinline__ float resid_old(const void* h, int ldh, int n0, int M
   return (m < M && n < N) ? ((const float*)h)[(size_t)m * ldh + n] : 0.f;
 }
 
-// 104 registers a thread: a CTA of 512 threads then leaves room for one CTA of the decode attention kernel
-// on its SM (and two CTAs of 256 threads likewise), so that kernels that follow one another overlap
+// 122 to 128 registers a thread: a CTA of 512 threads has its SM's registers to itself (the kernel behind
+// it comes in on the SMs that the grid leaves free and where CTAs have ended), two CTAs of 256 threads
+// likewise; a single CTA of 256 threads leaves half an SM to the CTAs of its neighbours in the stream.
 // LIGHT: half as many loads in flight a thread and at most 73 registers, so that seven CTAs of four warps
 // fit on an SM: for grids that then run as one wave where the ordinary form needs two, the second of them
 // three quarters empty.
