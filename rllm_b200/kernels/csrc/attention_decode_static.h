@@ -15,8 +15,11 @@
 // calls no cudaMalloc, cudaFree or allocating library routine.
 //
 // Rules for the caller:
-//  * Sizes: rllm_attention_decode_workspace(num_seqs, nq, d, max_seq_len) must not
-//    exceed RLLM_DECODE_STATIC_FLOATS and num_seqs * nkv must not exceed
+//  * Sizes: num_seqs * nq * ceil(max_seq_len / 128) * (d + 2) (half of what
+//    rllm_attention_decode_workspace reports; where that whole amount fits too, this
+//    entry point cuts short sequences into chunks of 64 keys exactly as the ordinary
+//    one does, else it keeps to chunks of 128 and its results may differ from the
+//    ordinary one's in the last bit) must not exceed RLLM_DECODE_STATIC_FLOATS and num_seqs * nkv must not exceed
 //    RLLM_DECODE_STATIC_COUNTERS; otherwise the call returns
 //    RLLM_E_STATIC_TOO_LARGE (-3) and launches nothing.
 //  * The first call on a device looks up the array's device address (once per

@@ -370,7 +370,16 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 // pairs [S, nq, max_chunks, 2].  Counters: int [S * nkv], zero before the call;
 // the kernel leaves them zero.
 // ---------------------------------------------------------------------------
-#define CHUNK 128        // keys per chunk (= per warp); walked in tiles of TBN = 32 or 16 keys
+#define CHUNK 128        // keys per chunk (= per warp) at most; walked in tiles of TBN = 32 or 16 keys
+// A sequence's chunks have 64 keys instead where the launch allows it (small_below > 0) and the work is small:
+// where sequences x kv heads x ceil(length / 128) stays below small_below, twice as many warps walk half as
+// many tiles one after the other, and the chain load - scores - softmax - product that a warp goes through for
+// each of its tiles is half as long (batch 8 at 2,304 keys in a decode step: +5 % tokens a second end to end,
+// batch 1: +3 %; at 4,096 keys and batch 8, or at batch 64, chunks of 128 are ahead by 3 to 4 %).  The rule
+// looks at the sequence's own length, so that a sequence's result depends on the number of sequences beside
+// it only through the order in which partial results are added.
+#define CHUNK_SMALL 64
+#define CHUNK_SMALL_BELOW 1536
 
 // a warp's shared memory: STAGES x (K tile, V tile), the Q tile [16][D], the cache row of each of the
 // chunk's keys, cosines and sines
@@ -419,7 +428,9 @@ __device__ __forceinline__ void copy_kv_pages(bf16* tile_k, bf16* tile_v, const 
   }
 }
 
-template <int D, int STAGES, int TBN>
+// SMALL: the smaller chunks are an option (small_below > 0) and the grid is laid out for them; without it the
+// chunk size is a constant of the kernel, which then is the kernel it was (registers and all).
+template <int D, int STAGES, int TBN, bool SMALL>
 __global__ void __launch_bounds__(128, (STAGES == 1 && D <= 64 ? 5 : 1))
 attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
                         bf16* __restrict__ kcache, bf16* __restrict__ vcache,
@@ -427,7 +438,8 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
                         const int* __restrict__ seq_lens, int nq, int nkv, int page_size, int num_pages,
                         int window, float scale_log2, int max_chunks, const double* __restrict__ inv_freq,
                         int rotary_dim, int write_kv, float* __restrict__ ws_o, float* __restrict__ ws_ml,
-                        int* __restrict__ counters, int* __restrict__ err, int tail_from, int first_wave) {
+                        int* __restrict__ counters, int* __restrict__ err, int tail_from, int first_wave,
+                        int small_below) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned char* mine = smem_raw + (size_t)warp * dec_warp_smem<D, STAGES, TBN>();
@@ -443,15 +455,25 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
   if (!write_kv) pdl_wait();
   const int g = nq / nkv;
   const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
-  const int chunk = blockIdx.x * (blockDim.x >> 5) + warp, kvh = blockIdx.y, s = blockIdx.z;
+  // Grid (CTAs of a sequence, kv heads, sequences), or, where the smaller chunks are an option, (kv heads,
+  // sequences, CTAs of a sequence): CTAs start in the order of their linear index, x first, so in the second
+  // form the CTAs whose chunks lie behind a short sequence's end (the grid is made for the longest allowed,
+  // in the smaller chunks) come last and keep no CTA with work out of the first wave (batch 8 at 4,092 keys:
+  // 7 % of a decode step); with many sequences the first form is 4 % ahead (a sequence's CTAs run, end and
+  // are merged together).
+  constexpr bool seq_major = !SMALL;
+  const int cta_x = seq_major ? blockIdx.x : blockIdx.z;
+  const int kvh = seq_major ? blockIdx.y : blockIdx.x, s = seq_major ? blockIdx.z : blockIdx.y;
+  const int chunk = cta_x * (blockDim.x >> 5) + warp;
   const int len = seq_lens[s];
   const int pos = len - 1;
   const int kmin = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int w0 = chunk * CHUNK;
+  const int ck = (SMALL && (long long)gridDim.x * gridDim.y * ((len + CHUNK - 1) / CHUNK) < small_below) ? CHUNK_SMALL : CHUNK;   // (SMALL: x, y = kv heads, sequences)
+  const int w0 = chunk * ck;
   const int nwarps = blockDim.x >> 5;
   {  // a CTA none of whose chunks holds a visible key has nothing to do
-    const int first = blockIdx.x * nwarps * CHUNK;
-    if (first >= len || first + nwarps * CHUNK <= kmin) {
+    const int first = cta_x * nwarps * ck;
+    if (first >= len || first + nwarps * ck <= kmin) {
       // It still waits for the kernel ahead (it has not yet, with write_kv): a CTA that exits counts as
       // having let the next kernel in, and that kernel may then assume that everything but this kernel is
       // complete.  These CTAs do no work, so the wait costs nothing.
@@ -459,19 +481,20 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
       return;
     }
   }
-  const bool active = w0 < len && w0 + CHUNK > kmin;
+  const bool active = w0 < len && w0 + ck > kmin;
   const int* bt = block_table + (size_t)s * max_blocks;
   const int half = rotary_dim >> 1;
   bf16* qrow = qkv + (size_t)s * q_stride;
   // keys to read from the cache: with write_kv the token's own key comes from qkv, not from the cache
   const int read_hi = write_kv ? pos : len;
   const int t_lo = active ? (kmin > w0 ? (kmin - w0) / TBN : 0) : 0;
-  const int t_hi = active ? min((CHUNK / TBN), (len - w0 + TBN - 1) / TBN) : 0;
+  const int t_hi = active ? min((ck / TBN), (len - w0 + TBN - 1) / TBN) : 0;
 
   // where the chunk's keys lie: all block-table lookups at once
   if (active) {
 #pragma unroll
     for (int i = 0; i < CHUNK / 32; ++i) {
+      if (i * 32 >= ck) break;
       const int j = w0 + i * 32 + lane;
       int row = -1;
       if (j >= kmin && j < read_hi) {
@@ -636,12 +659,14 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
       acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
       ll += pw[D + 1] * f;
     }
-    const size_t slot = ((size_t)s * nq + kvh * g + r) * max_chunks + blockIdx.x;
+    const size_t slot = ((size_t)s * nq + kvh * g + r) * max_chunks + cta_x;
     *(float4*)(ws_o + slot * D + q4 * 4) = acc;
     if (q4 == 0) *(float2*)(ws_ml + slot * 2) = make_float2(mm, ll);
   }
   // the last CTA of this (sequence, kv head) merges the CTAs' results, in order
-  const int ch_lo = kmin / CHUNK, ch_hi = (len + CHUNK - 1) / CHUNK;
+  // (the chunk size again from what it came from, rather than kept in a register through the tile loop)
+  const int ck_m = (SMALL && (long long)gridDim.x * gridDim.y * ((len + CHUNK - 1) / CHUNK) < small_below) ? CHUNK_SMALL : CHUNK;
+  const int ch_lo = kmin / ck_m, ch_hi = (len + ck_m - 1) / ck_m;
   const int cta_lo = ch_lo / nwarps, cta_hi = (ch_hi - 1) / nwarps + 1;
   const int ncta = cta_hi - cta_lo;
   __shared__ int s_last;
@@ -774,8 +799,38 @@ RLLM_EXPORT int rllm_attention_prefill_bf16(const void* q, int q_stride, void* o
 
 // floats of workspace that a decode call with these sizes needs
 RLLM_EXPORT long long rllm_attention_decode_workspace(int num_seqs, int nq, int d, int max_seq_len) {
-  const long long chunks = (max_seq_len + CHUNK - 1) / CHUNK;
+  const long long chunks = 2 * ((max_seq_len + CHUNK - 1) / CHUNK);     // (room for chunks of CHUNK_SMALL keys)
   return (long long)num_seqs * nq * chunks * (d + 2);
+}
+
+template <int D, int STAGES, int TBN, bool SMALL>
+static int launch_decode_small(int warps, bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc, const int* bt,
+                             int max_blocks, const int* seq_lens, int num_seqs, int nq, int nkv, int page_size,
+                             int num_pages, int window, float scale, int max_chunks, const double* inv_freq,
+                             int rotary_dim, int write_kv, float* ws, int* counters, int* err,
+                             cudaStream_t stream, int small_below) {
+  if (SMALL) max_chunks *= CHUNK / CHUNK_SMALL;      // the grid and the workspace's stride: room for the smaller chunks
+  const size_t smem = (size_t)warps * dec_warp_smem<D, STAGES, TBN>();
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES, TBN, SMALL>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  float* ws_o = ws;
+  float* ws_ml = ws + (size_t)num_seqs * nq * max_chunks * D;
+  const unsigned per_seq = (unsigned)((max_chunks + warps - 1) / warps);
+  dim3 grid = SMALL ? dim3(nkv, num_seqs, per_seq) : dim3(per_seq, nkv, num_seqs);
+  static int resident[5];        // by number of warps
+  if (!resident[warps]) resident[warps] = rllm_resident_ctas(attention_decode_kernel<D, STAGES, TBN, SMALL>, 32 * warps, smem) + 1;
+  const long long ctas = (long long)grid.x * grid.y * grid.z;
+  const int tail_from = (int)(ctas > resident[warps] - 1 ? ctas - (resident[warps] - 1) : 0);
+  cudaError_t e = rllm_launch_pdl(attention_decode_kernel<D, STAGES, TBN, SMALL>, grid, dim3(32 * warps), smem, stream, qkv,
+      q_stride, out, kc, vc, bt, max_blocks, seq_lens, nq, nkv, page_size, num_pages, window,
+      scale * 1.4426950408889634f, max_chunks, inv_freq, rotary_dim, write_kv, ws_o, ws_ml, counters, err, tail_from,
+      resident[warps] - 1, small_below);
+  return (int)e;
 }
 
 template <int D, int STAGES, int TBN>
@@ -783,27 +838,11 @@ static int launch_decode_cfg(int warps, bf16* qkv, int q_stride, bf16* out, bf16
                              int max_blocks, const int* seq_lens, int num_seqs, int nq, int nkv, int page_size,
                              int num_pages, int window, float scale, int max_chunks, const double* inv_freq,
                              int rotary_dim, int write_kv, float* ws, int* counters, int* err,
-                             cudaStream_t stream) {
-  const size_t smem = (size_t)warps * dec_warp_smem<D, STAGES, TBN>();
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES, TBN>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    configured = smem;
-  }
-  float* ws_o = ws;
-  float* ws_ml = ws + (size_t)num_seqs * nq * max_chunks * D;
-  dim3 grid((max_chunks + warps - 1) / warps, nkv, num_seqs);
-  static int resident[5];        // by number of warps
-  if (!resident[warps]) resident[warps] = rllm_resident_ctas(attention_decode_kernel<D, STAGES, TBN>, 32 * warps, smem) + 1;
-  const long long ctas = (long long)grid.x * grid.y * grid.z;
-  const int tail_from = (int)(ctas > resident[warps] - 1 ? ctas - (resident[warps] - 1) : 0);
-  cudaError_t e = rllm_launch_pdl(attention_decode_kernel<D, STAGES, TBN>, grid, dim3(32 * warps), smem, stream, qkv,
-      q_stride, out, kc, vc, bt, max_blocks, seq_lens, nq, nkv, page_size, num_pages, window,
-      scale * 1.4426950408889634f, max_chunks, inv_freq, rotary_dim, write_kv, ws_o, ws_ml, counters, err, tail_from,
-      resident[warps] - 1);
-  return (int)e;
+                             cudaStream_t stream, int small_below) {
+#define RLLM_DEC_CFG_ARGS warps, qkv, q_stride, out, kc, vc, bt, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, \
+      window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream, small_below
+  if (small_below) return launch_decode_small<D, STAGES, TBN, true>(RLLM_DEC_CFG_ARGS);
+  return launch_decode_small<D, STAGES, TBN, false>(RLLM_DEC_CFG_ARGS);
 }
 
 // Four warps a CTA.  With many chunks in all, one stage a warp, so that as many warps as possible are
@@ -814,10 +853,13 @@ template <int D>
 static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc, const int* bt, int max_blocks,
                          const int* seq_lens, int num_seqs, int nq, int nkv, int page_size, int num_pages,
                          int window, float scale, int max_chunks, const double* inv_freq, int rotary_dim,
-                         int write_kv, float* ws, int* counters, int* err, cudaStream_t stream) {
+                         int write_kv, float* ws, int* counters, int* err, cudaStream_t stream, bool allow_small) {
   const long long total = (long long)max_chunks * nkv * num_seqs;
+  // chunks of 64 keys are an option where even the longest sequences allowed would not make the work large
+  // (the kernel decides sequence by sequence, by the sequence's own length)
+  const int small_below = (allow_small && total < 4096) ? CHUNK_SMALL_BELOW : 0;
 #define RLLM_DEC_ARGS qkv, q_stride, out, kc, vc, bt, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, \
-      window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream
+      window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream, small_below
   // Heads of 128: a tile of 32 keys is 16 KB of K and V, and one stage a warp leaves the warp without loads
   // in flight while it multiplies; tiles of 16 keys in two stages keep them coming in the same shared memory
   // (batch 8 x 4,096 keys: 33.4 against 35.0 us; batch 32 x 2,096: 62.3 against 63.3 us; three CTAs an SM with
@@ -841,12 +883,12 @@ static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc,
 // these must be complete when that kernel starts, i.e. written by a kernel at least two launches ahead
 // (or by a copy); only qkv may come from the kernel directly ahead.  Without write_kv it waits first.
 // Every seq_lens[s] must be at least 1.
-RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, void* kcache, void* vcache,
-                                           const int* block_table, int max_blocks, const int* seq_lens,
-                                           int num_seqs, int max_seq_len, int nq, int nkv, int d, int page_size,
-                                           int num_pages, int window, float scale, const double* inv_freq,
-                                           int rotary_dim, int write_kv, float* workspace, int* counters,
-                                           int* err, cudaStream_t stream) {
+static int decode_bf16(void* qkv, int q_stride, void* out, void* kcache, void* vcache,
+                       const int* block_table, int max_blocks, const int* seq_lens,
+                       int num_seqs, int max_seq_len, int nq, int nkv, int d, int page_size,
+                       int num_pages, int window, float scale, const double* inv_freq,
+                       int rotary_dim, int write_kv, float* workspace, int* counters,
+                       int* err, cudaStream_t stream, bool allow_small) {
   if (num_seqs <= 0) return 0;
   if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0 || q_stride % 8 || max_seq_len <= 0 ||
       !workspace || !counters || !(scale > 0.f) || rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim && !inv_freq))
@@ -857,7 +899,7 @@ RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, v
   if ((long long)num_pages * nkv * page_size > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;   // cache rows are counted in an int
 #define RLLM_DECODE(DD) return launch_decode<DD>((bf16*)qkv, q_stride, (bf16*)out, (bf16*)kcache, (bf16*)vcache, \
       block_table, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, window, scale, max_splits, \
-      inv_freq, rotary_dim, write_kv, workspace, counters, err, stream)
+      inv_freq, rotary_dim, write_kv, workspace, counters, err, stream, allow_small)
   switch (d) {
     case 16: RLLM_DECODE(16);
     case 32: RLLM_DECODE(32);
@@ -865,6 +907,17 @@ RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, v
     case 128: RLLM_DECODE(128);
   }
   return RLLM_E_UNSUPPORTED;
+}
+
+RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, void* kcache, void* vcache,
+                                           const int* block_table, int max_blocks, const int* seq_lens,
+                                           int num_seqs, int max_seq_len, int nq, int nkv, int d, int page_size,
+                                           int num_pages, int window, float scale, const double* inv_freq,
+                                           int rotary_dim, int write_kv, float* workspace, int* counters,
+                                           int* err, cudaStream_t stream) {
+  return decode_bf16(qkv, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs, max_seq_len, nq,
+                     nkv, d, page_size, num_pages, window, scale, inv_freq, rotary_dim, write_kv, workspace, counters,
+                     err, stream, true);
 }
 
 // ---------------------------------------------------------------------------
@@ -909,7 +962,9 @@ RLLM_EXPORT int rllm_attention_decode_bf16_static(void* qkv, int q_stride, void*
                                                   cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || d <= 0 || max_seq_len <= 0) return RLLM_E_BADARG;
-  const long long need = rllm_attention_decode_workspace(num_seqs, nq, d, max_seq_len);
+  // (the fixed array's limit counts chunks of CHUNK keys; the smaller chunks are an option while they fit too)
+  const long long need = (long long)num_seqs * nq * ((max_seq_len + CHUNK - 1) / CHUNK) * (d + 2);
+  const bool allow_small = rllm_attention_decode_workspace(num_seqs, nq, d, max_seq_len) <= RLLM_DECODE_STATIC_FLOATS;
   if (need > RLLM_DECODE_STATIC_FLOATS || (long long)num_seqs * nkv > RLLM_DECODE_STATIC_COUNTERS)
     return RLLM_E_STATIC_TOO_LARGE;
   float* scratch = nullptr;
@@ -919,7 +974,7 @@ RLLM_EXPORT int rllm_attention_decode_bf16_static(void* qkv, int q_stride, void*
   // the merge counters must start at zero; an earlier call that was cut short may have left them set
   cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)num_seqs * nkv * sizeof(int), stream);
   if (e != cudaSuccess) return (int)e;
-  return rllm_attention_decode_bf16(qkv, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs,
-                                    max_seq_len, nq, nkv, d, page_size, num_pages, window, scale, inv_freq,
-                                    rotary_dim, write_kv, scratch, counters, err, stream);
+  return decode_bf16(qkv, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs,
+                     max_seq_len, nq, nkv, d, page_size, num_pages, window, scale, inv_freq,
+                     rotary_dim, write_kv, scratch, counters, err, stream, allow_small);
 }
